@@ -1,0 +1,591 @@
+"""Configuration dataclasses.
+
+Three public dataclasses mirror the reference's configuration surface
+(reference: chronicals/config/config.py:42-153 ``ChronicalsConfig``,
+:156-537 ``TrainingConfig``, :540-559 ``BenchmarkConfig``) so that user scripts
+written against the reference keep working, plus one addition,
+``ParallelConfig``, because the reference is single-GPU only.
+
+Field names and defaults of ``TrainingConfig`` are the public API and are kept
+verbatim.  Flags that only make sense for a tracing compiler
+(``torch_compile_*``, ``dynamo_*``, ``inductor_*``, ``triton_*``) are accepted
+and ignored: this framework launches hand-written sm_100a kernels directly and
+captures the step in a CUDA graph instead.
+"""
+from __future__ import annotations
+
+import dataclasses
+import json
+import os
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional
+
+import torch
+
+HF_READ_TOKEN = os.environ.get("HF_READ_TOKEN", "")
+HF_WRITE_TOKEN = os.environ.get("HF_WRITE_TOKEN", "")
+
+_DTYPES = {
+    "bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
+    "float16": torch.float16, "fp16": torch.float16,
+    "float32": torch.float32, "fp32": torch.float32,
+}
+
+# Architecture presets.  The first four are the reference's
+# (config.py:127-153); the rest are the architectures named by the benchmark
+# configurations this framework is measured on.
+_ARCH_PRESETS: Dict[str, Dict[str, Any]] = {
+    "qwen-0.5b": dict(hidden_size=896, intermediate_size=4864, num_hidden_layers=24,
+                      num_attention_heads=14, num_key_value_heads=2, head_dim=64,
+                      vocab_size=151936, rope_theta=1e6, attention_bias=True,
+                      tie_word_embeddings=True, max_position_embeddings=32768),
+    "qwen-1.5b": dict(hidden_size=1536, intermediate_size=8960, num_hidden_layers=28,
+                      num_attention_heads=12, num_key_value_heads=2, head_dim=128,
+                      vocab_size=151936, rope_theta=1e6, attention_bias=True,
+                      tie_word_embeddings=True, max_position_embeddings=32768),
+    "llama-1b": dict(hidden_size=2048, intermediate_size=5632, num_hidden_layers=22,
+                     num_attention_heads=32, num_key_value_heads=8, head_dim=64,
+                     vocab_size=128256, rope_theta=5e5, attention_bias=False,
+                     tie_word_embeddings=True, max_position_embeddings=8192),
+    "deepseek-mini": dict(hidden_size=1536, intermediate_size=4096, num_hidden_layers=24,
+                          num_attention_heads=24, num_key_value_heads=24, head_dim=64,
+                          vocab_size=102400, rope_theta=1e4, attention_bias=False,
+                          tie_word_embeddings=False, max_position_embeddings=4096),
+    "tiny-qwen2": dict(hidden_size=256, intermediate_size=688, num_hidden_layers=4,
+                       num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+                       vocab_size=32000, rope_theta=1e6, attention_bias=True,
+                       tie_word_embeddings=True, max_position_embeddings=4096),
+    "qwen2.5-7b": dict(hidden_size=3584, intermediate_size=18944, num_hidden_layers=28,
+                       num_attention_heads=28, num_key_value_heads=4, head_dim=128,
+                       vocab_size=152064, rope_theta=1e6, attention_bias=True,
+                       tie_word_embeddings=False, max_position_embeddings=32768),
+    "qwen2.5-14b": dict(hidden_size=5120, intermediate_size=13824, num_hidden_layers=48,
+                        num_attention_heads=40, num_key_value_heads=8, head_dim=128,
+                        vocab_size=152064, rope_theta=1e6, attention_bias=True,
+                        tie_word_embeddings=False, max_position_embeddings=32768),
+}
+_ARCH_PRESETS["qwen2.5-0.5b"] = _ARCH_PRESETS["qwen-0.5b"]
+_ARCH_PRESETS["qwen2.5-1.5b"] = _ARCH_PRESETS["qwen-1.5b"]
+
+# README-style keyword arguments (reference README.md:229-250, :850-883) that
+# describe *training*, not architecture.  ``ChronicalsConfig(**kw)`` accepts
+# them and hands them to ``to_training_config``.
+_README_TRAINING_KEYS = {
+    "learning_rate", "batch_size", "gradient_accumulation_steps", "max_steps",
+    "use_flash_attention", "use_fused_kernels", "use_sequence_packing",
+    "use_gradient_checkpointing", "use_torch_compile", "use_lora", "lora_rank",
+    "lora_alpha", "lora_dropout", "lora_target_modules", "use_lora_plus",
+    "lora_plus_ratio", "use_8bit_optimizer", "activation_offload",
+    "mixed_precision", "warmup_steps", "max_seq_length", "output_dir",
+    "weight_decay", "num_train_epochs", "seed",
+}
+
+
+@dataclass(init=False)
+class ChronicalsConfig:
+    """Model architecture description (reference config.py:42-125).
+
+    Also accepts the README's training-style keywords (``learning_rate=…``,
+    ``use_lora=…``); those are stored in ``training_overrides`` and turned
+    into a ``TrainingConfig`` by :meth:`to_training_config`.
+    """
+    hidden_size: int = 2048
+    intermediate_size: int = 5632
+    num_hidden_layers: int = 24
+    num_attention_heads: int = 16
+    num_key_value_heads: int = 16
+    head_dim: int = 128
+    vocab_size: int = 151936
+    max_position_embeddings: int = 4096
+    # multi-head latent attention fields are carried for API parity only
+    use_mla: bool = True
+    latent_dim: int = 512
+    rope_dim: int = 64
+    mla_compression_ratio: float = 0.125
+    use_fp8: bool = True
+    fp8_format_forward: str = "e4m3"
+    fp8_format_backward: str = "e5m2"
+    fp8_block_size: int = 128
+    fp8_amax_history_len: int = 32
+    fp8_margin: float = 1.0
+    fp8_use_online_scaling: bool = False
+    fp8_exclude_layers: List[str] = field(default_factory=lambda: ["embed", "lm_head", "norm"])
+    rms_norm_eps: float = 1e-6
+    hidden_act: str = "silu"
+    tie_word_embeddings: bool = True
+    attention_dropout: float = 0.0
+    hidden_dropout: float = 0.0
+    device: str = "cuda"
+    dtype: str = "bfloat16"
+    # additions of this framework
+    rope_theta: float = 1e6
+    attention_bias: bool = True
+    rope_scaling: Optional[Dict[str, Any]] = None
+    model_type: str = "qwen2"
+    training_overrides: Dict[str, Any] = field(default_factory=dict)
+
+    def __init__(self, **kwargs):
+        for f in dataclasses.fields(self):
+            if f.default is not dataclasses.MISSING:
+                setattr(self, f.name, f.default)
+            else:
+                setattr(self, f.name, f.default_factory())  # type: ignore[misc]
+        names = {f.name for f in dataclasses.fields(self)}
+        for k, v in kwargs.items():
+            if k in names:
+                setattr(self, k, v)
+            elif k in _README_TRAINING_KEYS:
+                self.training_overrides[k] = v
+            else:
+                raise TypeError(f"ChronicalsConfig got an unexpected keyword argument {k!r}")
+
+    # -- reference helpers (config.py:96-125) ---------------------------------
+    @property
+    def torch_dtype(self) -> torch.dtype:
+        return _DTYPES.get(self.dtype, torch.bfloat16)
+
+    def get_kv_cache_size_mb(self, batch_size: int = 1, seq_len: Optional[int] = None) -> float:
+        seq_len = seq_len or self.max_position_embeddings
+        elems = 2 * self.num_hidden_layers * batch_size * seq_len * self.num_key_value_heads * self.head_dim
+        return elems * torch.empty((), dtype=self.torch_dtype).element_size() / 2**20
+
+    def num_parameters(self, include_embeddings: bool = True) -> int:
+        h, i, l = self.hidden_size, self.intermediate_size, self.num_hidden_layers
+        q = self.num_attention_heads * self.head_dim
+        kv = self.num_key_value_heads * self.head_dim
+        attn = h * (q + 2 * kv) + q * h + ((q + 2 * kv) if self.attention_bias else 0)
+        mlp = 3 * h * i
+        per_layer = attn + mlp + 2 * h
+        total = l * per_layer + h
+        if include_embeddings:
+            total += self.vocab_size * h * (1 if self.tie_word_embeddings else 2)
+        return total
+
+    def get_model_size_mb(self) -> float:
+        return self.num_parameters() * torch.empty((), dtype=self.torch_dtype).element_size() / 2**20
+
+    @classmethod
+    def from_model_name(cls, name: str) -> "ChronicalsConfig":
+        key = name.lower().split("/")[-1]
+        for preset, kw in _ARCH_PRESETS.items():
+            if preset == key or preset in key:
+                return cls(**kw)
+        # tolerate "Qwen2.5-0.5B-Instruct" style names
+        for preset, kw in _ARCH_PRESETS.items():
+            if preset.replace("qwen-", "qwen2.5-") in key:
+                return cls(**kw)
+        raise ValueError(f"unknown model preset {name!r}; known: {sorted(_ARCH_PRESETS)}")
+
+    @classmethod
+    def from_hf_config(cls, cfg: Any) -> "ChronicalsConfig":
+        """Build from a HF ``config.json`` dict or a transformers config object."""
+        get = (lambda k, d=None: cfg.get(k, d)) if isinstance(cfg, dict) else (lambda k, d=None: getattr(cfg, k, d))
+        heads = get("num_attention_heads")
+        hd = get("head_dim") or get("hidden_size") // heads
+        mt = get("model_type", "qwen2")
+        rope_theta = get("rope_theta")
+        if rope_theta is None:
+            rp = get("rope_parameters") or {}
+            rope_theta = rp.get("rope_theta", 1e4) if isinstance(rp, dict) else 1e4
+        return cls(hidden_size=get("hidden_size"), intermediate_size=get("intermediate_size"),
+                   num_hidden_layers=get("num_hidden_layers"), num_attention_heads=heads,
+                   num_key_value_heads=get("num_key_value_heads", heads), head_dim=hd,
+                   vocab_size=get("vocab_size"), max_position_embeddings=get("max_position_embeddings", 4096),
+                   rms_norm_eps=get("rms_norm_eps", 1e-6), hidden_act=get("hidden_act", "silu"),
+                   tie_word_embeddings=bool(get("tie_word_embeddings", False)),
+                   rope_theta=float(rope_theta),
+                   attention_bias=bool(get("attention_bias", mt == "qwen2")),
+                   rope_scaling=get("rope_scaling"), model_type=mt)
+
+    def to_hf_config(self) -> Dict[str, Any]:
+        """``config.json`` content in the layout transformers expects."""
+        arch = {"qwen2": "Qwen2ForCausalLM", "llama": "LlamaForCausalLM",
+                "mistral": "MistralForCausalLM", "gemma": "GemmaForCausalLM"}.get(self.model_type, "Qwen2ForCausalLM")
+        return {
+            "architectures": [arch], "model_type": self.model_type,
+            "hidden_size": self.hidden_size, "intermediate_size": self.intermediate_size,
+            "num_hidden_layers": self.num_hidden_layers, "num_attention_heads": self.num_attention_heads,
+            "num_key_value_heads": self.num_key_value_heads, "head_dim": self.head_dim,
+            "vocab_size": self.vocab_size, "max_position_embeddings": self.max_position_embeddings,
+            "rms_norm_eps": self.rms_norm_eps, "hidden_act": self.hidden_act,
+            "tie_word_embeddings": self.tie_word_embeddings, "rope_theta": self.rope_theta,
+            "attention_bias": self.attention_bias, "rope_scaling": self.rope_scaling,
+            "torch_dtype": self.dtype, "attention_dropout": self.attention_dropout,
+        }
+
+    def to_dict(self) -> Dict[str, Any]:
+        return {f.name: getattr(self, f.name) for f in dataclasses.fields(self)}
+
+    def to_training_config(self, **extra) -> "TrainingConfig":
+        """Translate README-style keywords into a ``TrainingConfig``."""
+        o = dict(self.training_overrides)
+        o.update(extra)
+        kw: Dict[str, Any] = {}
+        if "batch_size" in o:
+            kw["per_device_train_batch_size"] = o.pop("batch_size")
+        if "mixed_precision" in o:
+            mp = str(o.pop("mixed_precision")).lower()
+            kw["bf16"] = mp in ("bf16", "bfloat16")
+        if "use_fused_kernels" in o:
+            v = bool(o.pop("use_fused_kernels"))
+            kw.update(use_fused_rmsnorm=v, use_fused_swiglu=v, use_fused_rope=v, use_fused_cross_entropy=v)
+        if "use_8bit_optimizer" in o and o.pop("use_8bit_optimizer"):
+            kw["optimizer_type"] = "8bit_adam"
+        if "activation_offload" in o:
+            kw["use_activation_offloading"] = bool(o.pop("activation_offload"))
+        if "use_flash_attention" in o:
+            kw["use_flash_varlen"] = bool(o.pop("use_flash_attention"))
+        if "warmup_steps" in o:
+            kw["warmup_steps"] = int(o.pop("warmup_steps"))
+        tnames = {f.name for f in dataclasses.fields(TrainingConfig)}
+        for k in list(o):
+            if k in tnames:
+                kw[k] = o.pop(k)
+        cfg = TrainingConfig(**{k: v for k, v in kw.items() if k in tnames})
+        # LoRA keywords have no TrainingConfig field in the reference; keep them as attributes
+        for k, v in {**o, **{k: v for k, v in kw.items() if k not in tnames}}.items():
+            setattr(cfg, k, v)
+        return cfg
+
+
+@dataclass
+class ParallelConfig:
+    """Multi-GPU layout (no counterpart in the reference, which is single-GPU).
+
+    ``comm_backend`` selects between the in-kernel peer-memory collectives
+    (``"fused"``) and plain NCCL (``"nccl"``), the comparison baseline.
+    """
+    dp: int = 1
+    tp: int = 1
+    zero_stage: int = 0
+    sequence_parallel: bool = False
+    bucket_mb: float = 32.0
+    comm_backend: str = "nccl"
+    wait_budget_us: int = 2_000_000
+
+    @property
+    def world_size(self) -> int:
+        return self.dp * self.tp
+
+
+@dataclass
+class TrainingConfig:
+    """Every training flag (reference config.py:156-537; names kept verbatim)."""
+    # output / loop
+    output_dir: str = "./chronicals_output"
+    num_train_epochs: int = 3
+    max_steps: int = -1
+    per_device_train_batch_size: int = 2
+    per_device_eval_batch_size: int = 2
+    gradient_accumulation_steps: int = 4
+    max_seq_length: int = 4096
+    # optimizer
+    optimizer_type: str = "fused_adamw"
+    learning_rate: float = 2e-5
+    weight_decay: float = 0.01
+    adam_beta1: float = 0.9
+    adam_beta2: float = 0.95
+    adam_epsilon: float = 1e-8
+    max_grad_norm: float = 1.0
+    # schedule
+    lr_scheduler_type: str = "wsd"
+    warmup_ratio: float = 0.03
+    lr_min_ratio: float = 0.1
+    wsd_stable_ratio: float = 0.80
+    # precision
+    bf16: bool = True
+    fp8: bool = True
+    use_deepseek_fp8: bool = True
+    fp8_block_size: int = 128
+    fp8_amax_history_len: int = 32
+    fp8_use_online_scaling: bool = False
+    # packing
+    use_sequence_packing: bool = True
+    packing_strategy: str = "bfd"
+    packing_efficiency_threshold: float = 0.0
+    use_flash_varlen: bool = True
+    mask_first_token_of_packed: bool = True
+    packing_batch_multiplier: int = 4
+    use_packed_prefetching: bool = True
+    use_double_buffer_prefetch: bool = False
+    use_mla: bool = True
+    # memory
+    use_gradient_checkpointing: bool = True
+    checkpoint_ratio: float = 0.177
+    use_activation_offloading: bool = False
+    offload_use_pin_memory: bool = True
+    offload_use_streams: bool = True
+    offload_min_size: int = 1024
+    offload_prefetch_ahead: int = 2
+    # loss
+    label_smoothing: float = 0.0
+    z_loss_weight: float = 1e-4
+    # logging / saving
+    logging_steps: int = 10
+    save_steps: int = 500
+    save_total_limit: int = 3
+    eval_steps: int = 500
+    visual_reporting: bool = True
+    report_every_n_steps: int = 100
+    seed: int = 42
+    # tracing-compiler flags: accepted, ignored
+    use_torch_compile: bool = True
+    torch_compile_mode: str = "default"
+    torch_compile_fullgraph: bool = False
+    torch_compile_backend: str = "inductor"
+    torch_compile_dynamic: Optional[bool] = None
+    torch_compile_disable: bool = False
+    torch_compile_warmup_steps: int = 5
+    torch_compile_regional: bool = True
+    torch_compile_optimizer: bool = True
+    triton_cache_dir: str = "/tmp/triton_cache"
+    triton_autotune_cache_dir: str = "/tmp/triton_autotune"
+    dynamo_cache_size_limit: int = 256
+    dynamo_suppress_errors: bool = True
+    dynamo_assume_static_by_default: bool = True
+    dynamo_inline_inbuilt_nn_modules: bool = True
+    dynamo_skip_triton_cache_check: bool = True
+    inductor_epilogue_fusion: bool = True
+    inductor_coordinate_descent_tuning: bool = True
+    inductor_aggressive_fusion: bool = True
+    inductor_max_autotune: bool = False
+    inductor_triton_cudagraphs: bool = False
+    torch_compile_check_graph_breaks: bool = False
+    torch_compile_min_compile_size: int = 1
+    torch_compile_verbose: bool = False
+    # CUDA graphs
+    use_cuda_graphs: bool = False
+    cuda_graph_warmup_steps: int = 3
+    cuda_graph_capture_mode: str = "thread_local"
+    cuda_graph_use_memory_pool: bool = True
+    cuda_graph_static_shapes: bool = True
+    cuda_graph_max_cached_graphs: int = 16
+    cuda_graph_shape_buckets: List[int] = field(default_factory=lambda: [128, 256, 512, 1024, 2048, 4096])
+    cuda_graph_fallback_on_error: bool = True
+    cuda_graph_use_manager: bool = True
+    cuda_graph_capture_training_step: bool = True
+    # fused kernels
+    use_fused_adamw: bool = True
+    use_fused_cross_entropy: bool = True
+    use_liger_kernel: bool = True
+    use_fused_rope: bool = True
+    use_fused_swiglu: bool = True
+    use_fused_rmsnorm: bool = True
+    # cross-entropy
+    ce_implementation: str = "cce"
+    cce_chunk_size: int = 8192
+    cce_use_kahan_summation: bool = True
+    cce_auto_chunk_size: bool = True
+    ce_small_vocab_threshold: int = 32000
+    ce_large_vocab_threshold: int = 100000
+    cce_use_triton: bool = True
+    cce_gradient_checkpointing: bool = True
+    use_chunked_cross_entropy: bool = False
+    ce_chunk_size: int = 8192
+    use_fused_linear_cross_entropy: bool = True
+    # data loading
+    num_workers: int = 4
+    prefetch_factor: int = 4
+    pin_memory: bool = True
+    use_memory_mapped: bool = True
+    use_data_prefetcher: bool = True
+    persistent_workers: bool = True
+    use_curriculum_learning: bool = False
+    curriculum_start_ratio: float = 0.25
+    # MFU
+    track_mfu: bool = True
+    gpu_peak_tflops: float = 312.0
+    fp8_exclude_patterns: List[str] = field(default_factory=lambda: ["embed", "lm_head", "norm"])
+    fused_grad_clip: bool = True
+    empty_cache_steps: int = 0
+    disable_gc_during_training: bool = True
+    non_blocking_transfers: bool = True
+    # profiling
+    enable_profiling: bool = False
+    profiling_output_dir: str = "./profiler_output"
+    profiling_wait_steps: int = 1
+    profiling_warmup_steps: int = 1
+    profiling_active_steps: int = 3
+    profiling_record_shapes: bool = True
+    profiling_profile_memory: bool = True
+    profiling_with_stack: bool = True
+    profiling_with_flops: bool = True
+    profiling_export_chrome_trace: bool = True
+    profiling_export_tensorboard: bool = False
+    detect_performance_regression: bool = False
+    regression_threshold_pct: float = 10.0
+    # overhead knobs
+    minimize_python_overhead: bool = True
+    prefetch_batches: bool = True
+    prefetch_count: int = 2
+    use_async_cuda: bool = True
+    minimize_sync_points: bool = True
+    batch_logging: bool = True
+    track_peak_memory: bool = True
+    use_memory_efficient_grad_accum: bool = True
+    activation_memory_limit_gb: float = 0.0
+    prepare_optimizer_sharding: bool = False
+    # ---- additions of this framework (absent from the reference) ----
+    warmup_steps: int = -1               # overrides warmup_ratio when >= 0
+    fp16: bool = False
+    parallel: ParallelConfig = field(default_factory=ParallelConfig)
+    save_safetensors: bool = True
+    shift_labels: bool = True            # labels are next-token shifted inside the trainer
+    log_jsonl: bool = True
+
+    @property
+    def effective_batch_size(self) -> int:
+        return self.per_device_train_batch_size * self.gradient_accumulation_steps * max(1, self.parallel.dp)
+
+    def to_dict(self) -> Dict[str, Any]:
+        d = dataclasses.asdict(self)
+        for k, v in self.__dict__.items():       # README-style extra attributes
+            if k not in d and isinstance(v, (int, float, str, bool, list, tuple, type(None))):
+                d[k] = v
+        return d
+
+    def to_json(self) -> str:
+        return json.dumps(self.to_dict(), indent=2, default=str)
+
+    @classmethod
+    def from_dict(cls, d: Dict[str, Any]) -> "TrainingConfig":
+        names = {f.name for f in dataclasses.fields(cls)}
+        kw = {k: v for k, v in d.items() if k in names and k != "parallel"}
+        cfg = cls(**kw)
+        if isinstance(d.get("parallel"), dict):
+            cfg.parallel = ParallelConfig(**d["parallel"])
+        for k, v in d.items():
+            if k not in names:
+                setattr(cfg, k, v)
+        return cfg
+
+
+@dataclass
+class BenchmarkConfig:
+    """Benchmark settings (reference config.py:540-559)."""
+    model_name: str = "qwen2.5-0.5b"
+    dataset_name: str = "synthetic"
+    batch_size: int = 8
+    seq_length: int = 1024
+    num_steps: int = 20
+    warmup_steps: int = 5
+    num_runs: int = 1
+    gradient_accumulation_steps: int = 1
+    output_file: str = "benchmark_results.json"
+    methods: List[str] = field(default_factory=lambda: ["chronicals"])
+
+
+MODEL_REGISTRY: Dict[str, Dict[str, Any]] = {
+    name: {"hf_name": hf, "preset": name} for name, hf in [
+        ("qwen2.5-0.5b", "Qwen/Qwen2.5-0.5B"), ("qwen2.5-1.5b", "Qwen/Qwen2.5-1.5B"),
+        ("qwen2.5-7b", "Qwen/Qwen2.5-7B"), ("qwen2.5-14b", "Qwen/Qwen2.5-14B"),
+        ("llama-1b", "meta-llama/Llama-3.2-1B"), ("tiny-qwen2", "synthetic/tiny-qwen2"),
+    ]
+}
+DATASET_REGISTRY: Dict[str, Dict[str, Any]] = {
+    "alpaca": {"hf_name": "tatsu-lab/alpaca", "template": "alpaca"},
+    "dolly": {"hf_name": "databricks/databricks-dolly-15k", "template": "dolly"},
+    "slimorca": {"hf_name": "Open-Orca/SlimOrca", "template": "chatml"},
+    "synthetic": {"hf_name": None, "template": None},
+}
+
+
+def get_model_config(name: str) -> ChronicalsConfig:
+    return ChronicalsConfig.from_model_name(MODEL_REGISTRY.get(name, {"preset": name})["preset"])
+
+
+# GPU-name → overrides (reference config.py:593-666 stops at H100/H200; a B200
+# branch is added, with dense bf16 peak 2250 TFLOP/s).
+_GPU_OVERRIDES = [
+    (("b200", "b100", "gb200"), dict(fp8=True, use_cuda_graphs=True, gpu_peak_tflops=2250.0,
+                                     per_device_train_batch_size=8, gradient_accumulation_steps=1,
+                                     use_gradient_checkpointing=False, use_flash_varlen=True)),
+    (("h100", "h200"), dict(fp8=True, use_cuda_graphs=False, gpu_peak_tflops=989.0,
+                            per_device_train_batch_size=2, gradient_accumulation_steps=2)),
+    (("a100",), dict(fp8=True, use_cuda_graphs=False, gpu_peak_tflops=312.0,
+                     per_device_train_batch_size=2, gradient_accumulation_steps=2)),
+    (("v100",), dict(fp8=False, use_fused_adamw=False, use_flash_varlen=False, gpu_peak_tflops=125.0)),
+    (("t4",), dict(fp8=False, use_fused_adamw=False, use_flash_varlen=False, gpu_peak_tflops=65.0)),
+    (("l40",), dict(fp8=True, use_cuda_graphs=True, gpu_peak_tflops=181.0)),
+    (("l4",), dict(fp8=True, use_cuda_graphs=True, gpu_peak_tflops=121.0)),
+]
+
+
+def get_optimal_config_for_gpu(gpu_name: Optional[str] = None) -> TrainingConfig:
+    if gpu_name is None:
+        gpu_name = torch.cuda.get_device_name(0) if torch.cuda.is_available() else "cpu"
+    low = gpu_name.lower()
+    cfg = TrainingConfig()
+    for keys, over in _GPU_OVERRIDES:
+        if any(k in low for k in keys):
+            for k, v in over.items():
+                setattr(cfg, k, v)
+            break
+    else:
+        cfg.fp8 = False
+        if low == "cpu":
+            cfg.bf16 = False
+    return cfg
+
+
+def measured_peaks(path: Optional[str] = None) -> Dict[str, float]:
+    """Measured roofline denominators written next to the package by the
+    benchmark driver, or a stated fallback when the file is absent."""
+    here = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    path = path or os.path.join(here, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            d = json.load(f)
+        d["source"] = "measured"
+        return d
+    except (OSError, ValueError):
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def roofline_analysis(model: ChronicalsConfig, tokens_per_step: int, seq_len: int,
+                      peak_tflops: Optional[float] = None) -> Dict[str, float]:
+    """Analytic step-time floor (the reference ships a static dict for A100 at
+    config.py:884-913; this computes it for any architecture and peak)."""
+    peaks = measured_peaks()
+    peak = (peak_tflops or peaks["bf16_tflops_sustained"]) * 1e12
+    n = model.num_parameters(include_embeddings=True)
+    gemm_flops = 6.0 * n * tokens_per_step
+    attn_flops = 6.0 * 2 * model.num_hidden_layers * tokens_per_step * seq_len * model.num_attention_heads * model.head_dim / 2
+    t = (gemm_flops + attn_flops) / peak
+    return {"gemm_flops": gemm_flops, "attn_flops": attn_flops, "floor_s": t,
+            "max_tokens_per_s": tokens_per_step / t, "peak_tflops": peak / 1e12}
+
+
+@dataclass
+class Qwen05BOptimalConfig:
+    """Hand-tuned preset for the 0.5B model (reference config.py:714-878), retuned for one B200."""
+    batch_size: int = 8
+    seq_length: int = 1024
+    gradient_accumulation_steps: int = 1
+    learning_rate: float = 2e-5
+    use_cuda_graphs: bool = True
+    use_gradient_checkpointing: bool = False
+
+    def to_training_config(self) -> TrainingConfig:
+        return TrainingConfig(per_device_train_batch_size=self.batch_size, max_seq_length=self.seq_length,
+                              gradient_accumulation_steps=self.gradient_accumulation_steps,
+                              learning_rate=self.learning_rate, use_cuda_graphs=self.use_cuda_graphs,
+                              use_gradient_checkpointing=self.use_gradient_checkpointing,
+                              gpu_peak_tflops=2250.0)
+
+
+ROOFLINE_ANALYSIS = roofline_analysis(ChronicalsConfig(**_ARCH_PRESETS["qwen-0.5b"]), 8192, 1024)
+
+
+@dataclass
+class BenchmarkOptimizedConfig(Qwen05BOptimalConfig):
+    """Benchmark preset (reference config.py:920-1037)."""
+    warmup_steps: int = 5
+    num_steps: int = 20
+
+
+def get_benchmark_config(model_name: str = "qwen2.5-0.5b") -> TrainingConfig:
+    cfg = BenchmarkOptimizedConfig().to_training_config()
+    cfg.logging_steps = 10**9
+    cfg.save_steps = 0
+    return cfg

@@ -1,0 +1,611 @@
+// Bandwidth-bound fused kernels: RMSNorm (+residual add) fwd/bwd, SwiGLU/GeGLU
+// fwd/bwd, in-place QK rotary embedding, embedding gather / deterministic
+// scatter-add, cross-entropy on materialised logits.  All bf16 in/out with fp32
+// math, 16-byte vector accesses, grids sized from the SM count.
+//
+// They replace the reference's Triton kernels (chronicals/kernels/
+// triton_kernels.py:303-478 RMSNorm, :830-986 SwiGLU, :1296-1367 GeGLU,
+// :1448-1625 QK-RoPE, :127-210 cross-entropy) and the Liger kernels its trainer
+// patches in.
+#include "common.cuh"
+
+namespace cb {
+
+constexpr int EW_THREADS = 256;
+
+struct alignas(16) Vec8 {
+  uint4 u;
+};
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 u;
+  u.x = pack_bf16x2(f[0], f[1]); u.y = pack_bf16x2(f[2], f[3]);
+  u.z = pack_bf16x2(f[4], f[5]); u.w = pack_bf16x2(f[6], f[7]);
+  return u;
+}
+
+// Sum over the TPR threads that share one row.  TPR == 32: shuffle only.  Otherwise the
+// group's warps exchange through shared memory; every thread of the block must call it.
+template <int TPR>
+__device__ __forceinline__ float group_sum(float v, float* sred) {
+  v = warp_sum(v);
+  if (TPR == 32) return v;
+  const int warp = threadIdx.x >> 5;
+  constexpr int WPG = TPR / 32;
+  if ((threadIdx.x & 31) == 0) sred[warp] = v;
+  __syncthreads();
+  const int g0 = (warp / WPG) * WPG;
+  float t = 0.f;
+#pragma unroll
+  for (int i = 0; i < WPG; ++i) t += sred[g0 + i];
+  __syncthreads();
+  return t;
+}
+
+// ------------------------------------------------------------------ RMSNorm forward
+// h = x (+ res);  y = h * rsqrt(mean(h^2) + eps) * (w + offset);  rstd saved.
+// N % 8 == 0, N <= 8 * TPR * VPL.
+template <int TPR, int VPL>
+__global__ void __launch_bounds__(EW_THREADS)
+rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ res, const bf16* __restrict__ w,
+                   bf16* __restrict__ y, bf16* __restrict__ h_out, float* __restrict__ rstd_out, int M, int N,
+                   float eps, float offset) {
+  __shared__ float sred[EW_THREADS / 32];
+  constexpr int RPB = EW_THREADS / TPR;
+  const int group = threadIdx.x / TPR;
+  const int t = threadIdx.x % TPR;
+  const int nvec = N / 8;
+  for (int base = blockIdx.x * RPB; base < M; base += gridDim.x * RPB) {
+    const int row = base + group;
+    const bool active = row < M;
+    float h[VPL][8];
+    float ss = 0.f;
+    if (active) {
+      const uint4* xp = reinterpret_cast<const uint4*>(x + static_cast<long long>(row) * N);
+      const uint4* rp = res ? reinterpret_cast<const uint4*>(res + static_cast<long long>(row) * N) : nullptr;
+      uint4* hp = h_out ? reinterpret_cast<uint4*>(h_out + static_cast<long long>(row) * N) : nullptr;
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) {
+        const int v = t + i * TPR;
+        if (v < nvec) {
+          unpack8(xp[v], h[i]);
+          if (rp) {
+            float r[8];
+            unpack8(rp[v], r);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) h[i][j] += r[j];
+            const uint4 hb = pack8(h[i]);   // the sum is stored in bf16; normalise what is stored
+            if (hp) hp[v] = hb;
+            unpack8(hb, h[i]);
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) ss += h[i][j] * h[i][j];
+        }
+      }
+    }
+    ss = group_sum<TPR>(ss, sred);
+    if (active) {
+      const float rstd = rsqrtf(ss / static_cast<float>(N) + eps);
+      if (t == 0 && rstd_out) rstd_out[row] = rstd;
+      const uint4* wp = reinterpret_cast<const uint4*>(w);
+      uint4* yp = reinterpret_cast<uint4*>(y + static_cast<long long>(row) * N);
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) {
+        const int v = t + i * TPR;
+        if (v < nvec) {
+          float wf[8], o[8];
+          unpack8(wp[v], wf);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] = h[i][j] * rstd * (wf[j] + offset);
+          yp[v] = pack8(o);
+        }
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ RMSNorm backward
+// xhat = h*rstd; g = dy*(w+offset); dx = rstd*(g - xhat*mean(g*xhat)) (+ dres_in);
+// dw[n] = sum_rows dy*xhat, accumulated per block in registers and written as one
+// [gridDim.x, N] fp32 partial (reduced by rmsnorm_dw_reduce_kernel).
+template <int TPR, int VPL>
+__global__ void __launch_bounds__(EW_THREADS)
+rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ h, const bf16* __restrict__ w,
+                   const float* __restrict__ rstd_in, const bf16* __restrict__ dres_in, bf16* __restrict__ dx,
+                   float* __restrict__ dw_part, int M, int N, float offset) {
+  __shared__ float sred[EW_THREADS / 32];
+  extern __shared__ float sdw[];  // [N] block accumulator, used when several row groups share a block
+  constexpr int RPB = EW_THREADS / TPR;
+  const int group = threadIdx.x / TPR;
+  const int t = threadIdx.x % TPR;
+  const int nvec = N / 8;
+  float dwacc[VPL][8];
+#pragma unroll
+  for (int i = 0; i < VPL; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dwacc[i][j] = 0.f;
+
+  for (int base = blockIdx.x * RPB; base < M; base += gridDim.x * RPB) {
+    const int row = base + group;
+    const bool active = row < M;
+    float g[VPL][8], xh[VPL][8];
+    float dot = 0.f;
+    float rstd = 0.f;
+    if (active) {
+      rstd = rstd_in[row];
+      const uint4* dyp = reinterpret_cast<const uint4*>(dy + static_cast<long long>(row) * N);
+      const uint4* hp = reinterpret_cast<const uint4*>(h + static_cast<long long>(row) * N);
+      const uint4* wp = reinterpret_cast<const uint4*>(w);
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) {
+        const int v = t + i * TPR;
+        if (v < nvec) {
+          float d[8], wf[8];
+          unpack8(dyp[v], d);
+          unpack8(hp[v], xh[i]);
+          unpack8(wp[v], wf);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            xh[i][j] *= rstd;
+            g[i][j] = d[j] * (wf[j] + offset);
+            dot += g[i][j] * xh[i][j];
+            dwacc[i][j] += d[j] * xh[i][j];
+          }
+        }
+      }
+    }
+    dot = group_sum<TPR>(dot, sred);
+    if (active) {
+      const float mean = dot / static_cast<float>(N);
+      const uint4* rp = dres_in ? reinterpret_cast<const uint4*>(dres_in + static_cast<long long>(row) * N) : nullptr;
+      uint4* dxp = reinterpret_cast<uint4*>(dx + static_cast<long long>(row) * N);
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) {
+        const int v = t + i * TPR;
+        if (v < nvec) {
+          float o[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] = rstd * (g[i][j] - xh[i][j] * mean);
+          if (rp) {
+            float r[8];
+            unpack8(rp[v], r);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] += r[j];
+          }
+          dxp[v] = pack8(o);
+        }
+      }
+    }
+  }
+  // block-level reduction of dw over the row groups, then one partial row per block
+  if (RPB > 1) {
+    for (int i = threadIdx.x; i < N; i += EW_THREADS) sdw[i] = 0.f;
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int v = t + i * TPR;
+      if (v < nvec)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) atomicAdd(&sdw[v * 8 + j], dwacc[i][j]);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < N; i += EW_THREADS) dw_part[static_cast<long long>(blockIdx.x) * N + i] = sdw[i];
+  } else {
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int v = t + i * TPR;
+      if (v < nvec)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) dw_part[static_cast<long long>(blockIdx.x) * N + v * 8 + j] = dwacc[i][j];
+    }
+  }
+}
+
+__global__ void rmsnorm_dw_reduce_kernel(const float* __restrict__ part, int nblocks, int N, bf16* __restrict__ dw,
+                                         int accumulate) {
+  const int n = blockIdx.x * blockDim.x + threadIdx.x;
+  if (n >= N) return;
+  float s = 0.f;
+  for (int b = 0; b < nblocks; ++b) s += part[static_cast<long long>(b) * N + n];
+  if (accumulate) s += __bfloat162float(dw[n]);
+  dw[n] = __float2bfloat16(s);
+}
+
+// ------------------------------------------------------------------ gated activations
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
+__device__ __forceinline__ float gelu_tanh(float x) {
+  const float k = 0.7978845608028654f;
+  return 0.5f * x * (1.f + tanhf(k * (x + 0.044715f * x * x * x)));
+}
+__device__ __forceinline__ float gelu_tanh_grad(float x) {
+  const float k = 0.7978845608028654f;
+  const float u = k * (x + 0.044715f * x * x * x);
+  const float th = tanhf(u);
+  return 0.5f * (1.f + th) + 0.5f * x * (1.f - th * th) * k * (1.f + 3.f * 0.044715f * x * x);
+}
+
+// out[m, i] = act(gate[m, i]) * up[m, i];  rows have pitch ld_in / ld_out (elements), I % 8 == 0
+template <int GELU>
+__global__ void __launch_bounds__(EW_THREADS)
+glu_fwd_kernel(const bf16* __restrict__ gate, const bf16* __restrict__ up, bf16* __restrict__ out, long long M, int I,
+               long long ld_in, long long ld_out) {
+  const int vpr = I / 8;
+  const long long total = M * vpr;
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long m = idx / vpr;
+    const int v = static_cast<int>(idx % vpr);
+    float g[8], u[8], o[8];
+    unpack8(*reinterpret_cast<const uint4*>(gate + m * ld_in + v * 8), g);
+    unpack8(*reinterpret_cast<const uint4*>(up + m * ld_in + v * 8), u);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = (GELU ? gelu_tanh(g[j]) : g[j] * sigmoidf_(g[j])) * u[j];
+    *reinterpret_cast<uint4*>(out + m * ld_out + v * 8) = pack8(o);
+  }
+}
+
+template <int GELU>
+__global__ void __launch_bounds__(EW_THREADS)
+glu_bwd_kernel(const bf16* __restrict__ dout, const bf16* __restrict__ gate, const bf16* __restrict__ up,
+               bf16* __restrict__ dgate, bf16* __restrict__ dup, long long M, int I, long long ld_dout,
+               long long ld_in, long long ld_din) {
+  const int vpr = I / 8;
+  const long long total = M * vpr;
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long m = idx / vpr;
+    const int v = static_cast<int>(idx % vpr);
+    float d[8], g[8], u[8], dg[8], du[8];
+    unpack8(*reinterpret_cast<const uint4*>(dout + m * ld_dout + v * 8), d);
+    unpack8(*reinterpret_cast<const uint4*>(gate + m * ld_in + v * 8), g);
+    unpack8(*reinterpret_cast<const uint4*>(up + m * ld_in + v * 8), u);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (GELU) {
+        du[j] = d[j] * gelu_tanh(g[j]);
+        dg[j] = d[j] * u[j] * gelu_tanh_grad(g[j]);
+      } else {
+        const float s = sigmoidf_(g[j]);
+        du[j] = d[j] * g[j] * s;
+        dg[j] = d[j] * u[j] * s * (1.f + g[j] * (1.f - s));
+      }
+    }
+    *reinterpret_cast<uint4*>(dgate + m * ld_din + v * 8) = pack8(dg);
+    *reinterpret_cast<uint4*>(dup + m * ld_din + v * 8) = pack8(du);
+  }
+}
+
+// ------------------------------------------------------------------ rotary embedding, in place
+// q: [T, hq, D] and k: [T, hk, D] with token pitches ldq / ldk (so both may live inside one
+// fused QKV buffer).  cos/sin: [P, D/2] fp32.  pos: [T] int64 or null (position = token index).
+// One thread rotates 8 pairs.  sign = -1 gives the inverse rotation (the backward).
+template <int INTERLEAVED>
+__global__ void __launch_bounds__(EW_THREADS)
+qk_rope_kernel(bf16* __restrict__ q, bf16* __restrict__ k, const float* __restrict__ cosT,
+               const float* __restrict__ sinT, const long long* __restrict__ pos, long long T, int hq, int hk, int D,
+               long long ldq, long long ldk, float sign) {
+  const int half = D / 2;
+  const int tph = half / 8;  // threads per head
+  const int heads = hq + hk;
+  const long long total = T * heads * tph;
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int c = static_cast<int>(idx % tph);
+    const int hh = static_cast<int>((idx / tph) % heads);
+    const long long t = idx / (static_cast<long long>(tph) * heads);
+    const long long p = pos ? pos[t] : t;
+    bf16* base = hh < hq ? q + t * ldq + static_cast<long long>(hh) * D : k + t * ldk + static_cast<long long>(hh - hq) * D;
+    const float4* cp = reinterpret_cast<const float4*>(cosT + p * half + c * 8);
+    const float4* sp = reinterpret_cast<const float4*>(sinT + p * half + c * 8);
+    const float4 c0 = cp[0], c1 = cp[1], s0 = sp[0], s1 = sp[1];
+    const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const float sn[8] = {s0.x * sign, s0.y * sign, s0.z * sign, s0.w * sign,
+                         s1.x * sign, s1.y * sign, s1.z * sign, s1.w * sign};
+    if (INTERLEAVED) {
+      uint4* p0 = reinterpret_cast<uint4*>(base + c * 16);
+      float a[8], b[8];
+      unpack8(p0[0], a);
+      unpack8(p0[1], b);
+      float o0[8], o1[8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float x1 = a[2 * j], x2 = a[2 * j + 1];
+        o0[2 * j] = x1 * cs[j] - x2 * sn[j];
+        o0[2 * j + 1] = x2 * cs[j] + x1 * sn[j];
+        const float y1 = b[2 * j], y2 = b[2 * j + 1];
+        o1[2 * j] = y1 * cs[4 + j] - y2 * sn[4 + j];
+        o1[2 * j + 1] = y2 * cs[4 + j] + y1 * sn[4 + j];
+      }
+      p0[0] = pack8(o0);
+      p0[1] = pack8(o1);
+    } else {
+      uint4* p1 = reinterpret_cast<uint4*>(base + c * 8);
+      uint4* p2 = reinterpret_cast<uint4*>(base + half + c * 8);
+      float x1[8], x2[8], o1[8], o2[8];
+      unpack8(*p1, x1);
+      unpack8(*p2, x2);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        o1[j] = x1[j] * cs[j] - x2[j] * sn[j];
+        o2[j] = x2[j] * cs[j] + x1[j] * sn[j];
+      }
+      *p1 = pack8(o1);
+      *p2 = pack8(o2);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ embedding
+__global__ void __launch_bounds__(128)
+embedding_fwd_kernel(const long long* __restrict__ ids, const bf16* __restrict__ table, bf16* __restrict__ out,
+                     long long T, int N, long long V) {
+  const int nvec = N / 8;
+  for (long long t = blockIdx.x; t < T; t += gridDim.x) {
+    long long id = ids[t];
+    if (id < 0 || id >= V) id = 0;   // out-of-range ids read row 0 instead of faulting
+    const uint4* src = reinterpret_cast<const uint4*>(table + id * N);
+    uint4* dst = reinterpret_cast<uint4*>(out + t * N);
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) dst[v] = src[v];
+  }
+}
+
+// Deterministic scatter-add: `sorted_ids` ascending with `perm` the source token of each
+// entry.  The block at the first entry of a run sums the run in fp32 and is the only
+// writer of that table row.
+__global__ void __launch_bounds__(128)
+embedding_bwd_kernel(const long long* __restrict__ sorted_ids, const long long* __restrict__ perm,
+                     const bf16* __restrict__ dout, bf16* __restrict__ dtable, long long T, int N, long long V,
+                     int accumulate) {
+  const long long i = blockIdx.x;
+  const long long id = sorted_ids[i];
+  if (id < 0 || id >= V) return;
+  if (i > 0 && sorted_ids[i - 1] == id) return;
+  const int nvec = N / 8;
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    float acc[8];
+    uint4* dst = reinterpret_cast<uint4*>(dtable + id * N) + v;
+    if (accumulate) unpack8(*dst, acc);
+    else
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (long long r = i; r < T && sorted_ids[r] == id; ++r) {
+      float d[8];
+      unpack8(reinterpret_cast<const uint4*>(dout + perm[r] * N)[v], d);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += d[j];
+    }
+    *dst = pack8(acc);
+  }
+}
+
+// ------------------------------------------------------------------ cross-entropy on materialised logits
+// One block per row.  Pass 1: online (max, sum-exp); pass 2 (optional): gradient in place.
+template <typename T>
+__device__ __forceinline__ float ldf(const T* p);
+template <>
+__device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
+template <>
+__device__ __forceinline__ float ldf<bf16>(const bf16* p) { return __bfloat162float(*p); }
+template <typename T>
+__device__ __forceinline__ void stf(T* p, float v);
+template <>
+__device__ __forceinline__ void stf<float>(float* p, float v) { *p = v; }
+template <>
+__device__ __forceinline__ void stf<bf16>(bf16* p, float v) { *p = __float2bfloat16(v); }
+
+template <typename T>
+__global__ void __launch_bounds__(EW_THREADS)
+ce_logits_kernel(const T* __restrict__ logits, const long long* __restrict__ labels, long long ld, int V,
+                 long long ignore_index, float smoothing, float z_weight, float* __restrict__ loss_rows,
+                 float* __restrict__ lse_out) {
+  __shared__ float sm[EW_THREADS / 32], ss[EW_THREADS / 32], sl[EW_THREADS / 32];
+  const long long row = blockIdx.x;
+  const T* lp = logits + row * ld;
+  float m = -INFINITY, s = 0.f, sumv = 0.f;
+  for (int c = threadIdx.x; c < V; c += blockDim.x) {
+    const float v = ldf<T>(lp + c);
+    const float nm = fmaxf(m, v);
+    s = s * __expf(m - nm) + __expf(v - nm);
+    m = nm;
+    sumv += v;
+  }
+  // combine (m, s) pairs across the block
+  for (int o = 16; o > 0; o >>= 1) {
+    const float om = __shfl_xor_sync(0xffffffffu, m, o), os = __shfl_xor_sync(0xffffffffu, s, o);
+    const float nm = fmaxf(m, om);
+    s = (m > -INFINITY ? s * __expf(m - nm) : 0.f) + (om > -INFINITY ? os * __expf(om - nm) : 0.f);
+    m = nm;
+    sumv += __shfl_xor_sync(0xffffffffu, sumv, o);
+  }
+  if ((threadIdx.x & 31) == 0) { sm[threadIdx.x >> 5] = m; ss[threadIdx.x >> 5] = s; sl[threadIdx.x >> 5] = sumv; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float M = -INFINITY, S = 0.f, L = 0.f;
+    for (int i = 0; i < EW_THREADS / 32; ++i) M = fmaxf(M, sm[i]);
+    for (int i = 0; i < EW_THREADS / 32; ++i) { if (sm[i] > -INFINITY) S += ss[i] * __expf(sm[i] - M); L += sl[i]; }
+    const float lse = M + __logf(S);
+    lse_out[row] = lse;
+    const long long lab = labels[row];
+    float loss = 0.f;
+    if (lab != ignore_index && lab >= 0 && lab < V) {
+      loss = lse - ldf<T>(lp + lab);
+      if (smoothing != 0.f) loss = (1.f - smoothing) * loss + smoothing * (lse - L / static_cast<float>(V));
+      loss += z_weight * lse * lse;
+    }
+    loss_rows[row] = loss;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(EW_THREADS)
+ce_logits_grad_kernel(const T* __restrict__ logits, T* __restrict__ dlogits, const long long* __restrict__ labels,
+                      const float* __restrict__ lse_in, const float* __restrict__ gscale, const float* __restrict__ gout,
+                      long long ld, int V, long long ignore_index, float smoothing, float z_weight) {
+  const long long row = blockIdx.x;
+  const long long lab = labels[row];
+  const bool valid = lab != ignore_index && lab >= 0 && lab < V;
+  const float lse = lse_in[row];
+  const float gs = valid ? gscale[row] * gout[0] : 0.f;
+  const float coef = 1.f + 2.f * z_weight * lse;
+  const float smv = smoothing / static_cast<float>(V);
+  for (int c = threadIdx.x; c < V; c += blockDim.x) {
+    float p = __expf(ldf<T>(logits + row * ld + c) - lse) * coef - smv;
+    if (c == lab) p -= (1.f - smoothing);
+    stf<T>(dlogits + row * ld + c, p * gs);
+  }
+}
+
+}  // namespace cb
+
+// =========================================================================================== host side
+namespace {
+int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return n;
+}
+int grid_for(long long work_items, int per_block, int max_waves = 8) {
+  long long b = (work_items + per_block - 1) / per_block;
+  const long long cap = static_cast<long long>(sm_count()) * max_waves;
+  if (b > cap) b = cap;
+  if (b < 1) b = 1;
+  return static_cast<int>(b);
+}
+// rows-per-thread-group choice: the smallest group whose registers hold the row (VPL = 4 vectors of 8)
+int pick_tpr(int N) {
+  const int nvec = N / 8;
+  if (nvec <= 32 * 4) return 32;
+  if (nvec <= 128 * 4) return 128;
+  if (nvec <= 256 * 4) return 256;
+  return 0;
+}
+}  // namespace
+
+extern "C" {
+
+int cb_rmsnorm_max_n() { return 256 * 4 * 8; }
+// number of [N] fp32 partial rows the backward writes (size the scratch as blocks * N floats)
+int cb_rmsnorm_bwd_blocks(int M, int N) {
+  const int tpr = pick_tpr(N);
+  if (tpr == 0) return 0;
+  return grid_for(M, cb::EW_THREADS / tpr, 2);
+}
+
+int cb_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* h_out, float* rstd, int M, int N,
+                   float eps, float offset, void* stream) {
+  if (N % 8 != 0) return -1;
+  const int tpr = pick_tpr(N);
+  if (tpr == 0) return -2;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const cb::bf16* xp = static_cast<const cb::bf16*>(x);
+  const cb::bf16* rp = static_cast<const cb::bf16*>(res);
+  const cb::bf16* wp = static_cast<const cb::bf16*>(w);
+  cb::bf16* yp = static_cast<cb::bf16*>(y);
+  cb::bf16* hp = static_cast<cb::bf16*>(h_out);
+  const int grid = grid_for(M, cb::EW_THREADS / tpr, 8);
+  if (tpr == 32) cb::rmsnorm_fwd_kernel<32, 4><<<grid, cb::EW_THREADS, 0, s>>>(xp, rp, wp, yp, hp, rstd, M, N, eps, offset);
+  else if (tpr == 128) cb::rmsnorm_fwd_kernel<128, 4><<<grid, cb::EW_THREADS, 0, s>>>(xp, rp, wp, yp, hp, rstd, M, N, eps, offset);
+  else cb::rmsnorm_fwd_kernel<256, 4><<<grid, cb::EW_THREADS, 0, s>>>(xp, rp, wp, yp, hp, rstd, M, N, eps, offset);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// dw_part: scratch of cb_rmsnorm_bwd_blocks(M, N) * N floats.
+int cb_rmsnorm_bwd(const void* dy, const void* h, const void* w, const float* rstd, const void* dres_in, void* dx,
+                   void* dw, float* dw_part, int M, int N, float offset, int accumulate_dw, void* stream) {
+  if (N % 8 != 0) return -1;
+  const int tpr = pick_tpr(N);
+  if (tpr == 0) return -2;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const cb::bf16* dyp = static_cast<const cb::bf16*>(dy);
+  const cb::bf16* hp = static_cast<const cb::bf16*>(h);
+  const cb::bf16* wp = static_cast<const cb::bf16*>(w);
+  const cb::bf16* rp = static_cast<const cb::bf16*>(dres_in);
+  cb::bf16* dxp = static_cast<cb::bf16*>(dx);
+  const int grid = cb_rmsnorm_bwd_blocks(M, N);
+  const size_t smem = static_cast<size_t>(N) * sizeof(float);
+  if (tpr == 32) cb::rmsnorm_bwd_kernel<32, 4><<<grid, cb::EW_THREADS, smem, s>>>(dyp, hp, wp, rstd, rp, dxp, dw_part, M, N, offset);
+  else if (tpr == 128) cb::rmsnorm_bwd_kernel<128, 4><<<grid, cb::EW_THREADS, smem, s>>>(dyp, hp, wp, rstd, rp, dxp, dw_part, M, N, offset);
+  else cb::rmsnorm_bwd_kernel<256, 4><<<grid, cb::EW_THREADS, smem, s>>>(dyp, hp, wp, rstd, rp, dxp, dw_part, M, N, offset);
+  if (dw != nullptr)
+    cb::rmsnorm_dw_reduce_kernel<<<(N + 255) / 256, 256, 0, s>>>(dw_part, grid, N, static_cast<cb::bf16*>(dw), accumulate_dw);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int cb_glu_fwd(const void* gate, const void* up, void* out, long long M, int I, long long ld_in, long long ld_out,
+               int gelu, void* stream) {
+  if (I % 8 != 0 || ld_in % 8 != 0 || ld_out % 8 != 0) return -1;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int grid = grid_for(M * (I / 8), cb::EW_THREADS, 16);
+  const cb::bf16* g = static_cast<const cb::bf16*>(gate);
+  const cb::bf16* u = static_cast<const cb::bf16*>(up);
+  if (gelu) cb::glu_fwd_kernel<1><<<grid, cb::EW_THREADS, 0, s>>>(g, u, static_cast<cb::bf16*>(out), M, I, ld_in, ld_out);
+  else cb::glu_fwd_kernel<0><<<grid, cb::EW_THREADS, 0, s>>>(g, u, static_cast<cb::bf16*>(out), M, I, ld_in, ld_out);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int cb_glu_bwd(const void* dout, const void* gate, const void* up, void* dgate, void* dup, long long M, int I,
+               long long ld_dout, long long ld_in, long long ld_din, int gelu, void* stream) {
+  if (I % 8 != 0 || ld_in % 8 != 0 || ld_dout % 8 != 0 || ld_din % 8 != 0) return -1;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int grid = grid_for(M * (I / 8), cb::EW_THREADS, 16);
+  const cb::bf16* d = static_cast<const cb::bf16*>(dout);
+  const cb::bf16* g = static_cast<const cb::bf16*>(gate);
+  const cb::bf16* u = static_cast<const cb::bf16*>(up);
+  if (gelu) cb::glu_bwd_kernel<1><<<grid, cb::EW_THREADS, 0, s>>>(d, g, u, static_cast<cb::bf16*>(dgate), static_cast<cb::bf16*>(dup), M, I, ld_dout, ld_in, ld_din);
+  else cb::glu_bwd_kernel<0><<<grid, cb::EW_THREADS, 0, s>>>(d, g, u, static_cast<cb::bf16*>(dgate), static_cast<cb::bf16*>(dup), M, I, ld_dout, ld_in, ld_din);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int cb_qk_rope(void* q, void* k, const float* cosT, const float* sinT, const long long* pos, long long T, int hq,
+               int hk, int D, long long ldq, long long ldk, int interleaved, int inverse, void* stream) {
+  if (D % 16 != 0 || ldq % 8 != 0 || ldk % 8 != 0) return -1;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const long long total = T * (hq + hk) * (D / 16);
+  const int grid = grid_for(total, cb::EW_THREADS, 16);
+  const float sign = inverse ? -1.f : 1.f;
+  if (interleaved) cb::qk_rope_kernel<1><<<grid, cb::EW_THREADS, 0, s>>>(static_cast<cb::bf16*>(q), static_cast<cb::bf16*>(k), cosT, sinT, pos, T, hq, hk, D, ldq, ldk, sign);
+  else cb::qk_rope_kernel<0><<<grid, cb::EW_THREADS, 0, s>>>(static_cast<cb::bf16*>(q), static_cast<cb::bf16*>(k), cosT, sinT, pos, T, hq, hk, D, ldq, ldk, sign);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int cb_embedding_fwd(const long long* ids, const void* table, void* out, long long T, int N, long long V, void* stream) {
+  if (N % 8 != 0) return -1;
+  const int grid = grid_for(T, 1, 32);
+  cb::embedding_fwd_kernel<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(ids, static_cast<const cb::bf16*>(table), static_cast<cb::bf16*>(out), T, N, V);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int cb_embedding_bwd(const long long* sorted_ids, const long long* perm, const void* dout, void* dtable, long long T,
+                     int N, long long V, int accumulate, void* stream) {
+  if (N % 8 != 0 || T <= 0) return -1;
+  cb::embedding_bwd_kernel<<<static_cast<unsigned>(T), 128, 0, static_cast<cudaStream_t>(stream)>>>(sorted_ids, perm, static_cast<const cb::bf16*>(dout), static_cast<cb::bf16*>(dtable), T, N, V, accumulate);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int cb_ce_logits(const void* logits, const long long* labels, long long rows, long long ld, int V, int is_bf16,
+                 long long ignore_index, float smoothing, float z_weight, float* loss_rows, float* lse, void* stream) {
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (rows <= 0) return -1;
+  if (is_bf16) cb::ce_logits_kernel<cb::bf16><<<static_cast<unsigned>(rows), cb::EW_THREADS, 0, s>>>(static_cast<const cb::bf16*>(logits), labels, ld, V, ignore_index, smoothing, z_weight, loss_rows, lse);
+  else cb::ce_logits_kernel<float><<<static_cast<unsigned>(rows), cb::EW_THREADS, 0, s>>>(static_cast<const float*>(logits), labels, ld, V, ignore_index, smoothing, z_weight, loss_rows, lse);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int cb_ce_logits_grad(const void* logits, void* dlogits, const long long* labels, const float* lse, const float* gscale,
+                      const float* gout, long long rows, long long ld, int V, int is_bf16, long long ignore_index,
+                      float smoothing, float z_weight, void* stream) {
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (rows <= 0) return -1;
+  if (is_bf16) cb::ce_logits_grad_kernel<cb::bf16><<<static_cast<unsigned>(rows), cb::EW_THREADS, 0, s>>>(static_cast<const cb::bf16*>(logits), static_cast<cb::bf16*>(dlogits), labels, lse, gscale, gout, ld, V, ignore_index, smoothing, z_weight);
+  else cb::ce_logits_grad_kernel<float><<<static_cast<unsigned>(rows), cb::EW_THREADS, 0, s>>>(static_cast<const float*>(logits), static_cast<float*>(dlogits), labels, lse, gscale, gout, ld, V, ignore_index, smoothing, z_weight);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // extern "C"

@@ -1,0 +1,669 @@
+// bf16 GEMM on the 5th-generation tensor cores (tcgen05.mma, accumulators in
+// TMEM, operands staged by TMA), persistent and warp-specialised:
+//
+//   warp 0 (one lane)  : TMA producer   global -> 128B-swizzled smem ring
+//   warp 1 (one lane)  : MMA issuer     tcgen05.mma into one of two TMEM accumulators
+//   warps 2..5         : epilogue       tcgen05.ld -> registers -> fused math -> global
+//
+// C[M,N] = A[M,K] * B[N,K]^T with fp32 accumulation.  Each operand may be
+// K-major (row = M/N index, K contiguous) or MN-major (row = K index, M/N
+// contiguous), which covers forward (K,K), dgrad (K,MN) and wgrad (MN,MN)
+// without transposing anything in memory.
+//
+// Epilogues:
+//   EPI_STORE   : C = acc (+bias[n]) (+addend[m,n]) (+C), bf16 or fp32 out
+//   EPI_LSE     : cut-cross-entropy forward - running (max, sum-exp) per row over
+//                 a range of vocab tiles, the target logit, optional sum of logits;
+//                 the logits never leave the SM
+//   EPI_DLOGITS : cut-cross-entropy backward - recomputed logits turned into
+//                 d(loss)/d(logits) in registers and written as bf16 for the two
+//                 gradient GEMMs
+//
+// This replaces the cuBLAS calls behind every nn.Linear of the reference's
+// training step and the fp32 cuBLAS chunk GEMMs of its cut-cross-entropy
+// (reference: chronicals/kernels/cut_cross_entropy.py:915-981).
+#include "common.cuh"
+
+#include <mutex>
+#include <unordered_map>
+
+namespace cb {
+
+constexpr int BLOCK_M = 128;
+constexpr int BLOCK_K = 64;
+constexpr int UMMA_K = 16;
+constexpr int GEMM_THREADS = 192;
+
+enum : int { EPI_STORE = 0, EPI_LSE = 1, EPI_DLOGITS = 2 };
+
+struct GemmArgs {
+  int M, N, K;
+  int num_m_blocks, num_n_tiles, tiles_per_item, num_items;
+  // EPI_STORE / EPI_DLOGITS output
+  void* C;
+  long long ldc;
+  int out_fp32;
+  int accumulate;
+  const bf16* bias;
+  const bf16* addend;
+  long long ld_add;
+  // cut-cross-entropy
+  const long long* labels;  // [M], global vocab ids, ignore_index allowed
+  float* part_m;            // [n_splits, M]
+  float* part_s;            // [n_splits, M]
+  float* part_sum;          // [n_splits, M] or null (only for label smoothing)
+  float* tgt;               // [M] target logit (zero-initialised by the host)
+  const float* lse;         // [M]
+  const float* gscale;      // [M]  valid / n_valid
+  const float* gout;        // [1]  upstream gradient of the scalar loss
+  float z_weight;
+  float smoothing;
+  int V_total;     // vocabulary size for the smoothing term
+  int col_offset;  // global vocab id of column 0 of B (vocab chunk or tensor-parallel shard)
+  int* status;
+};
+
+template <int BLOCK_N, int STAGES>
+struct SmemLayout {
+  static constexpr int A_BYTES = BLOCK_M * BLOCK_K * 2;
+  static constexpr int B_BYTES = BLOCK_N * BLOCK_K * 2;
+  static constexpr int BAR_OFFSET = STAGES * (A_BYTES + B_BYTES);
+  static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;  // barriers + alignment slack
+};
+
+template <int BLOCK_N, int A_MN, int B_MN, int STAGES, int EPI>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const GemmArgs g) {
+  using L = SmemLayout<BLOCK_N, STAGES>;
+  constexpr int A_BYTES = L::A_BYTES, B_BYTES = L::B_BYTES;
+  constexpr uint32_t TMEM_COLS = 2 * BLOCK_N;  // two accumulators; 256 or 512 (powers of two)
+  constexpr uint32_t IDESC = umma_idesc_bf16(BLOCK_M, BLOCK_N, A_MN, B_MN);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * A_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
+  uint64_t* empty = full + STAGES;
+  uint64_t* tfull = empty + STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full + s, 1);
+      mbar_init(empty + s, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull + a, 1);
+      mbar_init(tempty + a, 4);
+    }
+    mbar_fence_init();
+    *abort_flag = (g.status[0] != 0) ? 1 : 0;
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  __syncthreads();
+  if (*abort_flag) return;  // poisoned by an earlier timeout: uniform early exit, nothing allocated yet
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int num_kb = (g.K + BLOCK_K - 1) / BLOCK_K;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < g.num_items && ok; item += gridDim.x) {
+        const int m_blk = item % g.num_m_blocks;
+        const int split = item / g.num_m_blocks;
+        const int nt0 = split * g.tiles_per_item;
+        const int nt1 = min(nt0 + g.tiles_per_item, g.num_n_tiles);
+        for (int nt = nt0; nt < nt1 && ok; ++nt) {
+          for (int kb = 0; kb < num_kb; ++kb) {
+            if (!mbar_wait(empty + stage, phase ^ 1, abort_flag, g.status, CB_ERR_WAIT_EMPTY)) {
+              ok = false;
+              break;
+            }
+            mbar_expect_tx(full + stage, A_BYTES + B_BYTES);
+            uint8_t* a_dst = sA + stage * A_BYTES;
+            uint8_t* b_dst = sB + stage * B_BYTES;
+            if (A_MN == 0) {
+              tma_load_2d(a_dst, &tmA, full + stage, kb * BLOCK_K, m_blk * BLOCK_M);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BLOCK_M / 64; ++j)
+                tma_load_2d(a_dst + j * 8192, &tmA, full + stage, m_blk * BLOCK_M + j * 64, kb * BLOCK_K);
+            }
+            if (B_MN == 0) {
+              tma_load_2d(b_dst, &tmB, full + stage, kb * BLOCK_K, nt * BLOCK_N);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BLOCK_N / 64; ++j)
+                tma_load_2d(b_dst + j * 8192, &tmB, full + stage, nt * BLOCK_N + j * 64, kb * BLOCK_K);
+            }
+            if (++stage == STAGES) {
+              stage = 0;
+              phase ^= 1;
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t tile_cnt = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < g.num_items && ok; item += gridDim.x) {
+        const int split = item / g.num_m_blocks;
+        const int nt0 = split * g.tiles_per_item;
+        const int nt1 = min(nt0 + g.tiles_per_item, g.num_n_tiles);
+        for (int nt = nt0; nt < nt1 && ok; ++nt, ++tile_cnt) {
+          const uint32_t acc = tile_cnt & 1u;
+          const uint32_t acc_phase = (tile_cnt >> 1) & 1u;
+          if (!mbar_wait(tempty + acc, acc_phase ^ 1, abort_flag, g.status, CB_ERR_WAIT_TMEM_EMPTY)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
+          for (int kb = 0; kb < num_kb; ++kb) {
+            if (!mbar_wait(full + stage, phase, abort_flag, g.status, CB_ERR_WAIT_FULL)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            const uint32_t a_base = smem_u32(sA + stage * A_BYTES);
+            const uint32_t b_base = smem_u32(sB + stage * B_BYTES);
+#pragma unroll
+            for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+              const uint64_t adesc = A_MN ? umma_smem_desc(a_base + k * 2048, 8192, 1024)
+                                          : umma_smem_desc(a_base + k * 32, 16, 1024);
+              const uint64_t bdesc = B_MN ? umma_smem_desc(b_base + k * 2048, 8192, 1024)
+                                          : umma_smem_desc(b_base + k * 32, 16, 1024);
+              umma_f16_ss(d_tmem, adesc, bdesc, IDESC, (kb | k) != 0 ? 1u : 0u);
+            }
+            umma_commit(empty + stage);  // frees the smem stage once these MMAs retire
+            if (++stage == STAGES) {
+              stage = 0;
+              phase ^= 1;
+            }
+          }
+          if (ok) umma_commit(tfull + acc);  // accumulator complete
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------- epilogue (4 warps, one TMEM lane quarter each)
+    const int q = warp & 3;
+    const int row_in_tile = q * 32 + lane;
+    uint32_t tile_cnt = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < g.num_items && ok; item += gridDim.x) {
+      const int m_blk = item % g.num_m_blocks;
+      const int split = item / g.num_m_blocks;
+      const int nt0 = split * g.tiles_per_item;
+      const int nt1 = min(nt0 + g.tiles_per_item, g.num_n_tiles);
+      const int row = m_blk * BLOCK_M + row_in_tile;
+      const bool row_ok = row < g.M;
+
+      // per-row state of the cut-cross-entropy epilogues
+      float run_m = -INFINITY, run_s = 0.f, run_sum = 0.f;
+      int lab = -1;
+      float lse_r = 0.f, gs = 0.f, coef = 1.f;
+      if (EPI != EPI_STORE && row_ok) {
+        const long long l = g.labels[row];
+        const long long rel = l - g.col_offset;
+        lab = (l >= 0 && rel >= 0 && rel < g.N) ? static_cast<int>(rel) : -1;
+        if (EPI == EPI_DLOGITS) {
+          lse_r = g.lse[row];
+          gs = g.gscale[row] * g.gout[0];
+          coef = 1.f + 2.f * g.z_weight * lse_r;
+        }
+      }
+
+      for (int nt = nt0; nt < nt1 && ok; ++nt, ++tile_cnt) {
+        const uint32_t acc = tile_cnt & 1u;
+        const uint32_t acc_phase = (tile_cnt >> 1) & 1u;
+        bool w = mbar_wait(tfull + acc, acc_phase, abort_flag, g.status, CB_ERR_WAIT_TMEM_FULL);
+        w = __all_sync(0xffffffffu, w);
+        if (!w) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BLOCK_N;
+#pragma unroll 1
+        for (int c = 0; c < BLOCK_N / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_row + c * 32, r);
+          tmem_ld_wait();
+          const int col0 = nt * BLOCK_N + c * 32;
+          if (col0 >= g.N) continue;  // uniform across the warp
+          const bool full_chunk = (col0 + 32 <= g.N);
+
+          if (EPI == EPI_LSE) {
+            if (row_ok) {
+              float cmax = -INFINITY;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const float v = __uint_as_float(r[j]);
+                if (full_chunk || col0 + j < g.N) cmax = fmaxf(cmax, v);
+              }
+              const float nm = fmaxf(run_m, cmax);
+              const float nm2 = nm * 1.4426950408889634f;
+              float acc_s = 0.f, acc_l = 0.f;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const float v = __uint_as_float(r[j]);
+                if (full_chunk || col0 + j < g.N) {
+                  acc_s += exp2f(fmaf(v, 1.4426950408889634f, -nm2));
+                  acc_l += v;
+                }
+              }
+              run_s = run_s * exp2f((run_m - nm) * 1.4426950408889634f) + acc_s;
+              run_m = nm;
+              run_sum += acc_l;
+              const int rel = lab - col0;
+              if (rel >= 0 && rel < 32) {
+                float t = 0.f;
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (j == rel) t = __uint_as_float(r[j]);
+                g.tgt[row] = t;
+              }
+            }
+          } else {
+            if (row_ok) {
+              float v[32];
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+              if (EPI == EPI_DLOGITS) {
+                const float sm = g.smoothing / static_cast<float>(g.V_total);
+                const float l2 = lse_r * 1.4426950408889634f;
+                const int rel = lab - col0;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                  float p = exp2f(fmaf(v[j], 1.4426950408889634f, -l2)) * coef - sm;
+                  if (j == rel) p -= (1.f - g.smoothing);
+                  v[j] = p * gs;
+                }
+              } else {
+                if (g.bias != nullptr) {
+#pragma unroll
+                  for (int j = 0; j < 32; ++j)
+                    if (full_chunk || col0 + j < g.N) v[j] += __bfloat162float(g.bias[col0 + j]);
+                }
+                if (g.addend != nullptr) {
+                  const bf16* ap = g.addend + static_cast<long long>(row) * g.ld_add + col0;
+#pragma unroll
+                  for (int j = 0; j < 32; ++j)
+                    if (full_chunk || col0 + j < g.N) v[j] += __bfloat162float(ap[j]);
+                }
+              }
+              if (g.out_fp32) {
+                float* cp = reinterpret_cast<float*>(g.C) + static_cast<long long>(row) * g.ldc + col0;
+                const bool vec = full_chunk && ((reinterpret_cast<uintptr_t>(cp) & 15) == 0);
+                if (vec) {
+                  float4* c4 = reinterpret_cast<float4*>(cp);
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) {
+                    float4 o = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                    if (g.accumulate) {
+                      const float4 old = c4[j];
+                      o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                    }
+                    c4[j] = o;
+                  }
+                } else {
+#pragma unroll
+                  for (int j = 0; j < 32; ++j)
+                    if (col0 + j < g.N) cp[j] = g.accumulate ? cp[j] + v[j] : v[j];
+                }
+              } else {
+                bf16* cp = reinterpret_cast<bf16*>(g.C) + static_cast<long long>(row) * g.ldc + col0;
+                const bool vec = full_chunk && ((reinterpret_cast<uintptr_t>(cp) & 15) == 0);
+                if (vec) {
+                  uint4* c4 = reinterpret_cast<uint4*>(cp);
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    if (g.accumulate) {
+                      const uint4 old = c4[j];
+                      const float2 o0 = unpack_bf16x2(old.x), o1 = unpack_bf16x2(old.y);
+                      const float2 o2 = unpack_bf16x2(old.z), o3 = unpack_bf16x2(old.w);
+                      v[8 * j + 0] += o0.x; v[8 * j + 1] += o0.y; v[8 * j + 2] += o1.x; v[8 * j + 3] += o1.y;
+                      v[8 * j + 4] += o2.x; v[8 * j + 5] += o2.y; v[8 * j + 6] += o3.x; v[8 * j + 7] += o3.y;
+                    }
+                    uint4 o;
+                    o.x = pack_bf16x2(v[8 * j + 0], v[8 * j + 1]);
+                    o.y = pack_bf16x2(v[8 * j + 2], v[8 * j + 3]);
+                    o.z = pack_bf16x2(v[8 * j + 4], v[8 * j + 5]);
+                    o.w = pack_bf16x2(v[8 * j + 6], v[8 * j + 7]);
+                    c4[j] = o;
+                  }
+                } else {
+#pragma unroll
+                  for (int j = 0; j < 32; ++j)
+                    if (col0 + j < g.N) {
+                      const float o = g.accumulate ? __bfloat162float(cp[j]) + v[j] : v[j];
+                      cp[j] = __float2bfloat16(o);
+                    }
+                }
+              }
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty + acc);
+      }
+      if (EPI == EPI_LSE && ok && row_ok) {
+        const long long o = static_cast<long long>(split) * g.M + row;
+        g.part_m[o] = run_m;
+        g.part_s[o] = run_s;
+        if (g.part_sum != nullptr) g.part_sum[o] = run_sum;
+      }
+    }
+  }
+
+  // ------------------------------------------------------------- teardown
+  __syncthreads();
+  if (*abort_flag) {
+    // a wait was abandoned: give copies already in flight time to land before the smem is released
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------ combine kernels for cut-cross-entropy
+// lse[row] from the per-split partials; per-row loss with smoothing and z-loss.
+__global__ void cce_combine_rows_kernel(const float* __restrict__ part_m, const float* __restrict__ part_s,
+                                        const float* __restrict__ part_sum, const float* __restrict__ tgt,
+                                        const long long* __restrict__ labels, int M, int n_splits, int V_total,
+                                        float smoothing, float z_weight, long long ignore_index,
+                                        float* __restrict__ lse_out, float* __restrict__ loss_rows) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= M) return;
+  float m = -INFINITY;
+  for (int s = 0; s < n_splits; ++s) m = fmaxf(m, part_m[static_cast<long long>(s) * M + row]);
+  float sum = 0.f, sl = 0.f;
+  for (int s = 0; s < n_splits; ++s) {
+    const long long o = static_cast<long long>(s) * M + row;
+    const float pm = part_m[o];
+    if (pm > -INFINITY) sum += part_s[o] * __expf(pm - m);
+    if (part_sum != nullptr) sl += part_sum[o];
+  }
+  const float lse = m + __logf(sum);
+  lse_out[row] = lse;
+  const bool valid = labels[row] != ignore_index;
+  float loss = lse - tgt[row];
+  if (smoothing != 0.f) loss = (1.f - smoothing) * loss + smoothing * (lse - sl / static_cast<float>(V_total));
+  loss += z_weight * lse * lse;
+  loss_rows[row] = valid ? loss : 0.f;
+}
+
+// Single block: deterministic sum of per-row losses and the valid count; writes
+// out[0] = mean (or sum), out[1] = n_valid, and gscale[row] = valid / n_valid (or valid).
+__global__ void cce_finalize_kernel(const float* __restrict__ loss_rows, const long long* __restrict__ labels, int M,
+                                    long long ignore_index, int mean, float* __restrict__ out,
+                                    float* __restrict__ gscale) {
+  __shared__ float s_sum[32];
+  __shared__ float s_cnt[32];
+  __shared__ float s_n;
+  float sum = 0.f, cnt = 0.f;
+  for (int i = threadIdx.x; i < M; i += blockDim.x) {
+    sum += loss_rows[i];
+    cnt += (labels[i] != ignore_index) ? 1.f : 0.f;
+  }
+  sum = warp_sum(sum);
+  cnt = warp_sum(cnt);
+  if ((threadIdx.x & 31) == 0) {
+    s_sum[threadIdx.x >> 5] = sum;
+    s_cnt[threadIdx.x >> 5] = cnt;
+  }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    const int nw = blockDim.x >> 5;
+    float a = threadIdx.x < nw ? s_sum[threadIdx.x] : 0.f;
+    float b = threadIdx.x < nw ? s_cnt[threadIdx.x] : 0.f;
+    a = warp_sum(a);
+    b = warp_sum(b);
+    if (threadIdx.x == 0) {
+      const float n = fmaxf(b, 1.f);
+      out[0] = mean ? a / n : a;
+      out[1] = b;
+      s_n = mean ? n : 1.f;
+    }
+  }
+  __syncthreads();
+  const float inv = 1.f / s_n;
+  for (int i = threadIdx.x; i < M; i += blockDim.x) gscale[i] = (labels[i] != ignore_index) ? inv : 0.f;
+}
+
+}  // namespace cb
+
+// =========================================================================================== host side
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// 2-D bf16 tensor map: `inner` contiguous elements per row, `outer` rows, row pitch `ld` elements.
+int make_tmap(CUtensorMap* out, const void* base, unsigned long long inner, unsigned long long outer,
+              unsigned long long ld, unsigned box_inner, unsigned box_outer) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return -10;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (ld * 2) % 16 != 0) return -11;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -12;
+}
+
+int num_sms() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return n;
+}
+
+template <int BLOCK_N, int A_MN, int B_MN, int STAGES, int EPI>
+int launch(const CUtensorMap& ta, const CUtensorMap& tb, const cb::GemmArgs& g, cudaStream_t stream) {
+  auto kern = cb::gemm_tcgen05_kernel<BLOCK_N, A_MN, B_MN, STAGES, EPI>;
+  constexpr int smem = cb::SmemLayout<BLOCK_N, STAGES>::TOTAL;
+  static bool configured = false;
+  if (!configured) {
+    CB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    configured = true;
+  }
+  const int grid = g.num_items < num_sms() ? g.num_items : num_sms();
+  kern<<<grid, cb::GEMM_THREADS, smem, stream>>>(ta, tb, g);
+  return static_cast<int>(cudaGetLastError());
+}
+
+template <int EPI>
+int dispatch(int block_n, int a_mn, int b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const cb::GemmArgs& g,
+             cudaStream_t s) {
+  if (block_n == 256) {
+    if (!a_mn && !b_mn) return launch<256, 0, 0, 4, EPI>(ta, tb, g, s);
+    if (EPI == cb::EPI_STORE) {
+      if (!a_mn && b_mn) return launch<256, 0, 1, 4, cb::EPI_STORE>(ta, tb, g, s);
+      if (a_mn && b_mn) return launch<256, 1, 1, 4, cb::EPI_STORE>(ta, tb, g, s);
+      if (a_mn && !b_mn) return launch<256, 1, 0, 4, cb::EPI_STORE>(ta, tb, g, s);
+    }
+  } else {
+    if (!a_mn && !b_mn) return launch<128, 0, 0, 6, EPI>(ta, tb, g, s);
+    if (EPI == cb::EPI_STORE) {
+      if (!a_mn && b_mn) return launch<128, 0, 1, 6, cb::EPI_STORE>(ta, tb, g, s);
+      if (a_mn && b_mn) return launch<128, 1, 1, 6, cb::EPI_STORE>(ta, tb, g, s);
+      if (a_mn && !b_mn) return launch<128, 1, 0, 6, cb::EPI_STORE>(ta, tb, g, s);
+    }
+  }
+  return -20;
+}
+
+int pick_block_n(int M, int N, int forced) {
+  if (forced == 128 || forced == 256) return forced;
+  const int mb = (M + 127) / 128;
+  const int sms = num_sms();
+  long long best_cost = -1;
+  int best = 256;
+  for (int bn : {256, 128}) {
+    const long long tiles = static_cast<long long>(mb) * ((N + bn - 1) / bn);
+    const long long waves = (tiles + sms - 1) / sms;
+    const long long cost = waves * (bn + 24);  // +24: per-tile fixed overhead in the same unit
+    if (best_cost < 0 || cost < best_cost) {
+      best_cost = cost;
+      best = bn;
+    }
+  }
+  return best;
+}
+
+int build_maps(CUtensorMap* ta, CUtensorMap* tb, const void* A, const void* B, int M, int N, int K, long long lda,
+               long long ldb, int a_mn, int b_mn, int block_n) {
+  int e;
+  if (!a_mn) e = make_tmap(ta, A, K, M, lda, 64, cb::BLOCK_M);   // rows = M, K contiguous
+  else e = make_tmap(ta, A, M, K, lda, 64, 64);                   // rows = K, M contiguous
+  if (e) return e;
+  if (!b_mn) e = make_tmap(tb, B, K, N, ldb, 64, block_n);
+  else e = make_tmap(tb, B, N, K, ldb, 64, 64);
+  return e;
+}
+
+}  // namespace
+
+extern "C" {
+
+// C[M,N] = A * B^T (+bias) (+addend) (+C).  a_mn / b_mn: 0 when the operand is stored [M|N, K]
+// (K contiguous), 1 when stored [K, M|N].  lda/ldb/ldc/ld_add are row pitches in elements.
+// Returns 0 on a successful launch; negative for rejected arguments; positive CUDA error otherwise.
+int cb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, const void* addend, int M, int N, int K,
+                 long long lda, long long ldb, long long ldc, long long ld_add, int a_mn, int b_mn, int out_fp32,
+                 int accumulate, int force_block_n, int* status, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return -1;
+  const int bn = pick_block_n(M, N, force_block_n);
+  CUtensorMap ta, tb;
+  int e = build_maps(&ta, &tb, A, B, M, N, K, lda, ldb, a_mn, b_mn, bn);
+  if (e) return e;
+  cb::GemmArgs g = {};
+  g.M = M; g.N = N; g.K = K;
+  g.num_m_blocks = (M + 127) / 128;
+  g.num_n_tiles = (N + bn - 1) / bn;
+  g.tiles_per_item = 1;
+  g.num_items = g.num_m_blocks * g.num_n_tiles;
+  g.C = C; g.ldc = ldc; g.out_fp32 = out_fp32; g.accumulate = accumulate;
+  g.bias = static_cast<const cb::bf16*>(bias);
+  g.addend = static_cast<const cb::bf16*>(addend);
+  g.ld_add = ld_add;
+  g.status = status;
+  return dispatch<cb::EPI_STORE>(bn, a_mn, b_mn, ta, tb, g, static_cast<cudaStream_t>(stream));
+}
+
+// Number of vocab splits the forward pass of the fused linear-cross-entropy uses for a
+// [M, V] problem (the partial buffers are [n_splits, M]).
+int cb_cce_num_splits(int M, int V) {
+  const int tiles = (V + 255) / 256;
+  const int per = tiles < 16 ? tiles : 16;
+  return (tiles + per - 1) / per;
+}
+
+// Forward: per-row log-sum-exp partials of hidden[M,K] * weight[V,K]^T, target logit.
+int cb_cce_forward(const void* hidden, const void* weight, const long long* labels, int M, int V, int K,
+                   long long ldh, long long ldw, int col_offset, float* part_m, float* part_s, float* part_sum,
+                   float* tgt, int* status, void* stream) {
+  const int bn = 256;
+  CUtensorMap ta, tb;
+  int e = build_maps(&ta, &tb, hidden, weight, M, V, K, ldh, ldw, 0, 0, bn);
+  if (e) return e;
+  cb::GemmArgs g = {};
+  g.M = M; g.N = V; g.K = K;
+  g.num_m_blocks = (M + 127) / 128;
+  g.num_n_tiles = (V + bn - 1) / bn;
+  g.tiles_per_item = g.num_n_tiles < 16 ? g.num_n_tiles : 16;
+  const int n_splits = (g.num_n_tiles + g.tiles_per_item - 1) / g.tiles_per_item;
+  g.num_items = g.num_m_blocks * n_splits;
+  g.labels = labels;
+  g.part_m = part_m; g.part_s = part_s; g.part_sum = part_sum; g.tgt = tgt;
+  g.col_offset = col_offset;
+  g.status = status;
+  return dispatch<cb::EPI_LSE>(bn, 0, 0, ta, tb, g, static_cast<cudaStream_t>(stream));
+}
+
+int cb_cce_combine(const float* part_m, const float* part_s, const float* part_sum, const float* tgt,
+                   const long long* labels, int M, int n_splits, int V_total, float smoothing, float z_weight,
+                   long long ignore_index, int mean, float* lse, float* loss_rows, float* out, float* gscale,
+                   void* stream) {
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cb::cce_combine_rows_kernel<<<(M + 255) / 256, 256, 0, s>>>(part_m, part_s, part_sum, tgt, labels, M, n_splits,
+                                                              V_total, smoothing, z_weight, ignore_index, lse,
+                                                              loss_rows);
+  cb::cce_finalize_kernel<<<1, 1024, 0, s>>>(loss_rows, labels, M, ignore_index, mean, out, gscale);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Backward, step 1: G[M, Vc] = d(loss)/d(logits) for the vocab columns [col_offset, col_offset + Vc)
+// of `weight_chunk` (= weight + col_offset * ldw), written as bf16 with row pitch ldg.
+int cb_cce_dlogits(const void* hidden, const void* weight_chunk, const long long* labels, const float* lse,
+                   const float* gscale, const float* gout, void* G, int M, int Vc, int K, long long ldh,
+                   long long ldw, long long ldg, int col_offset, int V_total, float smoothing, float z_weight,
+                   int* status, void* stream) {
+  const int bn = pick_block_n(M, Vc, 0);
+  CUtensorMap ta, tb;
+  int e = build_maps(&ta, &tb, hidden, weight_chunk, M, Vc, K, ldh, ldw, 0, 0, bn);
+  if (e) return e;
+  cb::GemmArgs g = {};
+  g.M = M; g.N = Vc; g.K = K;
+  g.num_m_blocks = (M + 127) / 128;
+  g.num_n_tiles = (Vc + bn - 1) / bn;
+  g.tiles_per_item = 1;
+  g.num_items = g.num_m_blocks * g.num_n_tiles;
+  g.C = G; g.ldc = ldg; g.out_fp32 = 0; g.accumulate = 0;
+  g.labels = labels; g.lse = lse; g.gscale = gscale; g.gout = gout;
+  g.z_weight = z_weight; g.smoothing = smoothing; g.V_total = V_total; g.col_offset = col_offset;
+  g.status = status;
+  return dispatch<cb::EPI_DLOGITS>(bn, 0, 0, ta, tb, g, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,481 @@
+"""Fused operators: one public function per op, two implementations each.
+
+* CUDA tensors in bf16 run the hand-written sm_100a kernels (``_ext``), wrapped
+  in ``torch.autograd.Function`` so forward and backward are both ours.
+* Everything else (CPU, fp32) runs the pure-PyTorch formulas in ``ref`` through
+  ordinary autograd.  That path is also the test oracle.
+
+On a CUDA device the kernel library is mandatory; a missing library raises.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+
+from . import ref
+from . import _ext
+
+__all__ = [
+    "linear", "gemm", "rmsnorm", "add_rmsnorm", "swiglu", "geglu", "qk_rope_", "embedding",
+    "attention_varlen", "linear_cross_entropy", "cross_entropy_logits", "kernels_active",
+]
+
+
+def _fast(*tensors: torch.Tensor) -> bool:
+    """True when the CUDA kernels handle these tensors (all CUDA + bf16)."""
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda or t.dtype != torch.bfloat16:
+            return False
+    return True
+
+
+def kernels_active(device="cuda") -> bool:
+    return torch.cuda.is_available() and _ext.available()
+
+
+# ============================================================================ GEMM
+def _gemm_ok(t: torch.Tensor) -> bool:
+    return t.dim() == 2 and t.stride(1) == 1 and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
+         bias: Optional[torch.Tensor] = None, addend: Optional[torch.Tensor] = None,
+         out: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16,
+         accumulate: bool = False, block_n: int = 0) -> torch.Tensor:
+    """``C[M,N] = op(A) @ op(B)^T (+bias) (+addend) (+C)`` on the tcgen05 kernel.
+
+    ``a_mn=False``: ``a`` is ``[M, K]``; ``a_mn=True``: ``a`` is ``[K, M]``
+    (the operand is used transposed without a copy).  Same for ``b`` with N.
+    """
+    M = a.shape[1] if a_mn else a.shape[0]
+    K = a.shape[0] if a_mn else a.shape[1]
+    N = b.shape[1] if b_mn else b.shape[0]
+    Kb = b.shape[0] if b_mn else b.shape[1]
+    assert K == Kb, f"inner dimensions differ: {K} vs {Kb}"
+    if out is None:
+        assert not accumulate
+        out = torch.empty(M, N, dtype=out_dtype, device=a.device)
+    if not (_gemm_ok(a) and _gemm_ok(b) and out.stride(1) == 1):
+        # shapes the TMA path cannot address (row pitch not a multiple of 16 bytes): library fallback
+        A = a.t() if a_mn else a
+        B = b if b_mn else b.t()
+        r = (A.float() @ B.float())
+        if bias is not None:
+            r = r + bias.float()
+        if addend is not None:
+            r = r + addend.float()
+        if accumulate:
+            r = r + out.float()
+        out.copy_(r)
+        return out
+    if addend is not None:
+        assert addend.stride(1) == 1 and addend.dtype == torch.bfloat16
+    code = _ext.lib().cb_gemm_bf16(
+        a.data_ptr(), b.data_ptr(), out.data_ptr(), _ext.ptr(bias), _ext.ptr(addend), M, N, K,
+        a.stride(0), b.stride(0), out.stride(0), addend.stride(0) if addend is not None else 0,
+        int(a_mn), int(b_mn), int(out.dtype == torch.float32), int(accumulate), block_n,
+        _ext.status_buffer(a.device).data_ptr(), _ext.stream_ptr())
+    _ext.check(code, "gemm_bf16")
+    return out
+
+
+class _LinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, bias, residual):
+        x2 = x.reshape(-1, x.shape[-1])
+        res2 = residual.reshape(-1, w.shape[0]) if residual is not None else None
+        y = gemm(x2, w, bias=bias, addend=res2)
+        ctx.save_for_backward(x2, w)
+        ctx.has_bias = bias is not None
+        ctx.has_res = residual is not None
+        ctx.x_shape = x.shape
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, w, b_mn=True).view(ctx.x_shape)          # dX = dY @ W
+        if ctx.needs_input_grad[1]:
+            dw = gemm(dy2, x2, a_mn=True, b_mn=True)                 # dW = dY^T @ X
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = dy2.float().sum(0).to(dy.dtype)
+        dres = dy if ctx.has_res else None
+        return dx, dw, db, dres
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
+           residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x @ w.T + bias (+ residual)``; the residual add is fused in the GEMM epilogue."""
+    if _fast(x, w, bias, residual):
+        return _LinearFn.apply(x, w, bias, residual)
+    y = torch.nn.functional.linear(x, w, bias)
+    return y + residual if residual is not None else y
+
+
+# ============================================================================ RMSNorm
+class _RMSNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, residual, w, eps, offset):
+        N = x.shape[-1]
+        x2 = x.reshape(-1, N)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        M = x2.shape[0]
+        y = torch.empty_like(x2)
+        rstd = torch.empty(M, dtype=torch.float32, device=x.device)
+        h = None
+        if residual is not None:
+            r2 = residual.reshape(-1, N)
+            if not r2.is_contiguous():
+                r2 = r2.contiguous()
+            h = torch.empty_like(x2)
+        code = _ext.lib().cb_rmsnorm_fwd(x2.data_ptr(), _ext.ptr(r2) if residual is not None else None, w.data_ptr(),
+                                         y.data_ptr(), _ext.ptr(h), rstd.data_ptr(), M, N, eps, offset,
+                                         _ext.stream_ptr())
+        _ext.check(code, "rmsnorm_fwd")
+        ctx.save_for_backward(h if h is not None else x2, w, rstd)
+        ctx.offset = offset
+        ctx.has_res = residual is not None
+        ctx.shape = x.shape
+        ctx.set_materialize_grads(False)
+        if residual is not None:
+            return y.view(x.shape), h.view(x.shape)
+        return y.view(x.shape), None
+
+    @staticmethod
+    def backward(ctx, dy, dh):
+        h, w, rstd = ctx.saved_tensors
+        M, N = h.shape
+        if dy is None:
+            dy = torch.zeros_like(h)
+        dy2 = dy.reshape(M, N)
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dres = None
+        if dh is not None:
+            dres = dh.reshape(M, N)
+            if not dres.is_contiguous():
+                dres = dres.contiguous()
+        L = _ext.lib()
+        blocks = L.cb_rmsnorm_bwd_blocks(M, N)
+        part = torch.empty(blocks * N, dtype=torch.float32, device=h.device)
+        dx = torch.empty_like(h)
+        dw = torch.empty_like(w)
+        code = L.cb_rmsnorm_bwd(dy2.data_ptr(), h.data_ptr(), w.data_ptr(), rstd.data_ptr(), _ext.ptr(dres),
+                                dx.data_ptr(), dw.data_ptr(), part.data_ptr(), M, N, ctx.offset, 0, _ext.stream_ptr())
+        _ext.check(code, "rmsnorm_bwd")
+        dxv = dx.view(ctx.shape)
+        return dxv, (dxv if ctx.has_res else None), dw, None, None
+
+
+def _rms_fast(x, w) -> bool:
+    return _fast(x, w) and x.shape[-1] % 8 == 0 and x.shape[-1] <= 8192
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6, offset: float = 0.0) -> torch.Tensor:
+    if _rms_fast(x, weight):
+        return _RMSNormFn.apply(x, None, weight, eps, offset)[0]
+    return ref.rmsnorm(x, weight, eps, offset)
+
+
+def add_rmsnorm(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6
+                ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``h = x + residual; y = rmsnorm(h)``; returns ``(y, h)`` from one kernel."""
+    if _rms_fast(x, weight) and _fast(residual):
+        return _RMSNormFn.apply(x, residual, weight, eps, 0.0)
+    return ref.add_rmsnorm(x, residual, weight, eps)
+
+
+# ============================================================================ gated activations
+class _GLUFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gate_up, gelu):
+        I = gate_up.shape[-1] // 2
+        gu = gate_up.reshape(-1, 2 * I)
+        if not gu.is_contiguous():
+            gu = gu.contiguous()
+        M = gu.shape[0]
+        out = torch.empty(M, I, dtype=gu.dtype, device=gu.device)
+        code = _ext.lib().cb_glu_fwd(gu.data_ptr(), gu.data_ptr() + 2 * I, out.data_ptr(), M, I, 2 * I, I, int(gelu),
+                                     _ext.stream_ptr())
+        _ext.check(code, "glu_fwd")
+        ctx.save_for_backward(gu)
+        ctx.gelu = gelu
+        ctx.shape = gate_up.shape
+        return out.view(*gate_up.shape[:-1], I)
+
+    @staticmethod
+    def backward(ctx, dout):
+        (gu,) = ctx.saved_tensors
+        M, I2 = gu.shape
+        I = I2 // 2
+        d2 = dout.reshape(M, I)
+        if not d2.is_contiguous():
+            d2 = d2.contiguous()
+        dgu = torch.empty_like(gu)
+        code = _ext.lib().cb_glu_bwd(d2.data_ptr(), gu.data_ptr(), gu.data_ptr() + 2 * I, dgu.data_ptr(),
+                                     dgu.data_ptr() + 2 * I, M, I, I, I2, I2, int(ctx.gelu), _ext.stream_ptr())
+        _ext.check(code, "glu_bwd")
+        return dgu.view(ctx.shape), None
+
+
+def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
+    """``silu(gate) * up`` for a ``[..., 2I]`` tensor holding ``gate | up``."""
+    if _fast(gate_up) and (gate_up.shape[-1] // 2) % 8 == 0:
+        return _GLUFn.apply(gate_up, False)
+    return ref.swiglu_packed(gate_up)
+
+
+def geglu(gate_up: torch.Tensor) -> torch.Tensor:
+    if _fast(gate_up) and (gate_up.shape[-1] // 2) % 8 == 0:
+        return _GLUFn.apply(gate_up, True)
+    return ref.geglu_packed(gate_up)
+
+
+# ============================================================================ RoPE
+def _rope_launch(qkv: torch.Tensor, cos, sin, pos, hq, hk, d, interleaved, inverse):
+    T = qkv.shape[0]
+    ld = qkv.stride(0)
+    code = _ext.lib().cb_qk_rope(qkv.data_ptr(), qkv.data_ptr() + 2 * hq * d, cos.data_ptr(), sin.data_ptr(),
+                                 _ext.ptr(pos), T, hq, hk, d, ld, ld, int(interleaved), int(inverse),
+                                 _ext.stream_ptr())
+    _ext.check(code, "qk_rope")
+
+
+class _QKRopeFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, qkv, cos, sin, pos, hq, hk, d, interleaved):
+        _rope_launch(qkv, cos, sin, pos, hq, hk, d, interleaved, False)
+        ctx.mark_dirty(qkv)
+        ctx.save_for_backward(cos, sin, pos if pos is not None else torch.empty(0))
+        ctx.cfg = (hq, hk, d, interleaved, pos is not None)
+        return qkv
+
+    @staticmethod
+    def backward(ctx, dqkv):
+        cos, sin, pos = ctx.saved_tensors
+        hq, hk, d, interleaved, has_pos = ctx.cfg
+        g = dqkv if dqkv.is_contiguous() else dqkv.contiguous()
+        g = g.clone() if g.data_ptr() == dqkv.data_ptr() else g
+        _rope_launch(g, cos, sin, pos if has_pos else None, hq, hk, d, interleaved, True)
+        return g, None, None, None, None, None, None, None
+
+
+def qk_rope_(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, position_ids: Optional[torch.Tensor],
+             num_q_heads: int, num_kv_heads: int, head_dim: int, interleaved: bool = False) -> torch.Tensor:
+    """Rotate the Q and K heads of a packed ``[T, (hq + 2 hk) * d]`` QKV buffer
+    (V untouched).  In place on CUDA; returns the rotated buffer."""
+    if _fast(qkv) and qkv.dim() == 2 and head_dim % 16 == 0 and cos.is_cuda:
+        if position_ids is not None and position_ids.dtype != torch.int64:
+            position_ids = position_ids.long()
+        return _QKRopeFn.apply(qkv, cos, sin, position_ids, num_q_heads, num_kv_heads, head_dim, interleaved)
+    T = qkv.shape[0]
+    nq, nk = num_q_heads * head_dim, num_kv_heads * head_dim
+    q = qkv[:, :nq].reshape(T, num_q_heads, head_dim)
+    k = qkv[:, nq:nq + nk].reshape(T, num_kv_heads, head_dim)
+    q = ref.apply_rope(q, cos, sin, position_ids, interleaved)
+    k = ref.apply_rope(k, cos, sin, position_ids, interleaved)
+    return torch.cat((q.reshape(T, nq), k.reshape(T, nk), qkv[:, nq + nk:]), dim=-1)
+
+
+# ============================================================================ embedding
+class _EmbeddingFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ids, table):
+        flat = ids.reshape(-1)
+        T = flat.numel()
+        V, N = table.shape
+        out = torch.empty(T, N, dtype=table.dtype, device=table.device)
+        code = _ext.lib().cb_embedding_fwd(flat.data_ptr(), table.data_ptr(), out.data_ptr(), T, N, V,
+                                           _ext.stream_ptr())
+        _ext.check(code, "embedding_fwd")
+        ctx.save_for_backward(flat)
+        ctx.tshape = table.shape
+        return out.view(*ids.shape, N)
+
+    @staticmethod
+    def backward(ctx, dout):
+        (flat,) = ctx.saved_tensors
+        V, N = ctx.tshape
+        T = flat.numel()
+        d2 = dout.reshape(T, N)
+        if not d2.is_contiguous():
+            d2 = d2.contiguous()
+        sorted_ids, perm = torch.sort(flat)
+        dtable = torch.zeros(V, N, dtype=dout.dtype, device=dout.device)
+        code = _ext.lib().cb_embedding_bwd(sorted_ids.data_ptr(), perm.data_ptr(), d2.data_ptr(), dtable.data_ptr(),
+                                           T, N, V, 0, _ext.stream_ptr())
+        _ext.check(code, "embedding_bwd")
+        return None, dtable
+
+
+def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    if _fast(table) and ids.is_cuda and table.shape[1] % 8 == 0 and table.is_contiguous():
+        return _EmbeddingFn.apply(ids.long(), table)
+    return torch.nn.functional.embedding(ids, table)
+
+
+# ============================================================================ attention
+def attention_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: torch.Tensor,
+                     max_seqlen: Optional[int] = None, causal: bool = True,
+                     softmax_scale: Optional[float] = None, seqlens_host=None) -> torch.Tensor:
+    """Causal GQA attention over packed documents (``q [T,Hq,D]``, ``k/v [T,Hk,D]``)."""
+    from . import attention as _attn
+    return _attn.attention_varlen(q, k, v, cu_seqlens, max_seqlen, causal, softmax_scale, seqlens_host)
+
+
+# ============================================================================ fused linear + cross-entropy
+CCE_BWD_CHUNK = 8192   # vocab columns whose d(logits) exist at any one time in the backward
+
+
+class _LinearCEFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, hidden, weight, labels, ignore_index, smoothing, z_weight, mean):
+        L = _ext.lib()
+        M, K = hidden.shape
+        V = weight.shape[0]
+        dev = hidden.device
+        n_splits = L.cb_cce_num_splits(M, V)
+        part = torch.empty(3 if smoothing else 2, n_splits, M, dtype=torch.float32, device=dev)
+        tgt = torch.zeros(M, dtype=torch.float32, device=dev)
+        status = _ext.status_buffer(dev)
+        code = L.cb_cce_forward(hidden.data_ptr(), weight.data_ptr(), labels.data_ptr(), M, V, K, hidden.stride(0),
+                                weight.stride(0), 0, part[0].data_ptr(), part[1].data_ptr(),
+                                part[2].data_ptr() if smoothing else None, tgt.data_ptr(), status.data_ptr(),
+                                _ext.stream_ptr())
+        _ext.check(code, "cce_forward")
+        lse = torch.empty(M, dtype=torch.float32, device=dev)
+        loss_rows = torch.empty(M, dtype=torch.float32, device=dev)
+        out = torch.empty(2, dtype=torch.float32, device=dev)
+        gscale = torch.empty(M, dtype=torch.float32, device=dev)
+        code = L.cb_cce_combine(part[0].data_ptr(), part[1].data_ptr(), part[2].data_ptr() if smoothing else None,
+                                tgt.data_ptr(), labels.data_ptr(), M, n_splits, V, smoothing, z_weight, ignore_index,
+                                int(mean), lse.data_ptr(), loss_rows.data_ptr(), out.data_ptr(), gscale.data_ptr(),
+                                _ext.stream_ptr())
+        _ext.check(code, "cce_combine")
+        ctx.save_for_backward(hidden, weight, labels, lse, gscale)
+        ctx.cfg = (smoothing, z_weight)
+        ctx.set_materialize_grads(False)
+        return out[0], loss_rows
+
+    @staticmethod
+    def backward(ctx, gout, grows):
+        hidden, weight, labels, lse, gscale = ctx.saved_tensors
+        smoothing, z_weight = ctx.cfg
+        L = _ext.lib()
+        M, K = hidden.shape
+        V = weight.shape[0]
+        dev = hidden.device
+        status = _ext.status_buffer(dev)
+        if grows is None and gout is not None:
+            g1 = gout.float().reshape(1).contiguous()     # the usual case: scalar loss, no extra kernels
+        else:
+            # gradient arriving through the per-row losses (reduction='none'/'sum' users)
+            rows_scale = torch.zeros_like(gscale)
+            if gout is not None:
+                rows_scale = rows_scale + gscale * gout.float()
+            if grows is not None:
+                rows_scale = rows_scale + grows.float() * (labels != -100)
+            gscale = rows_scale.contiguous()
+            g1 = torch.ones(1, dtype=torch.float32, device=dev)
+        need_dh, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        Vc = min(CCE_BWD_CHUNK, (V + 7) // 8 * 8)
+        G = torch.empty(M, Vc, dtype=torch.bfloat16, device=dev)
+        dh32 = torch.empty(M, K, dtype=torch.float32, device=dev) if need_dh else None
+        dw = torch.empty_like(weight) if need_dw else None
+        for c0 in range(0, V, Vc):
+            vc = min(Vc, V - c0)
+            wc = weight[c0:c0 + vc]
+            code = L.cb_cce_dlogits(hidden.data_ptr(), wc.data_ptr(), labels.data_ptr(), lse.data_ptr(),
+                                    gscale.data_ptr(), g1.data_ptr(), G.data_ptr(), M, vc, K, hidden.stride(0),
+                                    weight.stride(0), G.stride(0), c0, V, smoothing, z_weight, status.data_ptr(),
+                                    _ext.stream_ptr())
+            _ext.check(code, "cce_dlogits")
+            Gc = G[:, :vc]
+            if need_dh:   # dH += G_c @ W_c
+                gemm(Gc, wc, b_mn=True, out=dh32, accumulate=c0 > 0)
+            if need_dw:   # dW_c = G_c^T @ H
+                gemm(Gc, hidden, a_mn=True, b_mn=True, out=dw[c0:c0 + vc])
+        dh = dh32.to(hidden.dtype) if need_dh else None
+        return dh, dw, None, None, None, None, None
+
+
+def linear_cross_entropy(hidden: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor,
+                         bias: Optional[torch.Tensor] = None, ignore_index: int = -100,
+                         label_smoothing: float = 0.0, z_loss_weight: float = 0.0, reduction: str = "mean",
+                         chunk_size: int = 8192) -> torch.Tensor:
+    """Cross-entropy of ``hidden @ weight.T`` against ``labels`` without ever
+    holding the ``[tokens, vocab]`` logits (labels must already be shifted)."""
+    h = hidden.reshape(-1, hidden.shape[-1])
+    y = labels.reshape(-1)
+    if (_fast(h, weight) and bias is None and y.is_cuda and h.shape[1] % 8 == 0 and weight.stride(1) == 1
+            and weight.stride(0) % 8 == 0 and ignore_index == -100):
+        if not h.is_contiguous():
+            h = h.contiguous()
+        y = y.long().contiguous()
+        loss, rows = _LinearCEFn.apply(h, weight, y, ignore_index, float(label_smoothing), float(z_loss_weight),
+                                       reduction == "mean")
+        if reduction == "none":
+            return rows
+        if reduction == "sum":
+            return rows.sum()
+        return loss
+    return ref.linear_cross_entropy_chunked(h, weight, y, bias, ignore_index, label_smoothing, z_loss_weight,
+                                            reduction, chunk_size)
+
+
+# ============================================================================ CE on materialised logits
+class _CELogitsFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, labels, ignore_index, smoothing, z_weight):
+        L = _ext.lib()
+        rows, V = logits.shape
+        dev = logits.device
+        loss_rows = torch.empty(rows, dtype=torch.float32, device=dev)
+        lse = torch.empty(rows, dtype=torch.float32, device=dev)
+        code = L.cb_ce_logits(logits.data_ptr(), labels.data_ptr(), rows, logits.stride(0), V,
+                              int(logits.dtype == torch.bfloat16), ignore_index, smoothing, z_weight,
+                              loss_rows.data_ptr(), lse.data_ptr(), _ext.stream_ptr())
+        _ext.check(code, "ce_logits")
+        ctx.save_for_backward(logits, labels, lse)
+        ctx.cfg = (ignore_index, smoothing, z_weight)
+        return loss_rows
+
+    @staticmethod
+    def backward(ctx, grows):
+        logits, labels, lse = ctx.saved_tensors
+        ignore_index, smoothing, z_weight = ctx.cfg
+        rows, V = logits.shape
+        dl = torch.empty_like(logits)
+        one = torch.ones(1, dtype=torch.float32, device=logits.device)
+        gs = grows.float().contiguous()
+        code = _ext.lib().cb_ce_logits_grad(logits.data_ptr(), dl.data_ptr(), labels.data_ptr(), lse.data_ptr(),
+                                            gs.data_ptr(), one.data_ptr(), rows, logits.stride(0), V,
+                                            int(logits.dtype == torch.bfloat16), ignore_index, smoothing, z_weight,
+                                            _ext.stream_ptr())
+        _ext.check(code, "ce_logits_grad")
+        return dl, None, None, None, None
+
+
+def cross_entropy_logits(logits: torch.Tensor, labels: torch.Tensor, ignore_index: int = -100,
+                         label_smoothing: float = 0.0, z_loss_weight: float = 0.0,
+                         reduction: str = "mean") -> torch.Tensor:
+    lg = logits.reshape(-1, logits.shape[-1])
+    y = labels.reshape(-1)
+    if lg.is_cuda and lg.dtype in (torch.bfloat16, torch.float32) and lg.stride(1) == 1:
+        rows = _CELogitsFn.apply(lg, y.long().contiguous(), ignore_index, float(label_smoothing), float(z_loss_weight))
+        if reduction == "none":
+            return rows
+        if reduction == "sum":
+            return rows.sum()
+        return rows.sum() / (y != ignore_index).sum().clamp_min(1)
+    return ref.cross_entropy_logits(lg, y, ignore_index, label_smoothing, z_loss_weight, reduction)

@@ -1,0 +1,124 @@
+"""ctypes binding of the in-tree CUDA kernel library.
+
+The kernels expose a plain C ABI (raw device pointers + a stream handle) so the
+library builds with nothing but ``nvcc`` and loads without a C++ binding layer.
+On a machine with a GPU the library is required: ``lib()`` raises instead of
+letting callers fall back silently to PyTorch.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from typing import Optional
+
+import torch
+
+_LIB: Optional[ctypes.CDLL] = None
+_LOCK = threading.Lock()
+_STATUS = {}
+
+_PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+LIB_PATH = os.path.join(_PKG, "_cb_kernels.so")
+
+P = c_void_p
+I = c_int
+L = c_longlong
+F = c_float
+
+_PROTOTYPES = {
+    "cb_gemm_bf16": [P, P, P, P, P, I, I, I, L, L, L, L, I, I, I, I, I, P, P],
+    "cb_cce_num_splits": [I, I],
+    "cb_cce_forward": [P, P, P, I, I, I, L, L, I, P, P, P, P, P, P],
+    "cb_cce_combine": [P, P, P, P, P, I, I, I, F, F, L, I, P, P, P, P, P],
+    "cb_cce_dlogits": [P, P, P, P, P, P, P, I, I, I, L, L, L, I, I, F, F, P, P],
+    "cb_rmsnorm_max_n": [],
+    "cb_rmsnorm_bwd_blocks": [I, I],
+    "cb_rmsnorm_fwd": [P, P, P, P, P, P, I, I, F, F, P],
+    "cb_rmsnorm_bwd": [P, P, P, P, P, P, P, P, I, I, F, I, P],
+    "cb_glu_fwd": [P, P, P, L, I, L, L, I, P],
+    "cb_glu_bwd": [P, P, P, P, P, L, I, L, L, L, I, P],
+    "cb_qk_rope": [P, P, P, P, P, L, I, I, I, L, L, I, I, P],
+    "cb_embedding_fwd": [P, P, P, L, I, L, P],
+    "cb_embedding_bwd": [P, P, P, P, L, I, L, I, P],
+    "cb_ce_logits": [P, P, L, L, I, I, L, F, F, P, P, P],
+    "cb_ce_logits_grad": [P, P, P, P, P, P, L, L, I, I, L, F, F, P],
+    "cb_opt_chunk": [],
+    "cb_adamw_multi": [P, P, P, P, P, P, P, P, I, I, P, P, I, P],
+    "cb_grad_clip_coef": [P, P, P, I, I, P, P, F, P, I, P],
+}
+
+
+def available() -> bool:
+    return os.path.exists(LIB_PATH)
+
+
+def lib() -> ctypes.CDLL:
+    """The loaded kernel library; builds it first when the sources are newer."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    with _LOCK:
+        if _LIB is not None:
+            return _LIB
+        from ..csrc import build as _build
+        if not _build.is_current():
+            _build.build()
+        handle = ctypes.CDLL(LIB_PATH)
+        for name, argtypes in _PROTOTYPES.items():
+            fn = getattr(handle, name, None)
+            if fn is None:
+                continue
+            fn.argtypes = argtypes
+            fn.restype = c_int
+        _LIB = handle
+    return _LIB
+
+
+def has_symbol(name: str) -> bool:
+    return hasattr(lib(), name)
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        raise KernelError(f"{what}: kernel launch rejected/failed with code {code}")
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def status_buffer(device: Optional[torch.device] = None) -> torch.Tensor:
+    """Per-device int32[16] status words shared by every kernel that can wait.
+    ``status[0] != 0`` after a step means a bounded device-side wait gave up."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    buf = _STATUS.get(key)
+    if buf is None:
+        buf = torch.zeros(16, dtype=torch.int32, device=torch.device("cuda", key))
+        _STATUS[key] = buf
+    return buf
+
+
+_STATUS_NAMES = {101: "TMA stage never filled", 102: "smem stage never drained", 103: "accumulator never completed",
+                 104: "accumulator never released", 201: "peer flag never arrived", 301: "wait abandoned"}
+
+
+def check_status(device: Optional[torch.device] = None, reset: bool = True) -> None:
+    """Host-side check (synchronises).  Raises ``KernelError`` when a device wait timed out."""
+    buf = status_buffer(device)
+    vals = buf.tolist()
+    if vals[0] != 0:
+        if reset:
+            buf.zero_()
+        raise KernelError(f"device-side wait timed out: code {vals[0]} ({_STATUS_NAMES.get(vals[0], '?')}), "
+                          f"block {vals[1]}, thread {vals[2]}")
+
+
+def ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
