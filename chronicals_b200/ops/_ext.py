@@ -66,14 +66,47 @@ def lib() -> ctypes.CDLL:
         if not _build.is_current():
             _build.build()
         handle = ctypes.CDLL(LIB_PATH)
+        proxy = _Library(handle)
         for name, argtypes in _PROTOTYPES.items():
             fn = getattr(handle, name, None)
             if fn is None:
                 continue
             fn.argtypes = argtypes
             fn.restype = c_int
-        _LIB = handle
+            n = _KERNELS_PER_CALL.get(name, 1)
+            setattr(proxy, name, _Counted(fn, n) if n else fn)
+        _LIB = proxy
     return _LIB
+
+
+# device kernels launched by one call of each entry point (0: host-only query)
+_KERNELS_PER_CALL = {"cb_cce_num_splits": 0, "cb_rmsnorm_max_n": 0, "cb_rmsnorm_bwd_blocks": 0, "cb_opt_chunk": 0,
+                     "cb_cce_combine": 2, "cb_rmsnorm_bwd": 2, "cb_grad_clip_coef": 2}
+LAUNCH_COUNT = [0]
+
+
+class _Counted:
+    """Callable wrapper that counts the kernels this process launched through the library."""
+    __slots__ = ("fn", "n")
+
+    def __init__(self, fn, n):
+        self.fn, self.n = fn, n
+
+    def __call__(self, *args):
+        LAUNCH_COUNT[0] += self.n
+        return self.fn(*args)
+
+
+class _Library:
+    def __init__(self, handle):
+        self._handle = handle
+
+    def __getattr__(self, name):           # symbols without a prototype entry (looked up lazily)
+        return getattr(self._handle, name)
+
+
+def launches() -> int:
+    return LAUNCH_COUNT[0]
 
 
 def has_symbol(name: str) -> bool:

@@ -99,6 +99,7 @@ class ChronicalsTrainer:
         self.optimizer = None
         self.scheduler = None
         self._graph = None
+        self.graph_kernel_launches = 0
         self._static: Dict[str, torch.Tensor] = {}
         self._loss_acc: Optional[torch.Tensor] = None
         self._setup_training()
@@ -340,6 +341,8 @@ class ChronicalsTrainer:
         torch.cuda.current_stream(self.device).wait_stream(side)
         torch.cuda.synchronize(self.device)
         self.optimizer.ensure_state()      # moments must exist before capture, or their zero-fill would be replayed
+        from ..ops import _ext
+        launched_before = _ext.launches()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             loss = self._forward_loss(inp)
@@ -348,6 +351,7 @@ class ChronicalsTrainer:
                 self.dp.reduce_gradients()
             self.optimizer.launch_step()
             loss_out = loss.detach()
+        self.graph_kernel_launches = _ext.launches() - launched_before     # own kernels per replay
         self._graph = {"graph": graph, "static": static, "loss": loss_out, "key": key}
 
     # ==================================================================================== train

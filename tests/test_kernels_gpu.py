@@ -1,0 +1,256 @@
+"""CUDA kernels against plain PyTorch fp32 references of the same ops (tiny and odd shapes)."""
+import math
+
+import pytest
+import torch
+
+from chronicals_b200 import ops
+from chronicals_b200.ops import _ext, ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _rand(*shape, scale=1.0, dtype=torch.bfloat16, seed=0):
+    g = torch.Generator(device="cpu").manual_seed(seed + sum(shape))
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+def _close(a, b, rtol=2e-2, atol=2e-2, what=""):
+    a, b = a.float(), b.float()
+    err = (a - b).abs().max().item()
+    ref_mag = b.abs().max().item()
+    assert err <= atol + rtol * ref_mag, f"{what}: max err {err:.4g} vs magnitude {ref_mag:.4g}"
+
+
+def test_library_loaded_and_status_clean():
+    assert _ext.available()
+    _ext.lib()
+    _ext.check_status()
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 256, 128), (200, 136, 72), (8192, 1152, 896),
+                                   (1000, 896, 4864), (130, 8, 64)])
+@pytest.mark.parametrize("block_n", [0, 128, 256])
+def test_gemm_forward_kk(M, N, K, block_n):
+    a, b = _rand(M, K), _rand(N, K, seed=1)
+    bias = _rand(N, seed=2)
+    add = _rand(M, N, seed=3)
+    y = ops.gemm(a, b, bias=bias, addend=add, block_n=block_n)
+    want = a.float() @ b.float().t() + bias.float() + add.float()
+    _close(y, want, rtol=1e-2, atol=1e-2 * math.sqrt(K), what=f"gemm kk {M}x{N}x{K} bn={block_n}")
+    _ext.check_status()
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 128, 192), (8192, 896, 1152), (520, 264, 136)])
+def test_gemm_dgrad_layout(M, N, K):
+    # dX[M, N] = dY[M, K] @ W[K, N]  -> B operand stored [K, N] (N contiguous)
+    dy, w = _rand(M, K), _rand(K, N, seed=1)
+    y = ops.gemm(dy, w, b_mn=True)
+    _close(y, dy.float() @ w.float(), rtol=1e-2, atol=1e-2 * math.sqrt(K), what="dgrad")
+    _ext.check_status()
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 256), (1152, 896, 8192), (264, 136, 520)])
+def test_gemm_wgrad_layout(M, N, K):
+    # dW[M, N] = dY[K, M]^T @ X[K, N]  -> both operands stored with K as the row index
+    dy, x = _rand(K, M), _rand(K, N, seed=1)
+    y = ops.gemm(dy, x, a_mn=True, b_mn=True)
+    _close(y, dy.float().t() @ x.float(), rtol=1e-2, atol=1e-2 * math.sqrt(K), what="wgrad")
+    y32 = torch.zeros(M, N, dtype=torch.float32, device=DEV)
+    ops.gemm(dy, x, a_mn=True, b_mn=True, out=y32)
+    ops.gemm(dy, x, a_mn=True, b_mn=True, out=y32, accumulate=True)
+    _close(y32, 2 * (dy.float().t() @ x.float()), rtol=1e-2, atol=2e-2 * math.sqrt(K), what="wgrad fp32 accumulate")
+    _ext.check_status()
+
+
+def test_linear_autograd_matches_torch():
+    x = _rand(300, 256).requires_grad_()
+    w = _rand(384, 256, scale=0.05, seed=1).requires_grad_()
+    b = _rand(384, seed=2).requires_grad_()
+    r = _rand(300, 384, seed=3).requires_grad_()
+    y = ops.linear(x, w, b, r)
+    g = _rand(300, 384, seed=4)
+    y.backward(g)
+    xr, wr, br, rr = (t.detach().float().requires_grad_() for t in (x, w, b, r))
+    yr = torch.nn.functional.linear(xr, wr, br) + rr
+    yr.backward(g.float())
+    _close(y, yr, what="linear fwd")
+    _close(x.grad, xr.grad, what="linear dx")
+    _close(w.grad, wr.grad, rtol=2e-2, atol=0.3, what="linear dw")
+    _close(b.grad, br.grad, rtol=2e-2, atol=0.3, what="linear db")
+    _close(r.grad, rr.grad, what="linear dres")
+
+
+@pytest.mark.parametrize("M,N", [(64, 896), (1000, 3584), (77, 5120), (16, 256), (33, 8192)])
+def test_rmsnorm_fwd_bwd(M, N):
+    x = _rand(M, N).requires_grad_()
+    w = (1 + 0.1 * _rand(N, seed=1).float()).to(torch.bfloat16).requires_grad_()
+    y = ops.rmsnorm(x, w, 1e-6)
+    g = _rand(M, N, seed=2)
+    y.backward(g)
+    xr, wr = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    yr = ref.rmsnorm(xr, wr, 1e-6)
+    yr.backward(g.float())
+    _close(y, yr, what="rmsnorm fwd")
+    _close(x.grad, xr.grad, what="rmsnorm dx")
+    _close(w.grad, wr.grad, rtol=2e-2, atol=0.05 * math.sqrt(M), what="rmsnorm dw")
+
+
+def test_add_rmsnorm_fused_residual():
+    x, r = _rand(130, 896).requires_grad_(), _rand(130, 896, seed=1).requires_grad_()
+    w = _rand(896, seed=2).requires_grad_()
+    y, h = ops.add_rmsnorm(x, r, w)
+    (y.float().sum() + 2 * h.float().sum()).backward()
+    xr, rr, wr = (t.detach().float().requires_grad_() for t in (x, r, w))
+    hr = (xr + rr).to(torch.bfloat16).float()
+    yr = ref.rmsnorm(xr + rr, wr)
+    (yr.sum() + 2 * (xr + rr).sum()).backward()
+    _close(h, hr, what="residual sum")
+    _close(y, yr, what="add_rmsnorm fwd")
+    _close(x.grad, xr.grad, what="add_rmsnorm dx")
+    _close(r.grad, rr.grad, what="add_rmsnorm dres")
+
+
+@pytest.mark.parametrize("fn,reff", [(ops.swiglu, ref.swiglu_packed), (ops.geglu, ref.geglu_packed)])
+def test_glu_fwd_bwd(fn, reff):
+    gu = _rand(257, 2 * 688).requires_grad_()
+    y = fn(gu)
+    g = _rand(257, 688, seed=1)
+    y.backward(g)
+    gur = gu.detach().float().requires_grad_()
+    yr = reff(gur)
+    yr.backward(g.float())
+    _close(y, yr, what="glu fwd")
+    _close(gu.grad, gur.grad, what="glu bwd")
+
+
+@pytest.mark.parametrize("interleaved", [False, True])
+@pytest.mark.parametrize("hq,hk,d", [(14, 2, 64), (5, 1, 128)])
+def test_qk_rope_in_place_and_inverse(interleaved, hq, hk, d):
+    T = 300
+    qkv = _rand(T, (hq + 2 * hk) * d)
+    cos, sin = ref.rope_cache(512, d, 1e6, device=DEV)
+    pos = (torch.arange(T, device=DEV) % 97).long()
+    orig = qkv.clone()
+    out = ops.qk_rope_(qkv.clone().requires_grad_(False), cos, sin, pos, hq, hk, d, interleaved)
+    q = orig[:, :hq * d].view(T, hq, d)
+    k = orig[:, hq * d:(hq + hk) * d].view(T, hk, d)
+    qr = ref.apply_rope(q.float(), cos, sin, pos, interleaved)
+    kr = ref.apply_rope(k.float(), cos, sin, pos, interleaved)
+    _close(out[:, :hq * d], qr.reshape(T, -1), what="rope q")
+    _close(out[:, hq * d:(hq + hk) * d], kr.reshape(T, -1), what="rope k")
+    assert torch.equal(out[:, (hq + hk) * d:], orig[:, (hq + hk) * d:]), "V must be untouched"
+    # backward = inverse rotation
+    x = orig.clone().requires_grad_()
+    y = ops.qk_rope_(x * 1.0, cos, sin, pos, hq, hk, d, interleaved)
+    y.backward(out.detach())
+    _close(x.grad[:, :hq * d], orig[:, :hq * d], what="rope inverse")
+
+
+def test_embedding_fwd_bwd_deterministic():
+    V, N, T = 1000, 896, 4096
+    table = _rand(V, N).requires_grad_()
+    ids = torch.randint(0, V, (T,), device=DEV)
+    ids[:100] = 7                     # a long run of one id
+    y = ops.embedding(ids, table)
+    assert torch.equal(y, table.detach()[ids])
+    g = _rand(T, N, seed=1)
+    y.backward(g)
+    want = torch.zeros(V, N, device=DEV).index_add_(0, ids, g.float())
+    _close(table.grad, want, rtol=1e-2, atol=0.1, what="embedding bwd")
+    g1 = table.grad.clone()
+    table.grad = None
+    ops.embedding(ids, table).backward(g)
+    assert torch.equal(g1, table.grad), "scatter-add must be run-to-run deterministic"
+
+
+@pytest.mark.parametrize("T,H,V", [(256, 256, 4096), (300, 896, 5000), (128, 64, 520)])
+@pytest.mark.parametrize("smoothing,z", [(0.0, 0.0), (0.1, 1e-4)])
+def test_linear_cross_entropy_fwd_bwd(T, H, V, smoothing, z):
+    h = _rand(T, H).requires_grad_()
+    w = _rand(V, H, scale=0.05, seed=1).requires_grad_()
+    y = torch.randint(0, V, (T,), device=DEV)
+    y[::7] = -100
+    loss = ops.linear_cross_entropy(h, w, y, None, -100, smoothing, z)
+    loss.backward()
+    hr, wr = h.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    lr_ = ref.linear_cross_entropy_dense(hr, wr, y, None, -100, smoothing, z)
+    lr_.backward()
+    assert abs(loss.item() - lr_.item()) < 2e-3 * max(1.0, abs(lr_.item())), (loss.item(), lr_.item())
+    _close(h.grad, hr.grad, rtol=3e-2, atol=1e-5, what="cce dh")
+    _close(w.grad, wr.grad, rtol=3e-2, atol=1e-5, what="cce dw")
+    _ext.check_status()
+
+
+def test_cross_entropy_logits_kernel():
+    lg = _rand(200, 3000, dtype=torch.float32).requires_grad_()
+    y = torch.randint(0, 3000, (200,), device=DEV)
+    y[::5] = -100
+    loss = ops.cross_entropy_logits(lg, y, -100, 0.1, 1e-4)
+    loss.backward()
+    lr_ = lg.detach().clone().requires_grad_()
+    want = ref.cross_entropy_logits(lr_, y, -100, 0.1, 1e-4)
+    want.backward()
+    assert abs(loss.item() - want.item()) < 1e-4
+    _close(lg.grad, lr_.grad, rtol=1e-3, atol=1e-7, what="ce grad")
+
+
+def test_attention_varlen_matches_reference():
+    T, hq, hk, d = 700, 14, 2, 64
+    q, k, v = _rand(T, hq, d), _rand(T, hk, d, seed=1), _rand(T, hk, d, seed=2)
+    cu = torch.tensor([0, 130, 131, 400, 640], dtype=torch.int32, device=DEV)
+    o = ops.attention_varlen(q, k, v, cu, 269)
+    want = ref.attention_varlen(q.float(), k.float(), v.float(), cu, 269)
+    _close(o[:640], want[:640], what="attention fwd")
+    assert o[640:].abs().max().item() == 0, "padding rows must be zero"
+
+
+def test_fused_adamw_matches_torch():
+    from chronicals_b200.optimizers.fused_adamw import FusedAdamW
+    torch.manual_seed(0)
+    shapes = [(1000, 33), (77,), (8192, 8), (5,)]
+    ps = [torch.nn.Parameter(torch.randn(*s, device=DEV).to(torch.bfloat16)) for s in shapes]
+    qs = [torch.nn.Parameter(p.detach().float().clone()) for p in ps]
+    o1 = FusedAdamW(ps, lr=1e-2, betas=(0.9, 0.95), weight_decay=0.01, max_grad_norm=1.0)
+    o2 = torch.optim.AdamW(qs, lr=1e-2, betas=(0.9, 0.95), weight_decay=0.01)
+    for step in range(4):
+        for p, q in zip(ps, qs):
+            g = torch.randn_like(q)
+            p.grad = g.to(torch.bfloat16)
+            q.grad = p.grad.float()
+        torch.nn.utils.clip_grad_norm_(qs, 1.0)
+        o1.step()
+        o2.step()
+        for p, q in zip(ps, qs):                     # keep the fp32 twin on the bf16 trajectory
+            q.data.copy_(q.data.to(torch.bfloat16).float())
+    for p, q in zip(ps, qs):
+        _close(p, q, rtol=1e-2, atol=1e-2, what="adamw params")
+    m1 = o1.state[ps[0]]["exp_avg"]
+    m2 = o2.state[qs[0]]["exp_avg"]
+    _close(m1, m2, rtol=1e-3, atol=1e-5, what="adamw exp_avg")
+
+
+def test_tiny_model_step_runs_and_graph_matches_eager():
+    from chronicals_b200 import ChronicalsConfig, ChronicalsTrainer, TrainingConfig, build_model
+    cfg = ChronicalsConfig.from_model_name("tiny-qwen2")
+    losses = {}
+    for graphs in (False, True):
+        model = build_model(cfg, dtype=torch.bfloat16, device=DEV, seed=0)
+        args = TrainingConfig(output_dir="/tmp/cb_gpu_test", gradient_accumulation_steps=1, learning_rate=1e-3,
+                              lr_scheduler_type="constant", warmup_ratio=0.0, logging_steps=1000, save_steps=0,
+                              use_gradient_checkpointing=False, fp8=False, visual_reporting=False,
+                              use_cuda_graphs=graphs, use_sequence_packing=False, z_loss_weight=1e-4)
+        args.log_jsonl = False
+        tr = ChronicalsTrainer(model, args, None)
+        g = torch.Generator().manual_seed(0)
+        out = []
+        for i in range(6):
+            ids = torch.randint(0, cfg.vocab_size, (2, 256), generator=g)
+            out.append(tr.training_step({"input_ids": ids, "labels": ids}).item())
+        losses[graphs] = out
+        _ext.check_status()
+    assert all(math.isfinite(x) for x in losses[False])
+    assert losses[False][-1] < losses[False][0] + 0.5
+    for a, b in zip(losses[False], losses[True]):
+        assert abs(a - b) < 5e-2, (losses[False], losses[True])
