@@ -1,0 +1,633 @@
+// Varlen causal GQA flash attention, forward and backward, on tcgen05 tensor
+// cores with the score tiles in TMEM.
+//
+// Layout: q [T, hq, D], k/v [T, hk, D] packed tokens (any row pitch, so they may
+// be slices of one fused QKV buffer); documents are the intervals of
+// cu_seqlens.  One CTA owns one 128-row block of one document and one query
+// head.  Every thread owns one row of the 128 x 128 score tile: it reads its row
+// from TMEM with tcgen05.ld, so the online softmax needs no cross-thread
+// shuffles, and writes P (bf16) into shared memory in the 128-byte-swizzled
+// layout the next MMA consumes.
+//
+//   forward : S = Q K^T -> P = softmax -> O += P V        (2 MMAs per kv block)
+//   backward: S, dP = dO V^T -> P, dS -> dV += P^T dO, dK += dS^T Q, dQ = dS K
+//
+// The same swizzled image of a [128 x 64] bf16 tile serves as a K-major operand
+// (rows = M/N) and as an MN-major operand (rows = K), so P^T and dS^T need no
+// transposed copy.  All tensor maps cover this GPU's own memory only.
+//
+// Replaces the reference's calls into flash-attn / SDPA (chronicals/kernels/
+// flash_attention_optimizer.py:845-994) and its forward-only Triton kernels
+// (:2460-3209); the reference has no attention backward of its own.
+#include "common.cuh"
+
+namespace cb {
+
+constexpr int ATT_THREADS = 128;
+constexpr float LOG2E = 1.4426950408889634f;
+
+struct AttnArgs {
+  int T, hq, hk, n_docs;
+  const int* cu;        // [n_docs + 1]
+  float scale;
+  bf16* O;              // [T, hq, D], row pitch ldo
+  long long ldo;
+  float* lse;           // [hq, T]
+  // backward
+  const float* delta;   // [hq, T]  rowsum(dO * O)
+  float* dq_acc;        // [T, hq, D] fp32, zero-initialised; accumulated with red.add
+  float* dk_part;       // [T, hq, D] fp32 per-query-head partials
+  float* dv_part;
+  int* status;
+};
+
+// which (document, block) a CTA owns; blocks of one document are handed out heaviest first
+__device__ __forceinline__ bool locate_block(const int* cu, int n_docs, int b, int& start, int& len, int& blk, int& nblk) {
+  for (int i = 0; i < n_docs; ++i) {
+    const int s = cu[i], e = cu[i + 1];
+    const int nb = (e - s + 127) >> 7;
+    if (b < nb) {
+      start = s; len = e - s; nblk = nb; blk = b;
+      return true;
+    }
+    b -= nb;
+  }
+  return false;
+}
+
+// store 32 consecutive values of thread-row r as bf16 into a [128 x 128] operand image made of two
+// 64-column panels of 16 KB, 128-byte rows, 16-byte chunks XOR-swizzled by (row & 7)
+__device__ __forceinline__ void store_row_chunk32(uint8_t* base, int r, int c32, const float (&v)[32]) {
+  const int panel = c32 >> 1;                 // chunks 0,1 -> panel 0 ; 2,3 -> panel 1
+  uint8_t* row = base + panel * 16384 + r * 128;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const int cc = (c32 & 1) * 4 + q;         // 16-byte chunk index within the 128-byte row
+    uint4 u;
+    u.x = pack_bf16x2(v[8 * q + 0], v[8 * q + 1]);
+    u.y = pack_bf16x2(v[8 * q + 2], v[8 * q + 3]);
+    u.z = pack_bf16x2(v[8 * q + 4], v[8 * q + 5]);
+    u.w = pack_bf16x2(v[8 * q + 6], v[8 * q + 7]);
+    *reinterpret_cast<uint4*>(row + ((cc ^ (r & 7)) << 4)) = u;
+  }
+}
+
+// descriptors over a [128 rows x D] bf16 tile stored as D/64 panels of 16 KB
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t base, int kk) {      // K = columns, k-step of 16 columns
+  return umma_smem_desc(base + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024);
+}
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t base, int kk) {     // K = rows, k-step of 16 rows
+  return umma_smem_desc(base + kk * 2048, 16384, 1024);
+}
+
+template <int D>
+struct FwdSmem {
+  static constexpr int TILE = 128 * D * 2;            // one [128 x D] operand
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_K = TILE;                  // 2 stages
+  static constexpr int OFF_V = 3 * TILE;              // 2 stages
+  static constexpr int OFF_P = 5 * TILE;              // [128 x 128]
+  static constexpr int OFF_BAR = OFF_P + 32768;
+  static constexpr int TOTAL = OFF_BAR + 128 + 1024;
+};
+
+template <int D>
+__global__ void __launch_bounds__(ATT_THREADS)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, const AttnArgs a) {
+  using L = FwdSmem<D>;
+  constexpr int PANELS = D / 64;
+  constexpr uint32_t TMEM_COLS = 256;                 // S: [0,128)  PV: [128, 128 + D)
+  constexpr uint32_t IDESC_S = umma_idesc_bf16(128, 128, 0, 0);
+  constexpr uint32_t IDESC_PV = umma_idesc_bf16(128, D, 0, 1);
+
+  int start, len, qb, nblk;
+  if (!locate_block(a.cu, a.n_docs, blockIdx.x, start, len, qb, nblk)) return;
+  qb = nblk - 1 - qb;                                  // heaviest (most kv blocks) first
+  const int h = blockIdx.y;
+  const int hkv = h / (a.hq / a.hk);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem + L::OFF_Q;
+  uint8_t* sK = smem + L::OFF_K;
+  uint8_t* sV = smem + L::OFF_V;
+  uint8_t* sP = smem + L::OFF_P;
+  uint64_t* kv_full = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);   // [2]
+  uint64_t* bar_q = kv_full + 2;
+  uint64_t* bar_s = kv_full + 3;
+  uint64_t* bar_o = kv_full + 4;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(kv_full + 5);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  if (tid == 0) {
+    mbar_init(kv_full, 1); mbar_init(kv_full + 1, 1);
+    mbar_init(bar_q, 1); mbar_init(bar_s, 1); mbar_init(bar_o, 1);
+    mbar_fence_init();
+    *abort_flag = a.status[0] != 0 ? 1 : 0;
+  }
+  __syncthreads();
+  if (*abort_flag) return;
+  if (warp == 0) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t t_row = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+
+  const int n_kv = qb + 1;
+  const int q_row0 = start + qb * 128;
+  auto load_kv = [&](int j) {
+    const int st = j & 1;
+    mbar_expect_tx(kv_full + st, 2 * L::TILE);
+#pragma unroll
+    for (int p = 0; p < PANELS; ++p) {
+      tma_load_2d(sK + st * L::TILE + p * 16384, &tmK, kv_full + st, hkv * D + p * 64, start + j * 128);
+      tma_load_2d(sV + st * L::TILE + p * 16384, &tmV, kv_full + st, hkv * D + p * 64, start + j * 128);
+    }
+  };
+  auto issue_s = [&](int j) {
+    const uint32_t qa = smem_u32(sQ), kb = smem_u32(sK + (j & 1) * L::TILE);
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk)
+      umma_f16_ss(tmem, desc_kmajor(qa, kk), desc_kmajor(kb, kk), IDESC_S, kk != 0);
+    umma_commit(bar_s);
+  };
+
+  bool ok = true;
+  if (tid == 0) {
+    mbar_expect_tx(bar_q, L::TILE);
+#pragma unroll
+    for (int p = 0; p < PANELS; ++p) tma_load_2d(sQ + p * 16384, &tmQ, bar_q, h * D + p * 64, q_row0);
+    load_kv(0);
+    if (n_kv > 1) load_kv(1);
+    ok &= mbar_wait(bar_q, 0, abort_flag, a.status, CB_ERR_WAIT_FULL);
+    ok &= mbar_wait(kv_full, 0, abort_flag, a.status, CB_ERR_WAIT_FULL);
+    if (ok) { tc_fence_after(); issue_s(0); }
+  }
+
+  const int r = tid;                                   // my row of the tile
+  const float sl2 = a.scale * LOG2E;
+  float m_run = -INFINITY, l_run = 0.f;
+  float o[D];
+#pragma unroll
+  for (int i = 0; i < D; ++i) o[i] = 0.f;
+
+  for (int j = 0; j < n_kv; ++j) {
+    ok &= mbar_wait(bar_s, j & 1, abort_flag, a.status, CB_ERR_WAIT_TMEM_FULL);
+    tc_fence_after();
+    const bool diag = (j == qb);
+    // pass 1: row maximum of the raw scores
+    float mx = -INFINITY;
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+      uint32_t s[32];
+      tmem_ld_32x32(t_row + c * 32, s);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const float v = __uint_as_float(s[i]);
+        if (!diag || c * 32 + i <= r) mx = fmaxf(mx, v);
+      }
+    }
+    if (j > 0) {
+      // previous P V product: fold into the running output before rescaling it
+      ok &= mbar_wait(bar_o, (j - 1) & 1, abort_flag, a.status, CB_ERR_WAIT_TMEM_FULL);
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t pv[32];
+        tmem_ld_32x32(t_row + 128 + c * 32, pv);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[c * 32 + i] += __uint_as_float(pv[i]);
+      }
+      if (tid == 0 && ok && j + 1 < n_kv) load_kv(j + 1);   // stage (j+1)&1 was released by P V of block j-1
+    }
+    const float m_new = fmaxf(m_run, mx);
+    const float alpha = exp2f((m_run - m_new) * sl2);
+    const float mb = m_new * sl2;
+    float rs = 0.f;
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+      uint32_t s[32];
+      float p[32];
+      tmem_ld_32x32(t_row + c * 32, s);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const float e = exp2f(fmaf(__uint_as_float(s[i]), sl2, -mb));
+        p[i] = (!diag || c * 32 + i <= r) ? e : 0.f;
+        rs += p[i];
+      }
+      store_row_chunk32(sP, r, c, p);
+    }
+    l_run = l_run * alpha + rs;
+    m_run = m_new;
+#pragma unroll
+    for (int i = 0; i < D; ++i) o[i] *= alpha;
+    tc_fence_before();
+    fence_async_smem();
+    if (__syncthreads_or(!ok)) { ok = false; break; }
+    if (tid == 0) {
+      tc_fence_after();
+      const uint32_t pa = smem_u32(sP), vb = smem_u32(sV + (j & 1) * L::TILE);
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk)
+        umma_f16_ss(tmem + 128, desc_kmajor(pa, kk), desc_mnmajor(vb, kk), IDESC_PV, kk != 0);
+      umma_commit(bar_o);
+      if (j + 1 < n_kv) {
+        ok &= mbar_wait(kv_full + ((j + 1) & 1), ((j + 1) >> 1) & 1, abort_flag, a.status, CB_ERR_WAIT_FULL);
+        if (ok) { tc_fence_after(); issue_s(j + 1); }
+      }
+    }
+  }
+  if (ok) {
+    ok &= mbar_wait(bar_o, (n_kv - 1) & 1, abort_flag, a.status, CB_ERR_WAIT_TMEM_FULL);
+    tc_fence_after();
+#pragma unroll
+    for (int c = 0; c < D / 32; ++c) {
+      uint32_t pv[32];
+      tmem_ld_32x32(t_row + 128 + c * 32, pv);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) o[c * 32 + i] += __uint_as_float(pv[i]);
+    }
+    const int rg = qb * 128 + r;
+    if (ok && rg < len) {
+      const float inv = 1.f / l_run;
+      const long long t = start + rg;
+      uint4* op = reinterpret_cast<uint4*>(a.O + t * a.ldo + static_cast<long long>(h) * D);
+#pragma unroll
+      for (int c = 0; c < D / 8; ++c) {
+        uint4 u;
+        u.x = pack_bf16x2(o[8 * c + 0] * inv, o[8 * c + 1] * inv);
+        u.y = pack_bf16x2(o[8 * c + 2] * inv, o[8 * c + 3] * inv);
+        u.z = pack_bf16x2(o[8 * c + 4] * inv, o[8 * c + 5] * inv);
+        u.w = pack_bf16x2(o[8 * c + 6] * inv, o[8 * c + 7] * inv);
+        op[c] = u;
+      }
+      a.lse[static_cast<long long>(h) * a.T + t] = m_run * a.scale + __logf(l_run);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem, TMEM_COLS); }
+}
+
+// delta[h, t] = sum_d dO[t, h, d] * O[t, h, d]; one warp per (t, h)
+__global__ void attn_delta_kernel(const bf16* __restrict__ dO, const bf16* __restrict__ O, long long ld_do,
+                                  long long ld_o, int T, int hq, int D, float* __restrict__ delta) {
+  const long long w = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (w >= static_cast<long long>(T) * hq) return;
+  const long long t = w / hq;
+  const int h = static_cast<int>(w % hq);
+  const bf16* a = dO + t * ld_do + static_cast<long long>(h) * D;
+  const bf16* b = O + t * ld_o + static_cast<long long>(h) * D;
+  float s = 0.f;
+  for (int i = lane * 2; i < D; i += 64) {
+    const float2 x = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(a + i));
+    const float2 y = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(b + i));
+    s += x.x * y.x + x.y * y.y;
+  }
+  s = warp_sum(s);
+  if (lane == 0) delta[static_cast<long long>(h) * T + t] = s;
+}
+
+}  // namespace cb
+
+// =========================================================================================== backward
+namespace cb {
+
+template <int D>
+struct BwdSmem {
+  static constexpr int TILE = 128 * D * 2;
+  static constexpr int STAGES = (D == 64) ? 2 : 1;   // Q / dO ring depth (shared-memory budget)
+  static constexpr int OFF_K = 0;
+  static constexpr int OFF_V = TILE;
+  static constexpr int OFF_Q = 2 * TILE;
+  static constexpr int OFF_DO = OFF_Q + STAGES * TILE;
+  static constexpr int OFF_P = OFF_DO + STAGES * TILE;
+  static constexpr int OFF_DS = OFF_P + 32768;
+  static constexpr int OFF_BAR = OFF_DS + 32768;
+  static constexpr int TOTAL = OFF_BAR + 128 + 1024;
+};
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+// One CTA: kv block `jb` of one document, one query head; loops over the query blocks i >= jb.
+template <int D>
+__global__ void __launch_bounds__(ATT_THREADS)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO, const AttnArgs a) {
+  using L = BwdSmem<D>;
+  constexpr int PANELS = D / 64;
+  constexpr int STAGES = L::STAGES;
+  constexpr uint32_t TMEM_COLS = 512;
+  constexpr uint32_t C_S = 0, C_DP = 128, C_DV = 256, C_DK = 256 + D;    // dQ reuses the S columns
+  constexpr uint32_t IDESC_S = umma_idesc_bf16(128, 128, 0, 0);
+  constexpr uint32_t IDESC_T = umma_idesc_bf16(128, D, 1, 1);            // P^T dO, dS^T Q
+  constexpr uint32_t IDESC_DQ = umma_idesc_bf16(128, D, 0, 1);           // dS K
+
+  int start, len, jb, nblk;
+  if (!locate_block(a.cu, a.n_docs, blockIdx.x, start, len, jb, nblk)) return;   // jb = 0 is the heaviest
+  const int h = blockIdx.y;
+  const int hkv = h / (a.hq / a.hk);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem + L::OFF_K;
+  uint8_t* sV = smem + L::OFF_V;
+  uint8_t* sQ = smem + L::OFF_Q;
+  uint8_t* sdO = smem + L::OFF_DO;
+  uint8_t* sP = smem + L::OFF_P;
+  uint8_t* sdS = smem + L::OFF_DS;
+  uint64_t* q_full = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);   // [2]
+  uint64_t* bar_kv = q_full + 2;
+  uint64_t* bar_s = q_full + 3;
+  uint64_t* bar_dp = q_full + 4;
+  uint64_t* bar_dq = q_full + 5;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_full + 6);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  if (tid == 0) {
+    mbar_init(q_full, 1); mbar_init(q_full + 1, 1);
+    mbar_init(bar_kv, 1); mbar_init(bar_s, 1); mbar_init(bar_dp, 1); mbar_init(bar_dq, 1);
+    mbar_fence_init();
+    *abort_flag = a.status[0] != 0 ? 1 : 0;
+  }
+  __syncthreads();
+  if (*abort_flag) return;
+  if (warp == 0) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t t_row = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+
+  const int kv_row0 = start + jb * 128;
+  const int n_it = nblk - jb;
+  auto load_q = [&](int it) {
+    const int st = it % STAGES;
+    const int row0 = start + (jb + it) * 128;
+    mbar_expect_tx(q_full + st, 2 * L::TILE);
+#pragma unroll
+    for (int p = 0; p < PANELS; ++p) {
+      tma_load_2d(sQ + st * L::TILE + p * 16384, &tmQ, q_full + st, h * D + p * 64, row0);
+      tma_load_2d(sdO + st * L::TILE + p * 16384, &tmdO, q_full + st, h * D + p * 64, row0);
+    }
+  };
+
+  bool ok = true;
+  if (tid == 0) {
+    mbar_expect_tx(bar_kv, 2 * L::TILE);
+#pragma unroll
+    for (int p = 0; p < PANELS; ++p) {
+      tma_load_2d(sK + p * 16384, &tmK, bar_kv, hkv * D + p * 64, kv_row0);
+      tma_load_2d(sV + p * 16384, &tmV, bar_kv, hkv * D + p * 64, kv_row0);
+    }
+    load_q(0);
+    if (STAGES > 1 && n_it > 1) load_q(1);
+    ok &= mbar_wait(bar_kv, 0, abort_flag, a.status, CB_ERR_WAIT_FULL);
+  }
+
+  const int r = tid;
+  const float sl2 = a.scale * LOG2E;
+  const uint32_t kA = smem_u32(sK), vA = smem_u32(sV), pA = smem_u32(sP), dsA = smem_u32(sdS);
+
+  for (int it = 0; it < n_it; ++it) {
+    const int st = it % STAGES;
+    const int i = jb + it;
+    const uint32_t qA = smem_u32(sQ + st * L::TILE), doA = smem_u32(sdO + st * L::TILE);
+    if (tid == 0) {
+      ok &= mbar_wait(q_full + st, (it / STAGES) & 1, abort_flag, a.status, CB_ERR_WAIT_FULL);
+      if (ok) {
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          umma_f16_ss(tmem + C_S, desc_kmajor(qA, kk), desc_kmajor(kA, kk), IDESC_S, kk != 0);
+        umma_commit(bar_s);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          umma_f16_ss(tmem + C_DP, desc_kmajor(doA, kk), desc_kmajor(vA, kk), IDESC_S, kk != 0);
+        umma_commit(bar_dp);
+      }
+    }
+    const int rg = i * 128 + r;                      // my query row within the document
+    const bool row_ok = rg < len;
+    const long long tq = start + rg;
+    const float lse2 = row_ok ? a.lse[static_cast<long long>(h) * a.T + tq] * LOG2E : 0.f;
+    const float dlt = row_ok ? a.delta[static_cast<long long>(h) * a.T + tq] : 0.f;
+    const bool diag = (it == 0);
+    ok &= mbar_wait(bar_s, it & 1, abort_flag, a.status, CB_ERR_WAIT_TMEM_FULL);
+    ok &= mbar_wait(bar_dp, it & 1, abort_flag, a.status, CB_ERR_WAIT_TMEM_FULL);
+    tc_fence_after();
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+      uint32_t s[32], dp[32];
+      float p[32], ds[32];
+      tmem_ld_32x32(t_row + C_S + c * 32, s);
+      tmem_ld_32x32(t_row + C_DP + c * 32, dp);
+      tmem_ld_wait();
+#pragma unroll
+      for (int k = 0; k < 32; ++k) {
+        const bool keep = row_ok && (!diag || c * 32 + k <= r);
+        const float e = exp2f(fmaf(__uint_as_float(s[k]), sl2, -lse2));
+        p[k] = keep ? e : 0.f;
+        ds[k] = p[k] * (__uint_as_float(dp[k]) - dlt) * a.scale;
+      }
+      store_row_chunk32(sP, r, c, p);
+      store_row_chunk32(sdS, r, c, ds);
+    }
+    tc_fence_before();
+    fence_async_smem();
+    if (__syncthreads_or(!ok)) { ok = false; break; }
+    if (tid == 0) {
+      tc_fence_after();
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk)                  // dV += P^T dO     (K = the 128 query rows)
+        umma_f16_ss(tmem + C_DV, desc_mnmajor(pA, kk), desc_mnmajor(doA, kk), IDESC_T, (it | kk) != 0);
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk)                  // dK += dS^T Q
+        umma_f16_ss(tmem + C_DK, desc_mnmajor(dsA, kk), desc_mnmajor(qA, kk), IDESC_T, (it | kk) != 0);
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk)                  // dQ = dS K        (K = the 128 kv rows)
+        umma_f16_ss(tmem + C_S, desc_kmajor(dsA, kk), desc_mnmajor(kA, kk), IDESC_DQ, kk != 0);
+      umma_commit(bar_dq);
+    }
+    ok &= mbar_wait(bar_dq, it & 1, abort_flag, a.status, CB_ERR_WAIT_TMEM_FULL);
+    tc_fence_after();
+    if (tid == 0 && ok && it + STAGES < n_it) load_q(it + STAGES);      // this stage's Q / dO are consumed
+#pragma unroll
+    for (int c = 0; c < D / 32; ++c) {
+      uint32_t dq[32];
+      tmem_ld_32x32(t_row + C_S + c * 32, dq);
+      tmem_ld_wait();
+      if (row_ok && ok) {
+        float* dst = a.dq_acc + (tq * a.hq + h) * D + c * 32;
+#pragma unroll
+        for (int k = 0; k < 32; k += 4)
+          red_add_v4(dst + k, __uint_as_float(dq[k]), __uint_as_float(dq[k + 1]), __uint_as_float(dq[k + 2]),
+                     __uint_as_float(dq[k + 3]));
+      }
+    }
+    tc_fence_before();
+    if (__syncthreads_or(!ok)) { ok = false; break; }
+  }
+  if (ok) {
+    tc_fence_after();
+    const int kg = jb * 128 + r;                      // my kv row within the document
+    const bool kv_ok = kg < len;
+    const long long tk = start + kg;
+#pragma unroll
+    for (int c = 0; c < D / 32; ++c) {
+      uint32_t dv[32], dk[32];
+      tmem_ld_32x32(t_row + C_DV + c * 32, dv);
+      tmem_ld_32x32(t_row + C_DK + c * 32, dk);
+      tmem_ld_wait();
+      if (kv_ok) {
+        float4* pv = reinterpret_cast<float4*>(a.dv_part + (tk * a.hq + h) * D + c * 32);
+        float4* pk = reinterpret_cast<float4*>(a.dk_part + (tk * a.hq + h) * D + c * 32);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          pv[k] = make_float4(__uint_as_float(dv[4 * k]), __uint_as_float(dv[4 * k + 1]),
+                              __uint_as_float(dv[4 * k + 2]), __uint_as_float(dv[4 * k + 3]));
+          pk[k] = make_float4(__uint_as_float(dk[4 * k]), __uint_as_float(dk[4 * k + 1]),
+                              __uint_as_float(dk[4 * k + 2]), __uint_as_float(dk[4 * k + 3]));
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem, TMEM_COLS); }
+}
+
+// dqkv[t] = bf16( dQ | sum over the query heads of a group of dK | same for dV ), one block per token
+__global__ void attn_bwd_finalize_kernel(const float* __restrict__ dq_acc, const float* __restrict__ dk_part,
+                                         const float* __restrict__ dv_part, bf16* __restrict__ dqkv, long long ld,
+                                         int T, int hq, int hk, int D, const int* __restrict__ cu, int n_docs) {
+  const long long t = blockIdx.x;
+  const int nq = hq * D, nk = hk * D, g = hq / hk;
+  bf16* out = dqkv + t * ld;
+  const bool valid = t < cu[n_docs];                  // padding tokens get zero gradients
+  for (int c = threadIdx.x; c < nq + 2 * nk; c += blockDim.x) {
+    float v = 0.f;
+    if (valid) {
+      if (c < nq) {
+        v = dq_acc[t * nq + c];
+      } else {
+        const int cc = (c - nq) % nk, which = (c - nq) / nk;
+        const int kvh = cc / D, d = cc % D;
+        const float* src = (which == 0 ? dk_part : dv_part) + (t * hq + static_cast<long long>(kvh) * g) * D + d;
+        for (int i = 0; i < g; ++i) v += src[static_cast<long long>(i) * D];
+      }
+    }
+    out[c] = __float2bfloat16(v);
+  }
+}
+
+}  // namespace cb
+
+// =========================================================================================== host side
+#include "host_common.h"
+
+namespace {
+
+int attn_maps(CUtensorMap* mq, CUtensorMap* mk, CUtensorMap* mv, const void* q, const void* k, const void* v, int T,
+              int hq, int hk, int D, long long ldq, long long ldk, long long ldv) {
+  int e = cbhost::make_tmap(mq, q, static_cast<unsigned long long>(hq) * D, T, ldq, 64, 128);
+  if (e) return e;
+  e = cbhost::make_tmap(mk, k, static_cast<unsigned long long>(hk) * D, T, ldk, 64, 128);
+  if (e) return e;
+  return cbhost::make_tmap(mv, v, static_cast<unsigned long long>(hk) * D, T, ldv, 64, 128);
+}
+
+template <typename K>
+int set_smem(K kern, int bytes) {
+  return static_cast<int>(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+}
+
+}  // namespace
+
+extern "C" {
+
+// q [T, hq, D] (row pitch ldq elements), k / v [T, hk, D]; cu: int32 [n_docs + 1] on the device.
+// o [T, hq, D] with pitch ldo; lse [hq, T] fp32.  Rows at or beyond cu[n_docs] are left untouched
+// (the caller zero-fills o).  D is 64 or 128, hq a multiple of hk.
+int cb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int* cu, int n_docs, int T,
+                int hq, int hk, int D, long long ldq, long long ldk, long long ldv, long long ldo, float scale,
+                int* status, void* stream) {
+  if ((D != 64 && D != 128) || hq % hk != 0 || T <= 0 || n_docs <= 0) return -1;
+  CUtensorMap mq, mk, mv;
+  int e = attn_maps(&mq, &mk, &mv, q, k, v, T, hq, hk, D, ldq, ldk, ldv);
+  if (e) return e;
+  cb::AttnArgs a = {};
+  a.T = T; a.hq = hq; a.hk = hk; a.n_docs = n_docs; a.cu = cu; a.scale = scale;
+  a.O = static_cast<cb::bf16*>(o); a.ldo = ldo; a.lse = lse; a.status = status;
+  dim3 grid((T + 127) / 128 + n_docs, hq);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (D == 64) {
+    static bool cfg = false;
+    if (!cfg) { e = set_smem(cb::attn_fwd_kernel<64>, cb::FwdSmem<64>::TOTAL); if (e) return e; cfg = true; }
+    cb::attn_fwd_kernel<64><<<grid, cb::ATT_THREADS, cb::FwdSmem<64>::TOTAL, s>>>(mq, mk, mv, a);
+  } else {
+    static bool cfg = false;
+    if (!cfg) { e = set_smem(cb::attn_fwd_kernel<128>, cb::FwdSmem<128>::TOTAL); if (e) return e; cfg = true; }
+    cb::attn_fwd_kernel<128><<<grid, cb::ATT_THREADS, cb::FwdSmem<128>::TOTAL, s>>>(mq, mk, mv, a);
+  }
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Backward.  scratch: delta [hq*T] fp32, dq_acc / dk_part / dv_part [T*hq*D] fp32 each (dq_acc is
+// zeroed here).  dqkv: bf16 [T, (hq + 2 hk) * D] with row pitch ld_dqkv receives dQ | dK | dV.
+int cb_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse,
+                const int* cu, int n_docs, int T, int hq, int hk, int D, long long ldq, long long ldk, long long ldv,
+                long long ldo, long long ld_do, float scale, float* delta, float* dq_acc, float* dk_part,
+                float* dv_part, void* dqkv, long long ld_dqkv, int* status, void* stream) {
+  if ((D != 64 && D != 128) || hq % hk != 0 || T <= 0 || n_docs <= 0) return -1;
+  CUtensorMap mq, mk, mv, mdo;
+  int e = attn_maps(&mq, &mk, &mv, q, k, v, T, hq, hk, D, ldq, ldk, ldv);
+  if (e) return e;
+  e = cbhost::make_tmap(&mdo, d_o, static_cast<unsigned long long>(hq) * D, T, ld_do, 64, 128);
+  if (e) return e;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const long long warps = static_cast<long long>(T) * hq;
+  cb::attn_delta_kernel<<<static_cast<unsigned>((warps * 32 + 255) / 256), 256, 0, s>>>(
+      static_cast<const cb::bf16*>(d_o), static_cast<const cb::bf16*>(o), ld_do, ldo, T, hq, D, delta);
+  CB_CHECK_CUDA(cudaMemsetAsync(dq_acc, 0, sizeof(float) * static_cast<size_t>(T) * hq * D, s));
+  cb::AttnArgs a = {};
+  a.T = T; a.hq = hq; a.hk = hk; a.n_docs = n_docs; a.cu = cu; a.scale = scale;
+  a.lse = const_cast<float*>(lse); a.delta = delta; a.dq_acc = dq_acc; a.dk_part = dk_part; a.dv_part = dv_part;
+  a.status = status;
+  dim3 grid((T + 127) / 128 + n_docs, hq);
+  if (D == 64) {
+    static bool cfg = false;
+    if (!cfg) { e = set_smem(cb::attn_bwd_kernel<64>, cb::BwdSmem<64>::TOTAL); if (e) return e; cfg = true; }
+    cb::attn_bwd_kernel<64><<<grid, cb::ATT_THREADS, cb::BwdSmem<64>::TOTAL, s>>>(mq, mk, mv, mdo, a);
+  } else {
+    static bool cfg = false;
+    if (!cfg) { e = set_smem(cb::attn_bwd_kernel<128>, cb::BwdSmem<128>::TOTAL); if (e) return e; cfg = true; }
+    cb::attn_bwd_kernel<128><<<grid, cb::ATT_THREADS, cb::BwdSmem<128>::TOTAL, s>>>(mq, mk, mv, mdo, a);
+  }
+  cb::attn_bwd_finalize_kernel<<<T, 256, 0, s>>>(dq_acc, dk_part, dv_part, static_cast<cb::bf16*>(dqkv), ld_dqkv, T,
+                                                  hq, hk, D, cu, n_docs);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // extern "C"

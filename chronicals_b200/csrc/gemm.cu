@@ -23,9 +23,7 @@
 // training step and the fp32 cuBLAS chunk GEMMs of its cut-cross-entropy
 // (reference: chronicals/kernels/cut_cross_entropy.py:915-981).
 #include "common.cuh"
-
-#include <mutex>
-#include <unordered_map>
+#include "host_common.h"
 
 namespace cb {
 
@@ -465,48 +463,8 @@ __global__ void cce_finalize_kernel(const float* __restrict__ loss_rows, const l
 // =========================================================================================== host side
 namespace {
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn get_encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-  });
-  return fn;
-}
-
-// 2-D bf16 tensor map: `inner` contiguous elements per row, `outer` rows, row pitch `ld` elements.
-int make_tmap(CUtensorMap* out, const void* base, unsigned long long inner, unsigned long long outer,
-              unsigned long long ld, unsigned box_inner, unsigned box_outer) {
-  EncodeTiledFn fn = get_encode_fn();
-  if (fn == nullptr) return -10;
-  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (ld * 2) % 16 != 0) return -11;
-  cuuint64_t dims[2] = {inner, outer};
-  cuuint64_t strides[1] = {ld * 2};
-  cuuint32_t box[2] = {box_inner, box_outer};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : -12;
-}
-
-int num_sms() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-  }
-  return n;
-}
+using cbhost::make_tmap;
+using cbhost::num_sms;
 
 template <int BLOCK_N, int A_MN, int B_MN, int STAGES, int EPI>
 int launch(const CUtensorMap& ta, const CUtensorMap& tb, const cb::GemmArgs& g, cudaStream_t stream) {

@@ -151,12 +151,8 @@ class Attention(nn.Module):
         T = x.shape[0]
         qkv = self.qkv_proj(x)
         qkv = ops.qk_rope_(qkv, cos, sin, position_ids, self.hq, self.hk, self.d, self.interleaved_rope)
-        nq, nk = self.hq * self.d, self.hk * self.d
-        q = qkv[:, :nq].view(T, self.hq, self.d)
-        k = qkv[:, nq:nq + nk].view(T, self.hk, self.d)
-        v = qkv[:, nq + nk:].view(T, self.hk, self.d)
-        o = ops.attention_varlen(q, k, v, cu_seqlens, max_seqlen, True, None, seqlens_host)
-        return self.o_proj(o.reshape(T, nq), residual)
+        o = ops.attention_qkv_packed(qkv, cu_seqlens, self.hq, self.hk, self.d, max_seqlen, seqlens_host)
+        return self.o_proj(o, residual)
 
 
 class MLP(nn.Module):

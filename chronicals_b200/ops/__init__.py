@@ -19,7 +19,7 @@ from . import _ext
 
 __all__ = [
     "linear", "gemm", "rmsnorm", "add_rmsnorm", "swiglu", "geglu", "qk_rope_", "embedding",
-    "attention_varlen", "linear_cross_entropy", "cross_entropy_logits", "kernels_active",
+    "attention_varlen", "attention_qkv_packed", "linear_cross_entropy", "cross_entropy_logits", "kernels_active",
 ]
 
 
@@ -85,15 +85,14 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
 
 class _LinearFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w, bias, residual):
-        x2 = x.reshape(-1, x.shape[-1])
-        res2 = residual.reshape(-1, w.shape[0]) if residual is not None else None
+    def forward(ctx, x2, w, bias, res2):
+        # 2-D in, 2-D out: the output is a fresh tensor (never a view), so later in-place ops
+        # on it (the rotary embedding) are legal for autograd
         y = gemm(x2, w, bias=bias, addend=res2)
         ctx.save_for_backward(x2, w)
         ctx.has_bias = bias is not None
-        ctx.has_res = residual is not None
-        ctx.x_shape = x.shape
-        return y.view(*x.shape[:-1], w.shape[0])
+        ctx.has_res = res2 is not None
+        return y
 
     @staticmethod
     def backward(ctx, dy):
@@ -103,12 +102,12 @@ class _LinearFn(torch.autograd.Function):
             dy2 = dy2.contiguous()
         dx = dw = db = None
         if ctx.needs_input_grad[0]:
-            dx = gemm(dy2, w, b_mn=True).view(ctx.x_shape)          # dX = dY @ W
+            dx = gemm(dy2, w, b_mn=True)                             # dX = dY @ W
         if ctx.needs_input_grad[1]:
             dw = gemm(dy2, x2, a_mn=True, b_mn=True)                 # dW = dY^T @ X
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = dy2.float().sum(0).to(dy.dtype)
-        dres = dy if ctx.has_res else None
+        dres = dy2 if ctx.has_res else None
         return dx, dw, db, dres
 
 
@@ -116,7 +115,12 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
            residual: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``x @ w.T + bias (+ residual)``; the residual add is fused in the GEMM epilogue."""
     if _fast(x, w, bias, residual):
-        return _LinearFn.apply(x, w, bias, residual)
+        x2 = x.reshape(-1, x.shape[-1])
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        res2 = residual.reshape(-1, w.shape[0]) if residual is not None else None
+        y = _LinearFn.apply(x2, w, bias, res2)
+        return y if x.dim() == 2 else y.view(*x.shape[:-1], w.shape[0])
     y = torch.nn.functional.linear(x, w, bias)
     return y + residual if residual is not None else y
 
@@ -264,8 +268,9 @@ class _QKRopeFn(torch.autograd.Function):
     def backward(ctx, dqkv):
         cos, sin, pos = ctx.saved_tensors
         hq, hk, d, interleaved, has_pos = ctx.cfg
+        # the incoming gradient is a fresh buffer owned by this node (produced by the attention
+        # backward), so the inverse rotation runs in place on it
         g = dqkv if dqkv.is_contiguous() else dqkv.contiguous()
-        g = g.clone() if g.data_ptr() == dqkv.data_ptr() else g
         _rope_launch(g, cos, sin, pos if has_pos else None, hq, hk, d, interleaved, True)
         return g, None, None, None, None, None, None, None
 
@@ -331,6 +336,21 @@ def attention_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqle
     """Causal GQA attention over packed documents (``q [T,Hq,D]``, ``k/v [T,Hk,D]``)."""
     from . import attention as _attn
     return _attn.attention_varlen(q, k, v, cu_seqlens, max_seqlen, causal, softmax_scale, seqlens_host)
+
+
+def attention_qkv_packed(qkv: torch.Tensor, cu_seqlens: torch.Tensor, num_q_heads: int, num_kv_heads: int,
+                         head_dim: int, max_seqlen: Optional[int] = None, seqlens_host=None) -> torch.Tensor:
+    """Causal GQA attention reading Q, K, V straight out of the fused ``[T, (hq + 2 hk) * D]``
+    projection output; returns ``[T, hq * D]``."""
+    from . import attention_cuda as _ac
+    if qkv.dim() == 2 and _ac.kernel_supports(qkv, head_dim):
+        return _ac.attention_qkv_packed(qkv, cu_seqlens, num_q_heads, num_kv_heads, head_dim)
+    T = qkv.shape[0]
+    nq, nk = num_q_heads * head_dim, num_kv_heads * head_dim
+    q = qkv[:, :nq].reshape(T, num_q_heads, head_dim)
+    k = qkv[:, nq:nq + nk].reshape(T, num_kv_heads, head_dim)
+    v = qkv[:, nq + nk:].reshape(T, num_kv_heads, head_dim)
+    return attention_varlen(q, k, v, cu_seqlens, max_seqlen, True, None, seqlens_host).reshape(T, nq)
 
 
 # ============================================================================ fused linear + cross-entropy

@@ -44,6 +44,8 @@ _PROTOTYPES = {
     "cb_embedding_bwd": [P, P, P, P, L, I, L, I, P],
     "cb_ce_logits": [P, P, L, L, I, I, L, F, F, P, P, P],
     "cb_ce_logits_grad": [P, P, P, P, P, P, L, L, I, I, L, F, F, P],
+    "cb_attn_fwd": [P, P, P, P, P, P, I, I, I, I, I, L, L, L, L, F, P, P],
+    "cb_attn_bwd": [P, P, P, P, P, P, P, I, I, I, I, I, L, L, L, L, L, F, P, P, P, P, P, L, P, P],
     "cb_opt_chunk": [],
     "cb_adamw_multi": [P, P, P, P, P, P, P, P, I, I, P, P, I, P],
     "cb_grad_clip_coef": [P, P, P, I, I, P, P, F, P, I, P],
@@ -81,7 +83,7 @@ def lib() -> ctypes.CDLL:
 
 # device kernels launched by one call of each entry point (0: host-only query)
 _KERNELS_PER_CALL = {"cb_cce_num_splits": 0, "cb_rmsnorm_max_n": 0, "cb_rmsnorm_bwd_blocks": 0, "cb_opt_chunk": 0,
-                     "cb_cce_combine": 2, "cb_rmsnorm_bwd": 2, "cb_grad_clip_coef": 2}
+                     "cb_cce_combine": 2, "cb_rmsnorm_bwd": 2, "cb_grad_clip_coef": 2, "cb_attn_bwd": 3}
 LAUNCH_COUNT = [0]
 
 

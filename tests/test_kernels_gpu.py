@@ -196,7 +196,33 @@ def test_cross_entropy_logits_kernel():
     _close(lg.grad, lr_.grad, rtol=1e-3, atol=1e-7, what="ce grad")
 
 
-def test_attention_varlen_matches_reference():
+@pytest.mark.parametrize("hq,hk,d", [(14, 2, 64), (4, 4, 64), (5, 1, 128)])
+@pytest.mark.parametrize("bounds", [[0, 130, 131, 400, 640], [0, 1024], [0, 128, 256, 700]])
+def test_attention_packed_fwd_bwd(hq, hk, d, bounds):
+    T = 768
+    nq, nk = hq * d, hk * d
+    qkv = _rand(T, nq + 2 * nk).requires_grad_()
+    cu = torch.tensor([min(b, T) for b in bounds], dtype=torch.int32, device=DEV)
+    valid = int(cu[-1].item())
+    o = ops.attention_qkv_packed(qkv, cu, hq, hk, d)
+    g = _rand(T, nq, seed=5)
+    o.backward(g)
+    xr = qkv.detach().float().requires_grad_()
+    q = xr[:, :nq].reshape(T, hq, d)
+    k = xr[:, nq:nq + nk].reshape(T, hk, d)
+    v = xr[:, nq + nk:].reshape(T, hk, d)
+    want = ref.attention_varlen(q, k, v, cu, None).reshape(T, nq)
+    want.backward(g.float())
+    _close(o[:valid], want[:valid], what="attention fwd")
+    if valid < T:
+        assert o[valid:].abs().max().item() == 0, "padding rows must be zero"
+    _close(qkv.grad[:, :nq], xr.grad[:, :nq], rtol=3e-2, atol=3e-2, what="attention dq")
+    _close(qkv.grad[:, nq:nq + nk], xr.grad[:, nq:nq + nk], rtol=3e-2, atol=3e-2, what="attention dk")
+    _close(qkv.grad[:, nq + nk:], xr.grad[:, nq + nk:], rtol=3e-2, atol=3e-2, what="attention dv")
+    _ext.check_status()
+
+
+def test_attention_varlen_separate_tensors():
     T, hq, hk, d = 700, 14, 2, 64
     q, k, v = _rand(T, hq, d), _rand(T, hk, d, seed=1), _rand(T, hk, d, seed=2)
     cu = torch.tensor([0, 130, 131, 400, 640], dtype=torch.int32, device=DEV)
