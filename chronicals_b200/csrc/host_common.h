@@ -4,6 +4,8 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdio.h>
+#include <stdlib.h>
 
 #include <mutex>
 
@@ -40,7 +42,22 @@ inline int make_tmap(CUtensorMap* out, const void* base, unsigned long long inne
   const CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
   CUresult r = fn(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : -12;
+  if (r != CUDA_SUCCESS) {
+    // A thread that has not yet touched this library's CUDA runtime (e.g. an autograd worker)
+    // may have no context bound for it: bind the primary context and try once more.
+    const int first = static_cast<int>(r);
+    cudaFree(nullptr);
+    r = fn(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r == CUDA_SUCCESS) {
+      if (getenv("CB_DEBUG_TMAP")) fprintf(stderr, "[chronicals_b200] tensor-map encode succeeded on retry (first CUresult %d)\n", first);
+      return 0;
+    }
+    fprintf(stderr, "[chronicals_b200] cuTensorMapEncodeTiled failed: CUresult %d base %p inner %llu outer %llu ld %llu "
+            "box %u x %u elem %d\n", static_cast<int>(r), base, inner, outer, ld, box_inner, box_outer, elem_bytes);
+    return -12;
+  }
+  return 0;
 }
 
 inline int num_sms() {
