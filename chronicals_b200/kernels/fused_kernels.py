@@ -1,0 +1,278 @@
+"""Fused op front-ends: functions, autograd-backed modules and losses.
+
+Covers the reference's kernel monolith (chronicals/kernels/triton_kernels.py:
+RMSNorm :593-774, SwiGLU / SiLU·Mul :1067-1284, GeGLU :1370-1432, in-place
+QK-RoPE :1785-2005, dispatchers and PyTorch fallbacks :2070-2277, chunked and
+fused linear cross-entropy :2305-2813 and :3147-3419, Liger-style CE :2979-3125,
+RMSNorm→Linear :4199-4303, Embedding(+RoPE) :4426-4560, GQA attention :4701-4791).
+Every function dispatches to the sm_100a kernels for CUDA bf16 tensors and to
+the PyTorch formulas otherwise; ``chronicals_b200.kernels.triton_kernels`` is an
+alias of this module so reference import paths keep working.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .. import ops
+from ..ops import ref
+from .cut_cross_entropy import (DEFAULT_CHUNK_SIZE, ChunkedCrossEntropyLoss, CutCrossEntropyLoss, cut_cross_entropy)
+
+# ------------------------------------------------------------------------------------------- RMSNorm
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    return ops.rmsnorm(x, weight, eps)
+
+
+fused_rmsnorm = rmsnorm
+rmsnorm_triton = rmsnorm
+rmsnorm_with_grad = rmsnorm
+
+
+def rmsnorm_pytorch(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    return ref.rmsnorm(x, weight, eps)
+
+
+class FusedRMSNorm(nn.Module):
+    def __init__(self, hidden_size: int, eps: float = 1e-6, offset: float = 0.0, device=None, dtype=None):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(hidden_size, device=device, dtype=dtype))
+        self.eps, self.offset = eps, offset
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return ops.rmsnorm(x, self.weight, self.eps, self.offset)
+
+
+# ------------------------------------------------------------------------------------------- gated activations
+def fused_swiglu(gate: torch.Tensor, up: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``silu(gate) * up``; with one argument the last dim holds ``gate | up``."""
+    if up is None:
+        return ops.swiglu(gate)
+    return ops.swiglu(torch.cat((gate, up), dim=-1))
+
+
+fused_swiglu_triton = fused_swiglu
+
+
+def swiglu_pytorch(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    return ref.swiglu(gate, up)
+
+
+def fused_geglu(gate: torch.Tensor, up: Optional[torch.Tensor] = None) -> torch.Tensor:
+    if up is None:
+        return ops.geglu(gate)
+    return ops.geglu(torch.cat((gate, up), dim=-1))
+
+
+class FusedSwiGLU(nn.Module):
+    """SwiGLU MLP: one gate|up GEMM, fused activation, down GEMM."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, bias: bool = False, device=None, dtype=None):
+        super().__init__()
+        self.gate_up_proj = nn.Linear(hidden_size, 2 * intermediate_size, bias=bias, device=device, dtype=dtype)
+        self.down_proj = nn.Linear(intermediate_size, hidden_size, bias=bias, device=device, dtype=dtype)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        gu = ops.linear(x, self.gate_up_proj.weight, self.gate_up_proj.bias)
+        return ops.linear(ops.swiglu(gu), self.down_proj.weight, self.down_proj.bias)
+
+
+class FusedSiLUMul(nn.Module):
+    def forward(self, gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+        return fused_swiglu(gate, up)
+
+
+class FusedGeGLU(nn.Module):
+    def forward(self, gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+        return fused_geglu(gate, up)
+
+
+# ------------------------------------------------------------------------------------------- RoPE
+def precompute_rope_cache(seq_len: int, head_dim: int, theta: float = 10000.0, device=None,
+                          scaling: Optional[dict] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``cos, sin`` of shape ``[seq_len, head_dim // 2]`` (fp32)."""
+    return ref.rope_cache(seq_len, head_dim, theta, scaling, device)
+
+
+def _rope_4d(q: torch.Tensor, k: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
+             position_ids: Optional[torch.Tensor], interleaved: bool) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``q [B, S, Hq, D]``, ``k [B, S, Hk, D]`` → rotated copies (packs into one buffer for the kernel)."""
+    B, S, hq, d = q.shape
+    hk = k.shape[2]
+    if cos.dim() == 2 and cos.shape[-1] == d:           # full-width tables: keep the first half
+        cos, sin = cos[..., : d // 2], sin[..., : d // 2]
+    T = B * S
+    pos = position_ids.reshape(T) if position_ids is not None else torch.arange(S, device=q.device).repeat(B)
+    buf = torch.cat((q.reshape(T, hq * d), k.reshape(T, hk * d)), dim=1)
+    if ops._fast(buf) and (hq * d + hk * d) % 8 == 0:
+        # V is absent: pass a zero-width V by describing only q and k heads
+        out = ops.qk_rope_(buf, cos.float().contiguous(), sin.float().contiguous(), pos, hq, hk, d, interleaved)
+    else:
+        qq = ref.apply_rope(q.reshape(T, hq, d), cos, sin, pos, interleaved)
+        kk = ref.apply_rope(k.reshape(T, hk, d), cos, sin, pos, interleaved)
+        return qq.view(B, S, hq, d), kk.view(B, S, hk, d)
+    return out[:, : hq * d].reshape(B, S, hq, d), out[:, hq * d:].reshape(B, S, hk, d)
+
+
+def fused_qk_rope(q: torch.Tensor, k: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
+                  position_ids: Optional[torch.Tensor] = None, interleaved: bool = False
+                  ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Rotary embedding of Q and K in one launch.  Default is the split-half (HuggingFace) pairing;
+    ``interleaved=True`` pairs ``(2i, 2i+1)``."""
+    if q.dim() == 3:                                       # packed [T, H, D]
+        qq, kk = _rope_4d(q[None], k[None], cos, sin, position_ids[None] if position_ids is not None else None,
+                          interleaved)
+        return qq[0], kk[0]
+    return _rope_4d(q, k, cos, sin, position_ids, interleaved)
+
+
+fused_qk_rope_inplace = fused_qk_rope
+
+
+def fused_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, position_ids: Optional[torch.Tensor] = None,
+               interleaved: bool = False) -> torch.Tensor:
+    """Single-tensor rotary embedding (``[..., T, H, D]``)."""
+    d = x.shape[-1]
+    if cos.shape[-1] == d:
+        cos, sin = cos[..., : d // 2], sin[..., : d // 2]
+    return ref.apply_rope(x, cos, sin, position_ids, interleaved)
+
+
+def rope_pytorch(q, k, cos, sin, position_ids=None):
+    return fused_rope(q, cos, sin, position_ids), fused_rope(k, cos, sin, position_ids)
+
+
+# ------------------------------------------------------------------------------------------- cross-entropy
+def fused_cross_entropy(*args, **kwargs) -> torch.Tensor:
+    """Both documented call forms:
+
+    * ``fused_cross_entropy(logits, targets, vocab_size=…)`` — loss on materialised logits;
+    * ``fused_cross_entropy(hidden, lm_head_weight, targets, chunk_size=…)`` — no logits.
+    """
+    kwargs.pop("vocab_size", None)
+    if len(args) >= 3 and isinstance(args[2], torch.Tensor) and not args[2].is_floating_point():
+        hidden, weight, targets = args[:3]
+        return cut_cross_entropy(hidden, weight, targets, *args[3:], **kwargs)
+    logits, targets = args[:2]
+    return ops.cross_entropy_logits(logits, targets, kwargs.get("ignore_index", -100),
+                                    kwargs.get("label_smoothing", 0.0), kwargs.get("z_loss_weight", 0.0),
+                                    kwargs.get("reduction", "mean"))
+
+
+fused_cross_entropy_triton = fused_cross_entropy
+liger_cross_entropy = fused_cross_entropy
+
+
+def cross_entropy_pytorch(logits, targets, ignore_index=-100, label_smoothing=0.0, z_loss_weight=0.0):
+    return ref.cross_entropy_logits(logits, targets, ignore_index, label_smoothing, z_loss_weight)
+
+
+def fused_linear_cross_entropy(hidden: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor,
+                               bias: Optional[torch.Tensor] = None, chunk_size: int = DEFAULT_CHUNK_SIZE,
+                               ignore_index: int = -100, label_smoothing: float = 0.0, z_loss_weight: float = 0.0
+                               ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Returns ``(loss, z_loss)`` like the reference; ``loss`` already contains the z-loss term."""
+    loss = cut_cross_entropy(hidden, weight, labels, bias, chunk_size, ignore_index, label_smoothing, z_loss_weight)
+    if z_loss_weight:
+        with torch.no_grad():
+            plain = cut_cross_entropy(hidden.detach(), weight.detach(), labels, bias, chunk_size, ignore_index,
+                                      label_smoothing, 0.0)
+            z = loss.detach() - plain
+    else:
+        z = torch.zeros((), device=loss.device, dtype=loss.dtype)
+    return loss, z
+
+
+triton_fused_linear_cross_entropy = fused_linear_cross_entropy
+fused_linear_cross_entropy_autograd = fused_linear_cross_entropy
+
+
+def chunked_cross_entropy(logits: torch.Tensor, labels: torch.Tensor, chunk_size: int = 4096,
+                          ignore_index: int = -100) -> torch.Tensor:
+    """Token-chunked CE on existing logits (keeps the fp32 upcast to one chunk at a time)."""
+    lg = logits.reshape(-1, logits.shape[-1])
+    y = labels.reshape(-1)
+    tot = torch.zeros((), dtype=torch.float32, device=lg.device)
+    for s in range(0, lg.shape[0], chunk_size):
+        tot = tot + ops.cross_entropy_logits(lg[s:s + chunk_size], y[s:s + chunk_size], ignore_index, reduction="sum")
+    return tot / (y != ignore_index).sum().clamp_min(1)
+
+
+class FusedLinearCrossEntropyLoss(CutCrossEntropyLoss):
+    """forward ``(hidden, weight, bias, labels)`` — argument order of the reference's module."""
+
+    def forward(self, hidden, weight, bias=None, labels=None):        # type: ignore[override]
+        if labels is None and bias is not None and not bias.is_floating_point():
+            bias, labels = None, bias
+        return super().forward(hidden, weight, labels, bias)
+
+
+TritonFusedLinearCrossEntropyLoss = FusedLinearCrossEntropyLoss
+LigerFusedLinearCrossEntropyLoss = FusedLinearCrossEntropyLoss
+
+
+# ------------------------------------------------------------------------------------------- fused composites
+def fused_rmsnorm_linear(x: torch.Tensor, norm_weight: torch.Tensor, weight: torch.Tensor,
+                         bias: Optional[torch.Tensor] = None, eps: float = 1e-6) -> torch.Tensor:
+    """``linear(rmsnorm(x))`` (norm kernel then the tcgen05 GEMM; differentiable)."""
+    return ops.linear(ops.rmsnorm(x, norm_weight, eps), weight, bias)
+
+
+class FusedRMSNormLinear(nn.Module):
+    def __init__(self, in_features: int, out_features: int, bias: bool = False, eps: float = 1e-6, device=None,
+                 dtype=None):
+        super().__init__()
+        self.norm_weight = nn.Parameter(torch.ones(in_features, device=device, dtype=dtype))
+        self.linear = nn.Linear(in_features, out_features, bias=bias, device=device, dtype=dtype)
+        self.eps = eps
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return fused_rmsnorm_linear(x, self.norm_weight, self.linear.weight, self.linear.bias, self.eps)
+
+
+def fused_embedding_rope(input_ids: torch.Tensor, embedding: torch.Tensor, cos: Optional[torch.Tensor] = None,
+                         sin: Optional[torch.Tensor] = None, position_ids: Optional[torch.Tensor] = None,
+                         num_heads: int = 1) -> torch.Tensor:
+    """Embedding gather; when ``cos``/``sin`` are given the rows are rotated per head, as the
+    reference's kernel does (rotary embeddings normally belong on Q/K — see ``fused_qk_rope``)."""
+    h = ops.embedding(input_ids, embedding)
+    if cos is None:
+        return h
+    shp = h.shape
+    d = shp[-1] // num_heads
+    x = h.reshape(-1, input_ids.shape[-1], num_heads, d) if input_ids.dim() > 1 else h.reshape(1, -1, num_heads, d)
+    return fused_rope(x, cos, sin, position_ids).reshape(shp)
+
+
+class FusedEmbeddingRoPE(nn.Module):
+    def __init__(self, vocab_size: int, hidden_size: int, num_heads: int = 1, max_seq_len: int = 4096,
+                 theta: float = 10000.0, device=None, dtype=None):
+        super().__init__()
+        self.embedding = nn.Embedding(vocab_size, hidden_size, device=device, dtype=dtype)
+        self.num_heads = num_heads
+        cos, sin = precompute_rope_cache(max_seq_len, hidden_size // num_heads, theta, device)
+        self.register_buffer("cos", cos, persistent=False)
+        self.register_buffer("sin", sin, persistent=False)
+
+    def forward(self, input_ids: torch.Tensor, position_ids: Optional[torch.Tensor] = None) -> torch.Tensor:
+        return fused_embedding_rope(input_ids, self.embedding.weight, self.cos, self.sin, position_ids, self.num_heads)
+
+
+def fused_gqa_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = True,
+                        softmax_scale: Optional[float] = None) -> torch.Tensor:
+    """Dense GQA attention ``q [B, Hq, S, D]``, ``k/v [B, Hk, S, D]`` → ``[B, Hq, S, D]``; runs as
+    ``B`` equal-length documents of the varlen kernel."""
+    B, hq, S, d = q.shape
+    hk = k.shape[1]
+    T = B * S
+    cu = torch.arange(0, T + 1, S, dtype=torch.int32, device=q.device)
+    o = ops.attention_varlen(q.transpose(1, 2).reshape(T, hq, d), k.transpose(1, 2).reshape(T, hk, d),
+                             v.transpose(1, 2).reshape(T, hk, d), cu, S, causal, softmax_scale, [S] * B)
+    return o.view(B, S, hq, d).transpose(1, 2)
+
+
+__all__ = [n for n in dir() if not n.startswith("_") and n not in ("math", "nn", "F", "torch", "ops", "ref",
+                                                                    "Optional", "Tuple")]

@@ -19,8 +19,8 @@ import torch.nn as nn
 from .fused_adamw import FusedAdamW
 
 # PEFT names ("…lora_A.default.weight"), this framework's ("…lora_A.q_proj"), and bare conventions
-_A_PATTERNS = [r"\.lora_A$", r"\.lora_A\.", r"lora_A_", r"\.A$", r"_A$", r"lora_down"]
-_B_PATTERNS = [r"\.lora_B$", r"\.lora_B\.", r"lora_B_", r"\.B$", r"_B$", r"lora_up"]
+_A_PATTERNS = [r"(^|\.)lora_A($|\.)", r"lora_A_", r"\.A$", r"_A$", r"lora_down"]
+_B_PATTERNS = [r"(^|\.)lora_B($|\.)", r"lora_B_", r"\.B$", r"_B$", r"lora_up"]
 
 
 class LoRAPlusParameterGroups:
