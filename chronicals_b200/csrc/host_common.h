@@ -34,6 +34,13 @@ inline int make_tmap(CUtensorMap* out, const void* base, unsigned long long inne
                      unsigned long long ld, unsigned box_inner, unsigned box_outer, int elem_bytes = 2) {
   EncodeTiledFn fn = get_encode_fn();
   if (fn == nullptr) return -10;
+  // The driver call needs a context bound to the calling thread.  A thread that has not used this
+  // library's CUDA runtime yet (an autograd worker, say) may have none: bind the primary context once.
+  static thread_local bool context_bound = false;
+  if (!context_bound) {
+    cudaFree(nullptr);
+    context_bound = true;
+  }
   if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (ld * elem_bytes) % 16 != 0) return -11;
   cuuint64_t dims[2] = {inner, outer};
   cuuint64_t strides[1] = {ld * elem_bytes};
