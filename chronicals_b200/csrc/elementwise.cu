@@ -609,3 +609,77 @@ int cb_ce_logits_grad(const void* logits, void* dlogits, const long long* labels
 }
 
 }  // extern "C"
+
+// =========================================================================================== allocation-free entry point
+// RMSNorm backward for callers that must not allocate (see chronicals_b200_noalloc.h).  The per-block
+// dW partials, which cb_rmsnorm_bwd takes from a caller-allocated buffer, live in a file-scope device
+// array here.  The array's name is only a host-side handle: its device address is fetched once per
+// device with cudaGetSymbolAddress and that pointer is what the kernels receive.
+#include "chronicals_b200_noalloc.h"
+
+#include <mutex>
+
+namespace {
+
+constexpr int NOALLOC_MAX_BLOCKS = CB_NOALLOC_RMSNORM_MAX_BLOCKS;
+constexpr int NOALLOC_MAX_N = CB_NOALLOC_RMSNORM_MAX_N;
+constexpr int NOALLOC_MAX_DEVICES = 64;
+
+static __device__ __align__(256) float g_noalloc_dw_partials[NOALLOC_MAX_BLOCKS * NOALLOC_MAX_N];
+
+std::mutex g_noalloc_mutex;
+float* g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {};
+
+// device address of the scratch array on the current device; resolved on first use per device
+int noalloc_scratch(float** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) return -3;
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_dw_partials);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (p == nullptr) return -4;
+    g_noalloc_ptr[dev] = p;
+  }
+  *out = g_noalloc_ptr[dev];
+  return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int cb_rmsnorm_bwd_noalloc_max_n() { return NOALLOC_MAX_N; }
+
+int cb_rmsnorm_bwd_noalloc(const void* dy, const void* h, const void* w, const float* rstd, const void* dres_in,
+                           void* dx, void* dw, int M, int N, float offset, int accumulate_dw, void* stream) {
+  if (M <= 0 || N <= 0 || N % 8 != 0) return -1;
+  if (N > NOALLOC_MAX_N) return -2;                     // beyond the built-in scratch: use cb_rmsnorm_bwd
+  const int tpr = pick_tpr(N);
+  if (tpr == 0) return -2;
+  float* part = nullptr;
+  const int rc = noalloc_scratch(&part);
+  if (rc != 0) return rc;
+  int grid = grid_for(M, cb::EW_THREADS / tpr, 1);
+  if (grid > NOALLOC_MAX_BLOCKS) grid = NOALLOC_MAX_BLOCKS;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const cb::bf16* dyp = static_cast<const cb::bf16*>(dy);
+  const cb::bf16* hp = static_cast<const cb::bf16*>(h);
+  const cb::bf16* wp = static_cast<const cb::bf16*>(w);
+  const cb::bf16* rp = static_cast<const cb::bf16*>(dres_in);
+  cb::bf16* dxp = static_cast<cb::bf16*>(dx);
+  const size_t smem = static_cast<size_t>(N) * sizeof(float);
+  // every block writes all N entries of its own partial row before the reduction reads them, so
+  // nothing left in the array by an earlier call can leak into this one
+  if (tpr == 32) cb::rmsnorm_bwd_kernel<32, 4><<<grid, cb::EW_THREADS, smem, s>>>(dyp, hp, wp, rstd, rp, dxp, part, M, N, offset);
+  else if (tpr == 128) cb::rmsnorm_bwd_kernel<128, 4><<<grid, cb::EW_THREADS, smem, s>>>(dyp, hp, wp, rstd, rp, dxp, part, M, N, offset);
+  else cb::rmsnorm_bwd_kernel<256, 4><<<grid, cb::EW_THREADS, smem, s>>>(dyp, hp, wp, rstd, rp, dxp, part, M, N, offset);
+  if (dw != nullptr)
+    cb::rmsnorm_dw_reduce_kernel<<<(N + 255) / 256, 256, 0, s>>>(part, grid, N, static_cast<cb::bf16*>(dw), accumulate_dw);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // extern "C"
