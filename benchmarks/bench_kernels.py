@@ -1,0 +1,236 @@
+"""Per-kernel micro-benchmarks with CUDA events: achieved TFLOP/s or GB/s and the fraction of the
+measured peaks (MEASURED_PEAKS.json beside the package, or the stated fallback).
+
+    python benchmarks/bench_kernels.py [--only gemm|attn|elementwise|cce|optim] [--iters N] [--json out.json]
+
+Inputs are larger than the 126 MB L2 or the L2 is flushed between iterations (a 256 MB write).
+Each number is the mean over ``iters`` launches after 3 warm-up launches, timed on the launching
+stream with a synchronize on both sides.  ``--one <name>`` runs a single named case a few times
+without timing (the form used under ncu).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+from chronicals_b200 import ops  # noqa: E402
+from chronicals_b200.config.config import measured_peaks  # noqa: E402
+from chronicals_b200.ops import _ext  # noqa: E402
+
+DEV = "cuda"
+_FLUSH = None
+
+
+def flush_l2():
+    global _FLUSH
+    if _FLUSH is None:
+        _FLUSH = torch.empty(256 * 2**20, dtype=torch.uint8, device=DEV)
+    _FLUSH.zero_()
+
+
+def timed(fn, iters=10, flush=True):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    tot = 0.0
+    for _ in range(iters):
+        if flush:
+            flush_l2()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        tot += a.elapsed_time(b)
+    return tot / iters
+
+
+def bf(*shape, scale=1.0):
+    return (torch.randn(*shape, device=DEV) * scale).to(torch.bfloat16)
+
+
+GEMM_CASES = {
+    # name: (M, N, K, a_mn, b_mn)  -- shapes of the 0.5B / 7B training step, T = 8192 tokens
+    "qkv_fwd_0.5b": (8192, 1152, 896, 0, 0), "o_fwd_0.5b": (8192, 896, 896, 0, 0),
+    "gateup_fwd_0.5b": (8192, 9728, 896, 0, 0), "down_fwd_0.5b": (8192, 896, 4864, 0, 0),
+    "gateup_dgrad_0.5b": (8192, 896, 9728, 0, 1), "down_dgrad_0.5b": (8192, 4864, 896, 0, 1),
+    "gateup_wgrad_0.5b": (9728, 896, 8192, 1, 1), "down_wgrad_0.5b": (896, 4864, 8192, 1, 1),
+    "gateup_fwd_7b": (8192, 37888, 3584, 0, 0), "down_fwd_7b": (8192, 3584, 18944, 0, 0),
+    "square_8k": (8192, 8192, 8192, 0, 0),
+}
+
+
+def gemm_inputs(M, N, K, a_mn, b_mn):
+    a = bf(K, M) if a_mn else bf(M, K)
+    b = bf(K, N) if b_mn else bf(N, K)
+    return a, b
+
+
+def run_gemm(results, peaks, iters, only=None):
+    for name, (M, N, K, a_mn, b_mn) in GEMM_CASES.items():
+        if only and only != name:
+            continue
+        a, b = gemm_inputs(M, N, K, a_mn, b_mn)
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+        ms = timed(lambda: ops.gemm(a, b, a_mn=bool(a_mn), b_mn=bool(b_mn), out=out), iters)
+        A = a.t() if a_mn else a
+        B = b if b_mn else b.t()
+        ms_lib = timed(lambda: torch.matmul(A, B, out=out), iters)
+        fl = 2.0 * M * N * K
+        results.append({"kernel": "gemm_tcgen05", "case": name, "shape": [M, N, K], "ms": ms,
+                        "tflops": fl / ms / 1e9, "frac_of_measured_bf16": fl / ms / 1e9 / peaks["bf16_tflops"],
+                        "cublas_ms": ms_lib, "cublas_tflops": fl / ms_lib / 1e9, "vs_cublas": ms_lib / ms})
+        _ext.check_status()
+
+
+def run_attn(results, peaks, iters, only=None):
+    from chronicals_b200.kernels.flash_attention_optimizer import attention_flops
+    cases = {"0.5b_8x1024": (14, 2, 64, [1024] * 8), "0.5b_2x4096": (14, 2, 64, [4096] * 2),
+             "7b_2x4096": (28, 4, 128, [4096] * 2), "lora_varlen": (14, 2, 64, None)}
+    for name, (hq, hk, d, lens) in cases.items():
+        if only and only != name:
+            continue
+        if lens is None:
+            g = torch.Generator().manual_seed(0)
+            raw = torch.empty(64).log_normal_(5.5, 1.0, generator=g).clamp(32, 2048).round().long().tolist()
+            lens, tot = [], 0
+            for l in raw:
+                if tot + l > 8192:
+                    break
+                lens.append(l)
+                tot += l
+        T = sum(lens)
+        qkv = bf(T, (hq + 2 * hk) * d).requires_grad_()
+        cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=DEV)
+        g = bf(T, hq * d)
+        ms_f = timed(lambda: ops.attention_qkv_packed(qkv.detach(), cu, hq, hk, d), iters)
+
+        def fb():
+            o = ops.attention_qkv_packed(qkv, cu, hq, hk, d)
+            o.backward(g)
+            qkv.grad = None
+        ms_fb = timed(fb, iters)
+        ff, fbw = attention_flops(lens, hq, d), attention_flops(lens, hq, d, backward=True)
+        results.append({"kernel": "attn_fwd", "case": name, "ms": ms_f, "tflops": ff / ms_f / 1e9,
+                        "frac_of_measured_bf16": ff / ms_f / 1e9 / peaks["bf16_tflops"]})
+        results.append({"kernel": "attn_fwd+bwd", "case": name, "ms": ms_fb, "tflops": fbw / ms_fb / 1e9,
+                        "frac_of_measured_bf16": fbw / ms_fb / 1e9 / peaks["bf16_tflops"]})
+        if len(set(lens)) == 1:
+            n, L = len(lens), lens[0]
+            q = bf(n, hq, L, d).requires_grad_()
+            k, v = bf(n, hk, L, d).requires_grad_(), bf(n, hk, L, d).requires_grad_()
+
+            def lib():
+                o = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
+                o.backward(torch.ones_like(o))
+            results[-1]["sdpa_fwd_bwd_ms"] = timed(lib, iters)
+        _ext.check_status()
+
+
+def run_elementwise(results, peaks, iters, only=None):
+    T, H, I = 8192, 896, 4864
+    bw = peaks["hbm_gbs"]
+
+    def rec(name, ms, nbytes):
+        results.append({"kernel": name, "ms": ms, "gbs": nbytes / ms / 1e6, "frac_of_measured_hbm": nbytes / ms / 1e6 / bw})
+
+    x, w = bf(T * 4, H), bf(H)
+    rec("rmsnorm_fwd[32768x896]", timed(lambda: ops.rmsnorm(x, w)), 2 * x.numel() * 2)
+    xg = x.clone().requires_grad_()
+    wg = w.clone().requires_grad_()
+    y = ops.rmsnorm(xg, wg)
+    gy = torch.randn_like(y)
+    rec("rmsnorm_bwd[32768x896]", timed(lambda: torch.autograd.grad(y, (xg, wg), gy, retain_graph=True)), 3 * x.numel() * 2)
+    gu = bf(T, 2 * I)
+    rec("swiglu_fwd[8192x4864]", timed(lambda: ops.swiglu(gu)), (gu.numel() + gu.numel() // 2) * 2)
+    gug = gu.clone().requires_grad_()
+    a = ops.swiglu(gug)
+    ga = torch.randn_like(a)
+    rec("swiglu_bwd[8192x4864]", timed(lambda: torch.autograd.grad(a, gug, ga, retain_graph=True)), (2 * gu.numel() + a.numel()) * 2)
+    from chronicals_b200.ops import ref
+    qkv = bf(T * 4, 1152)
+    cos, sin = ref.rope_cache(1024, 64, 1e6, device=DEV)
+    pos = (torch.arange(T * 4, device=DEV) % 1024)
+    rec("qk_rope[32768x(14+2)x64]", timed(lambda: ops.qk_rope_(qkv, cos, sin, pos, 14, 2, 64)), 2 * T * 4 * 1024 * 2)
+
+
+def run_cce(results, peaks, iters, only=None):
+    T, H, V = 8192, 896, 151936
+    h = bf(T, H).requires_grad_()
+    w = bf(V, H, scale=0.02).requires_grad_()
+    y = torch.randint(0, V, (T,), device=DEV)
+    ms_f = timed(lambda: ops.linear_cross_entropy(h.detach(), w.detach(), y), iters, flush=False)
+
+    def fb():
+        ops.linear_cross_entropy(h, w, y).backward()
+        h.grad = w.grad = None
+    ms_fb = timed(fb, max(3, iters // 2), flush=False)
+    fl = 2.0 * T * H * V
+    results.append({"kernel": "cce_fwd", "case": "0.5b", "ms": ms_f, "tflops": fl / ms_f / 1e9,
+                    "frac_of_measured_bf16": fl / ms_f / 1e9 / peaks["bf16_tflops"]})
+    results.append({"kernel": "cce_fwd+bwd", "case": "0.5b (4 GEMM passes)", "ms": ms_fb, "tflops": 4 * fl / ms_fb / 1e9,
+                    "frac_of_measured_bf16": 4 * fl / ms_fb / 1e9 / peaks["bf16_tflops"]})
+    _ext.check_status()
+
+
+def run_optim(results, peaks, iters, only=None):
+    from chronicals_b200.optimizers.fused_adamw import FusedAdamW
+    n = 400_000_000
+    p = torch.nn.Parameter(torch.zeros(n, device=DEV, dtype=torch.bfloat16))
+    p.grad = torch.randn(n, device=DEV).to(torch.bfloat16)
+    opt = FusedAdamW([p], lr=1e-4, max_grad_norm=1.0)
+    ms = timed(opt.step, iters, flush=False)
+    nbytes = n * (2 + 2 + 2 + 4 + 4 + 2 + 4 + 4)         # sq-norm read + p,g,m,v read + p,m,v write
+    results.append({"kernel": "adamw_multi + grad clip [400M bf16]", "ms": ms, "gbs": nbytes / ms / 1e6,
+                    "frac_of_measured_hbm": nbytes / ms / 1e6 / peaks["hbm_gbs"]})
+    torch_p = torch.nn.Parameter(torch.zeros(n, device=DEV, dtype=torch.bfloat16))
+    torch_p.grad = p.grad
+    o2 = torch.optim.AdamW([torch_p], lr=1e-4, fused=True)
+    results[-1]["torch_fused_adamw_ms"] = timed(o2.step, iters, flush=False)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--only", default=None)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--json", default=None)
+    ap.add_argument("--one", default=None, help="run one GEMM case 3 times without timing (for ncu)")
+    args = ap.parse_args()
+    peaks = measured_peaks()
+    if args.one:
+        M, N, K, a_mn, b_mn = GEMM_CASES[args.one]
+        a, b = gemm_inputs(M, N, K, a_mn, b_mn)
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+        for _ in range(3):
+            ops.gemm(a, b, a_mn=bool(a_mn), b_mn=bool(b_mn), out=out)
+        torch.cuda.synchronize()
+        _ext.check_status()
+        print("ok")
+        return
+    results = []
+    groups = {"gemm": run_gemm, "attn": run_attn, "elementwise": run_elementwise, "cce": run_cce, "optim": run_optim}
+    for name, fn in groups.items():
+        if args.only and args.only != name:
+            continue
+        fn(results, peaks, args.iters)
+    print(f"peaks ({peaks['source']}): bf16 {peaks['bf16_tflops']} TFLOP/s, HBM {peaks['hbm_gbs']} GB/s")
+    for r in results:
+        extra = "".join(f"  {k}={v:.3f}" if isinstance(v, float) else f"  {k}={v}" for k, v in r.items()
+                        if k not in ("kernel", "case", "ms"))
+        print(f"{r['kernel']:<28s} {r.get('case', ''):<22s} {r['ms']:8.3f} ms{extra}")
+    if args.json:
+        with open(args.json, "w") as f:
+            json.dump({"peaks": peaks, "results": results}, f, indent=1)
+
+
+if __name__ == "__main__":
+    main()

@@ -518,7 +518,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem, TMEM_COLS); }
 }
 
-// dqkv[t] = bf16( dQ | sum over the query heads of a group of dK | same for dV ), one block per token
+// dqkv[t] = bf16( dQ | sum over the query heads of a group of dK | same for dV ); one block per token,
+// four consecutive columns per thread (D is a multiple of 4, so a group never straddles heads)
 __global__ void attn_bwd_finalize_kernel(const float* __restrict__ dq_acc, const float* __restrict__ dk_part,
                                          const float* __restrict__ dv_part, bf16* __restrict__ dqkv, long long ld,
                                          int T, int hq, int hk, int D, const int* __restrict__ cu, int n_docs) {
@@ -526,19 +527,25 @@ __global__ void attn_bwd_finalize_kernel(const float* __restrict__ dq_acc, const
   const int nq = hq * D, nk = hk * D, g = hq / hk;
   bf16* out = dqkv + t * ld;
   const bool valid = t < cu[n_docs];                  // padding tokens get zero gradients
-  for (int c = threadIdx.x; c < nq + 2 * nk; c += blockDim.x) {
-    float v = 0.f;
+  for (int c = threadIdx.x * 4; c < nq + 2 * nk; c += blockDim.x * 4) {
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
     if (valid) {
       if (c < nq) {
-        v = dq_acc[t * nq + c];
+        v = *reinterpret_cast<const float4*>(dq_acc + t * nq + c);
       } else {
         const int cc = (c - nq) % nk, which = (c - nq) / nk;
         const int kvh = cc / D, d = cc % D;
         const float* src = (which == 0 ? dk_part : dv_part) + (t * hq + static_cast<long long>(kvh) * g) * D + d;
-        for (int i = 0; i < g; ++i) v += src[static_cast<long long>(i) * D];
+        for (int i = 0; i < g; ++i) {
+          const float4 x = *reinterpret_cast<const float4*>(src + static_cast<long long>(i) * D);
+          v.x += x.x; v.y += x.y; v.z += x.z; v.w += x.w;
+        }
       }
     }
-    out[c] = __float2bfloat16(v);
+    uint2 o;
+    o.x = pack_bf16x2(v.x, v.y);
+    o.y = pack_bf16x2(v.z, v.w);
+    *reinterpret_cast<uint2*>(out + c) = o;
   }
 }
 
@@ -625,7 +632,7 @@ int cb_attn_bwd(const void* q, const void* k, const void* v, const void* o, cons
     if (!cfg) { e = set_smem(cb::attn_bwd_kernel<128>, cb::BwdSmem<128>::TOTAL); if (e) return e; cfg = true; }
     cb::attn_bwd_kernel<128><<<grid, cb::ATT_THREADS, cb::BwdSmem<128>::TOTAL, s>>>(mq, mk, mv, mdo, a);
   }
-  cb::attn_bwd_finalize_kernel<<<T, 256, 0, s>>>(dq_acc, dk_part, dv_part, static_cast<cb::bf16*>(dqkv), ld_dqkv, T,
+  cb::attn_bwd_finalize_kernel<<<T, 128, 0, s>>>(dq_acc, dk_part, dv_part, static_cast<cb::bf16*>(dqkv), ld_dqkv, T,
                                                   hq, hk, D, cu, n_docs);
   return static_cast<int>(cudaGetLastError());
 }

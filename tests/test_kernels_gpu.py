@@ -197,9 +197,9 @@ def test_cross_entropy_logits_kernel():
 
 
 @pytest.mark.parametrize("hq,hk,d", [(14, 2, 64), (4, 4, 64), (5, 1, 128)])
-@pytest.mark.parametrize("bounds", [[0, 130, 131, 400, 640], [0, 1024], [0, 128, 256, 700]])
-def test_attention_packed_fwd_bwd(hq, hk, d, bounds):
-    T = 768
+@pytest.mark.parametrize("bounds,T", [([0, 130, 131, 400, 640], 768), ([0, 1024], 768), ([0, 128, 256, 700], 768),
+                                      ([0, 57, 301, 555], 555)])
+def test_attention_packed_fwd_bwd(hq, hk, d, bounds, T):
     nq, nk = hq * d, hk * d
     qkv = _rand(T, nq + 2 * nk).requires_grad_()
     cu = torch.tensor([min(b, T) for b in bounds], dtype=torch.int32, device=DEV)
