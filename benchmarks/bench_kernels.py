@@ -206,6 +206,20 @@ def main():
     ap.add_argument("--one", default=None, help="run one GEMM case 3 times without timing (for ncu)")
     args = ap.parse_args()
     peaks = measured_peaks()
+    if args.one and args.one.startswith("attn"):
+        hq, hk, d, L, n = 14, 2, 64, 1024, 8
+        T = n * L
+        qkv = bf(T, (hq + 2 * hk) * d).requires_grad_()
+        cu = torch.arange(0, T + 1, L, dtype=torch.int32, device=DEV)
+        g = bf(T, hq * d)
+        for _ in range(2):
+            o = ops.attention_qkv_packed(qkv, cu, hq, hk, d)
+            o.backward(g)
+            qkv.grad = None
+        torch.cuda.synchronize()
+        _ext.check_status()
+        print("ok")
+        return
     if args.one:
         M, N, K, a_mn, b_mn = GEMM_CASES[args.one]
         a, b = gemm_inputs(M, N, K, a_mn, b_mn)
@@ -216,20 +230,23 @@ def main():
         _ext.check_status()
         print("ok")
         return
-    results = []
+    class _Live(list):
+        def append(self, r):
+            super().append(r)
+            extra = "".join(f"  {k}={v:.3f}" if isinstance(v, float) else f"  {k}={v}" for k, v in r.items()
+                            if k not in ("kernel", "case", "ms"))
+            print(f"{r['kernel']:<28s} {r.get('case', ''):<22s} {r['ms']:8.3f} ms{extra}", flush=True)
+
+    print(f"peaks ({peaks['source']}): bf16 {peaks['bf16_tflops']} TFLOP/s, HBM {peaks['hbm_gbs']} GB/s", flush=True)
+    results = _Live()
     groups = {"gemm": run_gemm, "attn": run_attn, "elementwise": run_elementwise, "cce": run_cce, "optim": run_optim}
     for name, fn in groups.items():
         if args.only and args.only != name:
             continue
         fn(results, peaks, args.iters)
-    print(f"peaks ({peaks['source']}): bf16 {peaks['bf16_tflops']} TFLOP/s, HBM {peaks['hbm_gbs']} GB/s")
-    for r in results:
-        extra = "".join(f"  {k}={v:.3f}" if isinstance(v, float) else f"  {k}={v}" for k, v in r.items()
-                        if k not in ("kernel", "case", "ms"))
-        print(f"{r['kernel']:<28s} {r.get('case', ''):<22s} {r['ms']:8.3f} ms{extra}")
     if args.json:
         with open(args.json, "w") as f:
-            json.dump({"peaks": peaks, "results": results}, f, indent=1)
+            json.dump({"peaks": peaks, "results": list(results)}, f, indent=1)
 
 
 if __name__ == "__main__":

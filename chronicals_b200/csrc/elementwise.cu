@@ -204,14 +204,24 @@ rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ h, cons
   }
 }
 
+// 256 threads = 32 columns x 8 row slices; each slice sums every 8th partial row, then the slices combine
 __global__ void rmsnorm_dw_reduce_kernel(const float* __restrict__ part, int nblocks, int N, bf16* __restrict__ dw,
                                          int accumulate) {
-  const int n = blockIdx.x * blockDim.x + threadIdx.x;
-  if (n >= N) return;
+  __shared__ float red[8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int n = blockIdx.x * 32 + tx;
   float s = 0.f;
-  for (int b = 0; b < nblocks; ++b) s += part[static_cast<long long>(b) * N + n];
-  if (accumulate) s += __bfloat162float(dw[n]);
-  dw[n] = __float2bfloat16(s);
+  if (n < N)
+    for (int b = ty; b < nblocks; b += 8) s += part[static_cast<long long>(b) * N + n];
+  red[ty][tx] = s;
+  __syncthreads();
+  if (ty == 0 && n < N) {
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t += red[i][tx];
+    if (accumulate) t += __bfloat162float(dw[n]);
+    dw[n] = __float2bfloat16(t);
+  }
 }
 
 // ------------------------------------------------------------------ gated activations
@@ -534,7 +544,7 @@ int cb_rmsnorm_bwd(const void* dy, const void* h, const void* w, const float* rs
   else if (tpr == 128) cb::rmsnorm_bwd_kernel<128, 4><<<grid, cb::EW_THREADS, smem, s>>>(dyp, hp, wp, rstd, rp, dxp, dw_part, M, N, offset);
   else cb::rmsnorm_bwd_kernel<256, 4><<<grid, cb::EW_THREADS, smem, s>>>(dyp, hp, wp, rstd, rp, dxp, dw_part, M, N, offset);
   if (dw != nullptr)
-    cb::rmsnorm_dw_reduce_kernel<<<(N + 255) / 256, 256, 0, s>>>(dw_part, grid, N, static_cast<cb::bf16*>(dw), accumulate_dw);
+    cb::rmsnorm_dw_reduce_kernel<<<(N + 31) / 32, 256, 0, s>>>(dw_part, grid, N, static_cast<cb::bf16*>(dw), accumulate_dw);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -678,7 +688,7 @@ int cb_rmsnorm_bwd_noalloc(const void* dy, const void* h, const void* w, const f
   else if (tpr == 128) cb::rmsnorm_bwd_kernel<128, 4><<<grid, cb::EW_THREADS, smem, s>>>(dyp, hp, wp, rstd, rp, dxp, part, M, N, offset);
   else cb::rmsnorm_bwd_kernel<256, 4><<<grid, cb::EW_THREADS, smem, s>>>(dyp, hp, wp, rstd, rp, dxp, part, M, N, offset);
   if (dw != nullptr)
-    cb::rmsnorm_dw_reduce_kernel<<<(N + 255) / 256, 256, 0, s>>>(part, grid, N, static_cast<cb::bf16*>(dw), accumulate_dw);
+    cb::rmsnorm_dw_reduce_kernel<<<(N + 31) / 32, 256, 0, s>>>(part, grid, N, static_cast<cb::bf16*>(dw), accumulate_dw);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -25,6 +25,8 @@
 #include "common.cuh"
 #include "host_common.h"
 
+#include <string.h>
+
 namespace cb {
 
 constexpr int BLOCK_M = 128;
@@ -56,6 +58,7 @@ struct GemmArgs {
   const float* gout;        // [1]  upstream gradient of the scalar loss
   float z_weight;
   float smoothing;
+  int tma_store;   // 1: the epilogue stages tiles in shared memory and writes them with TMA stores
   int V_total;     // vocabulary size for the smoothing term
   int col_offset;  // global vocab id of column 0 of B (vocab chunk or tensor-parallel shard)
   int* status;
@@ -65,14 +68,15 @@ template <int BLOCK_N, int STAGES>
 struct SmemLayout {
   static constexpr int A_BYTES = BLOCK_M * BLOCK_K * 2;
   static constexpr int B_BYTES = BLOCK_N * BLOCK_K * 2;
-  static constexpr int BAR_OFFSET = STAGES * (A_BYTES + B_BYTES);
+  static constexpr int STG_OFFSET = STAGES * (A_BYTES + B_BYTES);   // epilogue staging: 4 warps x 2 x 4 KB
+  static constexpr int BAR_OFFSET = STG_OFFSET + 4 * 8192;
   static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;  // barriers + alignment slack
 };
 
 template <int BLOCK_N, int A_MN, int B_MN, int STAGES, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    const GemmArgs g) {
+                    const __grid_constant__ CUtensorMap tmC, const GemmArgs g) {
   using L = SmemLayout<BLOCK_N, STAGES>;
   constexpr int A_BYTES = L::A_BYTES, B_BYTES = L::B_BYTES;
   constexpr uint32_t TMEM_COLS = 2 * BLOCK_N;  // two accumulators; 256 or 512 (powers of two)
@@ -246,6 +250,108 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
         tc_fence_after();
         const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BLOCK_N;
+
+        if (EPI != EPI_LSE && g.tma_store) {
+          // ---- staged epilogue: TMEM -> registers -> fused math -> swizzled smem tile -> TMA store.
+          // Each warp owns 32 rows and two 4 KB staging buffers ([32 rows x 128 B], 16-byte chunks
+          // XOR-swizzled by row & 7 to match the tensor map); stores of one buffer overlap the
+          // math of the next.  Rows >= M and columns >= N are clipped by the TMA store itself.
+          uint8_t* stg = smem + L::STG_OFFSET + (warp - 2) * 8192;
+          const int row0w = m_blk * BLOCK_M + q * 32;
+          const int cols_per_store = g.out_fp32 ? 32 : 64;
+          int buf = 0;
+#pragma unroll 1
+          for (int c0 = 0; c0 < BLOCK_N; c0 += cols_per_store) {
+            const int colbase = nt * BLOCK_N + c0;
+            if (colbase >= g.N) break;  // uniform across the warp
+            uint32_t r[64];
+            tmem_ld_32x32(t_row + c0, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+            if (!g.out_fp32) tmem_ld_32x32(t_row + c0 + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+            tmem_ld_wait();
+            const int nhalf = g.out_fp32 ? 1 : 2;
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+              if (hh >= nhalf) break;
+              const int col0 = colbase + hh * 32;
+              float* v = reinterpret_cast<float*>(&r[hh * 32]);
+              if (EPI == EPI_DLOGITS) {
+                const float sm = g.smoothing / static_cast<float>(g.V_total);
+                const float l2 = lse_r * 1.4426950408889634f;
+                const int rel = lab - col0;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                  float p = exp2f(fmaf(v[j], 1.4426950408889634f, -l2)) * coef - sm;
+                  if (j == rel) p -= (1.f - g.smoothing);
+                  v[j] = p * gs;
+                }
+              } else {
+                if (g.bias != nullptr) {
+#pragma unroll
+                  for (int j = 0; j < 32; ++j)
+                    if (col0 + j < g.N) v[j] += __bfloat162float(g.bias[col0 + j]);
+                }
+                if (g.addend != nullptr && row_ok) {
+                  const bf16* ap = g.addend + static_cast<long long>(row) * g.ld_add + col0;
+                  if (col0 + 32 <= g.N && (reinterpret_cast<uintptr_t>(ap) & 15) == 0) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                      const uint4 u = reinterpret_cast<const uint4*>(ap)[j];
+                      const float2 a0 = unpack_bf16x2(u.x), a1 = unpack_bf16x2(u.y);
+                      const float2 a2 = unpack_bf16x2(u.z), a3 = unpack_bf16x2(u.w);
+                      v[8 * j + 0] += a0.x; v[8 * j + 1] += a0.y; v[8 * j + 2] += a1.x; v[8 * j + 3] += a1.y;
+                      v[8 * j + 4] += a2.x; v[8 * j + 5] += a2.y; v[8 * j + 6] += a3.x; v[8 * j + 7] += a3.y;
+                    }
+                  } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                      if (col0 + j < g.N) v[j] += __bfloat162float(ap[j]);
+                  }
+                }
+                if (g.accumulate && row_ok) {
+                  if (g.out_fp32) {
+                    const float* cp = reinterpret_cast<const float*>(g.C) + static_cast<long long>(row) * g.ldc + col0;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                      if (col0 + j < g.N) v[j] += cp[j];
+                  } else {
+                    const bf16* cp = reinterpret_cast<const bf16*>(g.C) + static_cast<long long>(row) * g.ldc + col0;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                      if (col0 + j < g.N) v[j] += __bfloat162float(cp[j]);
+                  }
+                }
+              }
+            }
+            // the buffer written two stores ago must have been read out by its TMA store
+            if (lane == 0) tma_store_wait_read<1>();
+            __syncwarp();
+            uint8_t* dstrow = stg + buf * 4096 + lane * 128;
+            if (g.out_fp32) {
+#pragma unroll
+              for (int cc = 0; cc < 8; ++cc) {
+                uint4 u = make_uint4(r[4 * cc], r[4 * cc + 1], r[4 * cc + 2], r[4 * cc + 3]);
+                *reinterpret_cast<uint4*>(dstrow + ((cc ^ (lane & 7)) << 4)) = u;
+              }
+            } else {
+#pragma unroll
+              for (int cc = 0; cc < 8; ++cc) {
+                uint4 u;
+                u.x = pack_bf16x2(__uint_as_float(r[8 * cc + 0]), __uint_as_float(r[8 * cc + 1]));
+                u.y = pack_bf16x2(__uint_as_float(r[8 * cc + 2]), __uint_as_float(r[8 * cc + 3]));
+                u.z = pack_bf16x2(__uint_as_float(r[8 * cc + 4]), __uint_as_float(r[8 * cc + 5]));
+                u.w = pack_bf16x2(__uint_as_float(r[8 * cc + 6]), __uint_as_float(r[8 * cc + 7]));
+                *reinterpret_cast<uint4*>(dstrow + ((cc ^ (lane & 7)) << 4)) = u;
+              }
+            }
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0 && row0w < g.M) {          // a box that starts past the last row has nothing to write
+              tma_store_2d(&tmC, stg + buf * 4096, colbase, row0w);
+              tma_store_commit();
+            }
+            buf ^= 1;
+          }
+        } else {
 #pragma unroll 1
         for (int c = 0; c < BLOCK_N / 32; ++c) {
           uint32_t r[32];
@@ -366,6 +472,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             }
           }
         }
+        }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(tempty + acc);
@@ -377,6 +484,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         if (g.part_sum != nullptr) g.part_sum[o] = run_sum;
       }
     }
+    if (EPI != EPI_LSE && g.tma_store && lane == 0) tma_store_wait_all();
   }
 
   // ------------------------------------------------------------- teardown
@@ -467,7 +575,8 @@ using cbhost::make_tmap;
 using cbhost::num_sms;
 
 template <int BLOCK_N, int A_MN, int B_MN, int STAGES, int EPI>
-int launch(const CUtensorMap& ta, const CUtensorMap& tb, const cb::GemmArgs& g, cudaStream_t stream) {
+int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const cb::GemmArgs& g,
+           cudaStream_t stream) {
   auto kern = cb::gemm_tcgen05_kernel<BLOCK_N, A_MN, B_MN, STAGES, EPI>;
   constexpr int smem = cb::SmemLayout<BLOCK_N, STAGES>::TOTAL;
   static bool configured = false;
@@ -476,26 +585,26 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const cb::GemmArgs& g, 
     configured = true;
   }
   const int grid = g.num_items < num_sms() ? g.num_items : num_sms();
-  kern<<<grid, cb::GEMM_THREADS, smem, stream>>>(ta, tb, g);
+  kern<<<grid, cb::GEMM_THREADS, smem, stream>>>(ta, tb, tc, g);
   return static_cast<int>(cudaGetLastError());
 }
 
 template <int EPI>
-int dispatch(int block_n, int a_mn, int b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const cb::GemmArgs& g,
-             cudaStream_t s) {
+int dispatch(int block_n, int a_mn, int b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
+             const cb::GemmArgs& g, cudaStream_t s) {
   if (block_n == 256) {
-    if (!a_mn && !b_mn) return launch<256, 0, 0, 4, EPI>(ta, tb, g, s);
+    if (!a_mn && !b_mn) return launch<256, 0, 0, 4, EPI>(ta, tb, tc, g, s);
     if (EPI == cb::EPI_STORE) {
-      if (!a_mn && b_mn) return launch<256, 0, 1, 4, cb::EPI_STORE>(ta, tb, g, s);
-      if (a_mn && b_mn) return launch<256, 1, 1, 4, cb::EPI_STORE>(ta, tb, g, s);
-      if (a_mn && !b_mn) return launch<256, 1, 0, 4, cb::EPI_STORE>(ta, tb, g, s);
+      if (!a_mn && b_mn) return launch<256, 0, 1, 4, cb::EPI_STORE>(ta, tb, tc, g, s);
+      if (a_mn && b_mn) return launch<256, 1, 1, 4, cb::EPI_STORE>(ta, tb, tc, g, s);
+      if (a_mn && !b_mn) return launch<256, 1, 0, 4, cb::EPI_STORE>(ta, tb, tc, g, s);
     }
   } else {
-    if (!a_mn && !b_mn) return launch<128, 0, 0, 6, EPI>(ta, tb, g, s);
+    if (!a_mn && !b_mn) return launch<128, 0, 0, 6, EPI>(ta, tb, tc, g, s);
     if (EPI == cb::EPI_STORE) {
-      if (!a_mn && b_mn) return launch<128, 0, 1, 6, cb::EPI_STORE>(ta, tb, g, s);
-      if (a_mn && b_mn) return launch<128, 1, 1, 6, cb::EPI_STORE>(ta, tb, g, s);
-      if (a_mn && !b_mn) return launch<128, 1, 0, 6, cb::EPI_STORE>(ta, tb, g, s);
+      if (!a_mn && b_mn) return launch<128, 0, 1, 6, cb::EPI_STORE>(ta, tb, tc, g, s);
+      if (a_mn && b_mn) return launch<128, 1, 1, 6, cb::EPI_STORE>(ta, tb, tc, g, s);
+      if (a_mn && !b_mn) return launch<128, 1, 0, 6, cb::EPI_STORE>(ta, tb, tc, g, s);
     }
   }
   return -20;
@@ -517,6 +626,19 @@ int pick_block_n(int M, int N, int forced) {
     }
   }
   return best;
+}
+
+// Tensor map of the output for the staged epilogue; returns 0 and sets *ok when C qualifies
+// (16-byte aligned base and row pitch), otherwise leaves the direct-store epilogue in charge.
+int build_out_map(CUtensorMap* tc, int* ok, const void* C, int M, int N, long long ldc, int out_fp32) {
+  const int eb = out_fp32 ? 4 : 2;
+  *ok = 0;
+  memset(tc, 0, sizeof(*tc));
+  if ((reinterpret_cast<uintptr_t>(C) & 15) != 0 || (ldc * eb) % 16 != 0) return 0;
+  const int e = make_tmap(tc, C, N, M, ldc, out_fp32 ? 32 : 64, 32, eb);
+  if (e) return e;
+  *ok = 1;
+  return 0;
 }
 
 int build_maps(CUtensorMap* ta, CUtensorMap* tb, const void* A, const void* B, int M, int N, int K, long long lda,
@@ -556,7 +678,10 @@ int cb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, const 
   g.addend = static_cast<const cb::bf16*>(addend);
   g.ld_add = ld_add;
   g.status = status;
-  return dispatch<cb::EPI_STORE>(bn, a_mn, b_mn, ta, tb, g, static_cast<cudaStream_t>(stream));
+  CUtensorMap tc;
+  e = build_out_map(&tc, &g.tma_store, C, M, N, ldc, out_fp32);
+  if (e) return e;
+  return dispatch<cb::EPI_STORE>(bn, a_mn, b_mn, ta, tb, tc, g, static_cast<cudaStream_t>(stream));
 }
 
 // Number of vocab splits the forward pass of the fused linear-cross-entropy uses for a
@@ -586,7 +711,9 @@ int cb_cce_forward(const void* hidden, const void* weight, const long long* labe
   g.part_m = part_m; g.part_s = part_s; g.part_sum = part_sum; g.tgt = tgt;
   g.col_offset = col_offset;
   g.status = status;
-  return dispatch<cb::EPI_LSE>(bn, 0, 0, ta, tb, g, static_cast<cudaStream_t>(stream));
+  CUtensorMap tc;
+  memset(&tc, 0, sizeof(tc));
+  return dispatch<cb::EPI_LSE>(bn, 0, 0, ta, tb, tc, g, static_cast<cudaStream_t>(stream));
 }
 
 int cb_cce_combine(const float* part_m, const float* part_s, const float* part_sum, const float* tgt,
@@ -621,7 +748,10 @@ int cb_cce_dlogits(const void* hidden, const void* weight_chunk, const long long
   g.labels = labels; g.lse = lse; g.gscale = gscale; g.gout = gout;
   g.z_weight = z_weight; g.smoothing = smoothing; g.V_total = V_total; g.col_offset = col_offset;
   g.status = status;
-  return dispatch<cb::EPI_DLOGITS>(bn, 0, 0, ta, tb, g, static_cast<cudaStream_t>(stream));
+  CUtensorMap tc;
+  e = build_out_map(&tc, &g.tma_store, G, M, Vc, ldg, 0);
+  if (e) return e;
+  return dispatch<cb::EPI_DLOGITS>(bn, 0, 0, ta, tb, tc, g, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"
