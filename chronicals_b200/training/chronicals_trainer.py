@@ -166,13 +166,18 @@ class ChronicalsTrainer:
             self.packer = SequencePacker(max_seq_length=a.max_seq_length, strategy=a.packing_strategy,
                                          mask_first_token_of_packed=a.mask_first_token_of_packed)
 
+        if self.world_size > 1 and self._get("broadcast_parameters", True):
+            with torch.no_grad():                                  # every rank starts from rank 0's weights
+                for p in self.model.parameters():
+                    self.dist.broadcast(p.data, src=0)
+        self._sharded_optimizer = False
         self._setup_optimizer()
         self.total_steps = self._estimate_total_steps()
         self._setup_scheduler()
 
         # data-parallel gradient reduction
         self.dp = None
-        if self.world_size > 1:
+        if self.world_size > 1 and not getattr(self, "_sharded_optimizer", False):
             from ..parallel.data_parallel import GradientReducer
             self.dp = GradientReducer(self.model, backend=a.parallel.comm_backend, bucket_mb=a.parallel.bucket_mb)
 
@@ -216,6 +221,17 @@ class ChronicalsTrainer:
                 betas=(a.adam_beta1, a.adam_beta2), eps=a.adam_epsilon, weight_decay=a.weight_decay,
                 max_grad_norm=a.max_grad_norm)
             self.use_external_grad_clip = False
+        elif (t == "fused_adamw" and a.use_fused_adamw and self.world_size > 1 and a.parallel.comm_backend == "fused"
+              and self.device.type == "cuda" and self._fused_comm_possible()):
+            # gradient reduce-scatter, clip, AdamW and parameter all-gather as peer-memory kernels
+            from ..parallel.zero import ShardedFusedAdamW
+            self.optimizer = ShardedFusedAdamW([p for p in self.model.parameters() if p.requires_grad],
+                                               lr=a.learning_rate, betas=(a.adam_beta1, a.adam_beta2),
+                                               eps=a.adam_epsilon, weight_decay=a.weight_decay,
+                                               max_grad_norm=a.max_grad_norm,
+                                               wait_budget_us=a.parallel.wait_budget_us)
+            self.use_external_grad_clip = False
+            self._sharded_optimizer = True
         elif t == "fused_adamw" and a.use_fused_adamw:
             self.optimizer = FusedAdamW([p for p in self.model.parameters() if p.requires_grad], lr=a.learning_rate,
                                         betas=(a.adam_beta1, a.adam_beta2), eps=a.adam_epsilon,
@@ -226,6 +242,17 @@ class ChronicalsTrainer:
                                               weight_decay=a.weight_decay, betas=(a.adam_beta1, a.adam_beta2),
                                               eps=a.adam_epsilon, max_grad_norm=a.max_grad_norm)
         self._active_optimizations["fused_optimizer"] = isinstance(self.optimizer, FusedAdamW)
+
+    def _fused_comm_possible(self) -> bool:
+        try:
+            from ..parallel import symm
+            ok = symm.peer_access_available() and all(p.dtype == torch.bfloat16 for p in self.model.parameters()
+                                                      if p.requires_grad)
+        except Exception:
+            ok = False
+        if not ok and self.rank == 0:
+            print("[parallel] fused collectives need peer access and bf16 parameters; using the NCCL path")
+        return ok
 
     def _setup_scheduler(self) -> None:
         a = self.args

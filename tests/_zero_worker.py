@@ -1,0 +1,82 @@
+"""Worker for the multi-GPU tests (one process per GPU, launched by torch.distributed.run)."""
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+from chronicals_b200.ops import _ext
+from chronicals_b200.optimizers.fused_adamw import FusedAdamW
+from chronicals_b200.parallel.bootstrap import init_distributed, shutdown
+
+
+def main():
+    out = sys.argv[1]
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    rank, local, world = init_distributed("nccl")
+    dev = torch.device("cuda", local)
+    from chronicals_b200.parallel import symm
+    from chronicals_b200.parallel.zero import ShardedFusedAdamW
+    res = {"world": world}
+
+    # ---- barrier with payload
+    ctx = symm.SymmetricContext()
+    pay = torch.tensor([float(rank + 1), 0, 0, 0], device=dev)
+    got = ctx.barrier(pay).clone()
+    torch.cuda.synchronize()
+    res["payload_ok"] = [got[r * 4].item() for r in range(world)] == [float(r + 1) for r in range(world)]
+    for _ in range(5):
+        ctx.barrier()
+    torch.cuda.synchronize()
+    _ext.check_status(dev)
+
+    # ---- sharded fused AdamW against the single-GPU optimizer on the averaged gradients
+    torch.manual_seed(0)
+    shapes = [(300, 64), (1000,), (513, 129), (7,)]
+    ref_p = [torch.nn.Parameter(torch.randn(*s, device=dev).to(torch.bfloat16)) for s in shapes]
+    my_p = [torch.nn.Parameter(p.detach().clone()) for p in ref_p]
+    o_ref = FusedAdamW(ref_p, lr=1e-2, betas=(0.9, 0.95), weight_decay=0.01, max_grad_norm=1.0)
+    o_my = ShardedFusedAdamW(my_p, lr=1e-2, betas=(0.9, 0.95), weight_decay=0.01, max_grad_norm=1.0)
+    for step in range(4):
+        gens = [torch.Generator(device="cpu").manual_seed(100 * step + r) for r in range(world)]
+        all_g = [[torch.randn(*s, generator=gens[r]).to(torch.bfloat16) for s in shapes] for r in range(world)]
+        for i, (p, q) in enumerate(zip(ref_p, my_p)):
+            avg = sum(all_g[r][i].float() for r in range(world)) / world
+            p.grad = avg.to(torch.bfloat16).to(dev)
+            q.grad = all_g[rank][i].to(dev)
+        o_ref.step()
+        o_my.step()
+    torch.cuda.synchronize()
+    _ext.check_status(dev)
+    err = max((p.float() - q.float()).abs().max().item() for p, q in zip(ref_p, my_p))
+    res["adamw_max_err"] = err
+    res["norm"] = [o_ref.last_grad_norm.item(), o_my.last_grad_norm.item()]
+    # every rank must hold identical parameters
+    flat = torch.cat([q.detach().float().reshape(-1) for q in my_p])
+    lo, hi = flat.clone(), flat.clone()
+    dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+    dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+    res["ranks_identical"] = bool(torch.equal(lo, hi))
+
+    # ---- bounded wait: a barrier nobody else joins gives up with an error status instead of hanging
+    if os.environ.get("CB_TEST_TIMEOUT", "1") == "1":
+        lone = symm.SymmetricContext(wait_budget_us=2000)
+        dist.barrier()
+        if rank == 0:
+            lone.barrier()                      # rank 1.. never call it
+            torch.cuda.synchronize()
+            try:
+                _ext.check_status(dev)
+                res["timeout_detected"] = False
+            except _ext.KernelError as e:
+                res["timeout_detected"] = "201" in str(e)
+        dist.barrier()
+    if rank == 0:
+        with open(out, "w") as f:
+            json.dump(res, f)
+    shutdown()
+
+
+if __name__ == "__main__":
+    main()

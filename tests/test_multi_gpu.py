@@ -1,0 +1,32 @@
+"""Multi-GPU tests of the peer-memory collectives (need >= 2 GPUs; run as child processes)."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _run_worker(tmp_path, world, script="_zero_worker.py", port=29541):
+    out = os.path.join(str(tmp_path), "res.json")
+    env = dict(os.environ, PYTHONPATH=ROOT, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", script), out]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    return json.load(open(out))
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_symmetric_barrier_sharded_adamw_and_bounded_wait(tmp_path):
+    world = min(torch.cuda.device_count(), 4)
+    res = _run_worker(tmp_path, world)
+    assert res["payload_ok"]
+    assert res["adamw_max_err"] < 2e-2, res
+    assert abs(res["norm"][0] - res["norm"][1]) < 2e-2 * max(1.0, res["norm"][0])
+    assert res["ranks_identical"]
+    assert res.get("timeout_detected") is True
