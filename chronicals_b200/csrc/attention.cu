@@ -86,8 +86,7 @@ struct FwdSmem {
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_K = TILE;                  // 2 stages
   static constexpr int OFF_V = 3 * TILE;              // 2 stages
-  static constexpr int OFF_P = 5 * TILE;              // [128 x 128]
-  static constexpr int OFF_BAR = OFF_P + 32768;
+  static constexpr int OFF_BAR = 5 * TILE;            // P never touches shared memory (it lives in TMEM)
   static constexpr int TOTAL = OFF_BAR + 128 + 1024;
 };
 
@@ -97,7 +96,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 const __grid_constant__ CUtensorMap tmV, const AttnArgs a) {
   using L = FwdSmem<D>;
   constexpr int PANELS = D / 64;
-  constexpr uint32_t TMEM_COLS = 256;                 // S: [0,128)  PV: [128, 128 + D)
+  // TMEM columns: S fp32 [0,128); P (bf16 pairs, 64 words per row) overwrites S in place as each
+  // thread finishes reading its row; P V product at [128, 128 + D)
+  constexpr uint32_t TMEM_COLS = 256;
   constexpr uint32_t IDESC_S = umma_idesc_bf16(128, 128, 0, 0);
   constexpr uint32_t IDESC_PV = umma_idesc_bf16(128, D, 0, 1);
 
@@ -112,7 +113,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint8_t* sQ = smem + L::OFF_Q;
   uint8_t* sK = smem + L::OFF_K;
   uint8_t* sV = smem + L::OFF_V;
-  uint8_t* sP = smem + L::OFF_P;
   uint64_t* kv_full = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);   // [2]
   uint64_t* bar_q = kv_full + 2;
   uint64_t* bar_s = kv_full + 3;
@@ -221,21 +221,26 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         p[i] = (!diag || c * 32 + i <= r) ? e : 0.f;
         rs += p[i];
       }
-      store_row_chunk32(sP, r, c, p);
+      // 32 probabilities -> 16 bf16 pairs -> TMEM words [16c, 16c + 16) of my row: always behind the
+      // fp32 columns [32c, 32c + 32) just read, so S is consumed before it is overwritten
+      uint32_t pk[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) pk[i] = pack_bf16x2(p[2 * i], p[2 * i + 1]);
+      tmem_st_32x16(t_row + c * 16, pk);
     }
+    tmem_st_wait();
     l_run = l_run * alpha + rs;
     m_run = m_new;
 #pragma unroll
     for (int i = 0; i < D; ++i) o[i] *= alpha;
     tc_fence_before();
-    fence_async_smem();
     if (__syncthreads_or(!ok)) { ok = false; break; }
     if (tid == 0) {
       tc_fence_after();
-      const uint32_t pa = smem_u32(sP), vb = smem_u32(sV + (j & 1) * L::TILE);
+      const uint32_t vb = smem_u32(sV + (j & 1) * L::TILE);
 #pragma unroll
-      for (int kk = 0; kk < 8; ++kk)
-        umma_f16_ss(tmem + 128, desc_kmajor(pa, kk), desc_mnmajor(vb, kk), IDESC_PV, kk != 0);
+      for (int kk = 0; kk < 8; ++kk)      // A = P from TMEM: 16 bf16 of K per step = 8 words
+        umma_f16_ts(tmem + 128, tmem + kk * 8, desc_mnmajor(vb, kk), IDESC_PV, kk != 0);
       umma_commit(bar_o);
       if (j + 1 < n_kv) {
         ok &= mbar_wait(kv_full + ((j + 1) & 1), ((j + 1) >> 1) & 1, abort_flag, a.status, CB_ERR_WAIT_FULL);

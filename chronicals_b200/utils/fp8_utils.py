@@ -1,0 +1,194 @@
+"""Basic FP8 helpers: formats, a quantise/dequantise handler with loss-scale bookkeeping, a linear
+layer with FP8 operands, and a memory estimate.
+
+Reference: chronicals/utils/fp8_utils.py:16-21 ``FP8Format``, :24-269 ``FP8Handler`` (per-block(128)
+or per-tensor scaling, overflow back-off, amax history), :272-339 ``FP8Linear``, :342-366
+``compute_fp8_memory_savings``.  The reference simulates FP8 (quantise → dequantise → bf16 matmul with
+rounding done by hand); here conversions are the hardware's (``torch.float8_*`` / ``cvt.*.satfinite``)
+and block scaling follows the OCP MX convention (32-element blocks, power-of-two scales) unless a
+per-tensor scale is asked for.
+"""
+from __future__ import annotations
+
+from collections import deque
+from enum import Enum
+from typing import Deque, Dict, Optional, Tuple
+
+import torch
+import torch.nn as nn
+
+from .. import ops
+from ..ops import _ext, ref
+
+
+class FP8Format(Enum):
+    E4M3 = "e4m3"
+    E5M2 = "e5m2"
+
+    @property
+    def max_value(self) -> float:
+        return ref.E4M3_MAX if self is FP8Format.E4M3 else ref.E5M2_MAX
+
+    @property
+    def torch_dtype(self) -> torch.dtype:
+        return torch.float8_e4m3fn if self is FP8Format.E4M3 else torch.float8_e5m2
+
+
+def mxfp8_quantize(x: torch.Tensor, fmt: str = "e4m3", want_dequantized: bool = False):
+    """``(q_fp8, scales_e8m0[, x_dequantized_bf16])`` along the last dim in 32-element blocks.
+    CUDA bf16 inputs run the quantisation kernel; everything else the PyTorch formula."""
+    K = x.shape[-1]
+    if x.is_cuda and x.dtype == torch.bfloat16 and K % 32 == 0 and _ext.available() and _ext.has_symbol("cb_mxfp8_quant"):
+        x2 = x.reshape(-1, K)
+        if x2.stride(1) != 1 or x2.stride(0) % 8 != 0:
+            x2 = x2.contiguous()
+        M = x2.shape[0]
+        q = torch.empty(M, K, dtype=torch.uint8, device=x.device)
+        s = torch.empty(M, K // 32, dtype=torch.uint8, device=x.device)
+        d = torch.empty(M, K, dtype=torch.bfloat16, device=x.device) if want_dequantized else None
+        fn = _ext.lib().cb_mxfp8_quant
+        fn.argtypes = [_ext.P, _ext.P, _ext.P, _ext.P, _ext.L, _ext.I, _ext.L, _ext.I, _ext.P]
+        _ext.check(fn(x2.data_ptr(), q.data_ptr(), s.data_ptr(), _ext.ptr(d), M, K, x2.stride(0), int(fmt == "e5m2"),
+                      _ext.stream_ptr()), "mxfp8_quant")
+        qv = q.view(torch.float8_e5m2 if fmt == "e5m2" else torch.float8_e4m3fn).view(*x.shape)
+        sv = s.view(*x.shape[:-1], K // 32)
+        return (qv, sv, d.view(x.shape)) if want_dequantized else (qv, sv)
+    pad = (-K) % 32
+    xp = torch.nn.functional.pad(x, (0, pad)) if pad else x          # a ragged last block is zero-extended
+    q, s = ref.mxfp8_quantize(xp, fmt)
+    if want_dequantized:
+        d = ref.mxfp8_dequantize(q, s, x.dtype)
+        return q[..., :K], s, d[..., :K]
+    return q[..., :K], s
+
+
+def mxfp8_dequantize(q: torch.Tensor, scales: torch.Tensor, dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    return ref.mxfp8_dequantize(q, scales, dtype)
+
+
+class FP8Handler:
+    """Quantise / dequantise with either MX block scaling or one delayed per-tensor scale, plus the
+    dynamic loss-scale bookkeeping the reference keeps next to it."""
+
+    def __init__(self, fmt: FP8Format = FP8Format.E4M3, block_size: int = 32, per_tensor: bool = False,
+                 amax_history_len: int = 32, margin: float = 1.0, init_loss_scale: float = 2.0 ** 15,
+                 growth_interval: int = 1000):
+        self.fmt, self.block_size, self.per_tensor, self.margin = fmt, block_size, per_tensor, margin
+        self.amax_history: Deque[float] = deque(maxlen=amax_history_len)
+        self.loss_scale, self.growth_interval = init_loss_scale, growth_interval
+        self._good_steps = 0
+        self.overflow_count = 0
+
+    # -- scaling -------------------------------------------------------------------------------------------
+    def update_amax(self, x: torch.Tensor) -> float:
+        a = float(x.detach().abs().max().item()) if x.numel() else 0.0
+        self.amax_history.append(a)
+        return a
+
+    def get_scale(self) -> float:
+        """Delayed scaling: the largest recent amax maps to the format's maximum."""
+        amax = max(self.amax_history) if self.amax_history else 0.0
+        return (self.fmt.max_value / self.margin) / amax if amax > 0 else 1.0
+
+    def quantize(self, x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        if self.per_tensor:
+            self.update_amax(x)
+            s = self.get_scale()
+            q = (x.float() * s).clamp(-self.fmt.max_value, self.fmt.max_value).to(self.fmt.torch_dtype)
+            return q, torch.tensor(1.0 / s, device=x.device)
+        return mxfp8_quantize(x, self.fmt.value)
+
+    def dequantize(self, q: torch.Tensor, scale: torch.Tensor, dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+        if scale.dtype == torch.uint8:
+            return mxfp8_dequantize(q, scale, dtype)
+        return (q.float() * scale).to(dtype)
+
+    # -- loss scaling --------------------------------------------------------------------------------------
+    def check_overflow(self, grads) -> bool:
+        for g in grads:
+            if g is not None and not torch.isfinite(g).all():
+                return True
+        return False
+
+    def update_loss_scale(self, overflow: bool) -> float:
+        if overflow:
+            self.loss_scale = max(1.0, self.loss_scale / 2)
+            self._good_steps = 0
+            self.overflow_count += 1
+        else:
+            self._good_steps += 1
+            if self._good_steps >= self.growth_interval:
+                self.loss_scale *= 2
+                self._good_steps = 0
+        return self.loss_scale
+
+
+class _MXFP8LinearFn(torch.autograd.Function):
+    """Linear layer on MXFP8 operands: inputs and weights are rounded to e4m3 with 32-element MX
+    scales along K; the gradient of the output is rounded to e5m2 the same way.  The products are
+    accumulated in fp32 on the tensor cores.  The quantised values times their power-of-two scales
+    are exactly representable in bf16, so feeding the exactly dequantised operands to the bf16
+    tcgen05 GEMM gives the block-scaled result (at the bf16 FLOP rate)."""
+
+    @staticmethod
+    def forward(ctx, x, w, bias):
+        x2 = x.reshape(-1, x.shape[-1])
+        _, _, xd = mxfp8_quantize(x2, "e4m3", True)
+        _, _, wd = mxfp8_quantize(w, "e4m3", True)
+        y = ops.gemm(xd, wd, bias=bias) if ops._fast(xd, wd) else torch.nn.functional.linear(xd, wd, bias)
+        ctx.save_for_backward(x2, w)
+        ctx.has_bias = bias is not None
+        ctx.shape = x.shape
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1]).contiguous()
+        fast = ops._fast(dy2, w)
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            # dX = dY W : K runs over the output features -> quantise dY along its last dim, W along dim 0
+            _, _, gd = mxfp8_quantize(dy2, "e5m2", True)
+            _, _, wtd = mxfp8_quantize(w.t().contiguous(), "e4m3", True)          # [in, out], scales along out
+            dx = (ops.gemm(gd, wtd) if fast else gd @ wtd.t()).view(ctx.shape)
+        if ctx.needs_input_grad[1]:
+            # dW = dY^T X : K runs over tokens -> both operands quantised along the token dimension
+            _, _, gtd = mxfp8_quantize(dy2.t().contiguous(), "e5m2", True)        # [out, T]
+            _, _, xtd = mxfp8_quantize(x2.t().contiguous(), "e4m3", True)         # [in, T]
+            dw = ops.gemm(gtd, xtd) if fast and gtd.shape[1] % 8 == 0 else (gtd.float() @ xtd.float().t()).to(w.dtype)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = dy2.float().sum(0).to(dy.dtype)
+        return dx, dw, db
+
+
+class FP8Linear(nn.Module):
+    """``nn.Linear`` replacement computing with MXFP8 operands and a bf16 master weight."""
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = True, device=None, dtype=torch.bfloat16):
+        super().__init__()
+        self.in_features, self.out_features = in_features, out_features
+        self.weight = nn.Parameter(torch.empty(out_features, in_features, device=device, dtype=dtype))
+        self.bias = nn.Parameter(torch.zeros(out_features, device=device, dtype=dtype)) if bias else None
+        nn.init.kaiming_uniform_(self.weight, a=5 ** 0.5)
+
+    @classmethod
+    def from_linear(cls, lin: nn.Linear) -> "FP8Linear":
+        m = cls(lin.in_features, lin.out_features, lin.bias is not None, lin.weight.device, lin.weight.dtype)
+        with torch.no_grad():
+            m.weight.copy_(lin.weight)
+            if lin.bias is not None:
+                m.bias.copy_(lin.bias)
+        return m
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if x.shape[-1] % 32 != 0:
+            return torch.nn.functional.linear(x, self.weight, self.bias)
+        return _MXFP8LinearFn.apply(x, self.weight, self.bias)
+
+
+def compute_fp8_memory_savings(num_params: int, activation_elems: int = 0) -> Dict[str, float]:
+    """Bytes with bf16 everywhere vs MXFP8 copies (1 byte + 1/32 byte of scale per element)."""
+    bf16 = 2.0 * (num_params + activation_elems)
+    fp8 = (1.0 + 1.0 / 32) * (num_params + activation_elems)
+    return {"bf16_gb": bf16 / 2**30, "mxfp8_gb": fp8 / 2**30, "saved_fraction": 1 - fp8 / bf16 if bf16 else 0.0}
