@@ -113,7 +113,9 @@ class ChronicalsTrainer:
         self._active_optimizations: Dict[str, bool] = {}
         # distributed context (initialised by the launcher / parallel.bootstrap)
         import torch.distributed as dist
-        self.dist = dist if dist.is_available() and dist.is_initialized() else None
+        # ``args.use_distributed = False`` keeps a trainer single-process inside a multi-rank job
+        self.dist = dist if (dist.is_available() and dist.is_initialized()
+                             and self._get("use_distributed", True)) else None
         self.rank = self.dist.get_rank() if self.dist else 0
         self.world_size = self.dist.get_world_size() if self.dist else 1
         if torch.cuda.is_available():

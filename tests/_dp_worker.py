@@ -38,8 +38,9 @@ def main():
         # single-process oracle on the concatenated batch (no process group used by this trainer)
         full = [{"input_ids": ids[s, :, :-1].contiguous(), "labels": ids[s, :, 1:].contiguous()} for s in range(steps)]
         m2 = build_model(cfg, dtype=torch.float32, seed=0)
-        t2 = ChronicalsTrainer(m2, make_args(out + ".single"), full)
-        t2.dp, t2.world_size, t2.dist = None, 1, None
+        a2 = make_args(out + ".single")
+        a2.use_distributed = False
+        t2 = ChronicalsTrainer(m2, a2, full)
         single = [h["loss"] for h in t2.train().log_history if "lr" in h]
         diff = max((p - q).abs().max().item() for p, q in zip(model.parameters(), m2.parameters()))
         with open(out, "w") as f:
