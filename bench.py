@@ -96,7 +96,7 @@ def _dist_setup():
     import torch
     sys.path.insert(0, ROOT)
     from chronicals_b200.parallel.bootstrap import init_distributed
-    rank, local_rank, world = init_distributed()
+    rank, local_rank, world = init_distributed(timeout_s=180.0)     # a wedged collective ends the run quickly
     if torch.cuda.is_available():
         torch.cuda.set_device(local_rank)
     return rank, local_rank, world

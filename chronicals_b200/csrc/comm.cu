@@ -255,6 +255,27 @@ int fill_table(cb::PeerTable* t, const unsigned long long* ptrs, int W) {
 
 extern "C" {
 
+// Enable loads/stores from kernels on `my_device` to memory of `peer_device` (idempotent).
+int cb_enable_peer_access(int my_device, int peer_device) {
+  int prev = 0;
+  cudaError_t e = cudaGetDevice(&prev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  e = cudaSetDevice(my_device);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  int can = 0;
+  e = cudaDeviceCanAccessPeer(&can, my_device, peer_device);
+  if (e == cudaSuccess && !can) e = cudaErrorPeerAccessUnsupported;
+  if (e == cudaSuccess) {
+    e = cudaDeviceEnablePeerAccess(peer_device, 0);
+    if (e == cudaErrorPeerAccessAlreadyEnabled) {
+      cudaGetLastError();   // clear the sticky-less error state
+      e = cudaSuccess;
+    }
+  }
+  cudaSetDevice(prev);
+  return static_cast<int>(e);
+}
+
 int cb_comm_max_ranks() { return cb::MAX_RANKS; }
 int cb_comm_pad_bytes() { return (cb::MAX_RANKS + cb::MAX_RANKS * cb::PAYLOAD_FLOATS / 2) * 8; }
 int cb_comm_payload_floats() { return cb::PAYLOAD_FLOATS; }

@@ -46,6 +46,23 @@ def _lib():
     return lib
 
 
+_PEER_ENABLED = set()
+
+
+def enable_peer_access(my_device: int, peer_device: int) -> None:
+    """Let kernels running on ``my_device`` dereference pointers into ``peer_device``'s memory."""
+    if my_device == peer_device or (my_device, peer_device) in _PEER_ENABLED:
+        return
+    lib = _lib()
+    fn = lib.cb_enable_peer_access
+    fn.argtypes = [_I, _I]
+    fn.restype = ctypes.c_int
+    code = fn(my_device, peer_device)
+    if code != 0:
+        raise RuntimeError(f"cudaDeviceEnablePeerAccess({my_device} -> {peer_device}) failed with CUDA error {code}")
+    _PEER_ENABLED.add((my_device, peer_device))
+
+
 def peer_access_available(group=None) -> bool:
     """True when every pair of local GPUs can address each other's memory."""
     if not torch.cuda.is_available():
@@ -88,9 +105,12 @@ class SymmetricBuffer:
                 continue
             st = torch.UntypedStorage._new_shared_cuda(*gathered[r])
             self._peer_storages.append(st)
+            # the mapping lives on the owner's device index in this process; kernels on our device
+            # reach it through peer access, which is switched on below
             nb = self.local.numel() * self.local.element_size()
-            raw = torch.empty(0, dtype=torch.uint8, device=dev).set_(st, 0, (nb,), (1,))
+            raw = torch.empty(0, dtype=torch.uint8, device=st.device).set_(st, 0, (nb,), (1,))
             self.peers.append(raw.view(dtype))
+            enable_peer_access(dev.index, st.device.index)
         self.ptrs = (ctypes.c_ulonglong * self.world)(*[p.data_ptr() for p in self.peers])
         dist.barrier(group=group)
 

@@ -194,8 +194,9 @@ class ChronicalsTrainer:
             self.profiler = PerformanceProfiler(enabled=True)
         self.num_params = sum(p.numel() for p in self.model.parameters())
         self.flops_per_token = 6 * self.num_params
+        # with several ranks the step is captured only when it contains no NCCL call (sharded fused optimizer)
         self.use_cuda_graphs = bool(a.use_cuda_graphs) and on_gpu and self.is_native_model \
-            and a.gradient_accumulation_steps == 1
+            and a.gradient_accumulation_steps == 1 and (self.world_size == 1 or self._sharded_optimizer)
         self._active_optimizations["cuda_graphs"] = self.use_cuda_graphs
         self._log_file = None
         if self.rank == 0 and self._get("log_jsonl", True):
@@ -373,7 +374,7 @@ class ChronicalsTrainer:
         from ..ops import _ext
         launched_before = _ext.launches()
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
+        with torch.cuda.graph(graph, capture_error_mode=str(self._get("cuda_graph_capture_mode", "thread_local"))):
             loss = self._forward_loss(inp)
             loss.backward()
             if self.dp is not None:
