@@ -14,7 +14,7 @@ from chronicals_b200.parallel.bootstrap import init_distributed, shutdown
 def main():
     out = sys.argv[1]
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
-    rank, local, world = init_distributed("nccl")
+    rank, local, world = init_distributed("nccl", timeout_s=60)
     dev = torch.device("cuda", local)
     from chronicals_b200.parallel import symm
     from chronicals_b200.parallel.zero import ShardedFusedAdamW
