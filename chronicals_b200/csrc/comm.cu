@@ -15,6 +15,7 @@
 // Waits never spin unbounded: after the limit the kernel records an error in the status word and
 // returns; the host raises on the next status check.  The reference is single-GPU and has no
 // counterpart for any of this.
+#include <cstring>
 #include "common.cuh"
 
 namespace cb {
@@ -275,6 +276,44 @@ int cb_enable_peer_access(int my_device, int peer_device) {
   cudaSetDevice(prev);
   return static_cast<int>(e);
 }
+
+// ---- symmetric allocations and their CUDA IPC handles --------------------------------------------------
+// A symmetric buffer is a plain cudaMalloc block on the calling thread's current device.  Its 64-byte IPC
+// handle is exchanged on the host; a peer process opens it on ITS current device with lazy peer access, so
+// the mapping lives in the opener's own context and no context is ever created on a foreign device.
+int cb_symm_alloc(void** out, unsigned long long nbytes) {
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, nbytes);
+  if (e != cudaSuccess) { cudaGetLastError(); return static_cast<int>(e); }
+  e = cudaMemset(p, 0, nbytes);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) { cudaFree(p); return static_cast<int>(e); }
+  *out = p;
+  return 0;
+}
+
+int cb_symm_free(void* p) { return static_cast<int>(cudaFree(p)); }
+
+int cb_ipc_export(void* p, unsigned char* handle64) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) { cudaGetLastError(); return static_cast<int>(e); }
+  memcpy(handle64, &h, 64);
+  return 0;
+}
+
+int cb_ipc_open(const unsigned char* handle64, void** out) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  void* p = nullptr;
+  cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) { cudaGetLastError(); return static_cast<int>(e); }
+  *out = p;
+  return 0;
+}
+
+int cb_ipc_close(void* p) { return static_cast<int>(cudaIpcCloseMemHandle(p)); }
 
 int cb_comm_max_ranks() { return cb::MAX_RANKS; }
 int cb_comm_pad_bytes() { return (cb::MAX_RANKS + cb::MAX_RANKS * cb::PAYLOAD_FLOATS / 2) * 8; }

@@ -72,47 +72,97 @@ def peer_access_available(group=None) -> bool:
     return all(torch.cuda.can_device_access_peer(me, j) for j in range(n) if j != me)
 
 
+class _DeviceBlock:
+    """A cudaMalloc block exposed through ``__cuda_array_interface__`` so torch can alias it."""
+
+    def __init__(self, ptr: int, nbytes: int, owner: bool):
+        self.ptr, self.nbytes, self.owner = ptr, nbytes, owner
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3,
+                                         "strides": None}
+
+    def release(self) -> None:
+        if self.ptr:
+            lib = _lib()
+            (lib.cb_symm_free if self.owner else lib.cb_ipc_close)(ctypes.c_void_p(self.ptr))
+            self.ptr = 0
+
+
+def _bind_ipc(lib) -> None:
+    lib.cb_symm_alloc.argtypes = [ctypes.POINTER(ctypes.c_void_p), ctypes.c_ulonglong]
+    lib.cb_symm_free.argtypes = [ctypes.c_void_p]
+    lib.cb_ipc_export.argtypes = [ctypes.c_void_p, ctypes.c_char_p]
+    lib.cb_ipc_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p)]
+    lib.cb_ipc_close.argtypes = [ctypes.c_void_p]
+    for n in ("cb_symm_alloc", "cb_symm_free", "cb_ipc_export", "cb_ipc_open", "cb_ipc_close"):
+        getattr(lib, n).restype = ctypes.c_int
+
+
 class SymmetricBuffer:
     """A tensor present on every rank, with all peers' copies mapped locally.
 
-    ``local`` is this rank's tensor; ``peers[r]`` a tensor aliasing rank ``r``'s memory
-    (``peers[rank] is local``); ``ptrs`` a host array of the W device pointers for kernel launches.
+    ``local`` is this rank's tensor; ``ptrs`` a host array of the W device pointers for kernel
+    launches (``ptrs[rank] == local.data_ptr()``).  The block comes from ``cudaMalloc`` directly, is
+    exported as a CUDA IPC handle and opened by each peer on its own device with lazy peer access,
+    so every mapping lives in the opening rank's context.  Peer memory is only ever touched by the
+    kernels of ``csrc/comm.cu`` through ``ptrs``; it is never handed to a library kernel.
     """
 
     def __init__(self, numel: int, dtype: torch.dtype, group=None, zero: bool = True):
         if not (dist.is_available() and dist.is_initialized()):
             raise RuntimeError("SymmetricBuffer needs an initialised process group")
+        lib = _lib()
+        _bind_ipc(lib)
         self.group = group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
         dev = torch.device("cuda", torch.cuda.current_device())
-        # a dedicated cudaMalloc block (not a slice of a cached segment), so the IPC handle maps exactly this buffer
-        nbytes = numel * torch.empty((), dtype=dtype).element_size()
-        nbytes = (nbytes + (2 << 20) - 1) // (2 << 20) * (2 << 20)
-        self._raw = torch.empty(nbytes, dtype=torch.uint8, device=dev)
-        if zero:
-            self._raw.zero_()
-        self.local = self._raw[: numel * torch.empty((), dtype=dtype).element_size()].view(dtype)
-        torch.cuda.synchronize()
-        info = self._raw.untyped_storage()._share_cuda_()
-        gathered: List[object] = [None] * self.world
-        dist.all_gather_object(gathered, info, group=group)
-        self._peer_storages = []
-        self.peers: List[torch.Tensor] = []
-        for r in range(self.world):
-            if r == self.rank:
-                self.peers.append(self.local)
-                continue
-            st = torch.UntypedStorage._new_shared_cuda(*gathered[r])
-            self._peer_storages.append(st)
-            # the mapping lives on the owner's device index in this process; kernels on our device
-            # reach it through peer access, which is switched on below
-            nb = self.local.numel() * self.local.element_size()
-            raw = torch.empty(0, dtype=torch.uint8, device=st.device).set_(st, 0, (nb,), (1,))
-            self.peers.append(raw.view(dtype))
-            enable_peer_access(dev.index, st.device.index)
-        self.ptrs = (ctypes.c_ulonglong * self.world)(*[p.data_ptr() for p in self.peers])
+        esz = torch.empty((), dtype=dtype).element_size()
+        used = numel * esz
+        nbytes = max(2 << 20, (used + (2 << 20) - 1) // (2 << 20) * (2 << 20))
+        torch.cuda.synchronize(dev)
+        with torch.cuda.device(dev):
+            out = ctypes.c_void_p()
+            code = lib.cb_symm_alloc(ctypes.byref(out), nbytes)        # zero-filled
+            if code != 0:
+                raise RuntimeError(f"symmetric allocation of {nbytes} bytes failed with CUDA error {code}")
+            self._block = _DeviceBlock(out.value, nbytes, True)
+            raw = torch.as_tensor(self._block, device=dev)
+            self.local = raw[:used].view(dtype)
+            handle = ctypes.create_string_buffer(64)
+            code = lib.cb_ipc_export(ctypes.c_void_p(self._block.ptr), handle)
+            if code != 0:
+                raise RuntimeError(f"cudaIpcGetMemHandle failed with CUDA error {code}")
+            gathered: List[object] = [None] * self.world
+            dist.all_gather_object(gathered, handle.raw, group=group)
+            self._peer_blocks: List[_DeviceBlock] = []
+            ptrs = []
+            for r in range(self.world):
+                if r == self.rank:
+                    ptrs.append(self._block.ptr)
+                    continue
+                p = ctypes.c_void_p()
+                code = lib.cb_ipc_open(gathered[r], ctypes.byref(p))
+                if code != 0:
+                    raise RuntimeError(f"cudaIpcOpenMemHandle for rank {r}'s buffer failed with CUDA error {code}")
+                self._peer_blocks.append(_DeviceBlock(p.value, nbytes, False))
+                ptrs.append(p.value)
+        self.ptrs = (ctypes.c_ulonglong * self.world)(*ptrs)
         dist.barrier(group=group)
+
+    def close(self) -> None:
+        """Unmap the peers' blocks and free the local one (after a barrier, so nobody still reads it)."""
+        if getattr(self, "_block", None) is None:
+            return
+        torch.cuda.synchronize()
+        if dist.is_initialized():
+            dist.barrier(group=self.group)
+        for b in self._peer_blocks:
+            b.release()
+        if dist.is_initialized():
+            dist.barrier(group=self.group)
+        self.local = None
+        self._block.release()
+        self._block = None
 
 
 class SymmetricContext:
