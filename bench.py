@@ -190,7 +190,15 @@ def run_ours(args):
     targs.save_final = False
     targs.log_jsonl = False
     targs.parallel.dp = world
-    targs.parallel.comm_backend = args.comm
+    comm = args.comm
+    if comm == "auto":
+        # the fused peer-memory path (reduce-scatter + AdamW + all-gather kernels) when every local GPU
+        # can address every other one; NCCL all-reduce otherwise
+        comm = "nccl"
+        if world > 1:
+            from chronicals_b200.parallel.symm import peer_access_available
+            comm = "fused" if peer_access_available() else "nccl"
+    targs.parallel.comm_backend = comm
     pin = True
     batches = _host_batches(4, cfg.vocab_size, 1000 + rank, pin)
 
@@ -244,7 +252,7 @@ def run_ours(args):
                        "global_batch": MICRO_BATCH * world, "micro_batch_per_gpu": MICRO_BATCH, "seq_len": SEQ_LEN,
                        "parallelism": f"dp{world}", "optimizer": "AdamW (fp32 moments) + global-norm clip",
                        "loss": "fused linear cross-entropy (no logits)", "cuda_graph": trainer.use_cuda_graphs,
-                       "comm": args.comm if world > 1 else "none",
+                       "comm": comm if world > 1 else "none",
                        "l2": "per-step working set is several GB (>> 126 MB L2); no explicit flush"},
             "mfu_6N_vs_2250TF": 6.0 * n_params * value / (2250e12 * world),
             "clocks": clocks,
@@ -392,7 +400,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default=MODEL)
-    ap.add_argument("--comm", default="nccl", choices=["nccl", "fused"])
+    ap.add_argument("--comm", default="auto", choices=["auto", "nccl", "fused"])
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--tiny", action="store_true", help="plumbing check of the reference arm on a tiny model")
     ap.add_argument("--ref-no-compile", action="store_true")

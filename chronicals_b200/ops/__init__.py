@@ -25,6 +25,8 @@ __all__ = [
 
 def _fast(*tensors: torch.Tensor) -> bool:
     """True when the CUDA kernels handle these tensors (all CUDA + bf16)."""
+    if _ext.reference_forced():
+        return False
     for t in tensors:
         if t is None:
             continue
@@ -491,7 +493,7 @@ def cross_entropy_logits(logits: torch.Tensor, labels: torch.Tensor, ignore_inde
                          reduction: str = "mean") -> torch.Tensor:
     lg = logits.reshape(-1, logits.shape[-1])
     y = labels.reshape(-1)
-    if lg.is_cuda and lg.dtype in (torch.bfloat16, torch.float32) and lg.stride(1) == 1:
+    if lg.is_cuda and not _ext.reference_forced() and lg.dtype in (torch.bfloat16, torch.float32) and lg.stride(1) == 1:
         rows = _CELogitsFn.apply(lg, y.long().contiguous(), ignore_index, float(label_smoothing), float(z_loss_weight))
         if reduction == "none":
             return rows

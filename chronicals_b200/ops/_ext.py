@@ -56,6 +56,30 @@ def available() -> bool:
     return os.path.exists(LIB_PATH)
 
 
+_FORCE_REFERENCE = False
+
+
+class force_reference:
+    """Context manager that routes every op in ``chronicals_b200.ops`` through its plain-PyTorch
+    formula (the test oracle), also on CUDA.  Used to time or compare the library-only execution of
+    the same model; never enabled by default."""
+
+    def __enter__(self):
+        global _FORCE_REFERENCE
+        self._prev = _FORCE_REFERENCE
+        _FORCE_REFERENCE = True
+        return self
+
+    def __exit__(self, *exc):
+        global _FORCE_REFERENCE
+        _FORCE_REFERENCE = self._prev
+        return False
+
+
+def reference_forced() -> bool:
+    return _FORCE_REFERENCE
+
+
 def lib() -> ctypes.CDLL:
     """The loaded kernel library; builds it first when the sources are newer."""
     global _LIB

@@ -52,7 +52,7 @@ def attention_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqle
                      seqlens_host: Optional[Sequence[int]] = None) -> torch.Tensor:
     d = q.shape[-1]
     scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(d)
-    if q.is_cuda and q.dtype == torch.bfloat16 and _ext.available() and _ext.has_symbol("cb_attn_fwd") \
+    if q.is_cuda and not _ext.reference_forced() and q.dtype == torch.bfloat16 and _ext.available() and _ext.has_symbol("cb_attn_fwd") \
             and d in (64, 128) and causal:
         from .attention_cuda import attention_varlen_cuda
         return attention_varlen_cuda(q, k, v, cu_seqlens, max_seqlen, scale)

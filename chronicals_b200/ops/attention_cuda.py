@@ -65,7 +65,7 @@ class _AttnPackedFn(torch.autograd.Function):
 
 
 def kernel_supports(t: torch.Tensor, d: int) -> bool:
-    return (t.is_cuda and t.dtype == torch.bfloat16 and d in (64, 128) and _ext.available()
+    return (t.is_cuda and not _ext.reference_forced() and t.dtype == torch.bfloat16 and d in (64, 128) and _ext.available()
             and _ext.has_symbol("cb_attn_fwd"))
 
 
