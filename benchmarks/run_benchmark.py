@@ -227,14 +227,16 @@ def benchmark_chronicals(a, lora: bool = False, graphs: Optional[bool] = None, p
     if lora:
         from chronicals_b200.lora import apply_lora_to_model
         apply_lora_to_model(model, rank=a.lora_rank, alpha=2.0 * a.lora_rank)
-        over.update(optimizer_type="lora_plus", learning_rate=2e-4, lora_plus_lr_ratio=16.0, weight_decay=0.0)
+        over.update(optimizer_type="lora_plus", learning_rate=2e-4, weight_decay=0.0)
     n_params = sum(p.numel() for p in model.parameters())
     trainable = sum(p.numel() for p in model.parameters() if p.requires_grad)
     targs = _training_config(a, **over)
+    if lora:
+        targs.lora_plus_ratio = 16.0
     trainer = ChronicalsTrainer(model, targs, None)
     data = load_alpaca_dataloader(cfg.vocab_size, a.batch_size, a.seq_length, 4, seed=0, packed=packed)
     data = [{k: v.to(dev) for k, v in b.items()} for b in data]
-    t = _time_steps(lambda i: trainer.training_step(data[i % len(data)]), a, a.batch_size * a.seq_length)
+    t = _time_steps(lambda i: trainer.training_step(data[i % len(data)]), a, a.batch_size * a.seq_length)   # one micro-step
     name = "chronicals_lora" if lora else ("chronicals" if targs.use_cuda_graphs else "chronicals_eager")
     if packed:
         name += "_packed"
@@ -327,3 +329,153 @@ METHODS: Dict[str, Callable[[Any], BenchmarkResult]] = {
     "unsloth": _skipped("unsloth", "unsloth"),
     "liger": _skipped("liger", "liger_kernel"),
 }
+
+
+# ------------------------------------------------------------------------------------------------ micro-benchmarks
+def micro_benchmark(a) -> Dict[str, float]:
+    """Forward, backward, optimizer and full-step device times of one training step (eager, no graph)."""
+    from chronicals_b200 import ChronicalsConfig, build_model
+    from chronicals_b200.optimizers import FusedAdamW
+    dev = _device()
+    cfg = ChronicalsConfig.from_model_name(a.model)
+    model = build_model(cfg, dtype=torch.bfloat16 if dev.type == "cuda" else torch.float32, device=dev, seed=0)
+    opt = FusedAdamW(model.parameters(), lr=2e-5, weight_decay=0.01, max_grad_norm=1.0) if dev.type == "cuda" \
+        else torch.optim.AdamW(model.parameters(), lr=2e-5)
+    batch = {k: v.to(dev) for k, v in load_alpaca_dataloader(cfg.vocab_size, a.batch_size, a.seq_length, 1)[0].items()}
+    out: Dict[str, List[float]] = {"forward_ms": [], "backward_ms": [], "optimizer_ms": [], "full_step_ms": []}
+    for it in range(a.warmup_steps + a.steps):
+        with CUDATimer() as tf:
+            loss = model(batch["input_ids"], labels=batch["labels"]).loss
+        with CUDATimer() as tb:
+            loss.backward()
+        with CUDATimer() as to:
+            opt.step()
+            opt.zero_grad(set_to_none=True)
+        if it >= a.warmup_steps:
+            out["forward_ms"].append(tf.ms)
+            out["backward_ms"].append(tb.ms)
+            out["optimizer_ms"].append(to.ms)
+            out["full_step_ms"].append(tf.ms + tb.ms + to.ms)
+    return {k: statistics.fmean(v) for k, v in out.items()}
+
+
+def print_gap_analysis(results: List[BenchmarkResult], a) -> None:
+    """Where the measured step time sits against the roofline of the measured peaks."""
+    from chronicals_b200 import ChronicalsConfig
+    from chronicals_b200.config.sota_config import TheoreticalPerformance
+    cfg = ChronicalsConfig.from_model_name(a.model)
+    tp = TheoreticalPerformance(cfg, a.batch_size * a.seq_length, a.seq_length)
+    floor_ms = 1e3 * tp.floor_seconds()
+    print(f"\ngap analysis ({a.model}, {a.batch_size}x{a.seq_length} tokens/step)")
+    print(f"  roofline floor: {floor_ms:.1f} ms/step = {tp.max_tokens_per_second():,.0f} tok/s "
+          f"(GEMM+attention FLOPs at {tp.peak_tflops:.0f} TFLOP/s measured, optimizer bytes at {tp.hbm_gbs:.0f} GB/s measured)")
+    for r in results:
+        if r.status == "ok":
+            print(f"  {r.method:<22} {r.ms_per_step:8.2f} ms  = {r.ms_per_step / floor_ms:5.2f}x floor, "
+                  f"{100 * r.tokens_per_sec / TARGET_TOKENS_PER_SEC:6.0f} % of the reference's 50k tok/s target")
+
+
+def print_comparison(results: List[BenchmarkResult]) -> None:
+    ok = [r for r in results if r.status == "ok"]
+    base = next((r for r in ok if r.method == "huggingface"), None)
+    print(f"\n{'method':<22}{'tok/s':>12}{'ms/step':>10}{'MFU %':>8}{'mem GB':>8}{'loss':>9}{'vs HF':>8}")
+    for r in results:
+        if r.status != "ok":
+            print(f"{r.method:<22}{r.status:>12}  {r.reason}")
+            continue
+        rel = f"{r.tokens_per_sec / base.tokens_per_sec:7.2f}x" if base else "      -"
+        print(f"{r.method:<22}{r.tokens_per_sec:>12,.0f}{r.ms_per_step:>10.2f}{100 * r.mfu:>8.1f}{r.peak_memory_gb:>8.1f}"
+              f"{r.final_loss:>9.3f}{rel:>8}")
+    print(f"published by the reference on 1x A100-40GB: {PUBLISHED['chronicals_full_ft_a100']:,.0f} tok/s full fine-tune, "
+          f"{PUBLISHED['chronicals_lora_a100']:,.0f} tok/s LoRA; Unsloth {PUBLISHED['unsloth_full_ft_a100']:,.0f} tok/s")
+
+
+def validate_losses(results: List[BenchmarkResult], tolerance: float = 0.15) -> bool:
+    """All methods start from a random model on the same data: their losses must agree closely
+    (ln V at initialisation).  Guards against a method that skips work."""
+    losses = [r.final_loss for r in results if r.status == "ok" and r.final_loss == r.final_loss]
+    return (max(losses) - min(losses) <= tolerance * max(1.0, max(losses))) if losses else True
+
+
+def build_parser() -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser(description="chronicals_b200 benchmark suite")
+    ap.add_argument("--model", default="qwen2.5-0.5b")
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--batch_size", type=int, default=8)
+    ap.add_argument("--seq_length", type=int, default=1024)
+    ap.add_argument("--grad_accum", type=int, default=1)
+    ap.add_argument("--warmup_steps", type=int, default=5)
+    ap.add_argument("--num_runs", type=int, default=1)
+    ap.add_argument("--methods", nargs="+", default=["chronicals"], choices=sorted(METHODS))
+    ap.add_argument("--output", default=None, help="write the results as JSON to this path")
+    ap.add_argument("--gap-analysis", action="store_true")
+    ap.add_argument("--micro-benchmark", action="store_true")
+    ap.add_argument("--full-suite", action="store_true", help="run every method")
+    ap.add_argument("--auto-batch", action="store_true", help="search the largest micro-batch that fits")
+    ap.add_argument("--use-cuda-graphs", dest="use_cuda_graphs", action="store_true", default=True)
+    ap.add_argument("--no-cuda-graphs", dest="use_cuda_graphs", action="store_false")
+    ap.add_argument("--use-compile", action="store_true", help="accepted for compatibility; there is no tracing compiler here")
+    ap.add_argument("--no-compile", action="store_true", help="accepted for compatibility")
+    ap.add_argument("--lora_rank", type=int, default=16)
+    ap.add_argument("--unsloth-lora", action="store_true", help="adds the unsloth and chronicals_lora methods")
+    ap.add_argument("--unsloth-full", action="store_true", help="adds the unsloth method")
+    ap.add_argument("--fair-compare", action="store_true", help="same data, same optimizer settings, loss validation")
+    ap.add_argument("--target-throughput", type=float, default=TARGET_TOKENS_PER_SEC)
+    ap.add_argument("--validate", action="store_true", help="check that all methods agree on the loss")
+    return ap
+
+
+def main(argv: Optional[List[str]] = None) -> int:
+    a = build_parser().parse_args(argv)
+    methods = sorted(METHODS) if a.full_suite else list(a.methods)
+    if a.unsloth_lora:
+        methods += [m for m in ("chronicals_lora", "unsloth") if m not in methods]
+    if a.unsloth_full and "unsloth" not in methods:
+        methods.append("unsloth")
+    if a.auto_batch and torch.cuda.is_available():
+        def one(b):
+            saved, a.batch_size = a.batch_size, b
+            try:
+                saved_steps, saved_w = a.steps, a.warmup_steps
+                a.steps, a.warmup_steps = 1, 0
+                benchmark_chronicals(a, graphs=False)
+                a.steps, a.warmup_steps = saved_steps, saved_w
+            finally:
+                a.batch_size = saved
+        a.batch_size = find_optimal_batch_size(one, start=a.batch_size)
+        print(f"auto batch size: {a.batch_size}")
+    results: List[BenchmarkResult] = []
+    for m in methods:
+        if torch.cuda.is_available():
+            torch.cuda.empty_cache()
+            torch.cuda.reset_peak_memory_stats()
+        try:
+            r = METHODS[m](a)
+        except Exception as e:                          # one failing baseline must not hide the others
+            r = BenchmarkResult(m, status="failed", reason=f"{type(e).__name__}: {e}"[:300])
+        results.append(r)
+        print(json.dumps(r.to_dict()), flush=True)
+    print_comparison(results)
+    if a.gap_analysis:
+        print_gap_analysis(results, a)
+    micro = micro_benchmark(a) if a.micro_benchmark else None
+    if micro:
+        print("\nmicro-benchmark (eager): " + ", ".join(f"{k} {v:.2f}" for k, v in micro.items()))
+    valid = validate_losses(results) if (a.validate or a.fair_compare) else None
+    if valid is not None:
+        print(f"loss agreement across methods: {'ok' if valid else 'MISMATCH'}")
+    if a.output:
+        payload = {"results": [r.to_dict() for r in results], "micro_benchmark": micro, "loss_agreement": valid,
+                   "methodology": {"timing": "CUDA events around the timed steps, after warm-up, synchronised on both sides",
+                                   "data": "synthetic seeded token ids; random-initialised weights (no network)",
+                                   "tokens_per_step": a.batch_size * a.seq_length * a.grad_accum, "steps": a.steps,
+                                   "warmup_steps": a.warmup_steps, "num_runs": a.num_runs, "dtype": "bf16",
+                                   "mfu": f"6*N*tok/s over {B200_DENSE_BF16_TFLOPS:.0f} TFLOP/s dense bf16",
+                                   "device": torch.cuda.get_device_name(0) if torch.cuda.is_available() else "cpu"}}
+        with open(a.output, "w") as f:
+            json.dump(payload, f, indent=1)
+    return 0 if (valid is None or valid) else 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,63 @@
+"""The benchmark suite and the examples run end to end on CPU with a tiny model."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _run(args, timeout=600):
+    env = dict(os.environ, PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""), CUDA_VISIBLE_DEVICES="")
+    r = subprocess.run([sys.executable, *args], cwd=ROOT, env=env, capture_output=True, text=True, timeout=timeout)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    return r.stdout
+
+
+def test_run_benchmark_suite_tiny(tmp_path):
+    out = tmp_path / "bench.json"
+    _run(["benchmarks/run_benchmark.py", "--model", "tiny-qwen2", "--steps", "2", "--warmup_steps", "1", "--batch_size", "2",
+          "--seq_length", "64", "--methods", "chronicals", "chronicals_lora", "native_pytorch", "unsloth", "--validate",
+          "--gap-analysis", "--output", str(out)])
+    data = json.loads(out.read_text())
+    by = {r["method"]: r for r in data["results"]}
+    assert by["chronicals"]["status"] == "ok" and by["chronicals"]["tokens_per_sec"] > 0
+    assert by["chronicals_lora"]["trainable_params"] < by["chronicals_lora"]["n_params"]
+    assert by["unsloth"]["status"] == "skipped"
+    assert data["loss_agreement"] is True
+    assert "CUDA events" in data["methodology"]["timing"]
+
+
+def test_benchmark_helpers():
+    sys.path.insert(0, ROOT)
+    from benchmarks.run_benchmark import MultiRunTimer, compute_mfu, load_alpaca_dataloader, synthetic_instruction_lengths
+    assert abs(compute_mfu(494_000_000, 180_000, 2250.0) - 6 * 494e6 * 180e3 / 2250e12) < 1e-9
+    t = MultiRunTimer(3).run(lambda: 2.0)
+    assert t.mean == 2.0 and t.std == 0.0 and t.best == 2.0
+    lens = synthetic_instruction_lengths(1000, seed=1, max_len=512)
+    assert min(lens) >= 8 and max(lens) <= 512
+    b = load_alpaca_dataloader(1000, 2, 64, 2, packed=True)
+    assert b and b[0]["input_ids"].shape == (1, 128) and b[0]["position_ids"].max() < 64
+
+
+def test_lora_example_trains_and_reloads(tmp_path):
+    sys.path.insert(0, ROOT)
+    from examples.lora_trainer import ChronicalsLoRATrainer, LoRAConfig, TrainerConfig, load_alpaca_dataset
+    cfg = TrainerConfig(output_dir=str(tmp_path), per_device_batch_size=2, max_seq_length=128, max_steps=4, logging_steps=100,
+                        use_cuda_graphs=False)
+    t = ChronicalsLoRATrainer("tiny-qwen2", LoRAConfig(r=4, lora_alpha=8.0), cfg, device="cpu")
+    state = t.train(load_alpaca_dataset(None, 48))
+    assert state.global_step == 4
+    out = t.save_model()
+    assert os.path.exists(os.path.join(out, "adapter_config.json"))
+    t2 = ChronicalsLoRATrainer.from_pretrained(out)
+    a = {k: v for k, v in t.model.hf_state_dict(include_lora=True).items() if "lora_B" in k}
+    b = t2.model.hf_state_dict(include_lora=True)
+    assert a and all((b[k].float().cpu() - v.float().cpu()).abs().max() < 1e-6 for k, v in a.items())
+
+
+@pytest.mark.parametrize("script", ["examples/quickstart_lora.py"])
+def test_quickstart_runs(script):
+    assert "done:" in _run([script])
