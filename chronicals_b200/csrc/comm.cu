@@ -27,15 +27,6 @@ struct PeerTable {
   void* ptr[MAX_RANKS];
 };
 
-__device__ __forceinline__ void st_release_sys_u64(unsigned long long* p, unsigned long long v) {
-  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
-}
-__device__ __forceinline__ unsigned long long ld_acquire_sys_u64(const unsigned long long* p) {
-  unsigned long long v;
-  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
-  return v;
-}
-
 // Flag pad layout per rank: [0, W) u64 epoch flags written by rank r into slot r;
 // [MAX_RANKS, MAX_RANKS + W * PAYLOAD) fp32 payload slots (as u64 words: 2 floats each).
 constexpr int PAYLOAD_FLOATS = 4;
@@ -235,6 +226,139 @@ allreduce_pull_kernel(PeerTable bufs, int W, long long n, float scale, bf16* __r
   }
 }
 
+
+// ------------------------------------------------------------------------------------------------------
+// Tensor/sequence parallel: all-gather by push, fused with the producing RMSNorm.
+//
+// y[row] = x[row] * rstd(row) * (offset + w)   (or y = x when `w` is null) for this rank's `rows` rows, stored
+// into EVERY rank's gather buffer at row (my_rank * rows + row).  When the last block has finished, the
+// kernel advances a device-resident epoch and writes it into flag slot `my_rank` of every rank's flag
+// array; a consumer on rank r waits for flags[src] >= epoch before it reads panel src.  Rows have N
+// elements (N % 8 == 0, N <= 8192).  One block handles one row at a time, values stay in registers.
+__global__ void __launch_bounds__(COMM_THREADS)
+rmsnorm_push_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, PeerTable dst, PeerTable flags, int W,
+                    int my_rank, int rows, int N, long long ld_dst, float eps, float offset, float* __restrict__ rstd_out,
+                    unsigned long long* __restrict__ epoch_ctr, unsigned int* __restrict__ done_ctr, int* status) {
+  __shared__ float sred[COMM_THREADS / 32];
+  __shared__ float s_rstd;
+  __shared__ unsigned int s_last;
+  const int nchunk = N >> 3;
+  if (status[0] == 0) {
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+      uint4 v[4];
+      float sq = 0.f;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int c = threadIdx.x + k * COMM_THREADS;
+        if (c < nchunk) {
+          v[k] = *reinterpret_cast<const uint4*>(x + static_cast<long long>(row) * N + (c << 3));
+          if (w != nullptr) {
+            const float2 a = unpack_bf16x2(v[k].x), b = unpack_bf16x2(v[k].y), c2 = unpack_bf16x2(v[k].z), d = unpack_bf16x2(v[k].w);
+            sq += a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y + c2.x * c2.x + c2.y * c2.y + d.x * d.x + d.y * d.y;
+          }
+        }
+      }
+      if (w != nullptr) {
+        sq = warp_sum(sq);
+        if ((threadIdx.x & 31) == 0) sred[threadIdx.x >> 5] = sq;
+        __syncthreads();
+        if (threadIdx.x < 32) {
+          float t = threadIdx.x < COMM_THREADS / 32 ? sred[threadIdx.x] : 0.f;
+          t = warp_sum(t);
+          if (threadIdx.x == 0) {
+            s_rstd = rsqrtf(t / static_cast<float>(N) + eps);
+            if (rstd_out != nullptr) rstd_out[row] = s_rstd;
+          }
+        }
+        __syncthreads();
+        const float rs = s_rstd;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int c = threadIdx.x + k * COMM_THREADS;
+          if (c < nchunk) {
+            const uint4 wu = *reinterpret_cast<const uint4*>(w + (c << 3));
+            const float2 a = unpack_bf16x2(v[k].x), b = unpack_bf16x2(v[k].y), c2 = unpack_bf16x2(v[k].z), d = unpack_bf16x2(v[k].w);
+            const float2 wa = unpack_bf16x2(wu.x), wb = unpack_bf16x2(wu.y), wc = unpack_bf16x2(wu.z), wd = unpack_bf16x2(wu.w);
+            v[k].x = pack_bf16x2(a.x * rs * (offset + wa.x), a.y * rs * (offset + wa.y));
+            v[k].y = pack_bf16x2(b.x * rs * (offset + wb.x), b.y * rs * (offset + wb.y));
+            v[k].z = pack_bf16x2(c2.x * rs * (offset + wc.x), c2.y * rs * (offset + wc.y));
+            v[k].w = pack_bf16x2(d.x * rs * (offset + wd.x), d.y * rs * (offset + wd.y));
+          }
+        }
+      }
+      const long long drow = static_cast<long long>(my_rank) * rows + row;
+      for (int r = 0; r < W; ++r) {
+        bf16* out = static_cast<bf16*>(dst.ptr[(my_rank + r) % W]) + drow * ld_dst;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int c = threadIdx.x + k * COMM_THREADS;
+          if (c < nchunk) *reinterpret_cast<uint4*>(out + (c << 3)) = v[k];
+        }
+      }
+    }
+  }
+  // completion: every block fences its stores system-wide and takes a ticket; the last one publishes
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int ticket = atomicAdd(done_ctr, 1u);
+    s_last = (ticket == gridDim.x - 1) ? 1u : 0u;
+  }
+  __syncthreads();
+  if (s_last) {
+    __threadfence_system();
+    __shared__ unsigned long long s_epoch;
+    if (threadIdx.x == 0) {
+      *done_ctr = 0u;
+      s_epoch = *epoch_ctr + 1ull;
+      *epoch_ctr = s_epoch;
+    }
+    __syncthreads();
+    if (threadIdx.x < W && status[0] == 0)
+      st_release_sys_u64(static_cast<unsigned long long*>(flags.ptr[threadIdx.x]) + my_rank, s_epoch);
+  }
+}
+
+// out[i] = residual[i] + sum_s stage[s * n + i]  (bf16, fp32 accumulation; n % 8 == 0) — the local half of a
+// reduce-scatter whose partial tiles were stored into `stage` by the peers' GEMM epilogues.
+__global__ void __launch_bounds__(COMM_THREADS)
+reduce_partials_kernel(const bf16* __restrict__ stage, const bf16* __restrict__ residual, bf16* __restrict__ out, int W,
+                       long long n, int* status) {
+  if (status[0] != 0) return;
+  const long long nvec = n >> 3;
+  for (long long v = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; v < nvec;
+       v += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (residual != nullptr) acc_bf16x8(*reinterpret_cast<const uint4*>(residual + (v << 3)), a);
+    for (int s = 0; s < W; ++s) acc_bf16x8(*reinterpret_cast<const uint4*>(stage + s * n + (v << 3)), a);
+    uint4 o;
+    o.x = pack_bf16x2(a[0], a[1]); o.y = pack_bf16x2(a[2], a[3]);
+    o.z = pack_bf16x2(a[4], a[5]); o.w = pack_bf16x2(a[6], a[7]);
+    *reinterpret_cast<uint4*>(out + (v << 3)) = o;
+  }
+}
+
+// Vocab-parallel cross-entropy combine by peer loads: bufs[r] holds rank r's [2, T] floats
+// (log-sum-exp over its vocabulary shard, target logit if the label is in its shard else 0).
+__global__ void vp_combine_kernel(PeerTable bufs, int W, int T, float* __restrict__ lse_out, float* __restrict__ tgt_out,
+                                  int* status) {
+  if (status[0] != 0) return;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= T) return;
+  float m = -INFINITY, tg = 0.f;
+  float l[MAX_RANKS];
+  for (int r = 0; r < W; ++r) {
+    const float* b = static_cast<const float*>(bufs.ptr[r]);
+    l[r] = b[i];
+    tg += b[T + i];
+    m = fmaxf(m, l[r]);
+  }
+  float s = 0.f;
+  for (int r = 0; r < W; ++r) s += __expf(l[r] - m);
+  lse_out[i] = m + __logf(s);
+  tgt_out[i] = tg;
+}
+
 }  // namespace cb
 
 namespace {
@@ -361,6 +485,40 @@ int cb_allreduce_pull(const unsigned long long* bufs, int W, long long n, float 
   if (fill_table(&t, bufs, W) || n % 8 != 0) return -1;
   cb::allreduce_pull_kernel<<<cb_comm_grid(), cb::COMM_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
       t, W, n, scale, static_cast<cb::bf16*>(out), status);
+  return static_cast<int>(cudaGetLastError());
+}
+
+
+// Tensor/sequence parallel push all-gather (optionally fused with RMSNorm when w != null).
+// dst / flags: host arrays of W device addresses (every rank's gather buffer and flag array).
+int cb_rmsnorm_push(const void* x, const void* w, const unsigned long long* dst, const unsigned long long* flags, int W,
+                    int my_rank, int rows, int N, long long ld_dst, float eps, float offset, float* rstd_out,
+                    unsigned long long* epoch_ctr, unsigned int* done_ctr, int* status, void* stream) {
+  if (rows <= 0 || N <= 0 || N % 8 != 0 || N > 8 * 4 * cb::COMM_THREADS || ld_dst % 8 != 0) return -1;
+  cb::PeerTable d, f;
+  if (fill_table(&d, dst, W) || fill_table(&f, flags, W)) return -2;
+  int grid = comm_sms() * 4;
+  if (grid > rows) grid = rows;
+  cb::rmsnorm_push_kernel<<<grid, cb::COMM_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const cb::bf16*>(x), static_cast<const cb::bf16*>(w), d, f, W, my_rank, rows, N, ld_dst, eps, offset,
+      rstd_out, epoch_ctr, done_ctr, status);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int cb_reduce_partials(const void* stage, const void* residual, void* out, int W, long long n, int* status, void* stream) {
+  if (n <= 0 || n % 8 != 0 || W < 1) return -1;
+  long long blocks = (n / 8 + cb::COMM_THREADS - 1) / cb::COMM_THREADS;
+  const long long cap = static_cast<long long>(comm_sms()) * 8;
+  if (blocks > cap) blocks = cap;
+  cb::reduce_partials_kernel<<<static_cast<int>(blocks), cb::COMM_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const cb::bf16*>(stage), static_cast<const cb::bf16*>(residual), static_cast<cb::bf16*>(out), W, n, status);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int cb_vp_combine(const unsigned long long* bufs, int W, int T, float* lse_out, float* tgt_out, int* status, void* stream) {
+  cb::PeerTable t;
+  if (fill_table(&t, bufs, W) || T <= 0) return -1;
+  cb::vp_combine_kernel<<<(T + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(t, W, T, lse_out, tgt_out, status);
   return static_cast<int>(cudaGetLastError());
 }
 

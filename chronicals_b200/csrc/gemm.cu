@@ -62,6 +62,19 @@ struct GemmArgs {
   int V_total;     // vocabulary size for the smoothing term
   int col_offset;  // global vocab id of column 0 of B (vocab chunk or tensor-parallel shard)
   int* status;
+  // ---- tensor-parallel fusion (all zero for ordinary GEMMs)
+  // all-gather -> GEMM: the rows of A arrive in panels of `panel_blocks` m-blocks, one panel per source
+  // rank, pushed into local memory by the peers; flag[src] reaches *panel_epoch once panel src is complete.
+  const unsigned long long* panel_flags;
+  const unsigned long long* panel_epoch;
+  int panel_blocks;
+  int panel_self;                 // the panel this rank produced itself (never waited for)
+  int rot_blocks;                 // m-blocks are visited starting here, so every rank begins with its own panel
+  unsigned long long peer_wait_ns;
+  // GEMM -> reduce-scatter: the output rows belong to `push_blocks` m-blocks per owner rank; the epilogue
+  // stores each tile through push_c[owner] (a peer mapping, pre-offset so that the global row indexes it)
+  unsigned long long push_c[16];
+  int push_blocks;
 };
 
 template <int BLOCK_N, int STAGES>
@@ -129,10 +142,34 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       uint32_t phase = 0;
       bool ok = true;
       for (int item = blockIdx.x; item < g.num_items && ok; item += gridDim.x) {
-        const int m_blk = item % g.num_m_blocks;
+        int m_blk = item % g.num_m_blocks + g.rot_blocks;
+        if (m_blk >= g.num_m_blocks) m_blk -= g.num_m_blocks;
         const int split = item / g.num_m_blocks;
         const int nt0 = split * g.tiles_per_item;
         const int nt1 = min(nt0 + g.tiles_per_item, g.num_n_tiles);
+        if (g.panel_blocks > 0) {
+          // rows of this m-block come from rank `src`: wait (bounded) until its push kernel has signalled
+          const int src = m_blk / g.panel_blocks;
+          if (src != g.panel_self) {
+            const unsigned long long want = *g.panel_epoch;
+            const uint64_t t0 = globaltimer_ns();
+            while (ld_acquire_sys_u64(g.panel_flags + src) < want) {
+              if (*abort_flag) { ok = false; break; }
+              if (globaltimer_ns() - t0 > g.peer_wait_ns) {
+                *abort_flag = 1;
+                atomicCAS(g.status, 0, CB_ERR_WAIT_PEER);
+                g.status[1] = src;
+                g.status[2] = blockIdx.x;
+                __threadfence();
+                ok = false;
+                break;
+              }
+              __nanosleep(128);
+            }
+            if (!ok) break;
+            fence_proxy_async_all();   // the peer's generic-proxy stores are read by TMA (async proxy) below
+          }
+        }
         for (int nt = nt0; nt < nt1 && ok; ++nt) {
           for (int kb = 0; kb < num_kb; ++kb) {
             if (!mbar_wait(empty + stage, phase ^ 1, abort_flag, g.status, CB_ERR_WAIT_EMPTY)) {
@@ -217,11 +254,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     uint32_t tile_cnt = 0;
     bool ok = true;
     for (int item = blockIdx.x; item < g.num_items && ok; item += gridDim.x) {
-      const int m_blk = item % g.num_m_blocks;
+      int m_blk = item % g.num_m_blocks + g.rot_blocks;
+      if (m_blk >= g.num_m_blocks) m_blk -= g.num_m_blocks;
       const int split = item / g.num_m_blocks;
       const int nt0 = split * g.tiles_per_item;
       const int nt1 = min(nt0 + g.tiles_per_item, g.num_n_tiles);
       const int row = m_blk * BLOCK_M + row_in_tile;
+      // reduce-scatter epilogue: this m-block's rows live on rank m_blk / push_blocks
+      bf16* push_base = g.push_blocks > 0 ? reinterpret_cast<bf16*>(g.push_c[m_blk / g.push_blocks]) : nullptr;
       const bool row_ok = row < g.M;
 
       // per-row state of the cut-cross-entropy epilogues
@@ -323,7 +363,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
               }
             }
             // the buffer written two stores ago must have been read out by its TMA store
-            if (lane == 0) tma_store_wait_read<1>();
+            if (push_base == nullptr && lane == 0) tma_store_wait_read<1>();
             __syncwarp();
             uint8_t* dstrow = stg + buf * 4096 + lane * 128;
             if (g.out_fp32) {
@@ -343,11 +383,28 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 *reinterpret_cast<uint4*>(dstrow + ((cc ^ (lane & 7)) << 4)) = u;
               }
             }
+            if (push_base != nullptr) {
+              // peer destination: plain 16-byte stores, 8 lanes per 128-byte row segment (full lines on the wire)
+              __syncwarp();
+              const int chunk = lane & 7;
+              const int ccol = colbase + chunk * 8;
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const int rr = (lane >> 3) + 4 * i;
+                const int grow = row0w + rr;
+                if (grow < g.M && ccol < g.N) {
+                  const uint4 u = *reinterpret_cast<const uint4*>(stg + buf * 4096 + rr * 128 + ((chunk ^ (rr & 7)) << 4));
+                  *reinterpret_cast<uint4*>(push_base + static_cast<long long>(grow) * g.ldc + ccol) = u;
+                }
+              }
+              __syncwarp();
+            } else {
             fence_async_smem();
             __syncwarp();
             if (lane == 0 && row0w < g.M) {          // a box that starts past the last row has nothing to write
               tma_store_2d(&tmC, stg + buf * 4096, colbase, row0w);
               tma_store_commit();
+            }
             }
             buf ^= 1;
           }
@@ -681,6 +738,59 @@ int cb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, const 
   CUtensorMap tc;
   e = build_out_map(&tc, &g.tma_store, C, M, N, ldc, out_fp32);
   if (e) return e;
+  return dispatch<cb::EPI_STORE>(bn, a_mn, b_mn, ta, tb, tc, g, static_cast<cudaStream_t>(stream));
+}
+
+// Tensor-parallel variants of cb_gemm_bf16 (bf16 output, no addend / accumulate).
+//  * panel_rows > 0 (all-gather -> GEMM): A's rows arrive in W panels of panel_rows rows pushed by the peers;
+//    panel_flags[src] (local, u64) reaches *panel_epoch when panel src is complete.  The kernel starts with
+//    this rank's own panel and waits (bounded by wait_ns) per panel while the others are still in flight.
+//  * push_rows > 0 (GEMM -> reduce-scatter): output rows [o * push_rows, (o + 1) * push_rows) are stored
+//    through push_ptrs[o] (peer mappings, host array of W addresses, pre-offset so that the global row
+//    number indexes them with pitch ldc); C is ignored.
+// panel_rows and push_rows must be multiples of 128; with push, N and ldc must be multiples of 8.
+int cb_gemm_bf16_tp(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, long long lda,
+                    long long ldb, long long ldc, int a_mn, int b_mn, int force_block_n,
+                    const unsigned long long* panel_flags, const unsigned long long* panel_epoch, int panel_rows,
+                    const unsigned long long* push_ptrs, int push_rows, int W, int my_rank,
+                    unsigned long long wait_ns, int* status, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || W < 1 || W > 16 || my_rank < 0 || my_rank >= W) return -1;
+  if (panel_rows < 0 || push_rows < 0 || panel_rows % 128 != 0 || push_rows % 128 != 0) return -2;
+  if (panel_rows > 0 && (panel_flags == nullptr || panel_epoch == nullptr || panel_rows * W < M)) return -3;
+  if (push_rows > 0 && (push_ptrs == nullptr || push_rows * W < M || N % 8 != 0 || ldc % 8 != 0)) return -4;
+  const int bn = pick_block_n(M, N, force_block_n);
+  CUtensorMap ta, tb;
+  int e = build_maps(&ta, &tb, A, B, M, N, K, lda, ldb, a_mn, b_mn, bn);
+  if (e) return e;
+  cb::GemmArgs g = {};
+  g.M = M; g.N = N; g.K = K;
+  g.num_m_blocks = (M + 127) / 128;
+  g.num_n_tiles = (N + bn - 1) / bn;
+  g.tiles_per_item = 1;
+  g.num_items = g.num_m_blocks * g.num_n_tiles;
+  g.C = C; g.ldc = ldc;
+  g.bias = static_cast<const cb::bf16*>(bias);
+  g.status = status;
+  g.peer_wait_ns = wait_ns;
+  CUtensorMap tc;
+  memset(&tc, 0, sizeof(tc));
+  if (panel_rows > 0) {
+    g.panel_flags = panel_flags;
+    g.panel_epoch = panel_epoch;
+    g.panel_blocks = panel_rows / 128;
+    g.panel_self = my_rank;
+    g.rot_blocks = (my_rank * g.panel_blocks) % g.num_m_blocks;
+  }
+  if (push_rows > 0) {
+    g.push_blocks = push_rows / 128;
+    for (int i = 0; i < W; ++i) g.push_c[i] = push_ptrs[i];
+    g.rot_blocks = (my_rank * g.push_blocks) % g.num_m_blocks;
+    g.tma_store = 1;           // staged epilogue; the tile leaves shared memory by plain stores to the peer
+    g.C = nullptr;
+  } else {
+    e = build_out_map(&tc, &g.tma_store, C, M, N, ldc, 0);
+    if (e) return e;
+  }
   return dispatch<cb::EPI_STORE>(bn, a_mn, b_mn, ta, tb, tc, g, static_cast<cudaStream_t>(stream));
 }
 

@@ -11,11 +11,11 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _run_worker(tmp_path, world, script="_zero_worker.py", port=29541):
+def _run_worker(tmp_path, world, script="_zero_worker.py", port=29541, extra=()):
     out = os.path.join(str(tmp_path), "res.json")
     env = dict(os.environ, PYTHONPATH=ROOT, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
-           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", script), out]
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", script), out, *extra]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=240)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     return json.load(open(out))
@@ -30,3 +30,14 @@ def test_symmetric_barrier_sharded_adamw_and_bounded_wait(tmp_path):
     assert abs(res["norm"][0] - res["norm"][1]) < 2e-2 * max(1.0, res["norm"][0])
     assert res["ranks_identical"]
     assert res.get("timeout_detected") is True
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("backend,port", [("nccl", 29543), ("fused", 29544)])
+def test_tensor_parallel_matches_single_gpu(tmp_path, backend, port):
+    """TP=2 with sequence parallelism and the vocab-parallel loss against the unsharded model on one GPU;
+    ``fused`` runs the push all-gather, the panel-waiting GEMM and the GEMM with the reduce-scatter epilogue."""
+    res = _run_worker(tmp_path, 2, "_tp_worker.py", port, extra=(backend, "untied"))
+    assert max(abs(a - b) for a, b in zip(res["loss_tp"], res["loss_full"])) < 3e-2, res
+    assert res["grad_rel_err_max"] < 6e-2, res
+    assert res["state_dict_ok"], res
