@@ -317,7 +317,8 @@ class TensorParallelCausalLM(nn.Module):
             self.lm_head_weight = nn.Parameter(_rows(full.lm_head.weight, self.v0, self.v0 + self.vs))
         self.embed_scale = full.embed_scale
         self.z_loss_weight = full.z_loss_weight
-        self._full_rope = full
+        self._rope_len = 0
+        self._rope_cache: Tuple[Optional[torch.Tensor], Optional[torch.Tensor]] = (None, None)
         for name, p in self.named_parameters():
             # norm weights and the embedding table are replicated: every rank applies them to its own tokens
             if name.endswith("norm_weight") or name.startswith("embed_tokens"):
@@ -326,6 +327,39 @@ class TensorParallelCausalLM(nn.Module):
     @classmethod
     def from_full(cls, full, tp: TPState) -> "TensorParallelCausalLM":
         return cls(full, tp)
+
+    @classmethod
+    def from_config(cls, cfg, tp: TPState, dtype=torch.bfloat16, device=None, seed: int = 0, std: float = 0.02
+                    ) -> "TensorParallelCausalLM":
+        """Random-initialised shards built without ever holding the full model (the full layout exists only
+        on the meta device).  Replicated parameters get the same values on every rank; shards differ."""
+        from ..models.decoder import CausalLM
+        with torch.device("meta"):
+            full = CausalLM(cfg, dtype=dtype)
+        model = cls(full, tp).to_empty(device=device)
+        shared = torch.Generator(device="cpu").manual_seed(seed)
+        own = torch.Generator(device="cpu").manual_seed(seed * 1000 + 17 + tp.rank)
+        with torch.no_grad():
+            for name, p in model.named_parameters():
+                replicated = getattr(p, REPLICATED_MARK, False) or name.endswith("norm_weight") or name.startswith("embed_tokens")
+                if name.endswith("norm_weight"):
+                    p.fill_(1.0 if model.norm_offset == 0.0 else 0.0)
+                elif name.endswith("bias"):
+                    p.zero_()
+                else:
+                    g = shared if replicated else own
+                    p.copy_(torch.empty(p.shape, dtype=torch.float32).normal_(0.0, std, generator=g).to(p.dtype))
+                if replicated:
+                    setattr(p, REPLICATED_MARK, True)
+        return model
+
+    def _rope(self, need: int, device) -> Tuple[torch.Tensor, torch.Tensor]:
+        cos, sin = self._rope_cache
+        if cos is None or need > self._rope_len or cos.device != torch.device(device):
+            n = max(need, min(self.config.max_position_embeddings, 1 << 16), 16)
+            cos, sin = ref.rope_cache(n, self.config.head_dim, self.config.rope_theta, self.config.rope_scaling, device)
+            self._rope_cache, self._rope_len = (cos.contiguous(), sin.contiguous()), n
+        return self._rope_cache
 
     def replicated_parameters(self) -> List[nn.Parameter]:
         return [p for p in self.parameters() if getattr(p, REPLICATED_MARK, False)]
@@ -355,7 +389,7 @@ class TensorParallelCausalLM(nn.Module):
         if position_ids is None:
             position_ids = torch.arange(S, device=dev).repeat(B) if derived else _positions_from_cu(cu_seqlens, T)
         pos = position_ids.reshape(T)
-        cos, sin = self._full_rope._rope(max(int(max_seqlen or S), 1), dev)
+        cos, sin = self._rope(max(int(max_seqlen or S), 1), dev)
         Tl = T // tp.world
         mine = slice(tp.rank * Tl, (tp.rank + 1) * Tl)
         x = ops.embedding(ids[mine].contiguous(), self.embed_tokens.weight)
