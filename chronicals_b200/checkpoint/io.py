@@ -42,10 +42,13 @@ def _model_hf_state(model) -> Dict[str, torch.Tensor]:
     return {k: v.detach() for k, v in model.state_dict().items()}
 
 
-def save_model(model, out_dir: str, max_shard_bytes: int = MAX_SHARD_BYTES, safe: bool = True) -> List[str]:
-    """Write weights (+``config.json`` when the model carries a config). Returns written file names."""
+def save_model(model, out_dir: str, max_shard_bytes: int = MAX_SHARD_BYTES, safe: bool = True,
+               state: Optional[Dict[str, torch.Tensor]] = None) -> List[str]:
+    """Write weights (+``config.json`` when the model carries a config). Returns written file names.
+    ``state`` overrides the model's own state dict (used for models whose full state has to be gathered
+    from several ranks first)."""
     os.makedirs(out_dir, exist_ok=True)
-    sd = {k: v.detach().to("cpu").contiguous().clone() for k, v in _model_hf_state(model).items()}
+    sd = {k: v.detach().to("cpu").contiguous().clone() for k, v in (state or _model_hf_state(model)).items()}
     cfg = getattr(model, "config", None)
     if cfg is not None and hasattr(cfg, "to_hf_config"):
         with open(os.path.join(out_dir, "config.json"), "w") as f:

@@ -427,6 +427,25 @@ class TensorParallelCausalLM(nn.Module):
             o += n
 
     @torch.no_grad()
+    def clip_grad_norm_(self, max_norm: float) -> torch.Tensor:
+        """Global-norm clipping where the norm spans every rank's shards (replicated tensors counted once);
+        all ranks apply the same coefficient, so replicated parameters stay identical.  Returns the norm."""
+        sharded = [p.grad for p in self.parameters() if p.grad is not None and not getattr(p, REPLICATED_MARK, False)]
+        repl = [p.grad for p in self.replicated_parameters() if p.grad is not None]
+        dev = (sharded or repl)[0].device
+        sq = torch.zeros(1, dtype=torch.float32, device=dev)
+        if sharded:
+            sq += torch.stack([g.float().pow(2).sum() for g in sharded]).sum()
+        dist.all_reduce(sq, group=self.tp.group)
+        if repl:
+            sq += torch.stack([g.float().pow(2).sum() for g in repl]).sum()
+        norm = sq.sqrt()
+        coef = (max_norm / (norm + 1e-6)).clamp(max=1.0)
+        grads = sharded + repl
+        torch._foreach_mul_(grads, coef.squeeze(0))
+        return norm.squeeze(0)
+
+    @torch.no_grad()
     def gather_full_state_dict(self) -> "OrderedDict[str, torch.Tensor]":
         """Re-assemble HuggingFace-named full tensors on every rank (checkpoint consolidation; not hot)."""
         tp, cfg = self.tp, self.config

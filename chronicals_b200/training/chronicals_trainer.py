@@ -172,6 +172,18 @@ class ChronicalsTrainer:
             with torch.no_grad():                                  # every rank starts from rank 0's weights
                 for p in self.model.parameters():
                     self.dist.broadcast(p.data, src=0)
+        # tensor + sequence parallel: every rank keeps 1/tp of the projections and of the vocabulary and sees
+        # the same batch; only the replicated norm/embedding gradients are summed across ranks
+        self.tp_model = False
+        if a.parallel.tp > 1:
+            if a.parallel.tp != self.world_size or not self.is_native_model:
+                raise ValueError("tensor parallelism needs a native model and parallel.tp == world size "
+                                 f"(tp={a.parallel.tp}, world={self.world_size})")
+            from ..parallel.tensor_parallel import TensorParallelCausalLM, TPState
+            backend = "fused" if (a.parallel.comm_backend == "fused" and self.device.type == "cuda") else "nccl"
+            self.model = TensorParallelCausalLM.from_full(self.model, TPState(backend=backend,
+                                                                            wait_budget_us=a.parallel.wait_budget_us))
+            self.tp_model = True
         self._sharded_optimizer = False
         self._setup_optimizer()
         self.total_steps = self._estimate_total_steps()
@@ -179,7 +191,7 @@ class ChronicalsTrainer:
 
         # data-parallel gradient reduction
         self.dp = None
-        if self.world_size > 1 and not getattr(self, "_sharded_optimizer", False):
+        if self.world_size > 1 and not getattr(self, "_sharded_optimizer", False) and not self.tp_model:
             from ..parallel.data_parallel import GradientReducer
             self.dp = GradientReducer(self.model, backend=a.parallel.comm_backend, bucket_mb=a.parallel.bucket_mb)
 
@@ -196,7 +208,8 @@ class ChronicalsTrainer:
         self.flops_per_token = 6 * self.num_params
         # with several ranks the step is captured only when it contains no NCCL call (sharded fused optimizer)
         self.use_cuda_graphs = bool(a.use_cuda_graphs) and on_gpu and self.is_native_model \
-            and a.gradient_accumulation_steps == 1 and (self.world_size == 1 or self._sharded_optimizer)
+            and a.gradient_accumulation_steps == 1 and (self.world_size == 1 or self._sharded_optimizer) \
+            and not self.tp_model
         self._active_optimizations["cuda_graphs"] = self.use_cuda_graphs
         self._log_file = None
         if self.rank == 0 and self._get("log_jsonl", True):
@@ -225,7 +238,7 @@ class ChronicalsTrainer:
                 max_grad_norm=a.max_grad_norm)
             self.use_external_grad_clip = False
         elif (t == "fused_adamw" and a.use_fused_adamw and self.world_size > 1 and a.parallel.comm_backend == "fused"
-              and self.device.type == "cuda" and self._fused_comm_possible()):
+              and not getattr(self, "tp_model", False) and self.device.type == "cuda" and self._fused_comm_possible()):
             # gradient reduce-scatter, clip, AdamW and parameter all-gather as peer-memory kernels
             from ..parallel.zero import ShardedFusedAdamW
             self.optimizer = ShardedFusedAdamW([p for p in self.model.parameters() if p.requires_grad],
@@ -236,9 +249,11 @@ class ChronicalsTrainer:
             self.use_external_grad_clip = False
             self._sharded_optimizer = True
         elif t == "fused_adamw" and a.use_fused_adamw:
+            # under tensor parallelism the clip coefficient needs the norm over all ranks' shards, computed outside
             self.optimizer = FusedAdamW([p for p in self.model.parameters() if p.requires_grad], lr=a.learning_rate,
                                         betas=(a.adam_beta1, a.adam_beta2), eps=a.adam_epsilon,
-                                        weight_decay=a.weight_decay, max_grad_norm=a.max_grad_norm)
+                                        weight_decay=a.weight_decay,
+                                        max_grad_norm=0.0 if getattr(self, "tp_model", False) else a.max_grad_norm)
             self.use_external_grad_clip = False      # clipping happens inside the optimizer kernel
         else:
             self.optimizer = create_optimizer(self.model, "adamw" if t == "fused_adamw" else t, lr=a.learning_rate,
@@ -304,6 +319,10 @@ class ChronicalsTrainer:
             return
         if self.dp is not None:
             self.dp.reduce_gradients()
+        if self.tp_model:
+            self.model.sync_replicated_grads()
+            if a.max_grad_norm and a.max_grad_norm > 0:
+                self.model.clip_grad_norm_(a.max_grad_norm)       # norm over all ranks' shards
         if self.use_external_grad_clip and a.max_grad_norm and a.max_grad_norm > 0:
             torch.nn.utils.clip_grad_norm_([p for p in self.model.parameters() if p.grad is not None], a.max_grad_norm)
         self.optimizer.step()
@@ -569,8 +588,10 @@ class ChronicalsTrainer:
     def save_checkpoint(self, name: str) -> str:
         a = self.args
         out = os.path.join(a.output_dir, name)
+        # a tensor-parallel model re-assembles the full HuggingFace-named tensors with a collective gather
+        full_state = self.model.gather_full_state_dict() if self.tp_model else None
         if self.rank == 0:
-            ckpt_io.save_model(self.model, out, safe=bool(self._get("save_safetensors", True)))
+            ckpt_io.save_model(self.model, out, safe=bool(self._get("save_safetensors", True)), state=full_state)
             lora_cfg = getattr(self.model, "lora_config", None)
             if lora_cfg is not None:
                 ckpt_io.save_lora_adapter(self.model, out, lora_cfg["rank"], lora_cfg["alpha"],
