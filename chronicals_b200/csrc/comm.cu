@@ -149,7 +149,7 @@ adamw_shard_allgather_kernel(PeerTable params, int W, int my_rank, long long lo,
                              const float* __restrict__ reduced, float* __restrict__ m, float* __restrict__ v,
                              float* __restrict__ master, const unsigned char* __restrict__ chunk_group,
                              const float* __restrict__ hyper, const float* __restrict__ gathered, float max_norm,
-                             float* __restrict__ norm_out, int* status) {
+                             float* __restrict__ norm_out, int W_store, int* status) {
   if (status[0] != 0) return;
   float tot = 0.f;
   for (int r = 0; r < W; ++r) tot += gathered[r * PAYLOAD_FLOATS];
@@ -203,7 +203,7 @@ adamw_shard_allgather_kernel(PeerTable params, int W, int my_rank, long long lo,
     uint4 o;
     o.x = pack_bf16x2(w[0], w[1]); o.y = pack_bf16x2(w[2], w[3]);
     o.z = pack_bf16x2(w[4], w[5]); o.w = pack_bf16x2(w[6], w[7]);
-    for (int r = 0; r < W; ++r)      // the all-gather: every rank receives the updated slice
+    for (int r = 0; r < W_store; ++r)      // the all-gather: every rank receives the updated slice
       *reinterpret_cast<uint4*>(static_cast<bf16*>(params.ptr[(my_rank + r) % W]) + lo + e) = o;
   }
 }
@@ -335,6 +335,19 @@ reduce_partials_kernel(const bf16* __restrict__ stage, const bf16* __restrict__ 
     o.x = pack_bf16x2(a[0], a[1]); o.y = pack_bf16x2(a[2], a[3]);
     o.z = pack_bf16x2(a[4], a[5]); o.w = pack_bf16x2(a[6], a[7]);
     *reinterpret_cast<uint4*>(out + (v << 3)) = o;
+  }
+}
+
+__global__ void __launch_bounds__(COMM_THREADS)
+allgather_pull_kernel(PeerTable shards, int W, long long n, bf16* __restrict__ out, int* status) {
+  if (status[0] != 0) return;
+  const long long nvec = n >> 3;
+  const long long total = nvec * W;
+  for (long long v = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; v < total;
+       v += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int r = static_cast<int>(v / nvec);
+    const long long i = v - r * nvec;
+    reinterpret_cast<uint4*>(out)[v] = reinterpret_cast<const uint4*>(shards.ptr[r])[i];
   }
 }
 
@@ -475,7 +488,32 @@ int cb_adamw_shard_allgather(const unsigned long long* params, int W, int my_ran
   cb::PeerTable t;
   if (fill_table(&t, params, W) || lo % 8 != 0 || hi % 8 != 0 || hi < lo) return -1;
   cb::adamw_shard_allgather_kernel<<<cb_comm_grid(), cb::COMM_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
-      t, W, my_rank, lo, hi, reduced, m, v, master, chunk_group, hyper, gathered, max_norm, norm_out, status);
+      t, W, my_rank, lo, hi, reduced, m, v, master, chunk_group, hyper, gathered, max_norm, norm_out, W, status);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// ZeRO-3 flavour of the update: parameters stay sharded, so the new bf16 values are written only to this
+// rank's shard (`shard`, n elements, n % 1024 == 0); the clip coefficient still comes from all W ranks'
+// norm shares in `gathered`.
+int cb_adamw_shard_local(void* shard, int W, long long n, const float* reduced, float* m, float* v, float* master,
+                         const unsigned char* chunk_group, const float* hyper, const float* gathered, float max_norm,
+                         float* norm_out, int* status, void* stream) {
+  if (n <= 0 || n % 8 != 0 || W < 1 || W > cb::MAX_RANKS) return -1;
+  cb::PeerTable t;
+  for (int i = 0; i < cb::MAX_RANKS; ++i) t.ptr[i] = nullptr;
+  t.ptr[0] = shard;
+  cb::adamw_shard_allgather_kernel<<<cb_comm_grid(), cb::COMM_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
+      t, W, 0, 0, n, reduced, m, v, master, chunk_group, hyper, gathered, max_norm, norm_out, 1, status);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Parameter all-gather by pull: out[r * n + i] = shards[r][i] (bf16, n % 8 == 0).  Shards only change in
+// the optimizer step (followed by a barrier), so no flag is needed while a step's forward/backward read them.
+int cb_allgather_pull(const unsigned long long* shards, int W, long long n, void* out, int* status, void* stream) {
+  cb::PeerTable t;
+  if (fill_table(&t, shards, W) || n <= 0 || n % 8 != 0) return -1;
+  cb::allgather_pull_kernel<<<cb_comm_grid(), cb::COMM_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
+      t, W, n, static_cast<cb::bf16*>(out), status);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -1,0 +1,315 @@
+"""ZeRO-3: parameters, gradients and optimizer state sharded over the data-parallel ranks.
+
+The reference has no sharding of any kind (single GPU; its config only carries a placeholder flag,
+chronicals/config/config.py:525-526), so this module is new.
+
+Units.  The model is cut into units — one per decoder layer plus one "outer" unit (embedding, final norm,
+LM head).  Each unit's parameters are laid out in one flat bf16 vector of which rank r permanently keeps
+only slice r (its *shard*, in peer-mapped symmetric memory) together with fp32 AdamW moments for that
+slice.  The full vector exists on a rank only while the unit computes:
+
+* before a unit's forward (and again before its backward) the full vector is re-materialised by
+  ``allgather_pull`` — one kernel that reads the W shards straight out of the peers' memory over NVLink.
+  Shards change only in the optimizer step, which ends with a barrier, so the pulls need no flags.  The
+  pull of the next unit runs on a side stream while the current unit computes.
+* the unit's parameters are views of that full vector; after use its storage is released
+  (``untyped_storage().resize_(0)``) and re-created before the backward — views saved by autograd stay valid.
+* gradients accumulate into a per-unit slot of a symmetric gradient buffer (two slots, alternating).  When
+  the next unit's backward starts, the finished unit is reduce-scattered: a barrier, then
+  ``rs_reduce_sqnorm`` pulls this rank's slice from all W gradient buffers, averages in fp32, keeps the
+  result for the optimizer and adds to the squared-norm share.
+* ``step()``: one barrier exchanges the norm shares, then ``adamw_shard_local`` updates each shard in place.
+
+On CPU (gloo) the same control flow runs on ``torch.distributed`` collectives — that path is the test
+oracle of the bookkeeping; the kernels are tested on GPUs against the unsharded optimizer.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Any, Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from ..ops import _ext
+
+ALIGN = 1024
+
+
+class _Unit:
+    def __init__(self, name: str, params: List[nn.Parameter], world: int):
+        self.name = name
+        self.params = params
+        self.offsets: List[int] = []
+        off = 0
+        for p in params:
+            self.offsets.append(off)
+            off += (p.numel() + 7) // 8 * 8
+        unit = ALIGN * world
+        self.n = (off + unit - 1) // unit * unit
+        self.shard_n = self.n // world
+        self.full: Optional[torch.Tensor] = None        # flat bf16 [n]; storage released between uses
+        self.resident = False
+        self.gather_event: Optional[torch.cuda.Event] = None
+        self.grad_slot: Optional[int] = None             # which gradient buffer holds this unit's gradients
+        self.pending_reduce = False
+
+
+class Zero3Engine:
+    """Wraps a ``CausalLM``; owns the shards and the optimizer.  Usage per step::
+
+        loss = engine.forward_backward(input_ids, labels=labels)
+        engine.step()
+    """
+
+    def __init__(self, model: nn.Module, lr: float = 1e-5, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.01,
+                 max_grad_norm: float = 1.0, group=None, wait_budget_us: int = 2_000_000, prefetch: bool = True):
+        if not (dist.is_available() and dist.is_initialized()):
+            raise RuntimeError("ZeRO-3 needs an initialised process group")
+        self.model = model
+        self.group = group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.lr, self.betas, self.eps, self.weight_decay, self.max_grad_norm = lr, tuple(betas), eps, weight_decay, max_grad_norm
+        self.step_count = 0
+        p0 = next(model.parameters())
+        self.device, self.dtype = p0.device, p0.dtype
+        self.fused = self.device.type == "cuda"
+        if self.fused and self.dtype != torch.bfloat16:
+            raise ValueError("the fused ZeRO-3 path handles bf16 parameters")
+        self.prefetch = prefetch and self.fused
+        layers = list(model.model.layers)
+        outer = [p for n, p in model.named_parameters() if not n.startswith("model.layers.")]
+        self.units: List[_Unit] = [_Unit("outer", outer, self.world)]
+        self.units += [_Unit(f"layer{i}", list(l.parameters()), self.world) for i, l in enumerate(layers)]
+        self.layer_units = self.units[1:]
+        self._build_shards(wait_budget_us)
+        self._install_hooks(layers)
+        self.last_grad_norm: Optional[torch.Tensor] = None
+
+    # ------------------------------------------------------------------------------------------ set-up
+    def _build_shards(self, wait_budget_us: int) -> None:
+        W, r, dev = self.world, self.rank, self.device
+        if self.fused:
+            from . import symm
+            self.symm = symm
+            self.ctx = symm.SymmetricContext(self.group, wait_budget_us)
+            self.status = self.ctx.status
+            self.lib = symm._lib()
+            for name, args in (("cb_allgather_pull", [ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_void_p,
+                                                       ctypes.c_void_p, ctypes.c_void_p]),
+                               ("cb_adamw_shard_local", [ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong] + [ctypes.c_void_p] * 7
+                                + [ctypes.c_float, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p])):
+                fn = getattr(self.lib, name)
+                fn.argtypes, fn.restype = args, ctypes.c_int
+            self.side = torch.cuda.Stream(device=dev)
+        max_layer_n = max((u.n for u in self.layer_units), default=ALIGN * W)
+        for u in self.units:
+            flat = torch.zeros(u.n, dtype=self.dtype, device=dev)
+            for p, off in zip(u.params, u.offsets):
+                flat[off:off + p.numel()].copy_(p.data.reshape(-1))
+            lo = r * u.shard_n
+            if self.fused:
+                u.shard = self.symm.SymmetricBuffer(u.shard_n, torch.bfloat16, self.group)
+                u.shard.local.copy_(flat[lo:lo + u.shard_n])
+                u.shard_t = u.shard.local
+            else:
+                u.shard_t = flat[lo:lo + u.shard_n].clone()
+            u.exp_avg = torch.zeros(u.shard_n, dtype=torch.float32, device=dev)
+            u.exp_avg_sq = torch.zeros(u.shard_n, dtype=torch.float32, device=dev)
+            u.reduced = torch.zeros(u.shard_n, dtype=torch.float32, device=dev)
+            u.chunk_group = torch.zeros(u.shard_n // ALIGN, dtype=torch.uint8, device=dev)
+            u.full = torch.empty(u.n, dtype=self.dtype, device=dev)
+            for p, off in zip(u.params, u.offsets):
+                p.data = u.full[off:off + p.numel()].view(p.shape)
+            self._release(u)
+            del flat
+        # gradient buffers: two alternating slots for the layers, one for the outer unit
+        if self.fused:
+            self.gslots = [self.symm.SymmetricBuffer(max_layer_n, torch.bfloat16, self.group) for _ in range(2)]
+            self.gouter = self.symm.SymmetricBuffer(self.units[0].n, torch.bfloat16, self.group)
+            self.gslot_t = [b.local for b in self.gslots]
+            self.gouter_t = self.gouter.local
+            self.partials = torch.zeros(self.ctx.grid, dtype=torch.float32, device=dev)
+            self.payload = torch.zeros(self.ctx.payload_floats, dtype=torch.float32, device=dev)
+            self.hyper = torch.zeros(8, dtype=torch.float32, device=dev)
+            self.norm_out = torch.zeros(3, dtype=torch.float32, device=dev)
+        else:
+            self.gslot_t = [torch.zeros(max_layer_n, dtype=self.dtype, device=dev) for _ in range(2)]
+            self.gouter_t = torch.zeros(self.units[0].n, dtype=self.dtype, device=dev)
+        self.sq_total = torch.zeros(1, dtype=torch.float32, device=dev)
+        if self.fused:
+            torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+
+    def _install_hooks(self, layers) -> None:
+        for i, layer in enumerate(layers):
+            layer.register_forward_pre_hook(lambda m, a, i=i: self._before_forward(i))
+            layer.register_forward_hook(lambda m, a, o, i=i: self._after_forward(i))
+            layer.register_full_backward_pre_hook(lambda m, g, i=i: self._before_backward(i))
+
+    # ------------------------------------------------------------------------------------------ parameters
+    def _release(self, u: _Unit) -> None:
+        u.full.untyped_storage().resize_(0)
+        u.resident = False
+        u.gather_event = None
+
+    def _gather(self, u: _Unit, side: bool) -> None:
+        """Re-materialise the unit's full parameter vector from all ranks' shards."""
+        if u.resident:
+            return
+        nbytes = u.n * u.full.element_size()
+        u.full.untyped_storage().resize_(nbytes)
+        if self.fused:
+            main = torch.cuda.current_stream()
+            stream = self.side if (side and self.prefetch) else main
+            if stream is not main:
+                stream.wait_stream(main)            # the block may be recycled memory still in use by queued work
+            with torch.cuda.stream(stream):
+                code = self.lib.cb_allgather_pull(u.shard.ptrs, self.world, u.shard_n, u.full.data_ptr(),
+                                                  self.status.data_ptr(), stream.cuda_stream)
+                _ext.check(code, "allgather_pull")
+                if stream is not main:
+                    u.gather_event = torch.cuda.Event()
+                    u.gather_event.record(stream)
+        else:
+            parts = [torch.empty_like(u.shard_t) for _ in range(self.world)]
+            dist.all_gather(parts, u.shard_t, group=self.group)
+            u.full.copy_(torch.cat(parts))
+        u.resident = True
+
+    def _wait(self, u: _Unit) -> None:
+        if u.gather_event is not None:
+            torch.cuda.current_stream().wait_event(u.gather_event)
+            u.gather_event = None
+
+    def _before_forward(self, i: int) -> None:
+        u = self.layer_units[i]
+        self._gather(u, side=False)
+        self._wait(u)
+        if i + 1 < len(self.layer_units):
+            self._gather(self.layer_units[i + 1], side=True)
+
+    def _after_forward(self, i: int) -> None:
+        if torch.is_grad_enabled() and i == len(self.layer_units) - 1:
+            return                                  # the last layer is the first one the backward needs
+        self._release(self.layer_units[i])
+
+    # ------------------------------------------------------------------------------------------ gradients
+    def _assign_grads(self, u: _Unit, buf: torch.Tensor) -> None:
+        buf[: u.n].zero_()
+        for p, off in zip(u.params, u.offsets):
+            p.grad = buf[off:off + p.numel()].view(p.shape)
+
+    def _before_backward(self, i: int) -> None:
+        u = self.layer_units[i]
+        nxt = i + 1                                   # the unit whose backward has just finished
+        if nxt < len(self.layer_units) and self.layer_units[nxt].pending_reduce:
+            self._reduce_unit(self.layer_units[nxt])
+        self._gather(u, side=False)
+        self._wait(u)
+        if i - 1 >= 0:
+            self._gather(self.layer_units[i - 1], side=True)
+        u.grad_slot = i % 2
+        self._assign_grads(u, self.gslot_t[u.grad_slot])
+        u.pending_reduce = True
+
+    def _reduce_unit(self, u: _Unit) -> None:
+        """Reduce-scatter (average) the unit's gradients into ``u.reduced`` (fp32, my slice)."""
+        lo, hi = self.rank * u.shard_n, (self.rank + 1) * u.shard_n
+        if self.fused:
+            buf = self.gouter if u is self.units[0] else self.gslots[u.grad_slot]
+            self.ctx.barrier()                        # every rank has finished this unit's backward
+            code = self.lib.cb_rs_reduce_sqnorm(buf.ptrs, self.world, lo, hi, u.reduced.data_ptr(), self.partials.data_ptr(),
+                                                self.payload.data_ptr(), self.status.data_ptr(), _ext.stream_ptr())
+            _ext.check(code, "rs_reduce_sqnorm")
+            self.sq_total += self.payload[0]
+        else:
+            buf_t = self.gouter_t if u is self.units[0] else self.gslot_t[u.grad_slot]
+            g = buf_t[: u.n].float()
+            dist.all_reduce(g, group=self.group)
+            u.reduced.copy_(g[lo:hi] / self.world)
+            self.sq_total += u.reduced.pow(2).sum()
+        for p in u.params:
+            p.grad = None
+        u.pending_reduce = False
+        if u is not self.units[0]:
+            self._release(u)
+
+    # ------------------------------------------------------------------------------------------ step API
+    def forward_backward(self, input_ids: torch.Tensor, labels: torch.Tensor, **kw) -> torch.Tensor:
+        outer = self.units[0]
+        self.sq_total.zero_()
+        self._gather(outer, side=False)
+        self._assign_grads(outer, self.gouter_t)
+        outer.pending_reduce = True
+        loss = self.model(input_ids, labels=labels, **kw).loss
+        loss.backward()
+        if self.layer_units and self.layer_units[0].pending_reduce:
+            self._reduce_unit(self.layer_units[0])
+        self._reduce_unit(outer)
+        self._release(outer)
+        return loss.detach()
+
+    @torch.no_grad()
+    def step(self) -> None:
+        self.step_count += 1
+        t = self.step_count
+        b1, b2 = self.betas
+        if self.fused:
+            self.hyper.copy_(torch.tensor([self.lr, self.weight_decay, b1, b2, self.eps, 1.0 - b1 ** t, 1.0 - b2 ** t, 0.0],
+                                          dtype=torch.float32), non_blocking=True)
+            self.payload.zero_()
+            self.payload[0:1].copy_(self.sq_total)
+            gathered = self.ctx.barrier(self.payload)
+            for u in self.units:
+                code = self.lib.cb_adamw_shard_local(u.shard_t.data_ptr(), self.world, u.shard_n, u.reduced.data_ptr(),
+                                                     u.exp_avg.data_ptr(), u.exp_avg_sq.data_ptr(), None,
+                                                     u.chunk_group.data_ptr(), self.hyper.data_ptr(), gathered.data_ptr(),
+                                                     float(self.max_grad_norm or 0.0), self.norm_out.data_ptr(),
+                                                     self.status.data_ptr(), _ext.stream_ptr())
+                _ext.check(code, "adamw_shard_local")
+            self.ctx.barrier()                        # new shards are visible before anyone pulls them
+            self.last_grad_norm = self.norm_out[1]
+            return
+        tot = self.sq_total.clone()
+        dist.all_reduce(tot, group=self.group)
+        norm = tot.sqrt()
+        clip = (self.max_grad_norm / (norm + 1e-6)).clamp(max=1.0) if self.max_grad_norm else torch.ones_like(norm)
+        for u in self.units:
+            g = u.reduced * clip
+            w = u.shard_t.float() * (1.0 - self.lr * self.weight_decay)
+            u.exp_avg.mul_(b1).add_(g, alpha=1 - b1)
+            u.exp_avg_sq.mul_(b2).addcmul_(g, g, value=1 - b2)
+            w -= (self.lr / (1 - b1 ** t)) * u.exp_avg / ((u.exp_avg_sq / (1 - b2 ** t)).sqrt() + self.eps)
+            u.shard_t.copy_(w.to(u.shard_t.dtype))
+        self.last_grad_norm = norm.squeeze(0)
+        dist.barrier(group=self.group)
+
+    # ------------------------------------------------------------------------------------------ state
+    @torch.no_grad()
+    def gather_full_state_dict(self) -> Dict[str, torch.Tensor]:
+        """HuggingFace-named full tensors on every rank (checkpoint consolidation; collective, not hot)."""
+        for u in self.units:
+            self._gather(u, side=False)
+        if self.fused:
+            torch.cuda.synchronize()
+        sd = {k: v.detach().clone() for k, v in self.model.hf_state_dict().items()}
+        for u in self.units:
+            self._release(u)
+        return sd
+
+    def state_dict(self) -> Dict[str, Any]:
+        """This rank's optimizer shard."""
+        return {"step_count": self.step_count, "rank": self.rank, "world": self.world,
+                "units": [{"name": u.name, "exp_avg": u.exp_avg.cpu(), "exp_avg_sq": u.exp_avg_sq.cpu(),
+                           "shard": u.shard_t.detach().cpu()} for u in self.units]}
+
+    def load_state_dict(self, sd: Dict[str, Any]) -> None:
+        if sd["world"] != self.world:
+            raise ValueError("ZeRO-3 state was written with a different world size; re-shard from a consolidated checkpoint")
+        self.step_count = int(sd["step_count"])
+        for u, s in zip(self.units, sd["units"]):
+            u.exp_avg.copy_(s["exp_avg"])
+            u.exp_avg_sq.copy_(s["exp_avg_sq"])
+            u.shard_t.copy_(s["shard"])

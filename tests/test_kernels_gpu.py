@@ -280,3 +280,40 @@ def test_tiny_model_step_runs_and_graph_matches_eager():
     assert losses[False][-1] < losses[False][0] + 0.5
     for a, b in zip(losses[False], losses[True]):
         assert abs(a - b) < 5e-2, (losses[False], losses[True])
+
+
+# ---------------------------------------------------------------------------------------------- MXFP8
+@pytest.mark.parametrize("fmt", ["e4m3", "e5m2"])
+@pytest.mark.parametrize("shape", [(257, 896), (64, 4864), (3, 32)])
+def test_mxfp8_quant_kernel_matches_reference(fmt, shape):
+    """Block-scaled quantisation (32-element blocks, e8m0 scales): scales must be bit-exact, payloads may
+    differ by at most one fp8 step where the fp32 division rounds differently, and the dequantised copy
+    must equal scale * payload exactly."""
+    from chronicals_b200.ops import ref
+    from chronicals_b200.utils.fp8_utils import mxfp8_quantize
+    g = torch.Generator().manual_seed(11)
+    x = (torch.randn(*shape, generator=g) * torch.exp(2.0 * torch.randn(shape[0], 1, generator=g))).to(torch.bfloat16).cuda()
+    x[0, :32] = 0                                                     # an all-zero block
+    q, s, d = mxfp8_quantize(x, fmt, want_dequantized=True)
+    q_ref, s_ref = ref.mxfp8_quantize(x.cpu(), fmt)
+    assert torch.equal(s.cpu(), s_ref), "e8m0 scales differ"
+    deq = ref.mxfp8_dequantize(q.cpu(), s.cpu(), torch.float32)
+    deq_ref = ref.mxfp8_dequantize(q_ref, s_ref, torch.float32)
+    step = 2.0 ** -3 if fmt == "e4m3" else 2.0 ** -2                  # relative spacing of the format's mantissa
+    tol = step * deq_ref.abs().clamp(min=1e-30)
+    assert bool(((deq - deq_ref).abs() <= tol + 1e-30).all())
+    assert (q.cpu().float() != q_ref.float()).float().mean().item() < 1e-3
+    assert torch.equal(d.cpu().float(), deq.to(torch.bfloat16).float())
+
+
+def test_fp8_linear_module_runs_kernels_and_matches_reference():
+    from chronicals_b200.ops import ref
+    from chronicals_b200.utils.fp8_utils import FP8Linear
+    torch.manual_seed(0)
+    lin = FP8Linear(256, 384, bias=True).cuda().to(torch.bfloat16)
+    x = torch.randn(96, 256, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    y = lin(x)
+    y.float().pow(2).mean().backward()
+    want = ref.mxfp8_linear(x.detach().float().cpu(), lin.weight.detach().float().cpu(), lin.bias.detach().float().cpu())
+    assert (y.float().cpu() - want).abs().max().item() < 0.06 * want.abs().max().item()
+    assert x.grad is not None and lin.weight.grad is not None and torch.isfinite(lin.weight.grad.float()).all()

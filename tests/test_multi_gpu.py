@@ -41,3 +41,12 @@ def test_tensor_parallel_matches_single_gpu(tmp_path, backend, port):
     assert max(abs(a - b) for a, b in zip(res["loss_tp"], res["loss_full"])) < 3e-2, res
     assert res["grad_rel_err_max"] < 6e-2, res
     assert res["state_dict_ok"], res
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_zero3_fused_matches_unsharded_optimizer(tmp_path):
+    """ZeRO-3 with the pull all-gather, pull reduce-scatter and sharded AdamW kernels against the
+    unsharded fused AdamW on the joint batch (bf16 parameters, so a few ulps of drift are allowed)."""
+    res = _run_worker(tmp_path, 2, "_zero3_worker.py", 29548, extra=("fused",))
+    assert max(abs(a - b) for a, b in zip(res["zero3_losses"], res["ref_losses"])) < 3e-2, res
+    assert res["max_param_diff"] < 2e-2, res
