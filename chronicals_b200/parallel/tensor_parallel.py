@@ -337,8 +337,9 @@ class TensorParallelCausalLM(nn.Module):
         with torch.device("meta"):
             full = CausalLM(cfg, dtype=dtype)
         model = cls(full, tp).to_empty(device=device)
-        shared = torch.Generator(device="cpu").manual_seed(seed)
-        own = torch.Generator(device="cpu").manual_seed(seed * 1000 + 17 + tp.rank)
+        gdev = torch.device(device) if device is not None else torch.device("cpu")
+        shared = torch.Generator(device=gdev).manual_seed(seed)
+        own = torch.Generator(device=gdev).manual_seed(seed * 1000 + 17 + tp.rank)
         with torch.no_grad():
             for name, p in model.named_parameters():
                 replicated = getattr(p, REPLICATED_MARK, False) or name.endswith("norm_weight") or name.startswith("embed_tokens")
@@ -348,7 +349,7 @@ class TensorParallelCausalLM(nn.Module):
                     p.zero_()
                 else:
                     g = shared if replicated else own
-                    p.copy_(torch.empty(p.shape, dtype=torch.float32).normal_(0.0, std, generator=g).to(p.dtype))
+                    p.copy_(torch.empty(p.shape, dtype=torch.float32, device=gdev).normal_(0.0, std, generator=g).to(p.dtype))
                 if replicated:
                     setattr(p, REPLICATED_MARK, True)
         return model
