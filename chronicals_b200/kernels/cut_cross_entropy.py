@@ -123,3 +123,63 @@ def estimate_memory_savings(batch_tokens: int, vocab_size: int, hidden_size: int
     fused_fwd = batch_tokens * 4 * 8                                   # per-token partial statistics
     return {"standard_gb": full / 2**30, "chunked_gb": chunked / 2**30, "fused_forward_gb": fused_fwd / 2**30,
             "reduction_factor": full / max(1, chunked)}
+
+
+class CutCrossEntropyForward:
+    """Forward half as a separate object (reference: cut_cross_entropy.py:559-692): returns
+    ``(loss, lse, target_logit, valid_mask)`` without materialising logits."""
+
+    @staticmethod
+    def forward(hidden: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                chunk_size: int = DEFAULT_CHUNK_SIZE, ignore_index: int = -100, label_smoothing: float = 0.0,
+                z_loss_weight: float = 0.0):
+        h = hidden.reshape(-1, hidden.shape[-1])
+        y = labels.reshape(-1)
+        valid = y != ignore_index
+        with torch.no_grad():
+            rows = cut_cross_entropy(h, weight, y, bias, chunk_size, ignore_index, 0.0, 0.0, reduction="none")
+            loss = cut_cross_entropy(h, weight, y, bias, chunk_size, ignore_index, label_smoothing, z_loss_weight)
+            safe = y.clamp_min(0)
+            tgt = (h.float() * weight[safe].float()).sum(-1)
+            if bias is not None:
+                tgt = tgt + bias[safe].float()
+            tgt = tgt * valid
+            lse = rows.float() + tgt                       # per-row loss = lse - target logit
+        return loss, lse, tgt, valid
+
+
+class CutCrossEntropyBackward:
+    """Backward half (reference: cut_cross_entropy.py:695-808): ``(grad_hidden, grad_weight, grad_bias)``."""
+
+    @staticmethod
+    def backward(grad_output: torch.Tensor, hidden: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor,
+                 bias: Optional[torch.Tensor] = None, chunk_size: int = DEFAULT_CHUNK_SIZE, ignore_index: int = -100,
+                 label_smoothing: float = 0.0, z_loss_weight: float = 0.0):
+        h = hidden.detach().requires_grad_(True)
+        w = weight.detach().requires_grad_(True)
+        b = bias.detach().requires_grad_(True) if bias is not None else None
+        with torch.enable_grad():
+            loss = cut_cross_entropy(h, w, labels, b, chunk_size, ignore_index, label_smoothing, z_loss_weight)
+            grads = torch.autograd.grad(loss, (h, w) + ((b,) if b is not None else ()), grad_output)
+        return grads[0], grads[1], (grads[2] if b is not None else None)
+
+
+class CutCrossEntropyFunction(torch.autograd.Function):
+    """``apply(hidden, weight, labels, bias, chunk_size, ignore_index, label_smoothing, z_loss_weight)``"""
+
+    @staticmethod
+    def forward(ctx, hidden, weight, labels, bias=None, chunk_size=DEFAULT_CHUNK_SIZE, ignore_index=-100,
+                label_smoothing=0.0, z_loss_weight=0.0):
+        ctx.save_for_backward(hidden, weight, labels, bias if bias is not None else torch.empty(0))
+        ctx.cfg = (chunk_size, ignore_index, label_smoothing, z_loss_weight)
+        with torch.no_grad():
+            return cut_cross_entropy(hidden, weight, labels, bias, chunk_size, ignore_index, label_smoothing, z_loss_weight)
+
+    @staticmethod
+    def backward(ctx, gout):
+        hidden, weight, labels, bias = ctx.saved_tensors
+        gh, gw, gb = CutCrossEntropyBackward.backward(gout, hidden, weight, labels, bias if bias.numel() else None, *ctx.cfg)
+        return gh, gw, None, gb, None, None, None, None
+
+
+TritonCCEFunction = CutCrossEntropyFunction

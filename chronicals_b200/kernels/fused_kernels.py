@@ -274,5 +274,168 @@ def fused_gqa_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causa
     return o.view(B, S, hq, d).transpose(1, 2)
 
 
+# ------------------------------------------------------------------------------------------- functional forward/backward pairs
+# The reference exposes explicit ``*_forward`` / ``*_backward`` entry points and ``autograd.Function`` classes
+# around its Triton kernels (triton_kernels.py:593-712, :1067-1178, :1370-1432, :1946-1988, :2308-2633,
+# :2979-3106, :3147-3315).  Here every op already is an autograd function in ``chronicals_b200.ops``; these
+# wrappers give the same call shapes on top of it.
+def _vjp(fn, inputs, grad_out):
+    xs = [t.detach().requires_grad_(True) for t in inputs]
+    with torch.enable_grad():
+        y = fn(*xs)
+    return torch.autograd.grad(y, xs, grad_out, allow_unused=True)
+
+
+def rmsnorm_forward(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6, offset: float = 0.0
+                    ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``(y, rstd)``; ``rstd`` is the per-row reciprocal RMS in fp32."""
+    with torch.no_grad():
+        y = ops.rmsnorm(x, weight, eps, offset)
+        rstd = torch.rsqrt(x.float().pow(2).mean(-1) + eps)
+    return y, rstd
+
+
+def rmsnorm_backward(dy: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, rstd: Optional[torch.Tensor] = None,
+                     eps: float = 1e-6, offset: float = 0.0) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``(dx, dw)``; ``rstd`` is accepted for signature parity and recomputed by the kernel."""
+    dx, dw = _vjp(lambda a, b: ops.rmsnorm(a, b, eps, offset), (x, weight), dy)
+    return dx, dw
+
+
+class LigerRMSNormFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, eps=1e-6, offset=0.0, *unused):
+        y, rstd = rmsnorm_forward(x, weight, eps, offset)
+        ctx.save_for_backward(x, weight, rstd)
+        ctx.cfg = (eps, offset)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight, rstd = ctx.saved_tensors
+        dx, dw = rmsnorm_backward(dy.contiguous(), x, weight, rstd, *ctx.cfg)
+        return (dx, dw) + (None,) * 8
+
+
+def swiglu_forward(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    with torch.no_grad():
+        return fused_swiglu(gate, up)
+
+
+def swiglu_backward(dout: torch.Tensor, gate: torch.Tensor, up: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    return _vjp(fused_swiglu, (gate, up), dout)
+
+
+def geglu_forward(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    with torch.no_grad():
+        return fused_geglu(gate, up)
+
+
+def geglu_backward(dout: torch.Tensor, gate: torch.Tensor, up: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    return _vjp(fused_geglu, (gate, up), dout)
+
+
+class _GLUFunctionBase(torch.autograd.Function):
+    _fwd = staticmethod(swiglu_forward)
+    _bwd = staticmethod(swiglu_backward)
+
+    @classmethod
+    def forward(cls, ctx, gate, up):
+        ctx.save_for_backward(gate, up)
+        return cls._fwd(gate, up)
+
+    @classmethod
+    def backward(cls, ctx, dout):
+        gate, up = ctx.saved_tensors
+        return cls._bwd(dout.contiguous(), gate, up)
+
+
+class LigerSwiGLUFunction(_GLUFunctionBase):
+    pass
+
+
+class LigerGeGLUFunction(_GLUFunctionBase):
+    _fwd = staticmethod(geglu_forward)
+    _bwd = staticmethod(geglu_backward)
+
+
+class FusedQKRoPEFunction(torch.autograd.Function):
+    """``apply(q, k, cos, sin, position_ids=None, interleaved=False) -> (q_rot, k_rot)``; the backward is the
+    same rotation with the sine negated."""
+
+    @staticmethod
+    def forward(ctx, q, k, cos, sin, position_ids=None, interleaved=False):
+        ctx.save_for_backward(cos, sin, position_ids if position_ids is not None else torch.empty(0))
+        ctx.interleaved = interleaved
+        with torch.no_grad():
+            return fused_qk_rope(q, k, cos, sin, position_ids, interleaved)
+
+    @staticmethod
+    def backward(ctx, dq, dk):
+        cos, sin, pos = ctx.saved_tensors
+        with torch.no_grad():
+            gq, gk = fused_qk_rope(dq.contiguous(), dk.contiguous(), cos, -sin, pos if pos.numel() else None, ctx.interleaved)
+        return gq, gk, None, None, None, None
+
+
+def fused_linear_cross_entropy_forward(hidden: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor,
+                                       bias: Optional[torch.Tensor] = None, chunk_size: int = DEFAULT_CHUNK_SIZE,
+                                       ignore_index: int = -100, label_smoothing: float = 0.0, z_loss_weight: float = 0.0):
+    """``(loss, z_loss, grad_hidden, grad_weight)`` computed in one call, as the reference's forward does."""
+    h = hidden.detach().requires_grad_(True)
+    w = weight.detach().requires_grad_(True)
+    with torch.enable_grad():
+        loss, z = fused_linear_cross_entropy(h, w, labels, bias, chunk_size, ignore_index, label_smoothing, z_loss_weight)
+        gh, gw = torch.autograd.grad(loss, (h, w))
+    return loss.detach(), z.detach(), gh, gw
+
+
+triton_fused_linear_cross_entropy_forward = fused_linear_cross_entropy_forward
+
+
+class FusedLinearCrossEntropyFunction(torch.autograd.Function):
+    """Gradients are produced during the forward pass and only scaled in the backward pass."""
+
+    @staticmethod
+    def forward(ctx, hidden, weight, labels, bias=None, chunk_size=DEFAULT_CHUNK_SIZE, ignore_index=-100,
+                label_smoothing=0.0, z_loss_weight=0.0):
+        loss, z, gh, gw = fused_linear_cross_entropy_forward(hidden, weight, labels, bias, chunk_size, ignore_index,
+                                                             label_smoothing, z_loss_weight)
+        ctx.save_for_backward(gh, gw)
+        return loss
+
+    @staticmethod
+    def backward(ctx, gout):
+        gh, gw = ctx.saved_tensors
+        return (gh * gout).to(gh.dtype), (gw * gout).to(gw.dtype), None, None, None, None, None, None
+
+
+TritonFusedLinearCrossEntropyFunction = FusedLinearCrossEntropyFunction
+
+
+def liger_cross_entropy_forward(logits: torch.Tensor, labels: torch.Tensor, ignore_index: int = -100,
+                                label_smoothing: float = 0.0, z_loss_weight: float = 0.0):
+    """``(loss, grad_logits)`` for materialised logits (the reference overwrites the logits with the gradient;
+    here the gradient is a separate tensor)."""
+    lg = logits.detach().requires_grad_(True)
+    with torch.enable_grad():
+        loss = ops.cross_entropy_logits(lg, labels, ignore_index, label_smoothing, z_loss_weight, "mean")
+        (g,) = torch.autograd.grad(loss, (lg,))
+    return loss.detach(), g
+
+
+class LigerCrossEntropyFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, labels, ignore_index=-100, label_smoothing=0.0, z_loss_weight=0.0):
+        loss, g = liger_cross_entropy_forward(logits, labels, ignore_index, label_smoothing, z_loss_weight)
+        ctx.save_for_backward(g)
+        return loss
+
+    @staticmethod
+    def backward(ctx, gout):
+        (g,) = ctx.saved_tensors
+        return (g * gout).to(g.dtype), None, None, None, None
+
+
 __all__ = [n for n in dir() if not n.startswith("_") and n not in ("math", "nn", "F", "torch", "ops", "ref",
                                                                     "Optional", "Tuple")]

@@ -37,6 +37,34 @@ def fused_lora_linear(x: torch.Tensor, W: torch.Tensor, A: torch.Tensor, B: torc
     return ops.linear(h, B * scaling, None, base)
 
 
+class FusedLoRALinearFunction(torch.autograd.Function):
+    """``apply(x, W, A, B, bias, scaling)``: frozen ``W`` (no weight gradient, as in the reference's
+    fused_lora_kernels.py:703-772), gradients for ``x``, ``A``, ``B`` and ``bias``."""
+
+    @staticmethod
+    def forward(ctx, x, W, A, B, bias=None, scaling=1.0):
+        x2 = x.reshape(-1, x.shape[-1])
+        with torch.no_grad():
+            h = ops.linear(x2, A)
+            y = ops.linear(h, B * scaling, None, ops.linear(x2, W, bias))
+        ctx.save_for_backward(x2, W, A, B, h)
+        ctx.scaling, ctx.has_bias, ctx.shape = scaling, bias is not None, x.shape
+        return y.view(*x.shape[:-1], W.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, W, A, B, h = ctx.saved_tensors
+        s = ctx.scaling
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        with torch.no_grad():
+            dh = ops.linear(dy2, (B * s).t().contiguous())                 # [T, r]
+            dx = ops.linear(dy2, W.t().contiguous()) + ops.linear(dh, A.t().contiguous())
+            dA = (dh.float().t() @ x2.float()).to(A.dtype)
+            dB = (s * (dy2.float().t() @ h.float())).to(B.dtype)
+            db = dy2.float().sum(0).to(dy.dtype) if ctx.has_bias else None
+        return dx.view(ctx.shape), None, dA, dB, db, None
+
+
 def lora_linear_pytorch(x, W, A, B, bias=None, lora_alpha: float = 16.0, lora_dropout: float = 0.0,
                         training: bool = True) -> torch.Tensor:
     xd = F.dropout(x, lora_dropout, training) if lora_dropout > 0 else x
@@ -131,5 +159,5 @@ def benchmark_lora(tokens: int = 8192, in_features: int = 896, out_features: int
     return res
 
 
-__all__ = ["fused_lora_down_dropout", "fused_lora_linear", "lora_linear_pytorch", "FusedLoRALinear",
+__all__ = ["fused_lora_down_dropout", "fused_lora_linear", "lora_linear_pytorch", "FusedLoRALinearFunction", "FusedLoRALinear",
            "FusedLoRAAdapter", "apply_lora_to_model", "get_lora_params", "count_lora_params", "benchmark_lora"]

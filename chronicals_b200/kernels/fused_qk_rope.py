@@ -68,5 +68,23 @@ def apply_rope(q: torch.Tensor, k: torch.Tensor, cos: torch.Tensor, sin: torch.T
     return fused_qk_rope(q, k, cos, sin, position_ids, interleaved)
 
 
+def fused_qk_rope_forward(q: torch.Tensor, k: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
+                          position_ids: Optional[torch.Tensor] = None, interleaved: bool = False, inplace: bool = False):
+    """Functional forward (reference: fused_qk_rope.py:474-568); ``inplace`` is accepted for parity — the
+    packed-QKV in-place rotation is :func:`fused_qkv_rope_inplace`."""
+    with torch.no_grad():
+        return fused_qk_rope(q, k, cos, sin, position_ids, interleaved)
+
+
+def fused_qk_rope_backward(dq: torch.Tensor, dk: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
+                           position_ids: Optional[torch.Tensor] = None, interleaved: bool = False):
+    """Gradient of the rotation = rotation by the negated angle."""
+    with torch.no_grad():
+        return fused_qk_rope(dq, dk, cos, -sin, position_ids, interleaved)
+
+
+from .fused_kernels import FusedQKRoPEFunction  # noqa: E402  (same autograd function under this module's name)
+
 __all__ = ["fused_qk_rope", "fused_qkv_rope_inplace", "precompute_rope_cache", "precompute_rope_cache_ntk",
-           "precompute_rope_cache_yarn", "FusedQKRoPE", "apply_rope", "fused_rope"]
+           "precompute_rope_cache_yarn", "FusedQKRoPE", "apply_rope", "fused_rope", "fused_qk_rope_forward",
+           "fused_qk_rope_backward", "FusedQKRoPEFunction"]

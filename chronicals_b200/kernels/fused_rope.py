@@ -84,5 +84,8 @@ def benchmark_rope(batch: int = 8, seq: int = 1024, hq: int = 14, hk: int = 2, d
     return res
 
 
+from .fused_kernels import FusedQKRoPEFunction  # noqa: E402
+
 __all__ = ["fused_qk_rope", "fused_q_rope_inplace", "fused_qk_rope_variable_length", "precompute_rope_cache",
-           "precompute_rope_cache_llama3", "FusedRotaryEmbedding", "positions_from_cu_seqlens", "benchmark_rope"]
+           "precompute_rope_cache_llama3", "FusedRotaryEmbedding", "positions_from_cu_seqlens", "benchmark_rope",
+           "FusedQKRoPEFunction"]

@@ -74,6 +74,14 @@ def _batch_fields(batch: Any) -> Dict[str, Any]:
     raise TypeError(f"unsupported batch type {type(batch)!r}")
 
 
+def setup_torch_compile_for_training(model=None, mode: str = "default", **kwargs):
+    """API parity with the reference (chronicals_trainer.py:273-364), which tunes ``torch._dynamo`` /
+    Inductor flags before compiling the model.  This framework has no tracing compiler on its hot path:
+    fusion is done by the hand-written kernels and launch overhead is removed by capturing the step in a
+    CUDA graph (``TrainingConfig.use_cuda_graphs``).  Returns the model unchanged plus what was (not) done."""
+    return model, {"compiled": False, "mode": mode, "reason": "hand-written kernels + CUDA-graph step replace torch.compile"}
+
+
 class ChronicalsTrainer:
     def __init__(self, model: nn.Module, args: Union[TrainingConfig, ChronicalsConfig, Any] = None,
                  train_dataloader: Optional[Iterable] = None, eval_dataloader: Optional[Iterable] = None,
