@@ -523,13 +523,256 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem, TMEM_COLS); }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Backward, occupancy-oriented variant (used for D = 64): 256 TMEM columns and ~97 KB of shared memory per
+// CTA, so two CTAs share an SM and one computes its softmax while the other has the tensor core.
+// The S, dP and dQ tiles take turns in the same 128 TMEM columns, and P and dS take turns in one shared
+// tile, which turns an iteration into three MMA phases:
+//   S = Q K^T            -> P = exp(S - lse)            (P to smem)
+//   dV += P^T dO ; dP = dO V^T  -> dS = P (dP - delta)  (P re-read from smem as bf16, dS overwrites it)
+//   dK += dS^T Q ; dQ = dS K    -> dQ added to global
+// dK / dV are added into [T, hk, D] fp32 accumulators with red.global.add (the query heads of a group are
+// different CTAs), which replaces the per-query-head partial buffers of the kernel above.
+template <int D>
+struct Bwd2Smem {
+  static constexpr int TILE = 128 * D * 2;
+  static constexpr int OFF_K = 0;
+  static constexpr int OFF_V = TILE;
+  static constexpr int OFF_Q = 2 * TILE;
+  static constexpr int OFF_DO = 3 * TILE;
+  static constexpr int OFF_P = 4 * TILE;              // P, then dS (bf16 [128 x 128] operand image)
+  static constexpr int OFF_BAR = OFF_P + 32768;
+  static constexpr int TOTAL = OFF_BAR + 128 + 1024;
+};
+
+// read back 32 consecutive bf16 values of thread-row r from the image written by store_row_chunk32
+__device__ __forceinline__ void load_row_chunk32(const uint8_t* base, int r, int c32, float (&v)[32]) {
+  const int panel = c32 >> 1;
+  const uint8_t* row = base + panel * 16384 + r * 128;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const int cc = (c32 & 1) * 4 + q;
+    const uint4 u = *reinterpret_cast<const uint4*>(row + ((cc ^ (r & 7)) << 4));
+    const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+    v[8 * q + 0] = a.x; v[8 * q + 1] = a.y; v[8 * q + 2] = b.x; v[8 * q + 3] = b.y;
+    v[8 * q + 4] = c.x; v[8 * q + 5] = c.y; v[8 * q + 6] = d.x; v[8 * q + 7] = d.y;
+  }
+}
+
+template <int D>
+__global__ void __launch_bounds__(ATT_THREADS, 2)
+attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO, const AttnArgs a) {
+  using L = Bwd2Smem<D>;
+  constexpr int PANELS = D / 64;
+  constexpr uint32_t TMEM_COLS = (128 + 2 * D) <= 256 ? 256 : 512;
+  constexpr uint32_t C_S = 0, C_DV = 128, C_DK = 128 + D;                // S, dP and dQ share the first 128 columns
+  constexpr uint32_t IDESC_S = umma_idesc_bf16(128, 128, 0, 0);
+  constexpr uint32_t IDESC_T = umma_idesc_bf16(128, D, 1, 1);            // P^T dO, dS^T Q
+  constexpr uint32_t IDESC_DQ = umma_idesc_bf16(128, D, 0, 1);           // dS K
+
+  int start, len, jb, nblk;
+  if (!locate_block(a.cu, a.n_docs, blockIdx.x, start, len, jb, nblk)) return;   // jb = 0 is the heaviest
+  const int h = blockIdx.y;
+  const int hkv = h / (a.hq / a.hk);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem + L::OFF_K;
+  uint8_t* sV = smem + L::OFF_V;
+  uint8_t* sQ = smem + L::OFF_Q;
+  uint8_t* sdO = smem + L::OFF_DO;
+  uint8_t* sP = smem + L::OFF_P;
+  uint64_t* q_full = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
+  uint64_t* bar_kv = q_full + 1;
+  uint64_t* bar_s = q_full + 2;
+  uint64_t* bar_dp = q_full + 3;
+  uint64_t* bar_dq = q_full + 4;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_full + 5);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  if (tid == 0) {
+    mbar_init(q_full, 1); mbar_init(bar_kv, 1); mbar_init(bar_s, 1); mbar_init(bar_dp, 1); mbar_init(bar_dq, 1);
+    mbar_fence_init();
+    *abort_flag = a.status[0] != 0 ? 1 : 0;
+  }
+  __syncthreads();
+  if (*abort_flag) return;
+  if (warp == 0) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t t_row = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+
+  const int kv_row0 = start + jb * 128;
+  const int n_it = nblk - jb;
+  auto load_q = [&](int it) {
+    const int row0 = start + (jb + it) * 128;
+    mbar_expect_tx(q_full, 2 * L::TILE);
+#pragma unroll
+    for (int p = 0; p < PANELS; ++p) {
+      tma_load_2d(sQ + p * 16384, &tmQ, q_full, h * D + p * 64, row0);
+      tma_load_2d(sdO + p * 16384, &tmdO, q_full, h * D + p * 64, row0);
+    }
+  };
+
+  bool ok = true;
+  if (tid == 0) {
+    mbar_expect_tx(bar_kv, 2 * L::TILE);
+#pragma unroll
+    for (int p = 0; p < PANELS; ++p) {
+      tma_load_2d(sK + p * 16384, &tmK, bar_kv, hkv * D + p * 64, kv_row0);
+      tma_load_2d(sV + p * 16384, &tmV, bar_kv, hkv * D + p * 64, kv_row0);
+    }
+    load_q(0);
+    ok &= mbar_wait(bar_kv, 0, abort_flag, a.status, CB_ERR_WAIT_FULL);
+  }
+
+  const int r = tid;
+  const float sl2 = a.scale * LOG2E;
+  const uint32_t kA = smem_u32(sK), vA = smem_u32(sV), pA = smem_u32(sP), qA = smem_u32(sQ), doA = smem_u32(sdO);
+
+  for (int it = 0; it < n_it; ++it) {
+    const int i = jb + it;
+    if (tid == 0) {
+      ok &= mbar_wait(q_full, it & 1, abort_flag, a.status, CB_ERR_WAIT_FULL);
+      if (ok) {
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          umma_f16_ss(tmem + C_S, desc_kmajor(qA, kk), desc_kmajor(kA, kk), IDESC_S, kk != 0);
+        umma_commit(bar_s);
+      }
+    }
+    const int rg = i * 128 + r;                      // my query row within the document
+    const bool row_ok = rg < len;
+    const long long tq = start + rg;
+    const float lse2 = row_ok ? a.lse[static_cast<long long>(h) * a.T + tq] * LOG2E : 0.f;
+    const float dlt = row_ok ? a.delta[static_cast<long long>(h) * a.T + tq] : 0.f;
+    const bool diag = (it == 0);
+    // ---- phase 1: P = exp(S - lse), masked, to shared memory
+    ok &= mbar_wait(bar_s, it & 1, abort_flag, a.status, CB_ERR_WAIT_TMEM_FULL);
+    tc_fence_after();
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+      uint32_t s[32];
+      float p[32];
+      tmem_ld_32x32(t_row + C_S + c * 32, s);
+      tmem_ld_wait();
+#pragma unroll
+      for (int k = 0; k < 32; ++k) {
+        const bool keep = row_ok && (!diag || c * 32 + k <= r);
+        const float e = exp2f(fmaf(__uint_as_float(s[k]), sl2, -lse2));
+        p[k] = keep ? e : 0.f;
+      }
+      store_row_chunk32(sP, r, c, p);
+    }
+    tc_fence_before();
+    fence_async_smem();
+    if (__syncthreads_or(!ok)) { ok = false; break; }
+    if (tid == 0) {
+      tc_fence_after();
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk)                  // dV += P^T dO     (K = the 128 query rows)
+        umma_f16_ss(tmem + C_DV, desc_mnmajor(pA, kk), desc_mnmajor(doA, kk), IDESC_T, (it | kk) != 0);
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk)             // dP = dO V^T      (over the columns S occupied)
+        umma_f16_ss(tmem + C_S, desc_kmajor(doA, kk), desc_kmajor(vA, kk), IDESC_S, kk != 0);
+      umma_commit(bar_dp);
+    }
+    // ---- phase 2: dS = P (dP - delta) scale, overwriting P in shared memory
+    ok &= mbar_wait(bar_dp, it & 1, abort_flag, a.status, CB_ERR_WAIT_TMEM_FULL);
+    tc_fence_after();
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+      uint32_t dp[32];
+      float p[32];
+      tmem_ld_32x32(t_row + C_S + c * 32, dp);
+      load_row_chunk32(sP, r, c, p);
+      tmem_ld_wait();
+#pragma unroll
+      for (int k = 0; k < 32; ++k) p[k] = p[k] * (__uint_as_float(dp[k]) - dlt) * a.scale;
+      store_row_chunk32(sP, r, c, p);
+    }
+    tc_fence_before();
+    fence_async_smem();
+    if (__syncthreads_or(!ok)) { ok = false; break; }
+    if (tid == 0) {
+      tc_fence_after();
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk)                  // dK += dS^T Q
+        umma_f16_ss(tmem + C_DK, desc_mnmajor(pA, kk), desc_mnmajor(qA, kk), IDESC_T, (it | kk) != 0);
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk)                  // dQ = dS K        (K = the 128 kv rows)
+        umma_f16_ss(tmem + C_S, desc_kmajor(pA, kk), desc_mnmajor(kA, kk), IDESC_DQ, kk != 0);
+      umma_commit(bar_dq);
+    }
+    // ---- phase 3: dQ out
+    ok &= mbar_wait(bar_dq, it & 1, abort_flag, a.status, CB_ERR_WAIT_TMEM_FULL);
+    tc_fence_after();
+    if (tid == 0 && ok && it + 1 < n_it) load_q(it + 1);                // Q / dO of this iteration are consumed
+#pragma unroll
+    for (int c = 0; c < D / 32; ++c) {
+      uint32_t dq[32];
+      tmem_ld_32x32(t_row + C_S + c * 32, dq);
+      tmem_ld_wait();
+      if (row_ok && ok) {
+        float* dst = a.dq_acc + (tq * a.hq + h) * D + c * 32;
+#pragma unroll
+        for (int k = 0; k < 32; k += 4)
+          red_add_v4(dst + k, __uint_as_float(dq[k]), __uint_as_float(dq[k + 1]), __uint_as_float(dq[k + 2]),
+                     __uint_as_float(dq[k + 3]));
+      }
+    }
+    tc_fence_before();
+    if (__syncthreads_or(!ok)) { ok = false; break; }
+  }
+  if (ok) {
+    tc_fence_after();
+    const int kg = jb * 128 + r;                      // my kv row within the document
+    const bool kv_ok = kg < len;
+    const long long tk = start + kg;
+#pragma unroll
+    for (int c = 0; c < D / 32; ++c) {
+      uint32_t dv[32], dk[32];
+      tmem_ld_32x32(t_row + C_DV + c * 32, dv);
+      tmem_ld_32x32(t_row + C_DK + c * 32, dk);
+      tmem_ld_wait();
+      if (kv_ok) {
+        float* pv = a.dv_part + (tk * a.hk + hkv) * D + c * 32;
+        float* pk = a.dk_part + (tk * a.hk + hkv) * D + c * 32;
+#pragma unroll
+        for (int k = 0; k < 32; k += 4) {
+          red_add_v4(pv + k, __uint_as_float(dv[k]), __uint_as_float(dv[k + 1]), __uint_as_float(dv[k + 2]),
+                     __uint_as_float(dv[k + 3]));
+          red_add_v4(pk + k, __uint_as_float(dk[k]), __uint_as_float(dk[k + 1]), __uint_as_float(dk[k + 2]),
+                     __uint_as_float(dk[k + 3]));
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem, TMEM_COLS); }
+}
+
 // dqkv[t] = bf16( dQ | sum over the query heads of a group of dK | same for dV ); one block per token,
 // four consecutive columns per thread (D is a multiple of 4, so a group never straddles heads)
 __global__ void attn_bwd_finalize_kernel(const float* __restrict__ dq_acc, const float* __restrict__ dk_part,
                                          const float* __restrict__ dv_part, bf16* __restrict__ dqkv, long long ld,
-                                         int T, int hq, int hk, int D, const int* __restrict__ cu, int n_docs) {
+                                         int T, int hq, int hk, int D, const int* __restrict__ cu, int n_docs,
+                                         int part_heads) {
+  // part_heads: heads per token in dk_part / dv_part — hq (one partial per query head, summed here) or hk
+  // (already accumulated per kv head by the kernel)
   const long long t = blockIdx.x;
-  const int nq = hq * D, nk = hk * D, g = hq / hk;
+  const int nq = hq * D, nk = hk * D, g = part_heads / hk;
   bf16* out = dqkv + t * ld;
   const bool valid = t < cu[n_docs];                  // padding tokens get zero gradients
   for (int c = threadIdx.x * 4; c < nq + 2 * nk; c += blockDim.x * 4) {
@@ -540,7 +783,7 @@ __global__ void attn_bwd_finalize_kernel(const float* __restrict__ dq_acc, const
       } else {
         const int cc = (c - nq) % nk, which = (c - nq) / nk;
         const int kvh = cc / D, d = cc % D;
-        const float* src = (which == 0 ? dk_part : dv_part) + (t * hq + static_cast<long long>(kvh) * g) * D + d;
+        const float* src = (which == 0 ? dk_part : dv_part) + (t * part_heads + static_cast<long long>(kvh) * g) * D + d;
         for (int i = 0; i < g; ++i) {
           const float4 x = *reinterpret_cast<const float4*>(src + static_cast<long long>(i) * D);
           v.x += x.x; v.y += x.y; v.z += x.z; v.w += x.w;
@@ -628,17 +871,22 @@ int cb_attn_bwd(const void* q, const void* k, const void* v, const void* o, cons
   a.lse = const_cast<float*>(lse); a.delta = delta; a.dq_acc = dq_acc; a.dk_part = dk_part; a.dv_part = dv_part;
   a.status = status;
   dim3 grid((T + 127) / 128 + n_docs, hq);
+  int part_heads = hq;
   if (D == 64) {
+    // two CTAs per SM; dK / dV accumulate per kv head with red.add, so those buffers start from zero
     static bool cfg = false;
-    if (!cfg) { e = set_smem(cb::attn_bwd_kernel<64>, cb::BwdSmem<64>::TOTAL); if (e) return e; cfg = true; }
-    cb::attn_bwd_kernel<64><<<grid, cb::ATT_THREADS, cb::BwdSmem<64>::TOTAL, s>>>(mq, mk, mv, mdo, a);
+    if (!cfg) { e = set_smem(cb::attn_bwd2_kernel<64>, cb::Bwd2Smem<64>::TOTAL); if (e) return e; cfg = true; }
+    part_heads = hk;
+    CB_CHECK_CUDA(cudaMemsetAsync(dk_part, 0, sizeof(float) * static_cast<size_t>(T) * hk * D, s));
+    CB_CHECK_CUDA(cudaMemsetAsync(dv_part, 0, sizeof(float) * static_cast<size_t>(T) * hk * D, s));
+    cb::attn_bwd2_kernel<64><<<grid, cb::ATT_THREADS, cb::Bwd2Smem<64>::TOTAL, s>>>(mq, mk, mv, mdo, a);
   } else {
     static bool cfg = false;
     if (!cfg) { e = set_smem(cb::attn_bwd_kernel<128>, cb::BwdSmem<128>::TOTAL); if (e) return e; cfg = true; }
     cb::attn_bwd_kernel<128><<<grid, cb::ATT_THREADS, cb::BwdSmem<128>::TOTAL, s>>>(mq, mk, mv, mdo, a);
   }
   cb::attn_bwd_finalize_kernel<<<T, 128, 0, s>>>(dq_acc, dk_part, dv_part, static_cast<cb::bf16*>(dqkv), ld_dqkv, T,
-                                                  hq, hk, D, cu, n_docs);
+                                                  hq, hk, D, cu, n_docs, part_heads);
   return static_cast<int>(cudaGetLastError());
 }
 
