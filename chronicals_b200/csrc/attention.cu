@@ -24,6 +24,7 @@
 namespace cb {
 
 constexpr int ATT_THREADS = 128;
+constexpr int BWD2_THREADS = 256;   // backward variant with two threads per score row
 constexpr float LOG2E = 1.4426950408889634f;
 
 struct AttnArgs {
@@ -560,7 +561,7 @@ __device__ __forceinline__ void load_row_chunk32(const uint8_t* base, int r, int
 }
 
 template <int D>
-__global__ void __launch_bounds__(ATT_THREADS, 2)
+__global__ void __launch_bounds__(BWD2_THREADS, 2)
 attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO, const AttnArgs a) {
   using L = Bwd2Smem<D>;
@@ -591,7 +592,10 @@ attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_full + 5);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
+  // 8 warps: warps w and w + 4 own the same 32 TMEM lanes (score rows) and split the columns in halves,
+  // which doubles the number of warps available to hide TMEM / shared-memory latency
   const int tid = threadIdx.x, warp = tid >> 5;
+  const int q4 = warp & 3, half = warp >> 2;
   if (tid == 0) {
     mbar_init(q_full, 1); mbar_init(bar_kv, 1); mbar_init(bar_s, 1); mbar_init(bar_dp, 1); mbar_init(bar_dq, 1);
     mbar_fence_init();
@@ -604,7 +608,7 @@ attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t t_row = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+  const uint32_t t_row = tmem + (static_cast<uint32_t>(q4 * 32) << 16);
 
   const int kv_row0 = start + jb * 128;
   const int n_it = nblk - jb;
@@ -630,7 +634,7 @@ attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     ok &= mbar_wait(bar_kv, 0, abort_flag, a.status, CB_ERR_WAIT_FULL);
   }
 
-  const int r = tid;
+  const int r = q4 * 32 + (tid & 31);
   const float sl2 = a.scale * LOG2E;
   const uint32_t kA = smem_u32(sK), vA = smem_u32(sV), pA = smem_u32(sP), qA = smem_u32(sQ), doA = smem_u32(sdO);
 
@@ -656,7 +660,7 @@ attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     ok &= mbar_wait(bar_s, it & 1, abort_flag, a.status, CB_ERR_WAIT_TMEM_FULL);
     tc_fence_after();
 #pragma unroll 1
-    for (int c = 0; c < 4; ++c) {
+    for (int c = half * 2; c < half * 2 + 2; ++c) {
       uint32_t s[32];
       float p[32];
       tmem_ld_32x32(t_row + C_S + c * 32, s);
@@ -686,7 +690,7 @@ attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     ok &= mbar_wait(bar_dp, it & 1, abort_flag, a.status, CB_ERR_WAIT_TMEM_FULL);
     tc_fence_after();
 #pragma unroll 1
-    for (int c = 0; c < 4; ++c) {
+    for (int c = half * 2; c < half * 2 + 2; ++c) {
       uint32_t dp[32];
       float p[32];
       tmem_ld_32x32(t_row + C_S + c * 32, dp);
@@ -714,7 +718,7 @@ attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     tc_fence_after();
     if (tid == 0 && ok && it + 1 < n_it) load_q(it + 1);                // Q / dO of this iteration are consumed
 #pragma unroll
-    for (int c = 0; c < D / 32; ++c) {
+    for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
       uint32_t dq[32];
       tmem_ld_32x32(t_row + C_S + c * 32, dq);
       tmem_ld_wait();
@@ -735,7 +739,7 @@ attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const bool kv_ok = kg < len;
     const long long tk = start + kg;
 #pragma unroll
-    for (int c = 0; c < D / 32; ++c) {
+    for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
       uint32_t dv[32], dk[32];
       tmem_ld_32x32(t_row + C_DV + c * 32, dv);
       tmem_ld_32x32(t_row + C_DK + c * 32, dk);
@@ -879,7 +883,7 @@ int cb_attn_bwd(const void* q, const void* k, const void* v, const void* o, cons
     part_heads = hk;
     CB_CHECK_CUDA(cudaMemsetAsync(dk_part, 0, sizeof(float) * static_cast<size_t>(T) * hk * D, s));
     CB_CHECK_CUDA(cudaMemsetAsync(dv_part, 0, sizeof(float) * static_cast<size_t>(T) * hk * D, s));
-    cb::attn_bwd2_kernel<64><<<grid, cb::ATT_THREADS, cb::Bwd2Smem<64>::TOTAL, s>>>(mq, mk, mv, mdo, a);
+    cb::attn_bwd2_kernel<64><<<grid, cb::BWD2_THREADS, cb::Bwd2Smem<64>::TOTAL, s>>>(mq, mk, mv, mdo, a);
   } else {
     static bool cfg = false;
     if (!cfg) { e = set_smem(cb::attn_bwd_kernel<128>, cb::BwdSmem<128>::TOTAL); if (e) return e; cfg = true; }
