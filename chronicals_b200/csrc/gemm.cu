@@ -75,6 +75,10 @@ struct GemmArgs {
   // stores each tile through push_c[owner] (a peer mapping, pre-offset so that the global row indexes it)
   unsigned long long push_c[16];
   int push_blocks;
+  // ---- split-K (skinny outputs with a long K): items beyond items_per_ksplit repeat the tiles for the next
+  // K range; partial tiles are added into a zero-initialised fp32 C with red.global.add
+  int items_per_ksplit;           // 0: no split
+  int kb_per_split;
 };
 
 template <int BLOCK_N, int STAGES>
@@ -141,7 +145,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int item = blockIdx.x; item < g.num_items && ok; item += gridDim.x) {
+      for (int item0 = blockIdx.x; item0 < g.num_items && ok; item0 += gridDim.x) {
+        const int ks = g.items_per_ksplit > 0 ? item0 / g.items_per_ksplit : 0;
+        const int item = item0 - ks * g.items_per_ksplit;
+        const int kb0 = g.items_per_ksplit > 0 ? ks * g.kb_per_split : 0;
+        const int kb1 = g.items_per_ksplit > 0 ? min(num_kb, kb0 + g.kb_per_split) : num_kb;
         int m_blk = item % g.num_m_blocks + g.rot_blocks;
         if (m_blk >= g.num_m_blocks) m_blk -= g.num_m_blocks;
         const int split = item / g.num_m_blocks;
@@ -171,7 +179,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
         }
         for (int nt = nt0; nt < nt1 && ok; ++nt) {
-          for (int kb = 0; kb < num_kb; ++kb) {
+          for (int kb = kb0; kb < kb1; ++kb) {
             if (!mbar_wait(empty + stage, phase ^ 1, abort_flag, g.status, CB_ERR_WAIT_EMPTY)) {
               ok = false;
               break;
@@ -208,7 +216,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       uint32_t phase = 0;
       uint32_t tile_cnt = 0;
       bool ok = true;
-      for (int item = blockIdx.x; item < g.num_items && ok; item += gridDim.x) {
+      for (int item0 = blockIdx.x; item0 < g.num_items && ok; item0 += gridDim.x) {
+        const int ks = g.items_per_ksplit > 0 ? item0 / g.items_per_ksplit : 0;
+        const int item = item0 - ks * g.items_per_ksplit;
+        const int kb0 = g.items_per_ksplit > 0 ? ks * g.kb_per_split : 0;
+        const int kb1 = g.items_per_ksplit > 0 ? min(num_kb, kb0 + g.kb_per_split) : num_kb;
         const int split = item / g.num_m_blocks;
         const int nt0 = split * g.tiles_per_item;
         const int nt1 = min(nt0 + g.tiles_per_item, g.num_n_tiles);
@@ -221,7 +233,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
-          for (int kb = 0; kb < num_kb; ++kb) {
+          for (int kb = kb0; kb < kb1; ++kb) {
             if (!mbar_wait(full + stage, phase, abort_flag, g.status, CB_ERR_WAIT_FULL)) {
               ok = false;
               break;
@@ -235,7 +247,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                                           : umma_smem_desc(a_base + k * 32, 16, 1024);
               const uint64_t bdesc = B_MN ? umma_smem_desc(b_base + k * 2048, 8192, 1024)
                                           : umma_smem_desc(b_base + k * 32, 16, 1024);
-              umma_f16_ss(d_tmem, adesc, bdesc, IDESC, (kb | k) != 0 ? 1u : 0u);
+              umma_f16_ss(d_tmem, adesc, bdesc, IDESC, (kb != kb0 || k != 0) ? 1u : 0u);
             }
             umma_commit(empty + stage);  // frees the smem stage once these MMAs retire
             if (++stage == STAGES) {
@@ -253,7 +265,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const int row_in_tile = q * 32 + lane;
     uint32_t tile_cnt = 0;
     bool ok = true;
-    for (int item = blockIdx.x; item < g.num_items && ok; item += gridDim.x) {
+    for (int item0 = blockIdx.x; item0 < g.num_items && ok; item0 += gridDim.x) {
+      const int item = g.items_per_ksplit > 0 ? item0 % g.items_per_ksplit : item0;
       int m_blk = item % g.num_m_blocks + g.rot_blocks;
       if (m_blk >= g.num_m_blocks) m_blk -= g.num_m_blocks;
       const int split = item / g.num_m_blocks;
@@ -355,9 +368,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                       if (col0 + j < g.N) v[j] += cp[j];
                   } else {
                     const bf16* cp = reinterpret_cast<const bf16*>(g.C) + static_cast<long long>(row) * g.ldc + col0;
+                    if (col0 + 32 <= g.N && (reinterpret_cast<uintptr_t>(cp) & 15) == 0) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                      if (col0 + j < g.N) v[j] += __bfloat162float(cp[j]);
+                      for (int j = 0; j < 4; ++j) {
+                        const uint4 u = reinterpret_cast<const uint4*>(cp)[j];
+                        const float2 a0 = unpack_bf16x2(u.x), a1 = unpack_bf16x2(u.y);
+                        const float2 a2 = unpack_bf16x2(u.z), a3 = unpack_bf16x2(u.w);
+                        v[8 * j + 0] += a0.x; v[8 * j + 1] += a0.y; v[8 * j + 2] += a1.x; v[8 * j + 3] += a1.y;
+                        v[8 * j + 4] += a2.x; v[8 * j + 5] += a2.y; v[8 * j + 6] += a3.x; v[8 * j + 7] += a3.y;
+                      }
+                    } else {
+#pragma unroll
+                      for (int j = 0; j < 32; ++j)
+                        if (col0 + j < g.N) v[j] += __bfloat162float(cp[j]);
+                    }
                   }
                 }
               }
@@ -477,7 +501,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     if (full_chunk || col0 + j < g.N) v[j] += __bfloat162float(ap[j]);
                 }
               }
-              if (g.out_fp32) {
+              if (g.out_fp32 && g.items_per_ksplit > 0) {
+                float* cp = reinterpret_cast<float*>(g.C) + static_cast<long long>(row) * g.ldc + col0;
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (full_chunk || col0 + j < g.N) atomicAdd(cp + j, v[j]);   // partial sums of the K ranges
+              } else if (g.out_fp32) {
                 float* cp = reinterpret_cast<float*>(g.C) + static_cast<long long>(row) * g.ldc + col0;
                 const bool vec = full_chunk && ((reinterpret_cast<uintptr_t>(cp) & 15) == 0);
                 if (vec) {
@@ -739,6 +768,39 @@ int cb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, const 
   e = build_out_map(&tc, &g.tma_store, C, M, N, ldc, out_fp32);
   if (e) return e;
   return dispatch<cb::EPI_STORE>(bn, a_mn, b_mn, ta, tb, tc, g, static_cast<cudaStream_t>(stream));
+}
+
+// Split-K GEMM for skinny outputs: C[M,N] (fp32, zeroed here) = A * B^T with the K range cut into pieces so
+// that about one CTA per SM is busy even when the output has only a few tiles (weight gradients of low-rank
+// adapters: M or N of 16..64 with K = tokens).  Partial tiles are summed with red.global.add.
+int cb_gemm_bf16_splitk(const void* A, const void* B, float* C, int M, int N, int K, long long lda, long long ldb,
+                        long long ldc, int a_mn, int b_mn, int* status, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return -1;
+  const int bn = 128;
+  CUtensorMap ta, tb, tc;
+  int e = build_maps(&ta, &tb, A, B, M, N, K, lda, ldb, a_mn, b_mn, bn);
+  if (e) return e;
+  memset(&tc, 0, sizeof(tc));
+  cb::GemmArgs g = {};
+  g.M = M; g.N = N; g.K = K;
+  g.num_m_blocks = (M + 127) / 128;
+  g.num_n_tiles = (N + bn - 1) / bn;
+  g.tiles_per_item = 1;
+  const int tiles = g.num_m_blocks * g.num_n_tiles;
+  const int num_kb = (K + 63) / 64;
+  int splits = num_sms() / tiles;
+  if (splits < 1) splits = 1;
+  if (splits > num_kb) splits = num_kb;
+  g.kb_per_split = (num_kb + splits - 1) / splits;
+  splits = (num_kb + g.kb_per_split - 1) / g.kb_per_split;
+  g.items_per_ksplit = tiles;
+  g.num_items = tiles * splits;
+  g.C = C; g.ldc = ldc; g.out_fp32 = 1;
+  g.tma_store = 0;
+  g.status = status;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  CB_CHECK_CUDA(cudaMemset2DAsync(C, sizeof(float) * ldc, 0, sizeof(float) * N, M, s));
+  return dispatch<cb::EPI_STORE>(bn, a_mn, b_mn, ta, tb, tc, g, s);
 }
 
 // Tensor-parallel variants of cb_gemm_bf16 (bf16 output, no addend / accumulate).

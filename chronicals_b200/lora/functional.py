@@ -34,7 +34,90 @@ def lora_cat_matrices(fl):
     return a_cat, b_big
 
 
+class _FusedLoRAFn(torch.autograd.Function):
+    """One autograd node for a frozen fused projection with per-split adapters (CUDA bf16 path).
+
+    With ``A_cat = [s_1 A_1; s_2 A_2; …]`` (``[R, in]``) and the block-diagonal ``B_big`` (``[out, R]``):
+
+    forward : ``hs = x A_catᵀ``; ``y = x Wᵀ + b (+ res)``; ``y += hs B_bigᵀ`` (K = R, accumulated in place);
+    backward: ``dhs = dy B_big``; ``dx = dy W + dhs A_cat``; ``dA_cat = dhsᵀ x`` and ``dB_big = dyᵀ hs`` by the
+              split-K GEMM (skinny outputs, K = tokens); the frozen ``W`` gets no weight-gradient GEMM.
+    ``ab`` is ``A_1, B_1, A_2, B_2, …`` in split order; ``meta`` carries the output slices and scalings.
+    """
+
+    @staticmethod
+    def forward(ctx, x2, w, bias, res2, meta, *ab):
+        slices, scalings = meta
+        As, Bs = ab[0::2], ab[1::2]
+        a_cat = torch.cat([a * sc for a, sc in zip(As, scalings)], dim=0) if len(As) > 1 else As[0] * scalings[0]
+        R = a_cat.shape[0]
+        contiguous_cover = slices[0].start == 0 and slices[-1].stop == w.shape[0] and all(
+            slices[i].stop == slices[i + 1].start for i in range(len(slices) - 1))
+        if contiguous_cover:
+            b_big = torch.block_diag(*Bs) if len(Bs) > 1 else Bs[0]
+        else:
+            b_big = torch.zeros(w.shape[0], R, dtype=w.dtype, device=w.device)
+            r0 = 0
+            for b, sl in zip(Bs, slices):
+                b_big[sl, r0:r0 + b.shape[1]] = b
+                r0 += b.shape[1]
+        hs = ops.gemm(x2, a_cat)                                      # [T, R], already scaled
+        y = ops.gemm(x2, w, bias=bias, addend=res2)
+        ops.gemm(hs, b_big, out=y, accumulate=True)
+        ctx.save_for_backward(x2, w, a_cat, hs, b_big)
+        ctx.meta = (slices, scalings, [b.shape[1] for b in Bs], bias is not None, res2 is not None)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w, a_cat, hs, b_big = ctx.saved_tensors
+        slices, scalings, ranks, has_bias, has_res = ctx.meta
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dhs = ops.gemm(dy2, b_big, b_mn=True)                               # [T, R]
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = ops.gemm(dy2, w, b_mn=True)                                # frozen base: dX only
+            ops.gemm(dhs, a_cat, b_mn=True, out=dx, accumulate=True)
+        da_cat = ops.gemm_splitk(dhs, x2, a_mn=True, b_mn=True)            # [R, in]  fp32
+        db_big = ops.gemm_splitk(dy2, hs, a_mn=True, b_mn=True)            # [out, R] fp32
+        grads = []
+        r0 = 0
+        for sl, sc, r in zip(slices, scalings, ranks):
+            grads.append((da_cat[r0:r0 + r] * sc).to(dy2.dtype))
+            grads.append(db_big[sl, r0:r0 + r].to(dy2.dtype))
+            r0 += r
+        db = dy2.float().sum(0).to(dy2.dtype) if (has_bias and ctx.needs_input_grad[2]) else None
+        dw = None
+        if ctx.needs_input_grad[1]:                                         # base weight left trainable on purpose
+            dw = ops.gemm(dy2, x2, a_mn=True, b_mn=True)
+        return (dx, dw, db, dy2 if has_res else None, None, *grads)
+
+
+def _fused_path_ok(fl, x: torch.Tensor) -> bool:
+    if not ops._fast(x, fl.weight) or fl.lora_dropout_p > 0:
+        return False
+    sl = fl.split_slices()
+    for s in fl.lora_A:
+        r = fl.lora_A[s].shape[0]
+        if r % 8 or sl[s].start % 8 or (sl[s].stop - sl[s].start) % 8:
+            return False
+    return x.shape[-1] % 8 == 0
+
+
 def fused_lora_forward(fl, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    names = [s for s in fl.splits if s in fl.lora_A]
+    if names and _fused_path_ok(fl, x):
+        x2 = x.reshape(-1, x.shape[-1])
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        res2 = residual.reshape(-1, fl.out_features) if residual is not None else None
+        sl = fl.split_slices()
+        meta = ([sl[s] for s in names], [float(fl.lora_scaling[s]) for s in names])
+        ab = [t for s in names for t in (fl.lora_A[s], fl.lora_B[s])]
+        y = _FusedLoRAFn.apply(x2, fl.weight, fl.bias, res2, meta, *ab)
+        return y if x.dim() == 2 else y.view(*x.shape[:-1], fl.out_features)
     base = ops.linear(x, fl.weight, fl.bias, residual)
     xd = F.dropout(x, fl.lora_dropout_p, training=True) if (fl.lora_dropout_p > 0 and fl.training) else x
     a_cat, b_big = lora_cat_matrices(fl)

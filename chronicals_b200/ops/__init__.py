@@ -18,7 +18,7 @@ from . import ref
 from . import _ext
 
 __all__ = [
-    "linear", "gemm", "rmsnorm", "add_rmsnorm", "swiglu", "geglu", "qk_rope_", "embedding",
+    "linear", "gemm", "gemm_splitk", "rmsnorm", "add_rmsnorm", "swiglu", "geglu", "qk_rope_", "embedding",
     "attention_varlen", "attention_qkv_packed", "linear_cross_entropy", "cross_entropy_logits", "kernels_active",
 ]
 
@@ -82,6 +82,24 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         int(a_mn), int(b_mn), int(out.dtype == torch.float32), int(accumulate), block_n,
         _ext.status_buffer(a.device).data_ptr(), _ext.stream_ptr())
     _ext.check(code, "gemm_bf16")
+    return out
+
+
+def gemm_splitk(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False) -> torch.Tensor:
+    """fp32 ``op(A) @ op(B)^T`` for skinny outputs with a long inner dimension (adapter weight gradients):
+    the K range is split across CTAs and the partial tiles are summed with ``red.global.add``."""
+    M = a.shape[1] if a_mn else a.shape[0]
+    K = a.shape[0] if a_mn else a.shape[1]
+    N = b.shape[1] if b_mn else b.shape[0]
+    if not (_gemm_ok(a) and _gemm_ok(b) and _fast(a, b)):
+        A = a.t() if a_mn else a
+        B = b if b_mn else b.t()
+        return A.float() @ B.float()
+    out = torch.empty(M, N, dtype=torch.float32, device=a.device)
+    code = _ext.lib().cb_gemm_bf16_splitk(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0),
+                                          out.stride(0), int(a_mn), int(b_mn), _ext.status_buffer(a.device).data_ptr(),
+                                          _ext.stream_ptr())
+    _ext.check(code, "gemm_splitk")
     return out
 
 

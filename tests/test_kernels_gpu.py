@@ -317,3 +317,62 @@ def test_fp8_linear_module_runs_kernels_and_matches_reference():
     want = ref.mxfp8_linear(x.detach().float().cpu(), lin.weight.detach().float().cpu(), lin.bias.detach().float().cpu())
     assert (y.float().cpu() - want).abs().max().item() < 0.06 * want.abs().max().item()
     assert x.grad is not None and lin.weight.grad is not None and torch.isfinite(lin.weight.grad.float()).all()
+
+
+def test_fused_lora_projection_matches_reference_formula():
+    """Frozen fused QKV projection with rank-16 adapters on every split: forward, dX, dA, dB against the
+    plain PEFT formula in fp32 (the base weight must receive no gradient)."""
+    from collections import OrderedDict
+    from chronicals_b200.models.decoder import FusedLinear
+    torch.manual_seed(0)
+    T, K = 384, 256
+    fl = FusedLinear(K, OrderedDict(q_proj=256, k_proj=64, v_proj=64), bias=True, dtype=torch.bfloat16, device="cuda")
+    with torch.no_grad():
+        fl.weight.normal_(0, 0.05)
+        fl.bias.normal_(0, 0.1)
+    fl.weight.requires_grad_(False)
+    fl.bias.requires_grad_(False)
+    for s in fl.splits:
+        fl.add_lora(s, 16, 32.0)
+        with torch.no_grad():
+            fl.lora_B[s].normal_(0, 0.05)
+    x = torch.randn(T, K, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    res = torch.randn(T, fl.out_features, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    y = fl(x, res)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    # fp32 oracle
+    xf, rf = x.detach().float().requires_grad_(True), res.detach().float().requires_grad_(True)
+    A = {s: fl.lora_A[s].detach().float().requires_grad_(True) for s in fl.splits}
+    B = {s: fl.lora_B[s].detach().float().requires_grad_(True) for s in fl.splits}
+    base = xf @ fl.weight.float().t() + fl.bias.float() + rf
+    parts = [fl.lora_scaling[s] * (xf @ A[s].t()) @ B[s].t() for s in fl.splits]
+    want = base + torch.cat(parts, dim=1)
+    want.backward(gy.float())
+
+    def close(a, b, tol):
+        return (a.float() - b).abs().max().item() <= tol * (b.abs().max().item() + 1e-6)
+    assert close(y, want.detach(), 2e-2)
+    assert close(x.grad, xf.grad, 3e-2) and close(res.grad, rf.grad, 1e-2)
+    for s in fl.splits:
+        assert close(fl.lora_A[s].grad, A[s].grad, 3e-2), s
+        assert close(fl.lora_B[s].grad, B[s].grad, 3e-2), s
+    assert fl.weight.grad is None
+
+
+@pytest.mark.parametrize("M,N,K,a_mn,b_mn", [(48, 896, 8192, True, True), (1152, 48, 8192, True, True), (16, 16, 300, False, False),
+                                             (200, 130, 4096, False, True)])
+def test_gemm_splitk_matches_fp32(M, N, K, a_mn, b_mn):
+    from chronicals_b200 import ops
+    g = torch.Generator().manual_seed(3)
+    a = torch.randn((K, M) if a_mn else (M, K), generator=g).to(torch.bfloat16)
+    b = torch.randn((K, N) if b_mn else (N, K), generator=g).to(torch.bfloat16)
+    # row pitches must be multiples of 8 elements for the TMA path
+    if (a.shape[1] % 8) or (b.shape[1] % 8):
+        pytest.skip("operand pitch not TMA-addressable")
+    out = ops.gemm_splitk(a.cuda(), b.cuda(), a_mn=a_mn, b_mn=b_mn)
+    A = a.float().t() if a_mn else a.float()
+    B = b.float() if b_mn else b.float().t()
+    want = A @ B
+    assert out.dtype == torch.float32
+    assert (out.cpu() - want).abs().max().item() < 2e-3 * want.abs().max().item() + 1e-3
