@@ -23,7 +23,8 @@ class _AliasFinder:
             mod = importlib.import_module(real)
         except ImportError:
             return None
-        sys.modules[fullname] = mod
+        # (sys.modules[fullname] must not be set here: the import system would then take the real module's
+        # own spec and execute the real module a second time)
         return importlib.util.spec_from_loader(fullname, loader=_AliasLoader(mod))
 
 

@@ -177,3 +177,10 @@ def test_functional_forward_backward_pairs_match_autograd():
     g1 = torch.autograd.grad(yy.sum(), (xx, A, B))
     g2 = torch.autograd.grad(want.sum(), (xx, A, B))
     assert all(torch.allclose(a, b, atol=1e-3) for a, b in zip(g1, g2))
+
+
+def test_alias_package_shares_module_objects():
+    import chronicals.config.config as a
+    import chronicals_b200.config.config as b
+    from chronicals_b200.models import decoder
+    assert a is b and a.ChronicalsConfig is decoder.ChronicalsConfig
