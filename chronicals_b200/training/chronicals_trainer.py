@@ -219,6 +219,21 @@ class ChronicalsTrainer:
             and a.gradient_accumulation_steps == 1 and (self.world_size == 1 or self._sharded_optimizer) \
             and not self.tp_model
         self._active_optimizations["cuda_graphs"] = self.use_cuda_graphs
+        # host-side failure detection: heartbeat over the process-group store, checked before each step
+        self.watchdog = None
+        if self.world_size > 1 and self._get("use_watchdog", True):
+            try:
+                from ..parallel.watchdog import watchdog_from_process_group
+                self.watchdog = watchdog_from_process_group(timeout=float(self._get("watchdog_timeout_s", 120.0)),
+                                                            interval=float(self._get("watchdog_interval_s", 2.0)))
+                if self.watchdog is not None:
+                    self.watchdog.start()
+            except Exception as e:                     # never fatal: the job then relies on collective timeouts
+                print(f"[watchdog] disabled: {e}")
+                self.watchdog = None
+        # tracing: NVTX ranges around the phases and an optional torch.profiler chrome trace
+        self._nvtx = bool(a.enable_profiling) and on_gpu
+        self._trace = None
         self._log_file = None
         if self.rank == 0 and self._get("log_jsonl", True):
             os.makedirs(a.output_dir, exist_ok=True)
@@ -343,6 +358,18 @@ class ChronicalsTrainer:
         Returns the detached loss tensor on the device (no host synchronisation)."""
         if self.use_cuda_graphs and do_step:
             return self._graphed_step(batch)
+        if self._nvtx:
+            nvtx = torch.cuda.nvtx
+            nvtx.range_push("data")
+            inp = self._prepare_inputs(batch)
+            nvtx.range_pop()
+            nvtx.range_push("forward")
+            loss = self._forward_loss(inp)
+            nvtx.range_pop()
+            nvtx.range_push("backward+optimizer" if do_step else "backward")
+            self._backward_and_maybe_step(loss, do_step)
+            nvtx.range_pop()
+            return loss.detach()
         inp = self._prepare_inputs(batch)
         loss = self._forward_loss(inp)
         self._backward_and_maybe_step(loss, do_step)
@@ -440,7 +467,13 @@ class ChronicalsTrainer:
         try:
             for epoch in range(start_epoch, max(1, a.num_train_epochs)):
                 self.state.epoch = epoch
-                avg = self._train_epoch_fast(epoch, skip_micro if epoch == start_epoch else 0)
+                try:
+                    avg = self._train_epoch_fast(epoch, skip_micro if epoch == start_epoch else 0)
+                except Exception as e:
+                    if self.watchdog is not None:                      # let the peers stop launching work
+                        self.watchdog.report_failure(e)
+                        self.watchdog.stop()
+                    raise
                 if a.max_steps > 0 and self.state.global_step >= a.max_steps:
                     break
                 if self.eval_dataloader is not None:
@@ -453,6 +486,12 @@ class ChronicalsTrainer:
         finally:
             if a.disable_gc_during_training and gc_was:
                 gc.enable()
+            if self._trace not in (None, False):
+                try:
+                    self._trace.stop()
+                except Exception:
+                    pass
+                self._trace = None
         self.state.total_time += time.perf_counter() - t_start
         if a.save_steps is not None and a.save_steps >= 0 and self._get("save_final", True):
             self.save_checkpoint("final")
@@ -494,11 +533,26 @@ class ChronicalsTrainer:
             if micro_in_epoch <= skip_micro:
                 continue
             do_step = (micro_in_epoch % accum) == 0
-            if self.profiler is not None:
-                with self.profiler.profile_step():
+            if self.watchdog is not None:
+                try:
+                    self.watchdog.check(self.state.global_step)     # before the first launch of the step
+                except Exception as e:
+                    self._on_peer_failure(e)
+                    raise
+            if self._trace is None and a.enable_profiling and self.rank == 0:
+                self._trace = self._start_trace()
+            try:
+                if self.profiler is not None:
+                    with self.profiler.profile_step():
+                        loss = self.training_step(batch, do_step)
+                else:
                     loss = self.training_step(batch, do_step)
-            else:
-                loss = self.training_step(batch, do_step)
+            except Exception as e:
+                if self.watchdog is not None:
+                    self.watchdog.report_failure(e)                # peers leave at their next check
+                raise
+            if self._trace not in (None, False):
+                self._trace.step()
             losses_since_log.append(loss)
             f = _batch_fields(batch)
             ntok = int(f["input_ids"].numel())
@@ -544,6 +598,40 @@ class ChronicalsTrainer:
         return epoch_loss_sum / max(1, epoch_loss_n)
 
     _train_epoch = _train_epoch_fast
+
+    def _start_trace(self):
+        """torch.profiler schedule from the ``profiling_*`` flags; writes a chrome trace per active window."""
+        a = self.args
+        try:
+            from torch.profiler import ProfilerActivity, profile, schedule, tensorboard_trace_handler
+            os.makedirs(a.profiling_output_dir, exist_ok=True)
+            acts = [ProfilerActivity.CPU] + ([ProfilerActivity.CUDA] if self.device.type == "cuda" else [])
+            prof = profile(activities=acts,
+                           schedule=schedule(wait=a.profiling_wait_steps, warmup=a.profiling_warmup_steps,
+                                             active=a.profiling_active_steps, repeat=1),
+                           on_trace_ready=tensorboard_trace_handler(a.profiling_output_dir),
+                           record_shapes=a.profiling_record_shapes, profile_memory=a.profiling_profile_memory,
+                           with_stack=a.profiling_with_stack, with_flops=a.profiling_with_flops)
+            prof.start()
+            return prof
+        except Exception as e:
+            print(f"[profiling] torch.profiler trace disabled: {e}")
+            return False
+
+    def _on_peer_failure(self, exc: Exception) -> None:
+        """A peer stopped answering or reported an error: launch nothing more, keep this rank's state."""
+        print(f"[rank {self.rank}] peer failure detected before step {self.state.global_step}: {exc}")
+        try:
+            out = os.path.join(self.args.output_dir, f"emergency-{self.state.global_step}")
+            os.makedirs(out, exist_ok=True)
+            st = {k: v for k, v in asdict(self.state).items() if k != "log_history"}
+            ckpt_io.save_training_state(out, self.optimizer, self.scheduler if self.rank == 0 else None, st,
+                                        self.state.log_history, self.rank, self.world_size)
+            if self.rank == 0 and not self.tp_model:
+                ckpt_io.save_model(self.model, out, safe=bool(self._get("save_safetensors", True)))
+            print(f"[rank {self.rank}] emergency state written to {out}")
+        except Exception as e:                                         # best effort
+            print(f"[rank {self.rank}] emergency checkpoint failed: {e}")
 
     def _log_step_fast(self, loss: float, tokens_per_sec: float) -> None:
         a = self.args

@@ -72,3 +72,22 @@ def test_gloo_rank_leaves_between_steps(tmp_path):
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
     res = json.load(open(out))
     assert res["detected_rank"] == 1 and res["steps_done"] == 2, (res, r.stderr[-1500:])
+
+
+def test_trainer_stops_launching_after_peer_failure(tmp_path):
+    """A rank that raises between steps publishes the error; the surviving rank notices at its next pre-step
+    check, writes an emergency state directory and raises ``PeerFailure`` instead of hanging in a collective."""
+    import json
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = os.path.join(str(tmp_path), "wd")
+    env = dict(os.environ, PYTHONPATH=root, CUDA_VISIBLE_DEVICES="")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29549", os.path.join(root, "tests", "_trainer_watchdog_worker.py"), out]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    assert os.path.exists(out + ".0.json") and os.path.exists(out + ".1.json"), r.stdout[-1500:] + r.stderr[-3000:]
+    r0, r1 = json.load(open(out + ".0.json")), json.load(open(out + ".1.json"))
+    assert r1["outcome"].startswith("raised:injected")
+    assert r0["outcome"] == "peer_failure" and r0["failed_rank"] == 1 and r0["step"] == 2, r0
+    assert any(n.startswith("emergency-") for n in r0["emergency"]), r0
