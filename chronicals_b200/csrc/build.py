@@ -30,6 +30,12 @@ NVCC_FLAGS = [
 ]
 
 
+def _flags() -> List[str]:
+    """``CHRONICALS_DEBUG_BOUNDS=1`` in the environment compiles the extra index checks in."""
+    extra = ["-DCHRONICALS_DEBUG_BOUNDS"] if os.environ.get("CHRONICALS_DEBUG_BOUNDS", "0") == "1" else []
+    return NVCC_FLAGS + extra
+
+
 def sources() -> List[str]:
     return sorted(os.path.join(HERE, f) for f in os.listdir(HERE) if f.endswith(".cu"))
 
@@ -44,7 +50,7 @@ def source_hash() -> str:
         h.update(os.path.basename(path).encode())
         with open(path, "rb") as f:
             h.update(f.read())
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join(_flags()).encode())
     return h.hexdigest()
 
 
@@ -64,7 +70,7 @@ def nvcc_path() -> str:
 
 def _compile_one(nvcc: str, src: str, verbose: bool) -> str:
     obj = os.path.join(OBJ_DIR, os.path.basename(src)[:-3] + ".o")
-    cmd = [nvcc, *NVCC_FLAGS, "-I", HERE, "-c", src, "-o", obj]
+    cmd = [nvcc, *_flags(), "-I", HERE, "-c", src, "-o", obj]
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")

@@ -9,6 +9,23 @@
 // patches in.
 #include "common.cuh"
 
+// ---- optional index checks (compile with -DCHRONICALS_DEBUG_BOUNDS, e.g. CHRONICALS_DEBUG_BOUNDS=1 in the
+// environment of csrc/build.py).  Release kernels already clamp or mask every gathered index; the debug build
+// additionally records the first offending value in a device word that cb_debug_word() reads back.  Nothing
+// traps: the kernel carries on with the clamped index.
+enum { CB_DBG_TOKEN_ID = 401, CB_DBG_ROPE_POSITION = 402, CB_DBG_LABEL = 403 };
+__device__ long long g_cb_debug_word[2] = {0, 0};
+#ifdef CHRONICALS_DEBUG_BOUNDS
+#define CB_DEBUG_CHECK(cond, code, value)                                                            \
+  do {                                                                                               \
+    if (!(cond) && atomicCAS(reinterpret_cast<unsigned long long*>(&g_cb_debug_word[0]), 0ull,       \
+                             static_cast<unsigned long long>(code)) == 0ull)                        \
+      g_cb_debug_word[1] = static_cast<long long>(value);                                            \
+  } while (0)
+#else
+#define CB_DEBUG_CHECK(cond, code, value) do { } while (0)
+#endif
+
 namespace cb {
 
 constexpr int EW_THREADS = 256;
@@ -296,7 +313,7 @@ template <int INTERLEAVED>
 __global__ void __launch_bounds__(EW_THREADS)
 qk_rope_kernel(bf16* __restrict__ q, bf16* __restrict__ k, const float* __restrict__ cosT,
                const float* __restrict__ sinT, const long long* __restrict__ pos, long long T, int hq, int hk, int D,
-               long long ldq, long long ldk, float sign) {
+               long long ldq, long long ldk, float sign, long long table_len) {
   const int half = D / 2;
   const int tph = half / 8;  // threads per head
   const int heads = hq + hk;
@@ -306,7 +323,9 @@ qk_rope_kernel(bf16* __restrict__ q, bf16* __restrict__ k, const float* __restri
     const int c = static_cast<int>(idx % tph);
     const int hh = static_cast<int>((idx / tph) % heads);
     const long long t = idx / (static_cast<long long>(tph) * heads);
-    const long long p = pos ? pos[t] : t;
+    long long p = pos ? pos[t] : t;
+    CB_DEBUG_CHECK(p >= 0 && p < table_len, CB_DBG_ROPE_POSITION, p);
+    p = p < 0 ? 0 : (p >= table_len ? table_len - 1 : p);   // never read outside the cos/sin tables
     bf16* base = hh < hq ? q + t * ldq + static_cast<long long>(hh) * D : k + t * ldk + static_cast<long long>(hh - hq) * D;
     const float4* cp = reinterpret_cast<const float4*>(cosT + p * half + c * 8);
     const float4* sp = reinterpret_cast<const float4*>(sinT + p * half + c * 8);
@@ -355,6 +374,7 @@ embedding_fwd_kernel(const long long* __restrict__ ids, const bf16* __restrict__
   const int nvec = N / 8;
   for (long long t = blockIdx.x; t < T; t += gridDim.x) {
     long long id = ids[t];
+    CB_DEBUG_CHECK(id >= 0 && id < V, CB_DBG_TOKEN_ID, id);
     if (id < 0 || id >= V) id = 0;   // out-of-range ids read row 0 instead of faulting
     const uint4* src = reinterpret_cast<const uint4*>(table + id * N);
     uint4* dst = reinterpret_cast<uint4*>(out + t * N);
@@ -502,6 +522,22 @@ extern "C" {
 
 int cb_rmsnorm_max_n() { return 256 * 4 * 8; }
 // number of [N] fp32 partial rows the backward writes (size the scratch as blocks * N floats)
+// Debug-build index checks: out[0] = first recorded code (0 = none), out[1] = offending value; clears the word.
+// Returns 1 when the library was compiled with the checks, 0 otherwise.
+int cb_debug_word(long long* out2) {
+  long long h[2] = {0, 0};
+  if (cudaMemcpyFromSymbol(h, g_cb_debug_word, sizeof(h)) != cudaSuccess) return -1;
+  out2[0] = h[0];
+  out2[1] = h[1];
+  const long long z[2] = {0, 0};
+  cudaMemcpyToSymbol(g_cb_debug_word, z, sizeof(z));
+#ifdef CHRONICALS_DEBUG_BOUNDS
+  return 1;
+#else
+  return 0;
+#endif
+}
+
 int cb_rmsnorm_bwd_blocks(int M, int N) {
   const int tpr = pick_tpr(N);
   if (tpr == 0) return 0;
@@ -573,15 +609,17 @@ int cb_glu_bwd(const void* dout, const void* gate, const void* up, void* dgate, 
   return static_cast<int>(cudaGetLastError());
 }
 
+// table_len: number of positions in the cos/sin tables; positions outside [0, table_len) are clamped.
 int cb_qk_rope(void* q, void* k, const float* cosT, const float* sinT, const long long* pos, long long T, int hq,
-               int hk, int D, long long ldq, long long ldk, int interleaved, int inverse, void* stream) {
-  if (D % 16 != 0 || ldq % 8 != 0 || ldk % 8 != 0) return -1;
+               int hk, int D, long long ldq, long long ldk, int interleaved, int inverse, long long table_len,
+               void* stream) {
+  if (D % 16 != 0 || ldq % 8 != 0 || ldk % 8 != 0 || table_len <= 0) return -1;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const long long total = T * (hq + hk) * (D / 16);
   const int grid = grid_for(total, cb::EW_THREADS, 16);
   const float sign = inverse ? -1.f : 1.f;
-  if (interleaved) cb::qk_rope_kernel<1><<<grid, cb::EW_THREADS, 0, s>>>(static_cast<cb::bf16*>(q), static_cast<cb::bf16*>(k), cosT, sinT, pos, T, hq, hk, D, ldq, ldk, sign);
-  else cb::qk_rope_kernel<0><<<grid, cb::EW_THREADS, 0, s>>>(static_cast<cb::bf16*>(q), static_cast<cb::bf16*>(k), cosT, sinT, pos, T, hq, hk, D, ldq, ldk, sign);
+  if (interleaved) cb::qk_rope_kernel<1><<<grid, cb::EW_THREADS, 0, s>>>(static_cast<cb::bf16*>(q), static_cast<cb::bf16*>(k), cosT, sinT, pos, T, hq, hk, D, ldq, ldk, sign, table_len);
+  else cb::qk_rope_kernel<0><<<grid, cb::EW_THREADS, 0, s>>>(static_cast<cb::bf16*>(q), static_cast<cb::bf16*>(k), cosT, sinT, pos, T, hq, hk, D, ldq, ldk, sign, table_len);
   return static_cast<int>(cudaGetLastError());
 }
 

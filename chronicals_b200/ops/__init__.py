@@ -270,7 +270,7 @@ def _rope_launch(qkv: torch.Tensor, cos, sin, pos, hq, hk, d, interleaved, inver
     T = qkv.shape[0]
     ld = qkv.stride(0)
     code = _ext.lib().cb_qk_rope(qkv.data_ptr(), qkv.data_ptr() + 2 * hq * d, cos.data_ptr(), sin.data_ptr(),
-                                 _ext.ptr(pos), T, hq, hk, d, ld, ld, int(interleaved), int(inverse),
+                                 _ext.ptr(pos), T, hq, hk, d, ld, ld, int(interleaved), int(inverse), cos.shape[0],
                                  _ext.stream_ptr())
     _ext.check(code, "qk_rope")
 

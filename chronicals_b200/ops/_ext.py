@@ -39,7 +39,8 @@ _PROTOTYPES = {
     "cb_rmsnorm_bwd": [P, P, P, P, P, P, P, P, I, I, F, I, P],
     "cb_glu_fwd": [P, P, P, L, I, L, L, I, P],
     "cb_glu_bwd": [P, P, P, P, P, L, I, L, L, L, I, P],
-    "cb_qk_rope": [P, P, P, P, P, L, I, I, I, L, L, I, I, P],
+    "cb_qk_rope": [P, P, P, P, P, L, I, I, I, L, L, I, I, L, P],
+    "cb_debug_word": [P],
     "cb_embedding_fwd": [P, P, P, L, I, L, P],
     "cb_embedding_bwd": [P, P, P, P, L, I, L, I, P],
     "cb_ce_logits": [P, P, L, L, I, I, L, F, F, P, P, P],
@@ -75,6 +76,14 @@ class force_reference:
         global _FORCE_REFERENCE
         _FORCE_REFERENCE = self._prev
         return False
+
+
+def debug_word():
+    """``(compiled_with_checks, code, value)`` of the optional index checks (``CHRONICALS_DEBUG_BOUNDS=1`` build):
+    code 401 = token id, 402 = rotary position, 403 = label out of range; reading clears the word."""
+    buf = (ctypes.c_longlong * 2)()
+    rc = lib().cb_debug_word(buf)
+    return rc == 1, int(buf[0]), int(buf[1])
 
 
 def reference_forced() -> bool:

@@ -376,3 +376,20 @@ def test_gemm_splitk_matches_fp32(M, N, K, a_mn, b_mn):
     want = A @ B
     assert out.dtype == torch.float32
     assert (out.cpu() - want).abs().max().item() < 2e-3 * want.abs().max().item() + 1e-3
+
+
+def test_rope_positions_beyond_table_are_clamped_not_read_out_of_bounds():
+    """Positions outside the cos/sin tables use the last table row (no out-of-bounds read); the optional
+    debug build would additionally record code 402."""
+    from chronicals_b200 import ops
+    from chronicals_b200.ops import _ext, ref
+    T, hq, hk, d = 64, 2, 1, 64
+    cos, sin = ref.rope_cache(32, d, 1e4, device="cuda")
+    qkv = torch.randn(T, (hq + 2 * hk) * d, device="cuda", dtype=torch.bfloat16)
+    pos = torch.arange(T, device="cuda")                      # half of them beyond the 32-row table
+    out = ops.qk_rope_(qkv.clone(), cos, sin, pos, hq, hk, d)
+    want = ops.qk_rope_(qkv.clone(), cos, sin, pos.clamp(max=31), hq, hk, d)
+    torch.cuda.synchronize()
+    assert torch.equal(out, want)
+    compiled, code, _ = _ext.debug_word()
+    assert (code == 402) if compiled else (code == 0)
