@@ -128,6 +128,12 @@ class SymmetricBuffer:
             self._block = _DeviceBlock(out.value, nbytes, True)
             raw = torch.as_tensor(self._block, device=dev)
             self.local = raw[:used].view(dtype)
+            # canary words behind the payload: a peer kernel that writes past the end of this buffer
+            # shows up in canary_ok() (checked on the host, between steps)
+            guard_at = (used + 255) // 256 * 256
+            self._guard = raw[guard_at:guard_at + 256] if guard_at + 256 <= nbytes else None
+            if self._guard is not None:
+                self._guard.fill_(0xA5)
             handle = ctypes.create_string_buffer(64)
             code = lib.cb_ipc_export(ctypes.c_void_p(self._block.ptr), handle)
             if code != 0:
@@ -148,6 +154,10 @@ class SymmetricBuffer:
                 ptrs.append(p.value)
         self.ptrs = (ctypes.c_ulonglong * self.world)(*ptrs)
         dist.barrier(group=group)
+
+    def canary_ok(self) -> bool:
+        """True while the 256 guard bytes behind the payload still hold their pattern (host-side check)."""
+        return self._guard is None or bool((self._guard == 0xA5).all().item())
 
     def close(self) -> None:
         """Unmap the peers' blocks and free the local one (after a barrier, so nobody still reads it)."""

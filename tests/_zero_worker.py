@@ -58,6 +58,9 @@ def main():
     dist.all_reduce(lo, op=dist.ReduceOp.MIN)
     dist.all_reduce(hi, op=dist.ReduceOp.MAX)
     res["ranks_identical"] = bool(torch.equal(lo, hi))
+    # canary words behind every symmetric buffer are intact and the barrier epochs only ever grew
+    res["canaries_ok"] = all(b.canary_ok() for b in (o_my.param_buf, o_my.grad_buf, o_my.ctx.pad, ctx.pad))
+    res["epochs"] = [int(ctx.epoch_ctr.item()), int(o_my.ctx.epoch_ctr.item())]
 
     # ---- bounded wait: a barrier nobody else joins gives up with an error status instead of hanging
     if os.environ.get("CB_TEST_TIMEOUT", "1") == "1":

@@ -29,6 +29,7 @@ def test_symmetric_barrier_sharded_adamw_and_bounded_wait(tmp_path):
     assert res["adamw_max_err"] < 2e-2, res
     assert abs(res["norm"][0] - res["norm"][1]) < 2e-2 * max(1.0, res["norm"][0])
     assert res["ranks_identical"]
+    assert res["canaries_ok"] and res["epochs"] == [6, 12], res          # 1 + 5 barriers; 3 per optimizer step x 4
     assert res.get("timeout_detected") is True
 
 
