@@ -1,0 +1,351 @@
+// Two-CTA tcgen05 GEMM: C[M,N] = A[M,K] * B[N,K]^T (bf16 in / out, fp32 accumulation) with one
+// 256 x 256 output tile per CTA pair (`tcgen05.mma.cta_group::2`).
+//
+// Why: with one CTA per tile (gemm.cu, 128 x 256) every k-block of 64 needs 48 KB of operands per 512 MMA
+// cycles and SM; the shared-memory ring then holds about one memory latency of data and every L2 miss reaches
+// the MMA issuer.  A CTA pair shares the B tile: each CTA loads its own 128 rows of A and only HALF of the
+// 256 rows of B (32 KB per k-block and SM), the tensor cores of both SMs read the two halves from both
+// shared memories, and the ring is six stages deep instead of four.
+//
+// Structure (192 threads per CTA, cluster of 2 along x):
+//   warp 0      TMA producer of this CTA's A rows and B half (ordinary, non-multicast TMA loads into the CTA's
+//               own shared memory, signalling the CTA's own `full` barrier)
+//   warp 1      leader CTA (rank 0): issues the MMAs for the pair once its own stage AND the peer's stage are
+//               full; `tcgen05.commit ... multicast::cluster` releases the stage / publishes the accumulator in
+//               both CTAs.  Peer CTA (rank 1): relays "my stage is full" to the leader with a remote mbarrier
+//               arrive.
+//   warps 2-5   epilogue: each CTA drains its own 128 TMEM lanes (its 128 rows of the 256-row tile) through a
+//               swizzled staging buffer and TMA stores; accumulators are double buffered (2 x 256 columns).
+// Every wait is bounded (common.cuh); a CTA that gives up still reaches the closing cluster barrier, and so
+// does its peer once its own waits expire, so the pair always leaves together.
+//
+// The reference has no GEMM of its own (cuBLAS behind nn.Linear); nothing to cite.
+#include <cstring>
+#include "common.cuh"
+#include "host_common.h"
+
+namespace cb2 {
+using namespace cb;
+
+constexpr int BM = 128;          // rows of A (and of the accumulator) per CTA
+constexpr int BN = 256;          // columns of the pair's tile
+constexpr int BNH = 128;         // rows of B loaded by each CTA
+constexpr int BK = 64;
+constexpr int STAGES = 6;
+constexpr int THREADS = 192;
+constexpr int A_BYTES = BM * BK * 2;
+constexpr int B_BYTES = BNH * BK * 2;
+constexpr int STG_OFFSET = STAGES * (A_BYTES + B_BYTES);
+constexpr int BAR_OFFSET = STG_OFFSET + 4 * 8192;
+constexpr int SMEM_TOTAL = BAR_OFFSET + 512 + 1024;
+
+struct Args {
+  int M, N, K;
+  int num_m_pairs, num_n_tiles, num_tiles;
+  int* status;
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t local_smem_addr, uint32_t cta_rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_smem_addr), "r"(cta_rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_shared_cluster_u32(uint32_t cluster_addr) {
+  uint32_t v;
+  asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(cluster_addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void tmem_alloc_2cta(uint32_t* smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_2cta() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_2cta(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_f16_ss_2cta(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                 uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// arrive on the barrier at this shared-memory offset in both CTAs of the pair once all earlier MMAs are done
+__device__ __forceinline__ void umma_commit_2cta(uint64_t* bar) {
+  const uint16_t mask = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"(mask)
+               : "memory");
+}
+
+template <int NACC>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
+gemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const __grid_constant__ CUtensorMap tmC, const Args g) {
+  constexpr uint32_t TMEM_COLS = NACC * BN;                              // NACC accumulators of 256 columns
+  constexpr uint32_t IDESC = umma_idesc_bf16(2 * BM, BN, 0, 0);          // M = 256 across the pair
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * A_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + BAR_OFFSET);       // my TMA stage landed
+  uint64_t* peer_full = full + STAGES;                                   // (leader) the peer's stage landed
+  uint64_t* empty = peer_full + STAGES;                                  // stage consumed (multicast commit)
+  uint64_t* tfull = empty + STAGES;                                      // accumulator complete (multicast commit)
+  uint64_t* tempty = tfull + 2;                                          // (leader) accumulator drained by both CTAs
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full + s, 1);
+      mbar_init(peer_full + s, 1);
+      mbar_init(empty + s, 1);
+    }
+    for (int a = 0; a < NACC; ++a) {
+      mbar_init(tfull + a, 1);
+      mbar_init(tempty + a, 8);                                          // 4 epilogue warps in each CTA
+    }
+    mbar_fence_init();
+    *abort_flag = (g.status[0] != 0) ? 1 : 0;
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  __syncthreads();
+  cluster_sync_all();                                                    // barriers of both CTAs are initialised
+  // Poisoned by an earlier timeout?  Both CTAs take the LEADER's view, so the pair always decides alike and
+  // no cluster barrier below is ever left waiting for a CTA that went home.
+  const uint32_t poisoned = ld_shared_cluster_u32(mapa_u32(smem_u32(const_cast<int*>(abort_flag)), 0));
+  cluster_sync_all();                                                    // nobody leaves while its flag is being read
+  if (poisoned != 0) return;
+  if (warp == 1) {
+    tmem_alloc_2cta(tmem_slot, TMEM_COLS);
+    tmem_relinquish_2cta();
+  }
+  tc_fence_before();
+  cluster_sync_all();                                                    // both halves of the pair hold their TMEM
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) g.status[4 + rank] = static_cast<int>(tmem_base) + 1;   // (diagnostic: allocation address)
+  const int num_kb = (g.K + BK - 1) / BK;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------- TMA producer (each CTA: its A rows, its B half)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = pair; t < g.num_tiles && ok; t += num_pairs) {
+        const int mp = t % g.num_m_pairs;
+        const int nt = t / g.num_m_pairs;
+        const int a_row = mp * 2 * BM + static_cast<int>(rank) * BM;
+        const int b_row = nt * BN + static_cast<int>(rank) * BNH;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(empty + stage, phase ^ 1, abort_flag, g.status, CB_ERR_WAIT_EMPTY)) {
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(full + stage, A_BYTES + B_BYTES);
+          tma_load_2d(sA + stage * A_BYTES, &tmA, full + stage, kb * BK, a_row);
+          tma_load_2d(sB + stage * B_BYTES, &tmB, full + stage, kb * BK, b_row);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      if (leader) {
+        // --------------------------------------------------------- MMA issuer for the pair
+        uint32_t tile_cnt = 0;
+        for (int t = pair; t < g.num_tiles && ok; t += num_pairs, ++tile_cnt) {
+          const uint32_t acc = tile_cnt % NACC;
+          const uint32_t acc_phase = (tile_cnt / NACC) & 1u;
+          if (!mbar_wait(tempty + acc, acc_phase ^ 1, abort_flag, g.status, CB_ERR_WAIT_TMEM_EMPTY)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + acc * BN;
+          for (int kb = 0; kb < num_kb; ++kb) {
+            if (!mbar_wait(full + stage, phase, abort_flag, g.status, CB_ERR_WAIT_FULL) ||
+                !mbar_wait(peer_full + stage, phase, abort_flag, g.status, CB_ERR_WAIT_PEER)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            const uint32_t a_base = smem_u32(sA + stage * A_BYTES);
+            const uint32_t b_base = smem_u32(sB + stage * B_BYTES);
+#pragma unroll
+            for (int k = 0; k < BK / 16; ++k) {
+              const uint64_t adesc = umma_smem_desc(a_base + k * 32, 16, 1024);
+              const uint64_t bdesc = umma_smem_desc(b_base + k * 32, 16, 1024);
+              umma_f16_ss_2cta(d_tmem, adesc, bdesc, IDESC, (kb | k) != 0 ? 1u : 0u);
+            }
+            umma_commit_2cta(empty + stage);      // frees this stage in both CTAs once the MMAs retire
+            if (++stage == STAGES) {
+              stage = 0;
+              phase ^= 1;
+            }
+          }
+          if (ok) umma_commit_2cta(tfull + acc);  // accumulator complete, visible to both epilogues
+        }
+      } else {
+        // --------------------------------------------------------- relay: tell the leader that my stage is full
+        const uint32_t remote0 = mapa_u32(smem_u32(peer_full), 0);
+        for (int t = pair; t < g.num_tiles && ok; t += num_pairs) {
+          for (int kb = 0; kb < num_kb; ++kb) {
+            if (!mbar_wait(full + stage, phase, abort_flag, g.status, CB_ERR_WAIT_FULL)) {
+              ok = false;
+              break;
+            }
+            mbar_arrive_remote(remote0 + stage * 8);
+            if (++stage == STAGES) {
+              stage = 0;
+              phase ^= 1;
+            }
+          }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------- epilogue (4 warps, one TMEM lane quarter each)
+    const int q = warp & 3;
+    const uint32_t tempty_leader = mapa_u32(smem_u32(tempty), 0);
+    uint8_t* stg = smem + STG_OFFSET + (warp - 2) * 8192;
+    uint32_t tile_cnt = 0;
+    bool ok = true;
+    for (int t = pair; t < g.num_tiles && ok; t += num_pairs, ++tile_cnt) {
+      const int mp = t % g.num_m_pairs;
+      const int nt = t / g.num_m_pairs;
+      const uint32_t acc = tile_cnt % NACC;
+      const uint32_t acc_phase = (tile_cnt / NACC) & 1u;
+      bool w = mbar_wait(tfull + acc, acc_phase, abort_flag, g.status, CB_ERR_WAIT_TMEM_FULL);
+      w = __all_sync(0xffffffffu, w);
+      if (!w) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+      const int row0w = mp * 2 * BM + static_cast<int>(rank) * BM + q * 32;
+      int buf = 0;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 64) {
+        const int colbase = nt * BN + c0;
+        if (colbase >= g.N) break;
+        uint32_t r[64];
+        tmem_ld_32x32(t_row + c0, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+        tmem_ld_32x32(t_row + c0 + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+        tmem_ld_wait();
+        if (lane == 0) tma_store_wait_read<1>();
+        __syncwarp();
+        uint8_t* dstrow = stg + buf * 4096 + lane * 128;
+#pragma unroll
+        for (int cc = 0; cc < 8; ++cc) {
+          uint4 u;
+          u.x = pack_bf16x2(__uint_as_float(r[8 * cc + 0]), __uint_as_float(r[8 * cc + 1]));
+          u.y = pack_bf16x2(__uint_as_float(r[8 * cc + 2]), __uint_as_float(r[8 * cc + 3]));
+          u.z = pack_bf16x2(__uint_as_float(r[8 * cc + 4]), __uint_as_float(r[8 * cc + 5]));
+          u.w = pack_bf16x2(__uint_as_float(r[8 * cc + 6]), __uint_as_float(r[8 * cc + 7]));
+          *reinterpret_cast<uint4*>(dstrow + ((cc ^ (lane & 7)) << 4)) = u;
+        }
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0 && row0w < g.M) {
+          tma_store_2d(&tmC, stg + buf * 4096, colbase, row0w);
+          tma_store_commit();
+        }
+        buf ^= 1;
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if (leader) mbar_arrive(tempty + acc);
+        else mbar_arrive_remote(tempty_leader + acc * 8);
+      }
+    }
+    if (lane == 0) tma_store_wait_all();
+  }
+
+  // ------------------------------------------------------------- teardown (the pair leaves together)
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  tc_fence_before();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_2cta(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace cb2
+
+extern "C" {
+
+// C[M,N] (bf16, row pitch ldc) = A[M,K] (pitch lda) * B[N,K]^T (pitch ldb).  Pitches in elements, multiples of 8;
+// base addresses 16-byte aligned.  Returns 0 on a successful launch, negative for rejected arguments.
+int cb_gemm2sm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                    long long ldc, int accumulators, int* status, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return -1;
+  if ((reinterpret_cast<uintptr_t>(C) & 15) != 0 || (ldc * 2) % 16 != 0) return -2;
+  CUtensorMap ta, tb, tc;
+  int e = cbhost::make_tmap(&ta, A, K, M, lda, 64, cb2::BM);
+  if (e) return e;
+  e = cbhost::make_tmap(&tb, B, K, N, ldb, 64, cb2::BNH);
+  if (e) return e;
+  e = cbhost::make_tmap(&tc, C, N, M, ldc, 64, 32);
+  if (e) return e;
+  cb2::Args g = {};
+  g.M = M; g.N = N; g.K = K;
+  g.num_m_pairs = (M + 2 * cb2::BM - 1) / (2 * cb2::BM);
+  g.num_n_tiles = (N + cb2::BN - 1) / cb2::BN;
+  g.num_tiles = g.num_m_pairs * g.num_n_tiles;
+  g.status = status;
+  static bool configured = false;
+  if (!configured) {
+    CB_CHECK_CUDA(cudaFuncSetAttribute(cb2::gemm2sm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, cb2::SMEM_TOTAL));
+    CB_CHECK_CUDA(cudaFuncSetAttribute(cb2::gemm2sm_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, cb2::SMEM_TOTAL));
+    configured = true;
+  }
+  int pairs = cbhost::num_sms() / 2;
+  if (pairs > g.num_tiles) pairs = g.num_tiles;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (accumulators == 2) cb2::gemm2sm_kernel<2><<<2 * pairs, cb2::THREADS, cb2::SMEM_TOTAL, s>>>(ta, tb, tc, g);
+  else cb2::gemm2sm_kernel<1><<<2 * pairs, cb2::THREADS, cb2::SMEM_TOTAL, s>>>(ta, tb, tc, g);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // extern "C"
