@@ -655,6 +655,11 @@ __global__ void cce_finalize_kernel(const float* __restrict__ loss_rows, const l
 }  // namespace cb
 
 // =========================================================================================== host side
+extern "C" int cb_gemm2sm_supported(const void* C, long long ldc, int out_fp32);
+extern "C" int cb_gemm2sm_bf16(const void* A, const void* B, void* C, const void* bias, const void* addend, int M, int N,
+                               int K, long long lda, long long ldb, long long ldc, long long ld_add, int a_mn, int b_mn,
+                               int out_fp32, int accumulate, int* status, void* stream);
+
 namespace {
 
 using cbhost::make_tmap;
@@ -714,6 +719,23 @@ int pick_block_n(int M, int N, int forced) {
   return best;
 }
 
+// Rounds of tiles, weighted by what one round costs relative to a round of the CTA-pair kernel (measured on
+// the 0.5B shapes: a 128x256 single-CTA round takes ~1.08 pair rounds, a 128x128 round ~0.9 because those tiles
+// are bound by operand bandwidth, not by the tensor pipe).  Short GEMMs stay on the single-CTA kernel, whose
+// fixed costs are lower.
+bool prefer_cta_pairs(int M, int N, int K) {
+  if (K < 1024 && N < 1024) return false;
+  const int sms = num_sms();
+  const long long t2 = static_cast<long long>((M + 255) / 256) * ((N + 255) / 256);
+  const long long t256 = static_cast<long long>((M + 127) / 128) * ((N + 255) / 256);
+  const long long t128 = static_cast<long long>((M + 127) / 128) * ((N + 127) / 128);
+  const int pairs = sms / 2;
+  const double c2 = static_cast<double>((t2 + pairs - 1) / pairs);
+  const double c256 = 1.08 * static_cast<double>((t256 + sms - 1) / sms);
+  const double c128 = 0.90 * static_cast<double>((t128 + sms - 1) / sms);
+  return c2 <= (c256 < c128 ? c256 : c128);
+}
+
 // Tensor map of the output for the staged epilogue; returns 0 and sets *ok when C qualifies
 // (16-byte aligned base and row pitch), otherwise leaves the direct-store epilogue in charge.
 int build_out_map(CUtensorMap* tc, int* ok, const void* C, int M, int N, long long ldc, int out_fp32) {
@@ -749,6 +771,12 @@ int cb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, const 
                  long long lda, long long ldb, long long ldc, long long ld_add, int a_mn, int b_mn, int out_fp32,
                  int accumulate, int force_block_n, int* status, void* stream) {
   if (M <= 0 || N <= 0 || K <= 0) return -1;
+  // force_block_n: 0 = choose (CTA-pair kernel or 128 / 256 wide single-CTA tiles), 128 / 256 = single-CTA tile
+  // of that width, 2 = CTA-pair kernel
+  if ((force_block_n == 2 || (force_block_n == 0 && prefer_cta_pairs(M, N, K))) && cb_gemm2sm_supported(C, ldc, out_fp32))
+    return cb_gemm2sm_bf16(A, B, C, bias, addend, M, N, K, lda, ldb, ldc, ld_add, a_mn, b_mn, out_fp32, accumulate,
+                           status, stream);
+  if (force_block_n == 2) force_block_n = 0;
   const int bn = pick_block_n(M, N, force_block_n);
   CUtensorMap ta, tb;
   int e = build_maps(&ta, &tb, A, B, M, N, K, lda, ldb, a_mn, b_mn, bn);

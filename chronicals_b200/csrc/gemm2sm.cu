@@ -42,6 +42,13 @@ constexpr int SMEM_TOTAL = BAR_OFFSET + 512 + 1024;
 struct Args {
   int M, N, K;
   int num_m_pairs, num_n_tiles, num_tiles;
+  void* C;                 // output (needed for accumulate; the stores go through the tensor map)
+  long long ldc;
+  int out_fp32;
+  int accumulate;
+  const bf16* bias;        // [N] or null
+  const bf16* addend;      // [M, N] with row pitch ld_add, or null (residual)
+  long long ld_add;
   int* status;
 };
 
@@ -93,12 +100,14 @@ __device__ __forceinline__ void umma_commit_2cta(uint64_t* bar) {
                : "memory");
 }
 
-template <int NACC>
+// A_MN / B_MN: 0 = operand stored [rows, K] (K contiguous), 1 = stored [K, rows] (rows contiguous), exactly as in
+// gemm.cu, so forward (0,0), dgrad (0,1) and wgrad (1,1) need no transposed copies.
+template <int NACC, int A_MN, int B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmC, const Args g) {
   constexpr uint32_t TMEM_COLS = NACC * BN;                              // NACC accumulators of 256 columns
-  constexpr uint32_t IDESC = umma_idesc_bf16(2 * BM, BN, 0, 0);          // M = 256 across the pair
+  constexpr uint32_t IDESC = umma_idesc_bf16(2 * BM, BN, A_MN, B_MN);    // M = 256 across the pair
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -149,7 +158,6 @@ gemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   cluster_sync_all();                                                    // both halves of the pair hold their TMEM
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  if (threadIdx.x == 0) g.status[4 + rank] = static_cast<int>(tmem_base) + 1;   // (diagnostic: allocation address)
   const int num_kb = (g.K + BK - 1) / BK;
 
   if (warp == 0) {
@@ -169,8 +177,20 @@ gemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             break;
           }
           mbar_expect_tx(full + stage, A_BYTES + B_BYTES);
-          tma_load_2d(sA + stage * A_BYTES, &tmA, full + stage, kb * BK, a_row);
-          tma_load_2d(sB + stage * B_BYTES, &tmB, full + stage, kb * BK, b_row);
+          uint8_t* a_dst = sA + stage * A_BYTES;
+          uint8_t* b_dst = sB + stage * B_BYTES;
+          if (A_MN == 0) {
+            tma_load_2d(a_dst, &tmA, full + stage, kb * BK, a_row);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d(a_dst + j * 8192, &tmA, full + stage, a_row + j * 64, kb * BK);
+          }
+          if (B_MN == 0) {
+            tma_load_2d(b_dst, &tmB, full + stage, kb * BK, b_row);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BNH / 64; ++j) tma_load_2d(b_dst + j * 8192, &tmB, full + stage, b_row + j * 64, kb * BK);
+          }
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1;
@@ -206,8 +226,10 @@ gemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const uint32_t b_base = smem_u32(sB + stage * B_BYTES);
 #pragma unroll
             for (int k = 0; k < BK / 16; ++k) {
-              const uint64_t adesc = umma_smem_desc(a_base + k * 32, 16, 1024);
-              const uint64_t bdesc = umma_smem_desc(b_base + k * 32, 16, 1024);
+              const uint64_t adesc = A_MN ? umma_smem_desc(a_base + k * 2048, 8192, 1024)
+                                          : umma_smem_desc(a_base + k * 32, 16, 1024);
+              const uint64_t bdesc = B_MN ? umma_smem_desc(b_base + k * 2048, 8192, 1024)
+                                          : umma_smem_desc(b_base + k * 32, 16, 1024);
               umma_f16_ss_2cta(d_tmem, adesc, bdesc, IDESC, (kb | k) != 0 ? 1u : 0u);
             }
             umma_commit_2cta(empty + stage);      // frees this stage in both CTAs once the MMAs retire
@@ -257,30 +279,102 @@ gemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       tc_fence_after();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
       const int row0w = mp * 2 * BM + static_cast<int>(rank) * BM + q * 32;
+      const int row = row0w + lane;
+      const bool row_ok = row < g.M;
+      const int cols_per_store = g.out_fp32 ? 32 : 64;
       int buf = 0;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 64) {
+      for (int c0 = 0; c0 < BN; c0 += cols_per_store) {
         const int colbase = nt * BN + c0;
-        if (colbase >= g.N) break;
+        if (colbase >= g.N) break;                          // uniform across the warp
         uint32_t r[64];
         tmem_ld_32x32(t_row + c0, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
-        tmem_ld_32x32(t_row + c0 + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+        if (!g.out_fp32) tmem_ld_32x32(t_row + c0 + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
         tmem_ld_wait();
-        if (lane == 0) tma_store_wait_read<1>();
+        const int nhalf = g.out_fp32 ? 1 : 2;
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          if (hh >= nhalf) break;
+          const int col0 = colbase + hh * 32;
+          float* v = reinterpret_cast<float*>(&r[hh * 32]);
+          if (g.bias != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < g.N) v[j] += __bfloat162float(g.bias[col0 + j]);
+          }
+          if (g.addend != nullptr && row_ok) {
+            const bf16* ap = g.addend + static_cast<long long>(row) * g.ld_add + col0;
+            if (col0 + 32 <= g.N && (reinterpret_cast<uintptr_t>(ap) & 15) == 0) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const uint4 u = reinterpret_cast<const uint4*>(ap)[j];
+                const float2 a0 = unpack_bf16x2(u.x), a1 = unpack_bf16x2(u.y);
+                const float2 a2 = unpack_bf16x2(u.z), a3 = unpack_bf16x2(u.w);
+                v[8 * j + 0] += a0.x; v[8 * j + 1] += a0.y; v[8 * j + 2] += a1.x; v[8 * j + 3] += a1.y;
+                v[8 * j + 4] += a2.x; v[8 * j + 5] += a2.y; v[8 * j + 6] += a3.x; v[8 * j + 7] += a3.y;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < g.N) v[j] += __bfloat162float(ap[j]);
+            }
+          }
+          if (g.accumulate && row_ok) {
+            if (g.out_fp32) {
+              const float* cp = reinterpret_cast<const float*>(g.C) + static_cast<long long>(row) * g.ldc + col0;
+              if (col0 + 32 <= g.N && (reinterpret_cast<uintptr_t>(cp) & 15) == 0) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  const float4 o = reinterpret_cast<const float4*>(cp)[j];
+                  v[4 * j] += o.x; v[4 * j + 1] += o.y; v[4 * j + 2] += o.z; v[4 * j + 3] += o.w;
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (col0 + j < g.N) v[j] += cp[j];
+              }
+            } else {
+              const bf16* cp = reinterpret_cast<const bf16*>(g.C) + static_cast<long long>(row) * g.ldc + col0;
+              if (col0 + 32 <= g.N && (reinterpret_cast<uintptr_t>(cp) & 15) == 0) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const uint4 u = reinterpret_cast<const uint4*>(cp)[j];
+                  const float2 a0 = unpack_bf16x2(u.x), a1 = unpack_bf16x2(u.y);
+                  const float2 a2 = unpack_bf16x2(u.z), a3 = unpack_bf16x2(u.w);
+                  v[8 * j + 0] += a0.x; v[8 * j + 1] += a0.y; v[8 * j + 2] += a1.x; v[8 * j + 3] += a1.y;
+                  v[8 * j + 4] += a2.x; v[8 * j + 5] += a2.y; v[8 * j + 6] += a3.x; v[8 * j + 7] += a3.y;
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (col0 + j < g.N) v[j] += __bfloat162float(cp[j]);
+              }
+            }
+          }
+        }
+        if (lane == 0) tma_store_wait_read<1>();            // the buffer written two stores ago has been read out
         __syncwarp();
         uint8_t* dstrow = stg + buf * 4096 + lane * 128;
+        if (g.out_fp32) {
 #pragma unroll
-        for (int cc = 0; cc < 8; ++cc) {
-          uint4 u;
-          u.x = pack_bf16x2(__uint_as_float(r[8 * cc + 0]), __uint_as_float(r[8 * cc + 1]));
-          u.y = pack_bf16x2(__uint_as_float(r[8 * cc + 2]), __uint_as_float(r[8 * cc + 3]));
-          u.z = pack_bf16x2(__uint_as_float(r[8 * cc + 4]), __uint_as_float(r[8 * cc + 5]));
-          u.w = pack_bf16x2(__uint_as_float(r[8 * cc + 6]), __uint_as_float(r[8 * cc + 7]));
-          *reinterpret_cast<uint4*>(dstrow + ((cc ^ (lane & 7)) << 4)) = u;
+          for (int cc = 0; cc < 8; ++cc) {
+            const uint4 u = make_uint4(r[4 * cc], r[4 * cc + 1], r[4 * cc + 2], r[4 * cc + 3]);
+            *reinterpret_cast<uint4*>(dstrow + ((cc ^ (lane & 7)) << 4)) = u;
+          }
+        } else {
+#pragma unroll
+          for (int cc = 0; cc < 8; ++cc) {
+            uint4 u;
+            u.x = pack_bf16x2(__uint_as_float(r[8 * cc + 0]), __uint_as_float(r[8 * cc + 1]));
+            u.y = pack_bf16x2(__uint_as_float(r[8 * cc + 2]), __uint_as_float(r[8 * cc + 3]));
+            u.z = pack_bf16x2(__uint_as_float(r[8 * cc + 4]), __uint_as_float(r[8 * cc + 5]));
+            u.w = pack_bf16x2(__uint_as_float(r[8 * cc + 6]), __uint_as_float(r[8 * cc + 7]));
+            *reinterpret_cast<uint4*>(dstrow + ((cc ^ (lane & 7)) << 4)) = u;
+          }
         }
         fence_async_smem();
         __syncwarp();
-        if (lane == 0 && row0w < g.M) {
+        if (lane == 0 && row0w < g.M) {                      // a box that starts past the last row has nothing to write
           tma_store_2d(&tmC, stg + buf * 4096, colbase, row0w);
           tma_store_commit();
         }
@@ -313,39 +407,64 @@ gemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
 }  // namespace cb2
 
+namespace {
+
+template <int A_MN, int B_MN>
+int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const cb2::Args& g, cudaStream_t s) {
+  auto kern = cb2::gemm2sm_kernel<2, A_MN, B_MN>;
+  static bool configured = false;
+  if (!configured) {
+    CB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, cb2::SMEM_TOTAL));
+    configured = true;
+  }
+  int pairs = cbhost::num_sms() / 2;
+  if (pairs > g.num_tiles) pairs = g.num_tiles;
+  kern<<<2 * pairs, cb2::THREADS, cb2::SMEM_TOTAL, s>>>(ta, tb, tc, g);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace
+
 extern "C" {
 
-// C[M,N] (bf16, row pitch ldc) = A[M,K] (pitch lda) * B[N,K]^T (pitch ldb).  Pitches in elements, multiples of 8;
-// base addresses 16-byte aligned.  Returns 0 on a successful launch, negative for rejected arguments.
-int cb_gemm2sm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
-                    long long ldc, int accumulators, int* status, void* stream) {
+// Whether cb_gemm2sm_bf16 can take this problem (TMA-store epilogue needs an aligned C and pitch).
+int cb_gemm2sm_supported(const void* C, long long ldc, int out_fp32) {
+  const int eb = out_fp32 ? 4 : 2;
+  return ((reinterpret_cast<uintptr_t>(C) & 15) == 0 && (ldc * eb) % 16 == 0) ? 1 : 0;
+}
+
+// C[M,N] = op(A) * op(B)^T (+bias) (+addend) (+C) on CTA pairs.  Same conventions as cb_gemm_bf16 (gemm.cu):
+// a_mn / b_mn = 0 for operands stored [rows, K], 1 for [K, rows]; pitches in elements.
+int cb_gemm2sm_bf16(const void* A, const void* B, void* C, const void* bias, const void* addend, int M, int N, int K,
+                    long long lda, long long ldb, long long ldc, long long ld_add, int a_mn, int b_mn, int out_fp32,
+                    int accumulate, int* status, void* stream) {
   if (M <= 0 || N <= 0 || K <= 0) return -1;
-  if ((reinterpret_cast<uintptr_t>(C) & 15) != 0 || (ldc * 2) % 16 != 0) return -2;
+  if (!cb_gemm2sm_supported(C, ldc, out_fp32)) return -2;
   CUtensorMap ta, tb, tc;
-  int e = cbhost::make_tmap(&ta, A, K, M, lda, 64, cb2::BM);
+  int e;
+  if (!a_mn) e = cbhost::make_tmap(&ta, A, K, M, lda, 64, cb2::BM);
+  else e = cbhost::make_tmap(&ta, A, M, K, lda, 64, 64);
   if (e) return e;
-  e = cbhost::make_tmap(&tb, B, K, N, ldb, 64, cb2::BNH);
+  if (!b_mn) e = cbhost::make_tmap(&tb, B, K, N, ldb, 64, cb2::BNH);
+  else e = cbhost::make_tmap(&tb, B, N, K, ldb, 64, 64);
   if (e) return e;
-  e = cbhost::make_tmap(&tc, C, N, M, ldc, 64, 32);
+  e = cbhost::make_tmap(&tc, C, N, M, ldc, out_fp32 ? 32 : 64, 32, out_fp32 ? 4 : 2);
   if (e) return e;
   cb2::Args g = {};
   g.M = M; g.N = N; g.K = K;
   g.num_m_pairs = (M + 2 * cb2::BM - 1) / (2 * cb2::BM);
   g.num_n_tiles = (N + cb2::BN - 1) / cb2::BN;
   g.num_tiles = g.num_m_pairs * g.num_n_tiles;
+  g.C = C; g.ldc = ldc; g.out_fp32 = out_fp32; g.accumulate = accumulate;
+  g.bias = static_cast<const cb::bf16*>(bias);
+  g.addend = static_cast<const cb::bf16*>(addend);
+  g.ld_add = ld_add;
   g.status = status;
-  static bool configured = false;
-  if (!configured) {
-    CB_CHECK_CUDA(cudaFuncSetAttribute(cb2::gemm2sm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, cb2::SMEM_TOTAL));
-    CB_CHECK_CUDA(cudaFuncSetAttribute(cb2::gemm2sm_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, cb2::SMEM_TOTAL));
-    configured = true;
-  }
-  int pairs = cbhost::num_sms() / 2;
-  if (pairs > g.num_tiles) pairs = g.num_tiles;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (accumulators == 2) cb2::gemm2sm_kernel<2><<<2 * pairs, cb2::THREADS, cb2::SMEM_TOTAL, s>>>(ta, tb, tc, g);
-  else cb2::gemm2sm_kernel<1><<<2 * pairs, cb2::THREADS, cb2::SMEM_TOTAL, s>>>(ta, tb, tc, g);
-  return static_cast<int>(cudaGetLastError());
+  if (!a_mn && !b_mn) return launch2<0, 0>(ta, tb, tc, g, s);
+  if (!a_mn && b_mn) return launch2<0, 1>(ta, tb, tc, g, s);
+  if (a_mn && b_mn) return launch2<1, 1>(ta, tb, tc, g, s);
+  return launch2<1, 0>(ta, tb, tc, g, s);
 }
 
 }  // extern "C"

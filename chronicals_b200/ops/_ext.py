@@ -47,7 +47,8 @@ _PROTOTYPES = {
     "cb_ce_logits_grad": [P, P, P, P, P, P, L, L, I, I, L, F, F, P],
     "cb_attn_fwd": [P, P, P, P, P, P, I, I, I, I, I, L, L, L, L, F, P, P],
     "cb_attn_bwd": [P, P, P, P, P, P, P, I, I, I, I, I, L, L, L, L, L, F, P, P, P, P, P, L, P, P],
-    "cb_gemm2sm_bf16": [P, P, P, I, I, I, L, L, L, I, P, P],
+    "cb_gemm2sm_bf16": [P, P, P, P, P, I, I, I, L, L, L, L, I, I, I, I, P, P],
+    "cb_gemm2sm_supported": [P, L, I],
     "cb_gemm_bf16_splitk": [P, P, P, I, I, I, L, L, L, I, I, P, P],
     "cb_opt_chunk": [],
     "cb_adamw_multi": [P, P, P, P, P, P, P, P, I, I, P, P, I, P],

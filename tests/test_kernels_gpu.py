@@ -393,3 +393,44 @@ def test_rope_positions_beyond_table_are_clamped_not_read_out_of_bounds():
     assert torch.equal(out, want)
     compiled, code, _ = _ext.debug_word()
     assert (code == 402) if compiled else (code == 0)
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+@pytest.mark.parametrize("M,N,K", [(512, 768, 320), (300, 200, 136), (1000, 896, 1024)])
+def test_gemm_cta_pair_kernel_matches_fp32(a_mn, b_mn, M, N, K):
+    """The cta_group::2 kernel (256x256 tile per CTA pair), forced with block_n=2, in all four operand layouts,
+    with ragged edges in M, N and K."""
+    from chronicals_b200 import ops
+    g = torch.Generator().manual_seed(5)
+    a = torch.randn((K, M) if a_mn else (M, K), generator=g).to(torch.bfloat16).cuda()
+    b = torch.randn((K, N) if b_mn else (N, K), generator=g).to(torch.bfloat16).cuda()
+    if a.shape[1] % 8 or b.shape[1] % 8:
+        pytest.skip("operand pitch not TMA-addressable")
+    out = ops.gemm(a, b, a_mn=a_mn, b_mn=b_mn, block_n=2)
+    A = a.float().t() if a_mn else a.float()
+    B = b.float() if b_mn else b.float().t()
+    want = A @ B
+    assert (out.float() - want).abs().max().item() < 1.5e-2 * want.abs().max().item()
+    _ext.check_status()
+
+
+def test_gemm_cta_pair_kernel_epilogues():
+    from chronicals_b200 import ops
+    g = torch.Generator().manual_seed(6)
+    M, N, K = 520, 896, 1024
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+    w = torch.randn(N, K, generator=g).to(torch.bfloat16).cuda()
+    bias = torch.randn(N, generator=g).to(torch.bfloat16).cuda()
+    res = torch.randn(M, N, generator=g).to(torch.bfloat16).cuda()
+    want = a.float() @ w.float().t() + bias.float() + res.float()
+    out = ops.gemm(a, w, bias=bias, addend=res, block_n=2)
+    assert (out.float() - want).abs().max().item() < 1.5e-2 * want.abs().max().item()
+    acc32 = torch.randn(M, N, generator=g).cuda()
+    want2 = acc32 + a.float() @ w.float().t()
+    ops.gemm(a, w, out=acc32, accumulate=True, block_n=2)
+    assert (acc32 - want2).abs().max().item() < 2e-3 * want2.abs().max().item()
+    acc16 = torch.randn(M, N, generator=g).to(torch.bfloat16).cuda()
+    want3 = acc16.float() + a.float() @ w.float().t()
+    ops.gemm(a, w, out=acc16, accumulate=True, block_n=2)
+    assert (acc16.float() - want3).abs().max().item() < 1.5e-2 * want3.abs().max().item()
+    _ext.check_status()
