@@ -207,6 +207,65 @@ sqnorm_finalize_kernel(const float* __restrict__ partials, int n, const float* _
   }
 }
 
+
+// ------------------------------------------------------------------------------------------------------
+// AdamW with 8-bit block-quantised moments (blocks of 256 elements, one fp32 absmax per block; the first
+// moment in a signed linear code q = round(m / absmax * 127), the square root of the second moment in an
+// unsigned code q = round(sqrt(v) / absmax * 255)).  One warp owns one block: dequantise, update in fp32,
+// find the new absmax with shuffles, re-quantise, store.  10 bytes of traffic per parameter instead of 18.
+// Replaces the reference's bitsandbytes wrappers (chronicals/optimizers/optimizers_8bit.py:117-336).
+template <typename T>
+__global__ void __launch_bounds__(256)
+adamw8bit_kernel(T* __restrict__ p, const T* __restrict__ g, signed char* __restrict__ mq, unsigned char* __restrict__ vq,
+                 float* __restrict__ m_absmax, float* __restrict__ v_absmax, long long n, float lr, float beta1,
+                 float beta2, float eps, float weight_decay, float bc1, float bc2) {
+  const long long nblk = (n + 255) / 256;
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const float step = lr / bc1, inv_bc2 = 1.f / bc2, decay = 1.f - lr * weight_decay;
+  for (long long b = warp0; b < nblk; b += nwarps) {
+    const float am = m_absmax[b] * (1.f / 127.f), av = v_absmax[b] * (1.f / 255.f);
+    float m[8], rv[8];
+    float mx_m = 0.f, mx_v = 0.f;
+    const long long base = b * 256 + lane * 8;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const long long i = base + j;
+      m[j] = 0.f;
+      rv[j] = 0.f;
+      if (i < n) {
+        const float gi = static_cast<float>(g[i]);
+        const float sv = static_cast<float>(vq[i]) * av;          // sqrt(v)
+        const float mi = beta1 * (static_cast<float>(mq[i]) * am) + (1.f - beta1) * gi;
+        const float vi = beta2 * sv * sv + (1.f - beta2) * gi * gi;
+        float x = static_cast<float>(p[i]) * decay;
+        x -= step * mi / (sqrtf(vi * inv_bc2) + eps);
+        p[i] = static_cast<T>(x);
+        m[j] = mi;
+        rv[j] = sqrtf(vi);
+        mx_m = fmaxf(mx_m, fabsf(mi));
+        mx_v = fmaxf(mx_v, rv[j]);
+      }
+    }
+    mx_m = fmaxf(warp_max(mx_m), 1e-30f);
+    mx_v = fmaxf(warp_max(mx_v), 1e-30f);
+    if (lane == 0) {
+      m_absmax[b] = mx_m;
+      v_absmax[b] = mx_v;
+    }
+    const float sm = 127.f / mx_m, sv2 = 255.f / mx_v;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const long long i = base + j;
+      if (i < n) {
+        mq[i] = static_cast<signed char>(fminf(fmaxf(rintf(m[j] * sm), -127.f), 127.f));
+        vq[i] = static_cast<unsigned char>(fminf(fmaxf(rintf(rv[j] * sv2), 0.f), 255.f));
+      }
+    }
+  }
+}
+
 }  // namespace cb
 
 extern "C" {
@@ -235,6 +294,29 @@ int cb_grad_clip_coef(const void* const* g, const long long* numel, const int* c
   if (is_bf16) cb::grad_sqnorm_kernel<cb::bf16><<<total_chunks, cb::OPT_THREADS, 0, s>>>(tt, partials);
   else cb::grad_sqnorm_kernel<float><<<total_chunks, cb::OPT_THREADS, 0, s>>>(tt, partials);
   cb::sqnorm_finalize_kernel<<<1, 1024, 0, s>>>(partials, total_chunks, extra_sq, max_norm, out);
+  return static_cast<int>(cudaGetLastError());
+}
+
+
+// 8-bit AdamW step on one tensor.  is_bf16 selects the parameter / gradient dtype (bf16 or fp32).
+int cb_adamw8bit(void* p, const void* g, void* mq, void* vq, float* m_absmax, float* v_absmax, long long n, int is_bf16,
+                 float lr, float beta1, float beta2, float eps, float weight_decay, float bc1, float bc2, void* stream) {
+  if (n <= 0) return -1;
+  const long long nblk = (n + 255) / 256;
+  long long blocks = (nblk + 7) / 8;                      // 8 warps (quantisation blocks) per CTA
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (blocks > static_cast<long long>(sms) * 8) blocks = static_cast<long long>(sms) * 8;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (is_bf16)
+    cb::adamw8bit_kernel<cb::bf16><<<static_cast<int>(blocks), 256, 0, s>>>(
+        static_cast<cb::bf16*>(p), static_cast<const cb::bf16*>(g), static_cast<signed char*>(mq),
+        static_cast<unsigned char*>(vq), m_absmax, v_absmax, n, lr, beta1, beta2, eps, weight_decay, bc1, bc2);
+  else
+    cb::adamw8bit_kernel<float><<<static_cast<int>(blocks), 256, 0, s>>>(
+        static_cast<float*>(p), static_cast<const float*>(g), static_cast<signed char*>(mq),
+        static_cast<unsigned char*>(vq), m_absmax, v_absmax, n, lr, beta1, beta2, eps, weight_decay, bc1, bc2);
   return static_cast<int>(cudaGetLastError());
 }
 

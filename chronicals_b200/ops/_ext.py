@@ -50,6 +50,7 @@ _PROTOTYPES = {
     "cb_gemm2sm_bf16": [P, P, P, P, P, I, I, I, L, L, L, L, I, I, I, I, P, P],
     "cb_gemm2sm_supported": [P, L, I],
     "cb_gemm_bf16_splitk": [P, P, P, I, I, I, L, L, L, I, I, P, P],
+    "cb_adamw8bit": [P, P, P, P, P, P, L, I, F, F, F, F, F, F, F, P],
     "cb_opt_chunk": [],
     "cb_adamw_multi": [P, P, P, P, P, P, P, P, I, I, P, P, I, P],
     "cb_grad_clip_coef": [P, P, P, I, I, P, P, F, P, I, P],

@@ -88,9 +88,21 @@ class ScheduleFreeAdamW(Optimizer):
 # ------------------------------------------------------------------------------------------- Muon
 def newton_schulz_orthogonalize(G: torch.Tensor, steps: int = 5) -> torch.Tensor:
     """Approximate orthogonalisation ``X <- 1.5 X - 0.5 (X X^T) X`` of a matrix scaled so its
-    singular values start below sqrt(3)."""
+    singular values start below sqrt(3).  CUDA bf16 matrices run the two products of every iteration on the
+    tcgen05 GEMM (``X X^T`` is the NT form, ``(X X^T) X`` the NN form, no transposed copies); everything
+    else uses fp32 matmuls."""
+    transposed = G.shape[0] > G.shape[1]
+    if (G.is_cuda and G.dtype == torch.bfloat16 and G.dim() == 2 and G.shape[0] % 8 == 0 and G.shape[1] % 8 == 0):
+        from .. import ops
+        if ops._fast(G):
+            X = (G.t() if transposed else G).contiguous()
+            X = (X.float() / (X.float().norm() + 1e-7)).to(torch.bfloat16)
+            for _ in range(steps):
+                A = ops.gemm(X, X)                                         # X X^T      [m, m]
+                AX = ops.gemm(A, X, b_mn=True, out_dtype=torch.float32)    # (X X^T) X  [m, n], fp32 out
+                X = (1.5 * X.float() - 0.5 * AX).to(torch.bfloat16)
+            return (X.t() if transposed else X).contiguous().to(G.dtype)
     X = G.float()
-    transposed = X.shape[0] > X.shape[1]
     if transposed:
         X = X.t()
     X = X / (X.norm() + 1e-7)

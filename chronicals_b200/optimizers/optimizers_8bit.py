@@ -38,6 +38,18 @@ class AdamW8bit(Optimizer):
         super().__init__(params, dict(lr=lr, betas=tuple(betas), eps=eps, weight_decay=weight_decay))
         self.min_8bit_size, self.block_size, self.is_paged = min_8bit_size, block_size, is_paged
 
+    def _kernel_ok(self, p, st) -> bool:
+        """The fused kernel handles contiguous CUDA parameters (bf16 or fp32) whose moments are 8-bit, resident
+        on the device (not paged) and quantised in blocks of 256."""
+        if not (p.is_cuda and p.is_contiguous() and p.dtype in (torch.bfloat16, torch.float32)):
+            return False
+        if self.block_size != 256 or self.is_paged or st["exp_avg"].dtype != torch.int8 or not st["exp_avg"].is_cuda:
+            return False
+        if p.grad.dtype != p.dtype:
+            return False
+        from ..ops import _ext
+        return _ext.available() and not _ext.reference_forced() and _ext.has_symbol("cb_adamw8bit")
+
     def _load(self, st, name, shape, signed):
         q = st[name]
         if q.dtype in (torch.int8, torch.uint8):
@@ -82,6 +94,16 @@ class AdamW8bit(Optimizer):
                         st["exp_avg_sq"] = torch.zeros_like(p, dtype=torch.float32)
                 st["step"] += 1
                 t = st["step"]
+                if self._kernel_ok(p, st):
+                    from ..ops import _ext
+                    gr = p.grad if p.grad.is_contiguous() else p.grad.contiguous()
+                    code = _ext.lib().cb_adamw8bit(p.data_ptr(), gr.data_ptr(), st["exp_avg"].data_ptr(),
+                                                   st["exp_avg_sq"].data_ptr(), st["exp_avg_absmax"].data_ptr(),
+                                                   st["exp_avg_sq_absmax"].data_ptr(), p.numel(),
+                                                   int(p.dtype == torch.bfloat16), float(g["lr"]), b1, b2, float(g["eps"]),
+                                                   float(g["weight_decay"]), 1.0 - b1 ** t, 1.0 - b2 ** t, _ext.stream_ptr())
+                    _ext.check(code, "adamw8bit")
+                    continue
                 grad = p.grad.float()
                 m = self._load(st, "exp_avg", p.shape, True).to(p.device)
                 v = self._load(st, "exp_avg_sq", p.shape, False).to(p.device)

@@ -434,3 +434,41 @@ def test_gemm_cta_pair_kernel_epilogues():
     ops.gemm(a, w, out=acc16, accumulate=True, block_n=2)
     assert (acc16.float() - want3).abs().max().item() < 1.5e-2 * want3.abs().max().item()
     _ext.check_status()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_adamw8bit_kernel_matches_python_path(dtype):
+    """Fused 8-bit AdamW (block-wise quantised moments) against the same optimizer run through the PyTorch
+    formulas: identical quantisation codes up to one rounding step, parameters equal to bf16/fp32 tolerance."""
+    from chronicals_b200.optimizers.optimizers_8bit import AdamW8bit
+    torch.manual_seed(0)
+    n = 256 * 37 + 100                                       # a ragged last block
+    p0 = torch.randn(n, device="cuda").to(dtype)
+    grads = [torch.randn(n, device="cuda").to(dtype) * (0.5 ** i) for i in range(4)]
+    pk = torch.nn.Parameter(p0.clone())
+    pr = torch.nn.Parameter(p0.clone())
+    ok = AdamW8bit([pk], lr=1e-2, weight_decay=0.01, min_8bit_size=1)
+    orf = AdamW8bit([pr], lr=1e-2, weight_decay=0.01, min_8bit_size=1)
+    for g in grads:
+        pk.grad, pr.grad = g.clone(), g.clone()
+        ok.step()
+        with _ext.force_reference():
+            orf.step()
+    tol = 2e-2 if dtype == torch.bfloat16 else 2e-3
+    assert (pk.float() - pr.float()).abs().max().item() < tol
+    sk, sr = ok.state[pk], orf.state[pr]
+    assert (sk["exp_avg"].int() - sr["exp_avg"].int()).abs().max().item() <= 2
+    assert (sk["exp_avg_sq"].int() - sr["exp_avg_sq"].int()).abs().max().item() <= 2
+    assert torch.allclose(sk["exp_avg_absmax"], sr["exp_avg_absmax"], rtol=2e-2, atol=1e-6)
+
+
+def test_newton_schulz_on_tensor_cores_orthogonalises():
+    from chronicals_b200.optimizers.optimizers import newton_schulz_orthogonalize
+    torch.manual_seed(0)
+    g = torch.randn(256, 896, device="cuda").to(torch.bfloat16)
+    x = newton_schulz_orthogonalize(g, steps=5).float()
+    want = newton_schulz_orthogonalize(g.float().cpu(), steps=5)
+    assert (x.cpu() - want).abs().max().item() < 0.05 * want.abs().max().item() + 5e-3
+    gram = x @ x.t()
+    d = gram.diagonal()
+    assert d.min().item() > 0.3 and d.max().item() < 1.3                      # singular values pulled towards 1
