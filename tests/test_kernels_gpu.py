@@ -469,6 +469,5 @@ def test_newton_schulz_on_tensor_cores_orthogonalises():
     x = newton_schulz_orthogonalize(g, steps=5).float()
     want = newton_schulz_orthogonalize(g.float().cpu(), steps=5)
     assert (x.cpu() - want).abs().max().item() < 0.05 * want.abs().max().item() + 5e-3
-    gram = x @ x.t()
-    d = gram.diagonal()
-    assert d.min().item() > 0.3 and d.max().item() < 1.3                      # singular values pulled towards 1
+    d = (x @ x.t()).diagonal()                                                 # squared row norms, 1 / 256 at the start
+    assert d.min().item() > 10.0 / 256 and d.max().item() < 1.3               # pulled towards an orthonormal set of rows
