@@ -49,6 +49,8 @@ struct Args {
   const bf16* bias;        // [N] or null
   const bf16* addend;      // [M, N] with row pitch ld_add, or null (residual)
   long long ld_add;
+  const float* row_scale;  // fp8 operands: C = (A_q B_q^T) * row_scale[m] * col_scale[n]; null for bf16 operands
+  const float* col_scale;
   int* status;
 };
 
@@ -92,6 +94,22 @@ __device__ __forceinline__ void umma_f16_ss_2cta(uint32_t tmem_d, uint64_t adesc
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// the same MMA for 8-bit floating-point operands (e4m3 / e5m2 chosen by the instruction descriptor), K = 32 per MMA
+__device__ __forceinline__ void umma_f8_ss_2cta(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// instruction descriptor for kind::f8f6f4: fp32 accumulator, operand formats 0 = e4m3, 1 = e5m2, both K-major
+__host__ __device__ constexpr uint32_t umma_idesc_fp8(int m, int n, int a_fmt, int b_fmt) {
+  return (1u << 4) | (static_cast<uint32_t>(a_fmt) << 7) | (static_cast<uint32_t>(b_fmt) << 10) |
+         (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+
 // arrive on the barrier at this shared-memory offset in both CTAs of the pair once all earlier MMAs are done
 __device__ __forceinline__ void umma_commit_2cta(uint64_t* bar) {
   const uint16_t mask = 3;
@@ -102,12 +120,17 @@ __device__ __forceinline__ void umma_commit_2cta(uint64_t* bar) {
 
 // A_MN / B_MN: 0 = operand stored [rows, K] (K contiguous), 1 = stored [K, rows] (rows contiguous), exactly as in
 // gemm.cu, so forward (0,0), dgrad (0,1) and wgrad (1,1) need no transposed copies.
-template <int NACC, int A_MN, int B_MN>
+// KIND: 0 = bf16 operands (kind::f16, 64 elements per k-block), 1 = e4m3 operands (kind::f8f6f4, 128 elements per
+// k-block, K-major only).  Either way a k-block row is 128 bytes and one MMA consumes 32 bytes of it, so the
+// shared-memory layout, the descriptors and the pipeline are identical.
+template <int NACC, int A_MN, int B_MN, int KIND>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmC, const Args g) {
   constexpr uint32_t TMEM_COLS = NACC * BN;                              // NACC accumulators of 256 columns
-  constexpr uint32_t IDESC = umma_idesc_bf16(2 * BM, BN, A_MN, B_MN);    // M = 256 across the pair
+  constexpr uint32_t IDESC = KIND ? umma_idesc_fp8(2 * BM, BN, 0, 0)
+                                  : umma_idesc_bf16(2 * BM, BN, A_MN, B_MN);      // M = 256 across the pair
+  constexpr int BKE = KIND ? 2 * BK : BK;                                // elements per k-block
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -158,7 +181,7 @@ gemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   cluster_sync_all();                                                    // both halves of the pair hold their TMEM
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const int num_kb = (g.K + BK - 1) / BK;
+  const int num_kb = (g.K + BKE - 1) / BKE;
 
   if (warp == 0) {
     // ------------------------------------------------------------- TMA producer (each CTA: its A rows, its B half)
@@ -180,13 +203,13 @@ gemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           uint8_t* a_dst = sA + stage * A_BYTES;
           uint8_t* b_dst = sB + stage * B_BYTES;
           if (A_MN == 0) {
-            tma_load_2d(a_dst, &tmA, full + stage, kb * BK, a_row);
+            tma_load_2d(a_dst, &tmA, full + stage, kb * BKE, a_row);
           } else {
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j) tma_load_2d(a_dst + j * 8192, &tmA, full + stage, a_row + j * 64, kb * BK);
           }
           if (B_MN == 0) {
-            tma_load_2d(b_dst, &tmB, full + stage, kb * BK, b_row);
+            tma_load_2d(b_dst, &tmB, full + stage, kb * BKE, b_row);
           } else {
 #pragma unroll
             for (int j = 0; j < BNH / 64; ++j) tma_load_2d(b_dst + j * 8192, &tmB, full + stage, b_row + j * 64, kb * BK);
@@ -230,7 +253,8 @@ gemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                                           : umma_smem_desc(a_base + k * 32, 16, 1024);
               const uint64_t bdesc = B_MN ? umma_smem_desc(b_base + k * 2048, 8192, 1024)
                                           : umma_smem_desc(b_base + k * 32, 16, 1024);
-              umma_f16_ss_2cta(d_tmem, adesc, bdesc, IDESC, (kb | k) != 0 ? 1u : 0u);
+              if (KIND) umma_f8_ss_2cta(d_tmem, adesc, bdesc, IDESC, (kb | k) != 0 ? 1u : 0u);
+              else umma_f16_ss_2cta(d_tmem, adesc, bdesc, IDESC, (kb | k) != 0 ? 1u : 0u);
             }
             umma_commit_2cta(empty + stage);      // frees this stage in both CTAs once the MMAs retire
             if (++stage == STAGES) {
@@ -297,6 +321,11 @@ gemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           if (hh >= nhalf) break;
           const int col0 = colbase + hh * 32;
           float* v = reinterpret_cast<float*>(&r[hh * 32]);
+          if (KIND && g.row_scale != nullptr) {
+            const float rs = row_ok ? g.row_scale[row] : 0.f;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] *= rs * (col0 + j < g.N ? g.col_scale[col0 + j] : 0.f);
+          }
           if (g.bias != nullptr) {
 #pragma unroll
             for (int j = 0; j < 32; ++j)
@@ -409,9 +438,9 @@ gemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
 namespace {
 
-template <int A_MN, int B_MN>
+template <int A_MN, int B_MN, int KIND = 0>
 int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const cb2::Args& g, cudaStream_t s) {
-  auto kern = cb2::gemm2sm_kernel<2, A_MN, B_MN>;
+  auto kern = cb2::gemm2sm_kernel<2, A_MN, B_MN, KIND>;
   static bool configured = false;
   if (!configured) {
     CB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, cb2::SMEM_TOTAL));
@@ -465,6 +494,34 @@ int cb_gemm2sm_bf16(const void* A, const void* B, void* C, const void* bias, con
   if (!a_mn && b_mn) return launch2<0, 1>(ta, tb, tc, g, s);
   if (a_mn && b_mn) return launch2<1, 1>(ta, tb, tc, g, s);
   return launch2<1, 0>(ta, tb, tc, g, s);
+}
+
+
+// FP8 (e4m3) GEMM on the tensor cores: C[M,N] (bf16) = (Aq[M,K] * Bq[N,K]^T) * row_scale[m] * col_scale[n] (+bias).
+// Aq / Bq hold e4m3 bytes with K contiguous; pitches in bytes, multiples of 16; K a multiple of 16.
+int cb_gemm2sm_fp8(const void* Aq, const void* Bq, void* C, const float* row_scale, const float* col_scale,
+                   const void* bias, int M, int N, int K, long long lda, long long ldb, long long ldc, int* status,
+                   void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || K % 16 != 0 || row_scale == nullptr || col_scale == nullptr) return -1;
+  if (!cb_gemm2sm_supported(C, ldc, 0)) return -2;
+  CUtensorMap ta, tb, tc;
+  int e = cbhost::make_tmap(&ta, Aq, K, M, lda, 128, cb2::BM, 1);
+  if (e) return e;
+  e = cbhost::make_tmap(&tb, Bq, K, N, ldb, 128, cb2::BNH, 1);
+  if (e) return e;
+  e = cbhost::make_tmap(&tc, C, N, M, ldc, 64, 32, 2);
+  if (e) return e;
+  cb2::Args g = {};
+  g.M = M; g.N = N; g.K = K;
+  g.num_m_pairs = (M + 2 * cb2::BM - 1) / (2 * cb2::BM);
+  g.num_n_tiles = (N + cb2::BN - 1) / cb2::BN;
+  g.num_tiles = g.num_m_pairs * g.num_n_tiles;
+  g.C = C; g.ldc = ldc;
+  g.bias = static_cast<const cb::bf16*>(bias);
+  g.row_scale = row_scale;
+  g.col_scale = col_scale;
+  g.status = status;
+  return launch2<0, 0, 1>(ta, tb, tc, g, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -82,6 +82,45 @@ mxfp8_quant_kernel(const bf16* __restrict__ x, unsigned char* __restrict__ q, un
   }
 }
 
+
+// Row-wise e4m3 quantisation for the FP8 tensor-core GEMM: scale[row] = amax(row) / 448 (fp32),
+// q[row, k] = e4m3(x[row, k] / scale[row]).  One warp per row, 16-byte loads, 8-byte stores.
+__global__ void __launch_bounds__(256)
+rowquant_e4m3_kernel(const bf16* __restrict__ x, unsigned char* __restrict__ q, float* __restrict__ scale, long long M,
+                     int K, long long ldx, long long ldq) {
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const int nvec = K >> 3;
+  for (long long row = warp0; row < M; row += nwarps) {
+    const bf16* xr = x + row * ldx;
+    float amax = 0.f;
+    for (int v = lane; v < nvec; v += 32) {
+      const uint4 u = *reinterpret_cast<const uint4*>(xr + (v << 3));
+      const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+      amax = fmaxf(amax, fmaxf(fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(b.x), fabsf(b.y))),
+                               fmaxf(fmaxf(fabsf(c.x), fabsf(c.y)), fmaxf(fabsf(d.x), fabsf(d.y)))));
+    }
+    amax = warp_max(amax);
+    const float sc = fmaxf(amax, 1e-30f) * (1.f / 448.f);
+    const float inv = 1.f / sc;
+    if (lane == 0) scale[row] = sc;
+    unsigned char* qr = q + row * ldq;
+    for (int v = lane; v < nvec; v += 32) {
+      const uint4 u = *reinterpret_cast<const uint4*>(xr + (v << 3));
+      const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+      const float f[8] = {a.x, a.y, b.x, b.y, c.x, c.y, d.x, d.y};
+      unsigned long long packed = 0ull;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const unsigned long long byte = __nv_cvt_float_to_fp8(f[j] * inv, __NV_SATFINITE, __NV_E4M3);
+        packed |= byte << (8 * j);
+      }
+      *reinterpret_cast<unsigned long long*>(qr + (v << 3)) = packed;
+    }
+  }
+}
+
 }  // namespace cb
 
 extern "C" {
@@ -102,6 +141,18 @@ int cb_mxfp8_quant(const void* x, void* q, void* scales, void* deq, long long M,
     cb::mxfp8_quant_kernel<0><<<static_cast<unsigned>(blocks), 256, 0, s>>>(
         static_cast<const cb::bf16*>(x), static_cast<unsigned char*>(q), static_cast<unsigned char*>(scales),
         static_cast<cb::bf16*>(deq), M, K, ldx);
+  return static_cast<int>(cudaGetLastError());
+}
+
+
+// x: bf16 [M, K] (pitch ldx elements, K a multiple of 16); q: e4m3 bytes [M, K] (pitch ldq bytes, multiple of 16);
+// scale: fp32 [M].
+int cb_rowquant_e4m3(const void* x, void* q, float* scale, long long M, int K, long long ldx, long long ldq, void* stream) {
+  if (M <= 0 || K <= 0 || K % 16 != 0 || ldx % 8 != 0 || ldq % 16 != 0) return -1;
+  long long blocks = (M + 7) / 8;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  cb::rowquant_e4m3_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const cb::bf16*>(x), static_cast<unsigned char*>(q), scale, M, K, ldx, ldq);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -49,6 +49,8 @@ _PROTOTYPES = {
     "cb_attn_bwd": [P, P, P, P, P, P, P, I, I, I, I, I, L, L, L, L, L, F, P, P, P, P, P, L, P, P],
     "cb_gemm2sm_bf16": [P, P, P, P, P, I, I, I, L, L, L, L, I, I, I, I, P, P],
     "cb_gemm2sm_supported": [P, L, I],
+    "cb_gemm2sm_fp8": [P, P, P, P, P, P, I, I, I, L, L, L, P, P],
+    "cb_rowquant_e4m3": [P, P, P, L, I, L, L, P],
     "cb_gemm_bf16_splitk": [P, P, P, I, I, I, L, L, L, I, I, P, P],
     "cb_adamw8bit": [P, P, P, P, P, P, L, I, F, F, F, F, F, F, F, P],
     "cb_opt_chunk": [],

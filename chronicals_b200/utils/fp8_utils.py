@@ -162,6 +162,93 @@ class _MXFP8LinearFn(torch.autograd.Function):
         return dx, dw, db
 
 
+def rowwise_quantize_e4m3(x: torch.Tensor):
+    """``(q_uint8 [M, K], scale_fp32 [M])`` with ``scale = amax(row) / 448`` and ``q = e4m3(x / scale)``.
+    CUDA bf16 inputs run ``rowquant_e4m3_kernel``; everything else the PyTorch formula (same rounding)."""
+    x2 = x.reshape(-1, x.shape[-1])
+    M, K = x2.shape
+    if x2.is_cuda and x2.dtype == torch.bfloat16 and K % 16 == 0 and _ext.available() and not _ext.reference_forced() \
+            and _ext.has_symbol("cb_rowquant_e4m3"):
+        if x2.stride(1) != 1 or x2.stride(0) % 8 != 0:
+            x2 = x2.contiguous()
+        q = torch.empty(M, K, dtype=torch.uint8, device=x2.device)
+        sc = torch.empty(M, dtype=torch.float32, device=x2.device)
+        _ext.check(_ext.lib().cb_rowquant_e4m3(x2.data_ptr(), q.data_ptr(), sc.data_ptr(), M, K, x2.stride(0), q.stride(0),
+                                              _ext.stream_ptr()), "rowquant_e4m3")
+        return q, sc
+    xf = x2.float()
+    sc = xf.abs().amax(-1).clamp_min(1e-30) / 448.0
+    q = (xf / sc[:, None]).to(torch.float8_e4m3fn).view(torch.uint8)
+    return q, sc
+
+
+def fp8_rowwise_matmul(xq: torch.Tensor, xs: torch.Tensor, wq: torch.Tensor, ws: torch.Tensor,
+                       bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``(xq ⊙ xs) @ (wq ⊙ ws)ᵀ + bias`` in bf16 from e4m3 operands.  On a GPU this is one
+    ``tcgen05.mma.kind::f8f6f4`` GEMM on CTA pairs with the two scale vectors applied in the epilogue."""
+    M, K = xq.shape
+    N = wq.shape[0]
+    if xq.is_cuda and _ext.available() and not _ext.reference_forced() and _ext.has_symbol("cb_gemm2sm_fp8") and K % 16 == 0 \
+            and N % 8 == 0:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=xq.device)
+        code = _ext.lib().cb_gemm2sm_fp8(xq.data_ptr(), wq.data_ptr(), out.data_ptr(), xs.data_ptr(), ws.data_ptr(),
+                                         _ext.ptr(bias), M, N, K, xq.stride(0), wq.stride(0), out.stride(0),
+                                         _ext.status_buffer(xq.device).data_ptr(), _ext.stream_ptr())
+        _ext.check(code, "gemm2sm_fp8")
+        return out
+    a = xq.view(torch.float8_e4m3fn).float() * xs[:, None]
+    b = wq.view(torch.float8_e4m3fn).float() * ws[:, None]
+    y = a @ b.t()
+    if bias is not None:
+        y = y + bias.float()
+    return y.to(torch.bfloat16 if xq.is_cuda else torch.float32)
+
+
+class _FP8RowwiseLinearFn(torch.autograd.Function):
+    """Forward on the FP8 tensor cores (activations quantised per token, weights per output channel, e4m3);
+    backward in bf16 from the saved high-precision operands."""
+
+    @staticmethod
+    def forward(ctx, x, w, bias):
+        x2 = x.reshape(-1, x.shape[-1])
+        xq, xs = rowwise_quantize_e4m3(x2)
+        wq, ws = rowwise_quantize_e4m3(w)
+        y = fp8_rowwise_matmul(xq, xs, wq, ws, bias)
+        ctx.save_for_backward(x2, w)
+        ctx.has_bias = bias is not None
+        ctx.shape = x.shape
+        return y.to(x.dtype).view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1]).contiguous()
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = (ops.gemm(dy2, w, b_mn=True) if ops._fast(dy2, w) else dy2 @ w).view(ctx.shape)
+        if ctx.needs_input_grad[1]:
+            dw = ops.gemm(dy2, x2, a_mn=True, b_mn=True) if ops._fast(dy2, x2) else dy2.t() @ x2
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = dy2.float().sum(0).to(dy.dtype)
+        return dx, dw, db
+
+
+class FP8RowwiseLinear(nn.Module):
+    """``nn.Linear`` whose forward product runs in e4m3 on the tensor cores (per-token / per-channel scales)."""
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = True, device=None, dtype=torch.bfloat16):
+        super().__init__()
+        self.in_features, self.out_features = in_features, out_features
+        self.weight = nn.Parameter(torch.empty(out_features, in_features, device=device, dtype=dtype))
+        self.bias = nn.Parameter(torch.zeros(out_features, device=device, dtype=dtype)) if bias else None
+        nn.init.kaiming_uniform_(self.weight, a=5 ** 0.5)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if x.shape[-1] % 16 != 0:
+            return torch.nn.functional.linear(x, self.weight, self.bias)
+        return _FP8RowwiseLinearFn.apply(x, self.weight, self.bias)
+
+
 class FP8Linear(nn.Module):
     """``nn.Linear`` replacement computing with MXFP8 operands and a bf16 master weight."""
 

@@ -471,3 +471,42 @@ def test_newton_schulz_on_tensor_cores_orthogonalises():
     assert (x.cpu() - want).abs().max().item() < 0.05 * want.abs().max().item() + 5e-3
     d = (x @ x.t()).diagonal()                                                 # squared row norms, 1 / 256 at the start
     assert d.min().item() > 10.0 / 256 and d.max().item() < 1.3               # pulled towards an orthonormal set of rows
+
+
+@pytest.mark.parametrize("M,N,K", [(512, 768, 256), (300, 200, 144), (1024, 896, 4864)])
+def test_fp8_tensor_core_gemm_matches_dequantised_fp32(M, N, K):
+    """kind::f8f6f4 GEMM on CTA pairs: e4m3 operands with per-row scales; the oracle multiplies the exactly
+    dequantised operands in fp32, so only the bf16 rounding of the output separates the two."""
+    from chronicals_b200.utils.fp8_utils import fp8_rowwise_matmul, rowwise_quantize_e4m3
+    g = torch.Generator().manual_seed(9)
+    x = (torch.randn(M, K, generator=g) * torch.exp(torch.randn(M, 1, generator=g))).to(torch.bfloat16).cuda()
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).cuda()
+    bias = torch.randn(N, generator=g).to(torch.bfloat16).cuda()
+    xq, xs = rowwise_quantize_e4m3(x)
+    wq, ws = rowwise_quantize_e4m3(w)
+    # the quantisation kernel against the PyTorch formula
+    with _ext.force_reference():
+        xq_ref, xs_ref = rowwise_quantize_e4m3(x)
+    assert torch.allclose(xs, xs_ref, rtol=1e-6)
+    assert (xq != xq_ref).float().mean().item() < 1e-3
+    y = fp8_rowwise_matmul(xq, xs, wq, ws, bias)
+    a = xq.view(torch.float8_e4m3fn).float() * xs[:, None]
+    b = wq.view(torch.float8_e4m3fn).float() * ws[:, None]
+    want = a @ b.t() + bias.float()
+    assert (y.float() - want).abs().max().item() < 1e-2 * want.abs().max().item()
+    # and the quantisation error against the unquantised product stays at the e4m3 level
+    full = x.float() @ w.float().t() + bias.float()
+    assert (y.float() - full).abs().max().item() < 0.12 * full.abs().max().item()
+    _ext.check_status()
+
+
+def test_fp8_rowwise_linear_module_trains():
+    from chronicals_b200.utils.fp8_utils import FP8RowwiseLinear
+    torch.manual_seed(0)
+    lin = FP8RowwiseLinear(256, 384).cuda()
+    x = torch.randn(128, 256, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    y = lin(x)
+    y.float().pow(2).mean().backward()
+    assert y.shape == (128, 384) and x.grad is not None and lin.weight.grad is not None
+    ref_y = torch.nn.functional.linear(x.detach(), lin.weight.detach(), lin.bias.detach())
+    assert (y.float() - ref_y.float()).abs().max().item() < 0.1 * ref_y.float().abs().max().item()
