@@ -92,6 +92,27 @@ def run_gemm(results, peaks, iters, only=None):
         _ext.check_status()
 
 
+def run_gemm_fp8(results, peaks, iters, only=None):
+    """e4m3 GEMM on the tensor cores (pre-quantised operands) against the bf16 GEMM of the same shape."""
+    from chronicals_b200.utils.fp8_utils import fp8_rowwise_matmul, rowwise_quantize_e4m3
+    for name in ("gateup_fwd_0.5b", "down_fwd_0.5b", "gateup_fwd_7b", "down_fwd_7b", "square_8k"):
+        if only and only != name:
+            continue
+        M, N, K, _, _ = GEMM_CASES[name]
+        a, b = bf(M, K), bf(N, K)
+        aq, asc = rowwise_quantize_e4m3(a)
+        bq, bsc = rowwise_quantize_e4m3(b)
+        ms = timed(lambda: fp8_rowwise_matmul(aq, asc, bq, bsc), iters)
+        ms_q = timed(lambda: rowwise_quantize_e4m3(a), iters)
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+        ms_bf16 = timed(lambda: ops.gemm(a, b, out=out), iters)
+        fl = 2.0 * M * N * K
+        results.append({"kernel": "gemm2sm_fp8", "case": name, "shape": [M, N, K], "ms": ms, "tflops": fl / ms / 1e9,
+                        "frac_of_measured_bf16": fl / ms / 1e9 / peaks["bf16_tflops"], "bf16_gemm_ms": ms_bf16,
+                        "speedup_vs_bf16": ms_bf16 / ms, "activation_quant_ms": ms_q})
+        _ext.check_status()
+
+
 def run_attn(results, peaks, iters, only=None):
     from chronicals_b200.kernels.flash_attention_optimizer import attention_flops
     cases = {"0.5b_8x1024": (14, 2, 64, [1024] * 8), "0.5b_2x4096": (14, 2, 64, [4096] * 2),
@@ -239,7 +260,7 @@ def main():
 
     print(f"peaks ({peaks['source']}): bf16 {peaks['bf16_tflops']} TFLOP/s, HBM {peaks['hbm_gbs']} GB/s", flush=True)
     results = _Live()
-    groups = {"gemm": run_gemm, "attn": run_attn, "elementwise": run_elementwise, "cce": run_cce, "optim": run_optim}
+    groups = {"gemm": run_gemm, "gemm_fp8": run_gemm_fp8, "attn": run_attn, "elementwise": run_elementwise, "cce": run_cce, "optim": run_optim}
     for name, fn in groups.items():
         if args.only and args.only != name:
             continue
