@@ -118,6 +118,10 @@ class FusedLinear(nn.Module):
         if self.has_lora and not self.lora_merged:
             from ..lora.functional import fused_lora_forward
             return fused_lora_forward(self, x, residual)
+        if getattr(self, "use_fp8_rowwise", False) and self.in_features % 16 == 0:
+            from ..utils.fp8_utils import _FP8RowwiseLinearFn
+            y = _FP8RowwiseLinearFn.apply(x, self.weight, self.bias)
+            return y if residual is None else y + residual
         if getattr(self, "use_mxfp8", False) and self.in_features % 32 == 0:
             from ..utils.fp8_utils import _MXFP8LinearFn
             y = _MXFP8LinearFn.apply(x, self.weight, self.bias)

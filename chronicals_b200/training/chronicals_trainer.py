@@ -153,7 +153,8 @@ class ChronicalsTrainer:
         self.fp8_context = None
         if a.fp8 and on_gpu and self.is_native_model and self._get("enable_mxfp8", False):
             from ..utils.fp8_deepseek import FP8Context, convert_model_to_fp8
-            convert_model_to_fp8(self.model, exclude_patterns=list(a.fp8_exclude_patterns))
+            convert_model_to_fp8(self.model, exclude_patterns=list(a.fp8_exclude_patterns),
+                                 mode=str(self._get("fp8_mode", "mxfp8")))
             self.fp8_context = FP8Context(self.model)
         self._active_optimizations["fp8"] = self.fp8_context is not None
 

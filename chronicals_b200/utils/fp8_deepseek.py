@@ -218,16 +218,22 @@ class _FusedFP8Mixin:
     """Marks this framework's fused projections to compute with MXFP8 operands."""
 
 
-def convert_model_to_fp8(model: nn.Module, exclude_patterns: Optional[List[str]] = None, verbose: bool = False) -> nn.Module:
+def convert_model_to_fp8(model: nn.Module, exclude_patterns: Optional[List[str]] = None, verbose: bool = False,
+                         mode: str = "mxfp8") -> nn.Module:
     """Replace eligible ``nn.Linear`` modules by ``FP8Linear`` (bf16 master weights are kept); fused
-    projections of native models are switched to their MXFP8 forward."""
+    projections of native models are switched to an FP8 forward: ``mode="mxfp8"`` = MX block-scaled operands
+    (32-element blocks, e8m0 scales) multiplied on the bf16 tensor path, ``mode="rowwise"`` = e4m3 operands
+    with per-token / per-channel scales multiplied by the FP8 tensor-core GEMM (``kind::f8f6f4``)."""
+    if mode not in ("mxfp8", "rowwise"):
+        raise ValueError(f"unknown fp8 mode {mode!r}")
     n = 0
     from ..models.decoder import FusedLinear
     pats = DEFAULT_FP8_EXCLUDE_PATTERNS if exclude_patterns is None else list(exclude_patterns)
     for name, mod in list(model.named_modules()):
         if isinstance(mod, FusedLinear):
             if not any(p in name.lower() for p in pats) and mod.in_features % 32 == 0:
-                mod.use_mxfp8 = True
+                mod.use_mxfp8 = mode == "mxfp8"
+                mod.use_fp8_rowwise = mode == "rowwise"
                 n += 1
     for parent_name, parent in list(model.named_modules()):
         for child_name, child in list(parent.named_children()):
