@@ -32,6 +32,8 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-prefetch", action="store_true")
+    ap.add_argument("--fp8", default="none", choices=["none", "rowwise", "mxfp8"],
+                    help="forward projections on FP8 operands (rowwise: e4m3 tensor-core GEMM; mxfp8: MX block scales, bf16 math)")
     a = ap.parse_args()
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     from chronicals_b200 import ChronicalsConfig, build_model
@@ -48,6 +50,9 @@ def main() -> int:
         cfg.num_hidden_layers = a.layers
     model = build_model(cfg, dtype=torch.bfloat16, device=dev, seed=None)
     n_params = sum(p.numel() for p in model.parameters())
+    if a.fp8 != "none":
+        from chronicals_b200.utils.fp8_deepseek import convert_model_to_fp8
+        convert_model_to_fp8(model, exclude_patterns=[], mode=a.fp8)
     eng = Zero3Engine(model, lr=1e-5, weight_decay=0.01, max_grad_norm=1.0, prefetch=not a.no_prefetch)
     torch.cuda.empty_cache()
     g = torch.Generator().manual_seed(100 + rank)
@@ -79,7 +84,7 @@ def main() -> int:
                           "tokens_per_step": tokens, "ms_per_step": ms, "tokens_per_sec": tokens / (ms / 1e3),
                           "n_params": n_params, "peak_mem_gb": torch.cuda.max_memory_allocated() / 2 ** 30,
                           "mfu_6N_vs_2250TF": 6.0 * n_params * tokens / (ms / 1e3) / (2250e12 * world),
-                          "prefetch": not a.no_prefetch, "loss": float(loss), "dtype": "bf16",
+                          "prefetch": not a.no_prefetch, "fp8": a.fp8, "loss": float(loss), "dtype": "bf16",
                           "data": "synthetic token ids, random-init weights"}), flush=True)
     shutdown()
     return 0
