@@ -119,8 +119,8 @@ class FusedLinear(nn.Module):
             from ..lora.functional import fused_lora_forward
             return fused_lora_forward(self, x, residual)
         if getattr(self, "use_fp8_rowwise", False) and self.in_features % 16 == 0:
-            from ..utils.fp8_utils import _FP8RowwiseLinearFn
-            y = _FP8RowwiseLinearFn.apply(x, self.weight, self.bias)
+            from ..utils.fp8_utils import fp8_rowwise_linear
+            y = fp8_rowwise_linear(x, self.weight, self.bias)
             return y if residual is None else y + residual
         if getattr(self, "use_mxfp8", False) and self.in_features % 32 == 0:
             from ..utils.fp8_utils import _MXFP8LinearFn

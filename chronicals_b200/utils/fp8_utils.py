@@ -139,7 +139,8 @@ class _MXFP8LinearFn(torch.autograd.Function):
         ctx.save_for_backward(x2, w)
         ctx.has_bias = bias is not None
         ctx.shape = x.shape
-        return y.view(*x.shape[:-1], w.shape[0])
+        # a 2-D input gets the GEMM output itself (not a view of it), so in-place ops on it stay legal
+        return y if x.dim() == 2 else y.view(*x.shape[:-1], w.shape[0])
 
     @staticmethod
     def backward(ctx, dy):
@@ -209,15 +210,14 @@ class _FP8RowwiseLinearFn(torch.autograd.Function):
     backward in bf16 from the saved high-precision operands."""
 
     @staticmethod
-    def forward(ctx, x, w, bias):
-        x2 = x.reshape(-1, x.shape[-1])
+    def forward(ctx, x2, w, bias):
+        # 2-D in, 2-D out: the output is a fresh tensor (never a view), so in-place ops on it stay legal
         xq, xs = rowwise_quantize_e4m3(x2)
         wq, ws = rowwise_quantize_e4m3(w)
         y = fp8_rowwise_matmul(xq, xs, wq, ws, bias)
         ctx.save_for_backward(x2, w)
         ctx.has_bias = bias is not None
-        ctx.shape = x.shape
-        return y.to(x.dtype).view(*x.shape[:-1], w.shape[0])
+        return y if y.dtype == x2.dtype else y.to(x2.dtype)
 
     @staticmethod
     def backward(ctx, dy):
@@ -225,12 +225,20 @@ class _FP8RowwiseLinearFn(torch.autograd.Function):
         dy2 = dy.reshape(-1, dy.shape[-1]).contiguous()
         dx = dw = db = None
         if ctx.needs_input_grad[0]:
-            dx = (ops.gemm(dy2, w, b_mn=True) if ops._fast(dy2, w) else dy2 @ w).view(ctx.shape)
+            dx = ops.gemm(dy2, w, b_mn=True) if ops._fast(dy2, w) else dy2 @ w
         if ctx.needs_input_grad[1]:
             dw = ops.gemm(dy2, x2, a_mn=True, b_mn=True) if ops._fast(dy2, x2) else dy2.t() @ x2
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = dy2.float().sum(0).to(dy.dtype)
         return dx, dw, db
+
+
+def fp8_rowwise_linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    x2 = x.reshape(-1, x.shape[-1])
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    y = _FP8RowwiseLinearFn.apply(x2, w, bias)
+    return y if x.dim() == 2 else y.view(*x.shape[:-1], w.shape[0])
 
 
 class FP8RowwiseLinear(nn.Module):
@@ -246,7 +254,7 @@ class FP8RowwiseLinear(nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if x.shape[-1] % 16 != 0:
             return torch.nn.functional.linear(x, self.weight, self.bias)
-        return _FP8RowwiseLinearFn.apply(x, self.weight, self.bias)
+        return fp8_rowwise_linear(x, self.weight, self.bias)
 
 
 class FP8Linear(nn.Module):
