@@ -310,8 +310,20 @@ def run_reference(args):
         model = model.to(dev)
         if world > 1:
             # the reference ships no multi-GPU support: its trainer is given a DistributedDataParallel model
+            # The wrapper forwards attribute look-ups to the wrapped model, so the reference's trainer finds
+            # `lm_head`, `config`, `model.layers` … exactly as on one GPU and takes the same code path at every N
+            # (with a plain DDP wrapper its `hasattr(model, "lm_head")` test fails and it silently falls back to
+            # a different loss path).
             from torch.nn.parallel import DistributedDataParallel as DDP
-            model = DDP(model, device_ids=[local_rank])
+
+            class TransparentDDP(DDP):
+                def __getattr__(self, name):
+                    try:
+                        return super().__getattr__(name)
+                    except AttributeError:
+                        return getattr(super().__getattr__("module"), name)
+
+            model = TransparentDDP(model, device_ids=[local_rank])
         # flag values of the reference's own benchmark recipe (benchmarks/run_benchmark.py:1027-1077),
         # with one optimizer step per 8 x 1024 micro-batch as the benchmark configuration names
         cfg = RefTrainingConfig()
