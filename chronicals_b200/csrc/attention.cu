@@ -37,7 +37,7 @@ struct AttnArgs {
   // backward
   const float* delta;   // [hq, T]  rowsum(dO * O)
   float* dq_acc;        // [T, hq, D] fp32, zero-initialised; accumulated with red.add
-  float* dk_part;       // [T, hq, D] fp32 per-query-head partials
+  float* dk_part;       // [T, hk, D] fp32, zero-initialised; accumulated with red.add over the group's query heads
   float* dv_part;
   int* status;
 };
@@ -312,228 +312,21 @@ __global__ void attn_delta_kernel(const bf16* __restrict__ dO, const bf16* __res
 // =========================================================================================== backward
 namespace cb {
 
-template <int D>
-struct BwdSmem {
-  static constexpr int TILE = 128 * D * 2;
-  static constexpr int STAGES = (D == 64) ? 2 : 1;   // Q / dO ring depth (shared-memory budget)
-  static constexpr int OFF_K = 0;
-  static constexpr int OFF_V = TILE;
-  static constexpr int OFF_Q = 2 * TILE;
-  static constexpr int OFF_DO = OFF_Q + STAGES * TILE;
-  static constexpr int OFF_P = OFF_DO + STAGES * TILE;
-  static constexpr int OFF_DS = OFF_P + 32768;
-  static constexpr int OFF_BAR = OFF_DS + 32768;
-  static constexpr int TOTAL = OFF_BAR + 128 + 1024;
-};
-
 __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
-// One CTA: kv block `jb` of one document, one query head; loops over the query blocks i >= jb.
-template <int D>
-__global__ void __launch_bounds__(ATT_THREADS)
-attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO, const AttnArgs a) {
-  using L = BwdSmem<D>;
-  constexpr int PANELS = D / 64;
-  constexpr int STAGES = L::STAGES;
-  constexpr uint32_t TMEM_COLS = 512;
-  constexpr uint32_t C_S = 0, C_DP = 128, C_DV = 256, C_DK = 256 + D;    // dQ reuses the S columns
-  constexpr uint32_t IDESC_S = umma_idesc_bf16(128, 128, 0, 0);
-  constexpr uint32_t IDESC_T = umma_idesc_bf16(128, D, 1, 1);            // P^T dO, dS^T Q
-  constexpr uint32_t IDESC_DQ = umma_idesc_bf16(128, D, 0, 1);           // dS K
-
-  int start, len, jb, nblk;
-  if (!locate_block(a.cu, a.n_docs, blockIdx.x, start, len, jb, nblk)) return;   // jb = 0 is the heaviest
-  const int h = blockIdx.y;
-  const int hkv = h / (a.hq / a.hk);
-
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sK = smem + L::OFF_K;
-  uint8_t* sV = smem + L::OFF_V;
-  uint8_t* sQ = smem + L::OFF_Q;
-  uint8_t* sdO = smem + L::OFF_DO;
-  uint8_t* sP = smem + L::OFF_P;
-  uint8_t* sdS = smem + L::OFF_DS;
-  uint64_t* q_full = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);   // [2]
-  uint64_t* bar_kv = q_full + 2;
-  uint64_t* bar_s = q_full + 3;
-  uint64_t* bar_dp = q_full + 4;
-  uint64_t* bar_dq = q_full + 5;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_full + 6);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-
-  const int tid = threadIdx.x, warp = tid >> 5;
-  if (tid == 0) {
-    mbar_init(q_full, 1); mbar_init(q_full + 1, 1);
-    mbar_init(bar_kv, 1); mbar_init(bar_s, 1); mbar_init(bar_dp, 1); mbar_init(bar_dq, 1);
-    mbar_fence_init();
-    *abort_flag = a.status[0] != 0 ? 1 : 0;
-  }
-  __syncthreads();
-  if (*abort_flag) return;
-  if (warp == 0) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = *tmem_slot;
-  const uint32_t t_row = tmem + (static_cast<uint32_t>(warp * 32) << 16);
-
-  const int kv_row0 = start + jb * 128;
-  const int n_it = nblk - jb;
-  auto load_q = [&](int it) {
-    const int st = it % STAGES;
-    const int row0 = start + (jb + it) * 128;
-    mbar_expect_tx(q_full + st, 2 * L::TILE);
-#pragma unroll
-    for (int p = 0; p < PANELS; ++p) {
-      tma_load_2d(sQ + st * L::TILE + p * 16384, &tmQ, q_full + st, h * D + p * 64, row0);
-      tma_load_2d(sdO + st * L::TILE + p * 16384, &tmdO, q_full + st, h * D + p * 64, row0);
-    }
-  };
-
-  bool ok = true;
-  if (tid == 0) {
-    mbar_expect_tx(bar_kv, 2 * L::TILE);
-#pragma unroll
-    for (int p = 0; p < PANELS; ++p) {
-      tma_load_2d(sK + p * 16384, &tmK, bar_kv, hkv * D + p * 64, kv_row0);
-      tma_load_2d(sV + p * 16384, &tmV, bar_kv, hkv * D + p * 64, kv_row0);
-    }
-    load_q(0);
-    if (STAGES > 1 && n_it > 1) load_q(1);
-    ok &= mbar_wait(bar_kv, 0, abort_flag, a.status, CB_ERR_WAIT_FULL);
-  }
-
-  const int r = tid;
-  const float sl2 = a.scale * LOG2E;
-  const uint32_t kA = smem_u32(sK), vA = smem_u32(sV), pA = smem_u32(sP), dsA = smem_u32(sdS);
-
-  for (int it = 0; it < n_it; ++it) {
-    const int st = it % STAGES;
-    const int i = jb + it;
-    const uint32_t qA = smem_u32(sQ + st * L::TILE), doA = smem_u32(sdO + st * L::TILE);
-    if (tid == 0) {
-      ok &= mbar_wait(q_full + st, (it / STAGES) & 1, abort_flag, a.status, CB_ERR_WAIT_FULL);
-      if (ok) {
-        tc_fence_after();
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk)
-          umma_f16_ss(tmem + C_S, desc_kmajor(qA, kk), desc_kmajor(kA, kk), IDESC_S, kk != 0);
-        umma_commit(bar_s);
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk)
-          umma_f16_ss(tmem + C_DP, desc_kmajor(doA, kk), desc_kmajor(vA, kk), IDESC_S, kk != 0);
-        umma_commit(bar_dp);
-      }
-    }
-    const int rg = i * 128 + r;                      // my query row within the document
-    const bool row_ok = rg < len;
-    const long long tq = start + rg;
-    const float lse2 = row_ok ? a.lse[static_cast<long long>(h) * a.T + tq] * LOG2E : 0.f;
-    const float dlt = row_ok ? a.delta[static_cast<long long>(h) * a.T + tq] : 0.f;
-    const bool diag = (it == 0);
-    ok &= mbar_wait(bar_s, it & 1, abort_flag, a.status, CB_ERR_WAIT_TMEM_FULL);
-    ok &= mbar_wait(bar_dp, it & 1, abort_flag, a.status, CB_ERR_WAIT_TMEM_FULL);
-    tc_fence_after();
-#pragma unroll 1
-    for (int c = 0; c < 4; ++c) {
-      uint32_t s[32], dp[32];
-      float p[32], ds[32];
-      tmem_ld_32x32(t_row + C_S + c * 32, s);
-      tmem_ld_32x32(t_row + C_DP + c * 32, dp);
-      tmem_ld_wait();
-#pragma unroll
-      for (int k = 0; k < 32; ++k) {
-        const bool keep = row_ok && (!diag || c * 32 + k <= r);
-        const float e = exp2f(fmaf(__uint_as_float(s[k]), sl2, -lse2));
-        p[k] = keep ? e : 0.f;
-        ds[k] = p[k] * (__uint_as_float(dp[k]) - dlt) * a.scale;
-      }
-      store_row_chunk32(sP, r, c, p);
-      store_row_chunk32(sdS, r, c, ds);
-    }
-    tc_fence_before();
-    fence_async_smem();
-    if (__syncthreads_or(!ok)) { ok = false; break; }
-    if (tid == 0) {
-      tc_fence_after();
-#pragma unroll
-      for (int kk = 0; kk < 8; ++kk)                  // dV += P^T dO     (K = the 128 query rows)
-        umma_f16_ss(tmem + C_DV, desc_mnmajor(pA, kk), desc_mnmajor(doA, kk), IDESC_T, (it | kk) != 0);
-#pragma unroll
-      for (int kk = 0; kk < 8; ++kk)                  // dK += dS^T Q
-        umma_f16_ss(tmem + C_DK, desc_mnmajor(dsA, kk), desc_mnmajor(qA, kk), IDESC_T, (it | kk) != 0);
-#pragma unroll
-      for (int kk = 0; kk < 8; ++kk)                  // dQ = dS K        (K = the 128 kv rows)
-        umma_f16_ss(tmem + C_S, desc_kmajor(dsA, kk), desc_mnmajor(kA, kk), IDESC_DQ, kk != 0);
-      umma_commit(bar_dq);
-    }
-    ok &= mbar_wait(bar_dq, it & 1, abort_flag, a.status, CB_ERR_WAIT_TMEM_FULL);
-    tc_fence_after();
-    if (tid == 0 && ok && it + STAGES < n_it) load_q(it + STAGES);      // this stage's Q / dO are consumed
-#pragma unroll
-    for (int c = 0; c < D / 32; ++c) {
-      uint32_t dq[32];
-      tmem_ld_32x32(t_row + C_S + c * 32, dq);
-      tmem_ld_wait();
-      if (row_ok && ok) {
-        float* dst = a.dq_acc + (tq * a.hq + h) * D + c * 32;
-#pragma unroll
-        for (int k = 0; k < 32; k += 4)
-          red_add_v4(dst + k, __uint_as_float(dq[k]), __uint_as_float(dq[k + 1]), __uint_as_float(dq[k + 2]),
-                     __uint_as_float(dq[k + 3]));
-      }
-    }
-    tc_fence_before();
-    if (__syncthreads_or(!ok)) { ok = false; break; }
-  }
-  if (ok) {
-    tc_fence_after();
-    const int kg = jb * 128 + r;                      // my kv row within the document
-    const bool kv_ok = kg < len;
-    const long long tk = start + kg;
-#pragma unroll
-    for (int c = 0; c < D / 32; ++c) {
-      uint32_t dv[32], dk[32];
-      tmem_ld_32x32(t_row + C_DV + c * 32, dv);
-      tmem_ld_32x32(t_row + C_DK + c * 32, dk);
-      tmem_ld_wait();
-      if (kv_ok) {
-        float4* pv = reinterpret_cast<float4*>(a.dv_part + (tk * a.hq + h) * D + c * 32);
-        float4* pk = reinterpret_cast<float4*>(a.dk_part + (tk * a.hq + h) * D + c * 32);
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          pv[k] = make_float4(__uint_as_float(dv[4 * k]), __uint_as_float(dv[4 * k + 1]),
-                              __uint_as_float(dv[4 * k + 2]), __uint_as_float(dv[4 * k + 3]));
-          pk[k] = make_float4(__uint_as_float(dk[4 * k]), __uint_as_float(dk[4 * k + 1]),
-                              __uint_as_float(dk[4 * k + 2]), __uint_as_float(dk[4 * k + 3]));
-        }
-      }
-    }
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (*abort_flag) {
-    const uint64_t t0 = globaltimer_ns();
-    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
-    __syncthreads();
-  }
-  if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem, TMEM_COLS); }
-}
-
 // ---------------------------------------------------------------------------------------------------
-// Backward, occupancy-oriented variant (used for D = 64): 256 TMEM columns and ~97 KB of shared memory per
-// CTA, so two CTAs share an SM and one computes its softmax while the other has the tensor core.
+// Backward.  One CTA: kv block `jb` of one document, one query head; loops over the query blocks i >= jb.
+// For D = 64 it needs 256 TMEM columns and ~97 KB of shared memory, so two CTAs share an SM and one computes
+// its softmax while the other has the tensor core (D = 128: 512 columns, 160 KB, one CTA per SM).
 // The S, dP and dQ tiles take turns in the same 128 TMEM columns, and P and dS take turns in one shared
 // tile, which turns an iteration into three MMA phases:
 //   S = Q K^T            -> P = exp(S - lse)            (P to smem)
 //   dV += P^T dO ; dP = dO V^T  -> dS = P (dP - delta)  (P re-read from smem as bf16, dS overwrites it)
 //   dK += dS^T Q ; dQ = dS K    -> dQ added to global
 // dK / dV are added into [T, hk, D] fp32 accumulators with red.global.add (the query heads of a group are
-// different CTAs), which replaces the per-query-head partial buffers of the kernel above.
+// different CTAs).
 template <int D>
 struct Bwd2Smem {
   static constexpr int TILE = 128 * D * 2;
@@ -853,8 +646,8 @@ int cb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse
   return static_cast<int>(cudaGetLastError());
 }
 
-// Backward.  scratch: delta [hq*T] fp32, dq_acc / dk_part / dv_part [T*hq*D] fp32 each (dq_acc is
-// zeroed here).  dqkv: bf16 [T, (hq + 2 hk) * D] with row pitch ld_dqkv receives dQ | dK | dV.
+// Backward.  scratch: delta [hq*T] fp32, dq_acc [T*hq*D] fp32, dk_part / dv_part [T*hk*D] fp32 (all three
+// accumulators are zeroed here).  dqkv: bf16 [T, (hq + 2 hk) * D] with row pitch ld_dqkv receives dQ | dK | dV.
 int cb_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse,
                 const int* cu, int n_docs, int T, int hq, int hk, int D, long long ldq, long long ldk, long long ldv,
                 long long ldo, long long ld_do, float scale, float* delta, float* dq_acc, float* dk_part,
@@ -875,19 +668,19 @@ int cb_attn_bwd(const void* q, const void* k, const void* v, const void* o, cons
   a.lse = const_cast<float*>(lse); a.delta = delta; a.dq_acc = dq_acc; a.dk_part = dk_part; a.dv_part = dv_part;
   a.status = status;
   dim3 grid((T + 127) / 128 + n_docs, hq);
-  int part_heads = hq;
+  // Two threads per score row, S / dP / dQ sharing TMEM columns, dK / dV accumulated per kv head with red.add
+  // (so those buffers start from zero).  D = 64 additionally fits two CTAs per SM.
+  const int part_heads = hk;
+  CB_CHECK_CUDA(cudaMemsetAsync(dk_part, 0, sizeof(float) * static_cast<size_t>(T) * hk * D, s));
+  CB_CHECK_CUDA(cudaMemsetAsync(dv_part, 0, sizeof(float) * static_cast<size_t>(T) * hk * D, s));
   if (D == 64) {
-    // two CTAs per SM; dK / dV accumulate per kv head with red.add, so those buffers start from zero
     static bool cfg = false;
     if (!cfg) { e = set_smem(cb::attn_bwd2_kernel<64>, cb::Bwd2Smem<64>::TOTAL); if (e) return e; cfg = true; }
-    part_heads = hk;
-    CB_CHECK_CUDA(cudaMemsetAsync(dk_part, 0, sizeof(float) * static_cast<size_t>(T) * hk * D, s));
-    CB_CHECK_CUDA(cudaMemsetAsync(dv_part, 0, sizeof(float) * static_cast<size_t>(T) * hk * D, s));
     cb::attn_bwd2_kernel<64><<<grid, cb::BWD2_THREADS, cb::Bwd2Smem<64>::TOTAL, s>>>(mq, mk, mv, mdo, a);
   } else {
     static bool cfg = false;
-    if (!cfg) { e = set_smem(cb::attn_bwd_kernel<128>, cb::BwdSmem<128>::TOTAL); if (e) return e; cfg = true; }
-    cb::attn_bwd_kernel<128><<<grid, cb::ATT_THREADS, cb::BwdSmem<128>::TOTAL, s>>>(mq, mk, mv, mdo, a);
+    if (!cfg) { e = set_smem(cb::attn_bwd2_kernel<128>, cb::Bwd2Smem<128>::TOTAL); if (e) return e; cfg = true; }
+    cb::attn_bwd2_kernel<128><<<grid, cb::BWD2_THREADS, cb::Bwd2Smem<128>::TOTAL, s>>>(mq, mk, mv, mdo, a);
   }
   cb::attn_bwd_finalize_kernel<<<T, 128, 0, s>>>(dq_acc, dk_part, dv_part, static_cast<cb::bf16*>(dqkv), ld_dqkv, T,
                                                   hq, hk, D, cu, n_docs, part_heads);

@@ -45,14 +45,14 @@ class _AttnPackedFn(torch.autograd.Function):
         if not do.is_contiguous():
             do = do.contiguous()
         dev = qkv.device
-        # the kernels use 16-byte vector accesses on dq_acc / dk_part / dv_part: every region must start
-        # on a 16-byte boundary whatever T is (T * nq is a multiple of 4 because D is 64 or 128)
+        # the kernels use 16-byte vector accesses on dq_acc / dk_acc / dv_acc: every region must start on a
+        # 16-byte boundary whatever T is (T * nq and T * nk are multiples of 4 because D is 64 or 128)
         n_delta = (hq * T + 63) // 64 * 64
-        scratch = torch.empty(n_delta + 3 * T * nq, dtype=torch.float32, device=dev)
+        scratch = torch.empty(n_delta + T * nq + 2 * T * nk, dtype=torch.float32, device=dev)
         delta = scratch[:hq * T]
         dq_acc = scratch[n_delta: n_delta + T * nq]
-        dk_part = scratch[n_delta + T * nq: n_delta + 2 * T * nq]
-        dv_part = scratch[n_delta + 2 * T * nq:]
+        dk_part = scratch[n_delta + T * nq: n_delta + T * nq + T * nk]        # per kv head, accumulated by the kernel
+        dv_part = scratch[n_delta + T * nq + T * nk:]
         dqkv = torch.empty(T, nq + 2 * nk, dtype=qkv.dtype, device=dev)
         esz = qkv.element_size()
         code = _ext.lib().cb_attn_bwd(qkv.data_ptr(), qkv.data_ptr() + nq * esz, qkv.data_ptr() + (nq + nk) * esz,
