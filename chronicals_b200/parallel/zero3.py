@@ -252,6 +252,17 @@ class Zero3Engine:
         return loss.detach()
 
     @torch.no_grad()
+    def forward_only(self, input_ids: torch.Tensor, labels: Optional[torch.Tensor] = None, **kw):
+        """Evaluation forward: units are gathered and released by the same hooks, nothing is kept for a backward."""
+        outer = self.units[0]
+        self._gather(outer, side=False)
+        out = self.model(input_ids, labels=labels, **kw)
+        for u in self.units:
+            if u.resident:
+                self._release(u)
+        return out
+
+    @torch.no_grad()
     def step(self) -> None:
         self.step_count += 1
         t = self.step_count
@@ -313,3 +324,36 @@ class Zero3Engine:
             u.exp_avg.copy_(s["exp_avg"])
             u.exp_avg_sq.copy_(s["exp_avg_sq"])
             u.shard_t.copy_(s["shard"])
+
+
+class Zero3Optimizer(torch.optim.Optimizer):
+    """Optimizer-shaped handle on a :class:`Zero3Engine` so that learning-rate schedulers, checkpoint code and the
+    trainer loop can treat ZeRO-3 like any other optimizer.  ``param_groups[0]["lr"]`` is copied into the engine
+    before every step; gradients live inside the engine, so ``zero_grad`` has nothing to do."""
+
+    def __init__(self, engine: Zero3Engine):
+        self.engine = engine
+        self._handle = torch.nn.Parameter(torch.zeros(1, device=engine.device), requires_grad=False)
+        super().__init__([self._handle], dict(lr=engine.lr, betas=engine.betas, eps=engine.eps,
+                                              weight_decay=engine.weight_decay))
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        g = self.param_groups[0]
+        self.engine.lr, self.engine.weight_decay = float(g["lr"]), float(g["weight_decay"])
+        self.engine.step()
+        return None
+
+    def zero_grad(self, set_to_none: bool = True) -> None:
+        return None
+
+    @property
+    def last_grad_norm(self):
+        return self.engine.last_grad_norm
+
+    def state_dict(self):
+        return {"zero3": self.engine.state_dict(), "lr": self.param_groups[0]["lr"]}
+
+    def load_state_dict(self, sd) -> None:
+        self.engine.load_state_dict(sd["zero3"])
+        self.param_groups[0]["lr"] = sd.get("lr", self.param_groups[0]["lr"])

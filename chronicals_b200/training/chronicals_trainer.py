@@ -218,7 +218,7 @@ class ChronicalsTrainer:
         # with several ranks the step is captured only when it contains no NCCL call (sharded fused optimizer)
         self.use_cuda_graphs = bool(a.use_cuda_graphs) and on_gpu and self.is_native_model \
             and a.gradient_accumulation_steps == 1 and (self.world_size == 1 or self._sharded_optimizer) \
-            and not self.tp_model
+            and not self.tp_model and self.zero3 is None
         self._active_optimizations["cuda_graphs"] = self.use_cuda_graphs
         # host-side failure detection: heartbeat over the process-group store, checked before each step
         self.watchdog = None
@@ -254,6 +254,22 @@ class ChronicalsTrainer:
         a = self.args
         t = a.optimizer_type
         self.use_external_grad_clip = True
+        self.zero3 = None
+        if a.parallel.zero_stage == 3 and self.world_size > 1 and not getattr(self, "tp_model", False):
+            # parameters, gradients and AdamW state sharded over the data-parallel ranks (parallel/zero3.py)
+            if not self.is_native_model:
+                raise ValueError("ZeRO-3 needs a native model")
+            if a.gradient_accumulation_steps != 1:
+                raise ValueError("ZeRO-3 reduces gradients every micro-step: set gradient_accumulation_steps = 1")
+            from ..parallel.zero3 import Zero3Engine, Zero3Optimizer
+            self.zero3 = Zero3Engine(self.model, lr=a.learning_rate, betas=(a.adam_beta1, a.adam_beta2), eps=a.adam_epsilon,
+                                     weight_decay=a.weight_decay, max_grad_norm=a.max_grad_norm,
+                                     wait_budget_us=a.parallel.wait_budget_us)
+            self.optimizer = Zero3Optimizer(self.zero3)
+            self.use_external_grad_clip = False
+            self._sharded_optimizer = True           # no separate gradient reducer
+            self._active_optimizations["fused_optimizer"] = True
+            return
         if self._get("use_lora_plus", False) or t in ("lora_plus", "loraplus"):
             from ..optimizers.lora_plus_optimizer import create_lora_plus_optimizer
             self.optimizer = create_lora_plus_optimizer(
@@ -359,6 +375,14 @@ class ChronicalsTrainer:
         Returns the detached loss tensor on the device (no host synchronisation)."""
         if self.use_cuda_graphs and do_step:
             return self._graphed_step(batch)
+        if self.zero3 is not None:
+            inp = self._prepare_inputs(batch)
+            loss = self.zero3.forward_backward(inp["input_ids"], labels=inp["labels"], position_ids=inp.get("position_ids"),
+                                               cu_seqlens=inp.get("cu_seqlens"), max_seqlen=inp.get("max_seqlen"),
+                                               seqlens_host=inp.get("seqlens_host"),
+                                               shift_labels=bool(self._get("shift_labels", True)))
+            self.optimizer.step()
+            return loss
         if self._nvtx:
             nvtx = torch.cuda.nvtx
             nvtx.range_push("data")
@@ -670,7 +694,15 @@ class ChronicalsTrainer:
         self.model.eval()
         tot, n = torch.zeros((), device=self.device), 0
         for batch in dl:
-            tot += self._forward_loss(self._prepare_inputs(batch)).float()
+            inp = self._prepare_inputs(batch)
+            if self.zero3 is not None:
+                with torch.no_grad():
+                    tot += self.zero3.forward_only(inp["input_ids"], labels=inp["labels"],
+                                                   position_ids=inp.get("position_ids"), cu_seqlens=inp.get("cu_seqlens"),
+                                                   max_seqlen=inp.get("max_seqlen"),
+                                                   shift_labels=bool(self._get("shift_labels", True))).loss.float()
+            else:
+                tot += self._forward_loss(inp).float()
             n += 1
         if self.world_size > 1:
             t = torch.stack((tot, torch.tensor(float(n), device=self.device)))
@@ -686,7 +718,8 @@ class ChronicalsTrainer:
         a = self.args
         out = os.path.join(a.output_dir, name)
         # a tensor-parallel model re-assembles the full HuggingFace-named tensors with a collective gather
-        full_state = self.model.gather_full_state_dict() if self.tp_model else None
+        full_state = self.model.gather_full_state_dict() if self.tp_model else (
+            self.zero3.gather_full_state_dict() if self.zero3 is not None else None)
         if self.rank == 0:
             ckpt_io.save_model(self.model, out, safe=bool(self._get("save_safetensors", True)), state=full_state)
             lora_cfg = getattr(self.model, "lora_config", None)

@@ -22,6 +22,7 @@ def make_args(out):
 
 def main():
     out = sys.argv[1]
+    zero3 = len(sys.argv) > 2 and sys.argv[2] == "zero3"
     rank, _, world = init_distributed("gloo")
     cfg = ChronicalsConfig.from_model_name("tiny-qwen2")
     cfg.num_hidden_layers, cfg.vocab_size, cfg.dtype = 2, 2048, "float32"
@@ -31,8 +32,13 @@ def main():
     mine = [{"input_ids": ids[s, rank * per:(rank + 1) * per, :-1].contiguous(),
              "labels": ids[s, rank * per:(rank + 1) * per, 1:].contiguous()} for s in range(steps)]
     model = build_model(cfg, dtype=torch.float32, seed=0)
-    tr = ChronicalsTrainer(model, make_args(out + f".r{rank}"), mine)
+    a1 = make_args(out + f".r{rank}")
+    if zero3:
+        a1.parallel.zero_stage = 3
+        a1.max_grad_norm = 0.5
+    tr = ChronicalsTrainer(model, a1, mine)
     st = tr.train()
+    trained = tr.zero3.gather_full_state_dict() if zero3 else None
     dp_losses = [h["loss"] for h in st.log_history if "lr" in h]
     if rank == 0:
         # single-process oracle on the concatenated batch (no process group used by this trainer)
@@ -40,9 +46,15 @@ def main():
         m2 = build_model(cfg, dtype=torch.float32, seed=0)
         a2 = make_args(out + ".single")
         a2.use_distributed = False
+        if zero3:
+            a2.max_grad_norm = 0.5
         t2 = ChronicalsTrainer(m2, a2, full)
         single = [h["loss"] for h in t2.train().log_history if "lr" in h]
-        diff = max((p - q).abs().max().item() for p, q in zip(model.parameters(), m2.parameters()))
+        if zero3:
+            want = m2.hf_state_dict()
+            diff = max((trained[k] - want[k]).abs().max().item() for k in want)
+        else:
+            diff = max((p - q).abs().max().item() for p, q in zip(model.parameters(), m2.parameters()))
         with open(out, "w") as f:
             json.dump({"dp_losses": dp_losses, "single_losses": single, "max_param_diff": diff}, f)
     dist.barrier()
