@@ -221,6 +221,40 @@ rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ h, cons
   }
 }
 
+// Column sums of a bf16 matrix (bias gradients): part[block, n] = sum over the block's rows of x[row, n].
+// Thread t of a block owns the 8 columns of vector (blockIdx.y * blockDim.x + t); blocks along x split the rows.
+__global__ void __launch_bounds__(EW_THREADS)
+colsum_partial_kernel(const bf16* __restrict__ x, long long ld, long long M, int N, float* __restrict__ part) {
+  const int v = blockIdx.y * blockDim.x + threadIdx.x;
+  if (v >= N / 8) return;
+  const long long rows_per = (M + gridDim.x - 1) / gridDim.x;
+  const long long r0 = blockIdx.x * rows_per;
+  const long long r1 = (r0 + rows_per < M) ? r0 + rows_per : M;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  long long r = r0;
+  for (; r + 4 <= r1; r += 4) {                    // four independent 16-byte loads in flight
+    uint4 u[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) u[i] = *reinterpret_cast<const uint4*>(x + (r + i) * ld + (static_cast<long long>(v) << 3));
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float f[8];
+      unpack8(u[i], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += f[j];
+    }
+  }
+  for (; r < r1; ++r) {
+    float f[8];
+    unpack8(*reinterpret_cast<const uint4*>(x + r * ld + (static_cast<long long>(v) << 3)), f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] += f[j];
+  }
+  float* o = part + static_cast<long long>(blockIdx.x) * N + (v << 3);
+  reinterpret_cast<float4*>(o)[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+  reinterpret_cast<float4*>(o)[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+}
+
 // 256 threads = 32 columns x 8 row slices; each slice sums every 8th partial row, then the slices combine
 __global__ void rmsnorm_dw_reduce_kernel(const float* __restrict__ part, int nblocks, int N, bf16* __restrict__ dw,
                                          int accumulate) {
@@ -581,6 +615,26 @@ int cb_rmsnorm_bwd(const void* dy, const void* h, const void* w, const float* rs
   else cb::rmsnorm_bwd_kernel<256, 4><<<grid, cb::EW_THREADS, smem, s>>>(dyp, hp, wp, rstd, rp, dxp, dw_part, M, N, offset);
   if (dw != nullptr)
     cb::rmsnorm_dw_reduce_kernel<<<(N + 31) / 32, 256, 0, s>>>(dw_part, grid, N, static_cast<cb::bf16*>(dw), accumulate_dw);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// out[n] (bf16) = sum over rows of x[row, n]; x bf16 [M, N] with pitch ld (N and ld multiples of 8);
+// part: fp32 scratch of cb_colsum_blocks(M) * N elements.
+int cb_colsum_blocks(long long M) {
+  long long b = (M + 63) / 64;
+  const long long cap = static_cast<long long>(sm_count()) * 2;
+  if (b > cap) b = cap;
+  return static_cast<int>(b < 1 ? 1 : b);
+}
+
+int cb_colsum_bf16(const void* x, void* out, float* part, long long M, int N, long long ld, void* stream) {
+  if (M <= 0 || N <= 0 || N % 8 != 0 || ld % 8 != 0) return -1;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int blocks = cb_colsum_blocks(M);
+  const int nvec = N / 8;
+  dim3 grid(blocks, (nvec + cb::EW_THREADS - 1) / cb::EW_THREADS);
+  cb::colsum_partial_kernel<<<grid, cb::EW_THREADS, 0, s>>>(static_cast<const cb::bf16*>(x), ld, M, N, part);
+  cb::rmsnorm_dw_reduce_kernel<<<(N + 31) / 32, 256, 0, s>>>(part, blocks, N, static_cast<cb::bf16*>(out), 0);
   return static_cast<int>(cudaGetLastError());
 }
 

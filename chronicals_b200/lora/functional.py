@@ -88,7 +88,7 @@ class _FusedLoRAFn(torch.autograd.Function):
             grads.append((da_cat[r0:r0 + r] * sc).to(dy2.dtype))
             grads.append(db_big[sl, r0:r0 + r].to(dy2.dtype))
             r0 += r
-        db = dy2.float().sum(0).to(dy2.dtype) if (has_bias and ctx.needs_input_grad[2]) else None
+        db = ops.colsum(dy2) if (has_bias and ctx.needs_input_grad[2]) else None
         dw = None
         if ctx.needs_input_grad[1]:                                         # base weight left trainable on purpose
             dw = ops.gemm(dy2, x2, a_mn=True, b_mn=True)

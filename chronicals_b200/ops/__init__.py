@@ -18,7 +18,7 @@ from . import ref
 from . import _ext
 
 __all__ = [
-    "linear", "gemm", "gemm_splitk", "rmsnorm", "add_rmsnorm", "swiglu", "geglu", "qk_rope_", "embedding",
+    "linear", "gemm", "gemm_splitk", "colsum", "rmsnorm", "add_rmsnorm", "swiglu", "geglu", "qk_rope_", "embedding",
     "attention_varlen", "attention_qkv_packed", "linear_cross_entropy", "cross_entropy_logits", "kernels_active",
 ]
 
@@ -103,6 +103,20 @@ def gemm_splitk(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: b
     return out
 
 
+def colsum(x: torch.Tensor) -> torch.Tensor:
+    """Column sums of a 2-D tensor in its own dtype with fp32 accumulation (bias gradients)."""
+    if _fast(x) and x.dim() == 2 and x.stride(1) == 1 and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 \
+            and x.data_ptr() % 16 == 0:
+        L = _ext.lib()
+        M, N = x.shape
+        part = torch.empty(L.cb_colsum_blocks(M) * N, dtype=torch.float32, device=x.device)
+        out = torch.empty(N, dtype=x.dtype, device=x.device)
+        _ext.check(L.cb_colsum_bf16(x.data_ptr(), out.data_ptr(), part.data_ptr(), M, N, x.stride(0), _ext.stream_ptr()),
+                   "colsum")
+        return out
+    return x.float().sum(0).to(x.dtype)
+
+
 class _LinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x2, w, bias, res2):
@@ -126,7 +140,7 @@ class _LinearFn(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             dw = gemm(dy2, x2, a_mn=True, b_mn=True)                 # dW = dY^T @ X
         if ctx.has_bias and ctx.needs_input_grad[2]:
-            db = dy2.float().sum(0).to(dy.dtype)
+            db = colsum(dy2)
         dres = dy2 if ctx.has_res else None
         return dx, dw, db, dres
 

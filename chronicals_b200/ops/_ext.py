@@ -37,6 +37,8 @@ _PROTOTYPES = {
     "cb_rmsnorm_bwd_blocks": [I, I],
     "cb_rmsnorm_fwd": [P, P, P, P, P, P, I, I, F, F, P],
     "cb_rmsnorm_bwd": [P, P, P, P, P, P, P, P, I, I, F, I, P],
+    "cb_colsum_blocks": [L],
+    "cb_colsum_bf16": [P, P, P, L, I, L, P],
     "cb_glu_fwd": [P, P, P, L, I, L, L, I, P],
     "cb_glu_bwd": [P, P, P, P, P, L, I, L, L, L, I, P],
     "cb_qk_rope": [P, P, P, P, P, L, I, I, I, L, L, I, I, L, P],

@@ -208,7 +208,7 @@ class _NormGatherLinear(torch.autograd.Function):
         dh = ft.gemm_push_reduce(dy, weight, None, b_mn=True)               # my rows of sum_r dy_r @ W_r (barrier inside)
         dx, dnw = _rmsnorm_bwd(dh, x, norm_w, rstd, offset)
         dw = ops.gemm(dy, hf, a_mn=True, b_mn=True)                         # dyᵀ @ hf; every panel has landed by now
-        db = dy.float().sum(dim=0).to(dy.dtype) if ctx.has_bias else None
+        db = ops.colsum(dy) if ctx.has_bias else None
         return dx, dnw, dw, db, None, None, None
 
 

@@ -159,7 +159,7 @@ class _MXFP8LinearFn(torch.autograd.Function):
             _, _, xtd = mxfp8_quantize(x2.t().contiguous(), "e4m3", True)         # [in, T]
             dw = ops.gemm(gtd, xtd) if fast and gtd.shape[1] % 8 == 0 else (gtd.float() @ xtd.float().t()).to(w.dtype)
         if ctx.has_bias and ctx.needs_input_grad[2]:
-            db = dy2.float().sum(0).to(dy.dtype)
+            db = ops.colsum(dy2)
         return dx, dw, db
 
 
@@ -229,7 +229,7 @@ class _FP8RowwiseLinearFn(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             dw = ops.gemm(dy2, x2, a_mn=True, b_mn=True) if ops._fast(dy2, x2) else dy2.t() @ x2
         if ctx.has_bias and ctx.needs_input_grad[2]:
-            db = dy2.float().sum(0).to(dy.dtype)
+            db = ops.colsum(dy2)
         return dx, dw, db
 
 

@@ -510,3 +510,15 @@ def test_fp8_rowwise_linear_module_trains():
     assert y.shape == (128, 384) and x.grad is not None and lin.weight.grad is not None
     ref_y = torch.nn.functional.linear(x.detach(), lin.weight.detach(), lin.bias.detach())
     assert (y.float() - ref_y.float()).abs().max().item() < 0.1 * ref_y.float().abs().max().item()
+
+
+@pytest.mark.parametrize("M,N", [(8192, 1152), (300, 896), (1, 64), (1000, 4864)])
+def test_colsum_kernel(M, N):
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(M, N, generator=g).to(torch.bfloat16).cuda()
+    out = ops.colsum(x)
+    want = x.float().sum(0)
+    assert out.dtype == torch.bfloat16 and out.shape == (N,)
+    assert (out.float() - want).abs().max().item() < 1e-2 * want.abs().max().item() + 1e-2
+    view = x[:, : N // 2] if (N // 2) % 8 == 0 else x                      # a strided view (column slice)
+    assert (ops.colsum(view).float() - view.float().sum(0)).abs().max().item() < 1e-2 * want.abs().max().item() + 1e-2
