@@ -143,6 +143,9 @@ class RMSNorm(nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return ops.rmsnorm(x, self.weight, self.eps, self.offset)
 
+    def with_residual(self, x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        return ops.rmsnorm_residual(x, self.weight, self.eps, self.offset)
+
 
 class Attention(nn.Module):
     def __init__(self, cfg: ChronicalsConfig, dtype, device=None):
@@ -188,8 +191,12 @@ class DecoderLayer(nn.Module):
         self._use_checkpoint = False
 
     def _body(self, h, cos, sin, position_ids, cu_seqlens, max_seqlen, seqlens_host):
-        h = self.self_attn(self.input_layernorm(h), h, cos, sin, position_ids, cu_seqlens, max_seqlen, seqlens_host)
-        return self.mlp(self.post_attention_layernorm(h), h)
+        # pre-norm residual blocks: the norm returns the stream itself as second value so that both gradient
+        # contributions of the stream meet inside the norm's backward kernel
+        n1, r1 = self.input_layernorm.with_residual(h)
+        h = self.self_attn(n1, r1, cos, sin, position_ids, cu_seqlens, max_seqlen, seqlens_host)
+        n2, r2 = self.post_attention_layernorm.with_residual(h)
+        return self.mlp(n2, r2)
 
     def forward(self, h, cos, sin, position_ids, cu_seqlens, max_seqlen, seqlens_host=None):
         if self._use_checkpoint and self.training and torch.is_grad_enabled():

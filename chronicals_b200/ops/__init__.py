@@ -18,7 +18,7 @@ from . import ref
 from . import _ext
 
 __all__ = [
-    "linear", "gemm", "gemm_splitk", "colsum", "rmsnorm", "add_rmsnorm", "swiglu", "geglu", "qk_rope_", "embedding",
+    "linear", "gemm", "gemm_splitk", "colsum", "rmsnorm", "rmsnorm_residual", "add_rmsnorm", "swiglu", "geglu", "qk_rope_", "embedding",
     "attention_varlen", "attention_qkv_packed", "linear_cross_entropy", "cross_entropy_logits", "kernels_active",
 ]
 
@@ -213,6 +213,60 @@ class _RMSNormFn(torch.autograd.Function):
         _ext.check(code, "rmsnorm_bwd")
         dxv = dx.view(ctx.shape)
         return dxv, (dxv if ctx.has_res else None), dw, None, None
+
+
+class _RMSNormPassFn(torch.autograd.Function):
+    """``(rmsnorm(x), x)``: the second output is the input itself, handed on as the residual of the following
+    projection.  Its gradient comes back here and is added inside the RMSNorm backward kernel (``dres_in``), so the
+    two gradient contributions of the residual stream are summed without a separate elementwise kernel."""
+
+    @staticmethod
+    def forward(ctx, x, w, eps, offset):
+        N = x.shape[-1]
+        x2 = x.reshape(-1, N)
+        M = x2.shape[0]
+        y = torch.empty_like(x2)
+        rstd = torch.empty(M, dtype=torch.float32, device=x.device)
+        code = _ext.lib().cb_rmsnorm_fwd(x2.data_ptr(), None, w.data_ptr(), y.data_ptr(), None, rstd.data_ptr(), M, N, eps,
+                                         offset, _ext.stream_ptr())
+        _ext.check(code, "rmsnorm_fwd")
+        ctx.save_for_backward(x2, w, rstd)
+        ctx.offset = offset
+        ctx.shape = x.shape
+        ctx.set_materialize_grads(False)
+        return y.view(x.shape), x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, dy, dpass):
+        x2, w, rstd = ctx.saved_tensors
+        M, N = x2.shape
+        if dy is None:
+            return (dpass, None, None, None)
+        dy2 = dy.reshape(M, N)
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dres = None
+        if dpass is not None:
+            dres = dpass.reshape(M, N)
+            if not dres.is_contiguous():
+                dres = dres.contiguous()
+        L = _ext.lib()
+        part = torch.empty(L.cb_rmsnorm_bwd_blocks(M, N) * N, dtype=torch.float32, device=x2.device)
+        dx = torch.empty_like(x2)
+        dw = torch.empty_like(w)
+        code = L.cb_rmsnorm_bwd(dy2.data_ptr(), x2.data_ptr(), w.data_ptr(), rstd.data_ptr(), _ext.ptr(dres), dx.data_ptr(),
+                                dw.data_ptr(), part.data_ptr(), M, N, ctx.offset, 0, _ext.stream_ptr())
+        _ext.check(code, "rmsnorm_bwd")
+        return dx.view(ctx.shape), dw, None, None
+
+
+def rmsnorm_residual(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6, offset: float = 0.0
+                     ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``(rmsnorm(x), x)`` for the pre-norm residual pattern ``x + f(rmsnorm(x))``: use the second value as the
+    residual so that its gradient is folded into the norm's backward kernel."""
+    if _rms_fast(x, weight) and x.is_contiguous():
+        return _RMSNormPassFn.apply(x, weight, eps, offset)
+    return ref.rmsnorm(x, weight, eps, offset), x
 
 
 def _rms_fast(x, w) -> bool:
