@@ -113,6 +113,28 @@ def run_gemm_fp8(results, peaks, iters, only=None):
         _ext.check_status()
 
 
+def run_gemm_mxfp8(results, peaks, iters, only=None):
+    """Block-scaled MXFP8 GEMM (``tcgen05.mma.kind::mxf8f6f4.block_scale``, pre-quantised operands with packed
+    e8m0 scales) against the bf16 GEMM of the same shape; also the cost of quantising the activation."""
+    from chronicals_b200.utils.fp8_utils import mxfp8_block_scaled_matmul, mxfp8_quantize_packed
+    for name in ("small_2k", "gateup_fwd_0.5b", "down_fwd_0.5b", "gateup_fwd_7b", "down_fwd_7b", "square_8k"):
+        if only and only != name:
+            continue
+        M, N, K = (2048, 2048, 2048) if name == "small_2k" else GEMM_CASES[name][:3]
+        a, b = bf(M, K), bf(N, K)
+        aq, sa = mxfp8_quantize_packed(a)
+        bq, sb = mxfp8_quantize_packed(b)
+        ms = timed(lambda: mxfp8_block_scaled_matmul(aq, sa, bq, sb), iters)
+        ms_q = timed(lambda: mxfp8_quantize_packed(a), iters)
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+        ms_bf16 = timed(lambda: ops.gemm(a, b, out=out), iters)
+        fl = 2.0 * M * N * K
+        results.append({"kernel": "mxgemm_block_scaled", "case": name, "shape": [M, N, K], "ms": ms, "tflops": fl / ms / 1e9,
+                        "frac_of_measured_bf16": fl / ms / 1e9 / peaks["bf16_tflops"], "bf16_gemm_ms": ms_bf16,
+                        "speedup_vs_bf16": ms_bf16 / ms, "activation_quant_ms": ms_q})
+        _ext.check_status()
+
+
 def run_attn(results, peaks, iters, only=None):
     from chronicals_b200.kernels.flash_attention_optimizer import attention_flops
     cases = {"0.5b_8x1024": (14, 2, 64, [1024] * 8), "0.5b_2x4096": (14, 2, 64, [4096] * 2),
@@ -224,7 +246,7 @@ def main():
     ap.add_argument("--only", default=None)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--json", default=None)
-    ap.add_argument("--one", default=None, help="run one GEMM case 3 times without timing (for ncu)")
+    ap.add_argument("--one", default=None, help="run one GEMM case 3 times without timing (for ncu); mx:<case> runs the block-scaled MXFP8 GEMM")
     args = ap.parse_args()
     peaks = measured_peaks()
     if args.one and args.one.startswith("attn"):
@@ -237,6 +259,17 @@ def main():
             o = ops.attention_qkv_packed(qkv, cu, hq, hk, d)
             o.backward(g)
             qkv.grad = None
+        torch.cuda.synchronize()
+        _ext.check_status()
+        print("ok")
+        return
+    if args.one and args.one.startswith("mx:"):
+        from chronicals_b200.utils.fp8_utils import mxfp8_block_scaled_matmul, mxfp8_quantize_packed
+        M, N, K = GEMM_CASES[args.one[3:]][:3]
+        aq, sa = mxfp8_quantize_packed(bf(M, K))
+        bq, sb = mxfp8_quantize_packed(bf(N, K))
+        for _ in range(3):
+            mxfp8_block_scaled_matmul(aq, sa, bq, sb)
         torch.cuda.synchronize()
         _ext.check_status()
         print("ok")
@@ -260,7 +293,7 @@ def main():
 
     print(f"peaks ({peaks['source']}): bf16 {peaks['bf16_tflops']} TFLOP/s, HBM {peaks['hbm_gbs']} GB/s", flush=True)
     results = _Live()
-    groups = {"gemm": run_gemm, "gemm_fp8": run_gemm_fp8, "attn": run_attn, "elementwise": run_elementwise, "cce": run_cce, "optim": run_optim}
+    groups = {"gemm": run_gemm, "gemm_fp8": run_gemm_fp8, "gemm_mxfp8": run_gemm_mxfp8, "attn": run_attn, "elementwise": run_elementwise, "cce": run_cce, "optim": run_optim}
     for name, fn in groups.items():
         if args.only and args.only != name:
             continue

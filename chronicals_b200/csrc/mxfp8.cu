@@ -20,7 +20,7 @@ namespace cb {
 template <int E5M2>
 __global__ void __launch_bounds__(256)
 mxfp8_quant_kernel(const bf16* __restrict__ x, unsigned char* __restrict__ q, unsigned char* __restrict__ scales,
-                   bf16* __restrict__ deq, long long M, int K, long long ldx) {
+                   bf16* __restrict__ deq, long long M, int K, long long ldx, int packed_kb4) {
   const int nblk = K / 32;
   const long long total = M * nblk;
   const float fmt_max = E5M2 ? 57344.f : 448.f;
@@ -51,7 +51,12 @@ mxfp8_quant_kernel(const bf16* __restrict__ x, unsigned char* __restrict__ q, un
     }
     const float inv = exp2f(static_cast<float>(-e));
     const float sc = exp2f(static_cast<float>(e));
-    scales[m * nblk + kb] = static_cast<unsigned char>(e + 127);
+    // packed_kb4 > 0: the 512-byte atoms ([128 rows][4 blocks], byte (r%32)*16 + (r/32%4)*4 + kb%4) that the
+    // block-scaled tensor-core GEMM copies to tensor memory as they are
+    const long long sidx = packed_kb4 > 0
+        ? ((m >> 7) * packed_kb4 + (kb >> 2)) * 512 + (m & 31) * 16 + ((m >> 5) & 3) * 4 + (kb & 3)
+        : m * nblk + kb;
+    scales[sidx] = static_cast<unsigned char>(e + 127);
     unsigned char out[32];
 #pragma unroll
     for (int i = 0; i < 32; i += 2) {
@@ -136,11 +141,32 @@ int cb_mxfp8_quant(const void* x, void* q, void* scales, void* deq, long long M,
   if (e5m2)
     cb::mxfp8_quant_kernel<1><<<static_cast<unsigned>(blocks), 256, 0, s>>>(
         static_cast<const cb::bf16*>(x), static_cast<unsigned char*>(q), static_cast<unsigned char*>(scales),
-        static_cast<cb::bf16*>(deq), M, K, ldx);
+        static_cast<cb::bf16*>(deq), M, K, ldx, 0);
   else
     cb::mxfp8_quant_kernel<0><<<static_cast<unsigned>(blocks), 256, 0, s>>>(
         static_cast<const cb::bf16*>(x), static_cast<unsigned char*>(q), static_cast<unsigned char*>(scales),
-        static_cast<cb::bf16*>(deq), M, K, ldx);
+        static_cast<cb::bf16*>(deq), M, K, ldx, 0);
+  return static_cast<int>(cudaGetLastError());
+}
+
+
+// As cb_mxfp8_quant, but the scales go into the packed atoms of the block-scaled GEMM: `sf` has
+// ceil(M/128) * ceil(K/128) * 512 bytes and must have been filled with a finite scale (127) beforehand where
+// M or K/32 is not a multiple of 128 or 4, since bytes of rows and blocks outside the matrix are not written.
+int cb_mxfp8_quant_packed(const void* x, void* q, void* sf, long long M, int K, long long ldx, int e5m2, void* stream) {
+  if (M <= 0 || K <= 0 || K % 32 != 0 || ldx % 8 != 0) return -1;
+  long long blocks = (M * (K / 32) + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int kb4 = (K + 127) / 128;
+  if (e5m2)
+    cb::mxfp8_quant_kernel<1><<<static_cast<unsigned>(blocks), 256, 0, s>>>(
+        static_cast<const cb::bf16*>(x), static_cast<unsigned char*>(q), static_cast<unsigned char*>(sf), nullptr, M, K,
+        ldx, kb4);
+  else
+    cb::mxfp8_quant_kernel<0><<<static_cast<unsigned>(blocks), 256, 0, s>>>(
+        static_cast<const cb::bf16*>(x), static_cast<unsigned char*>(q), static_cast<unsigned char*>(sf), nullptr, M, K,
+        ldx, kb4);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -66,6 +66,80 @@ def mxfp8_dequantize(q: torch.Tensor, scales: torch.Tensor, dtype: torch.dtype =
     return ref.mxfp8_dequantize(q, scales, dtype)
 
 
+# --------------------------------------------------------------------------- block-scaled tensor-core GEMM
+def pack_mx_scales(scales: torch.Tensor) -> torch.Tensor:
+    """Row-major e8m0 scales ``[R, KB]`` → the 512-byte atoms the block-scaled MMA reads: for every
+    128 rows × 4 blocks one atom with byte ``(r % 32) * 16 + (r // 32 % 4) * 4 + kb % 4``, atoms ordered
+    ``[row block][kb // 4]``.  Rows and blocks beyond the matrix hold 127 (scale 1.0)."""
+    R, KB = scales.shape
+    rb, kb4 = (R + 127) // 128, (KB + 3) // 4
+    full = torch.full((rb * 128, kb4 * 4), 127, dtype=torch.uint8, device=scales.device)
+    full[:R, :KB] = scales
+    # [rb, r//32%4, r%32, kb4, kb%4] -> [rb, kb4, r%32, r//32%4, kb%4]
+    return full.view(rb, 4, 32, kb4, 4).permute(0, 3, 2, 1, 4).contiguous().view(-1)
+
+
+def unpack_mx_scales(packed: torch.Tensor, R: int, KB: int) -> torch.Tensor:
+    """Inverse of :func:`pack_mx_scales`."""
+    rb, kb4 = (R + 127) // 128, (KB + 3) // 4
+    full = packed.view(rb, kb4, 32, 4, 4).permute(0, 3, 2, 1, 4).contiguous().view(rb * 128, kb4 * 4)
+    return full[:R, :KB].contiguous()
+
+
+def block_scaled_available() -> bool:
+    return _ext.available() and not _ext.reference_forced() and _ext.has_symbol("cb_mxgemm")
+
+
+def mxfp8_quantize_packed(x: torch.Tensor, fmt: str = "e4m3"):
+    """``(q_uint8 [M, K], packed_scales)`` for the block-scaled GEMM; K a multiple of 32."""
+    x2 = x.reshape(-1, x.shape[-1])
+    M, K = x2.shape
+    if x2.is_cuda and x2.dtype == torch.bfloat16 and K % 32 == 0 and block_scaled_available() \
+            and _ext.has_symbol("cb_mxfp8_quant_packed"):
+        if x2.stride(1) != 1 or x2.stride(0) % 8 != 0:
+            x2 = x2.contiguous()
+        q = torch.empty(M, K, dtype=torch.uint8, device=x2.device)
+        nbytes = ((M + 127) // 128) * ((K + 127) // 128) * 512
+        if M % 128 or K % 128:
+            sf = torch.full((nbytes,), 127, dtype=torch.uint8, device=x2.device)
+        else:
+            sf = torch.empty(nbytes, dtype=torch.uint8, device=x2.device)
+        fn = _ext.lib().cb_mxfp8_quant_packed
+        fn.argtypes = [_ext.P, _ext.P, _ext.P, _ext.L, _ext.I, _ext.L, _ext.I, _ext.P]
+        _ext.check(fn(x2.data_ptr(), q.data_ptr(), sf.data_ptr(), M, K, x2.stride(0), int(fmt == "e5m2"),
+                      _ext.stream_ptr()), "mxfp8_quant_packed")
+        return q, sf
+    q, s = ref.mxfp8_quantize(x2, fmt)
+    return q.view(torch.uint8), pack_mx_scales(s)
+
+
+def mxfp8_block_scaled_matmul(aq: torch.Tensor, sfa: torch.Tensor, bq: torch.Tensor, sfb: torch.Tensor,
+                              bias: Optional[torch.Tensor] = None, a_fmt: str = "e4m3", b_fmt: str = "e4m3") -> torch.Tensor:
+    """``C[M, N] = Σ_k (aq·2^sfa)[m, k] (bq·2^sfb)[n, k] + bias`` in bf16; ``aq [M, K]``, ``bq [N, K]`` fp8 bytes,
+    scales packed by :func:`pack_mx_scales`.  On a GPU this is one ``tcgen05.mma.kind::mxf8f6f4.block_scale``
+    GEMM (the tensor core applies the scales); elsewhere the operands are dequantised and multiplied in fp32."""
+    M, K = aq.shape
+    N = bq.shape[0]
+    if aq.is_cuda and block_scaled_available() and K % 32 == 0 and not (a_fmt == "e5m2" and b_fmt == "e5m2"):
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=aq.device)
+        fn = _ext.lib().cb_mxgemm
+        fn.argtypes = [_ext.P, _ext.P, _ext.P, _ext.P, _ext.P, _ext.P, _ext.I, _ext.I, _ext.I, _ext.L, _ext.L, _ext.L,
+                       _ext.I, _ext.I, _ext.P, _ext.P]
+        code = fn(aq.data_ptr(), bq.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), out.data_ptr(), _ext.ptr(bias), M, N, K,
+                  aq.stride(0), bq.stride(0), out.stride(0), int(a_fmt == "e5m2"), int(b_fmt == "e5m2"),
+                  _ext.status_buffer(aq.device).data_ptr(), _ext.stream_ptr())
+        _ext.check(code, "mxgemm")
+        return out
+    fa = torch.float8_e5m2 if a_fmt == "e5m2" else torch.float8_e4m3fn
+    fb = torch.float8_e5m2 if b_fmt == "e5m2" else torch.float8_e4m3fn
+    a = ref.mxfp8_dequantize(aq.view(fa), unpack_mx_scales(sfa, M, K // 32))
+    b = ref.mxfp8_dequantize(bq.view(fb), unpack_mx_scales(sfb, N, K // 32))
+    y = a @ b.t()
+    if bias is not None:
+        y = y + bias.float()
+    return y.to(torch.bfloat16 if aq.is_cuda else torch.float32)
+
+
 class FP8Handler:
     """Quantise / dequantise with either MX block scaling or one delayed per-tensor scale, plus the
     dynamic loss-scale bookkeeping the reference keeps next to it."""
@@ -123,19 +197,32 @@ class FP8Handler:
         return self.loss_scale
 
 
+def _block_scaled_ok(x2: torch.Tensor, w: torch.Tensor) -> bool:
+    return (x2.is_cuda and x2.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and block_scaled_available()
+            and x2.shape[1] % 32 == 0 and w.shape[0] % 8 == 0)
+
+
 class _MXFP8LinearFn(torch.autograd.Function):
     """Linear layer on MXFP8 operands: inputs and weights are rounded to e4m3 with 32-element MX
     scales along K; the gradient of the output is rounded to e5m2 the same way.  The products are
-    accumulated in fp32 on the tensor cores.  The quantised values times their power-of-two scales
-    are exactly representable in bf16, so feeding the exactly dequantised operands to the bf16
-    tcgen05 GEMM gives the block-scaled result (at the bf16 FLOP rate)."""
+    accumulated in fp32 on the tensor cores.
+
+    On a GPU all three GEMMs (forward, dX, dW) are block-scaled ``tcgen05.mma.kind::mxf8f6f4`` products:
+    the tensor core reads the fp8 bytes and applies the e8m0 scales itself.  Where that kernel does not
+    apply (CPU, shapes with K not a multiple of 32) the exactly dequantised operands — an fp8 value times a
+    power of two is representable in bf16 — go through the bf16 GEMM, which gives the same products."""
 
     @staticmethod
     def forward(ctx, x, w, bias):
         x2 = x.reshape(-1, x.shape[-1])
-        _, _, xd = mxfp8_quantize(x2, "e4m3", True)
-        _, _, wd = mxfp8_quantize(w, "e4m3", True)
-        y = ops.gemm(xd, wd, bias=bias) if ops._fast(xd, wd) else torch.nn.functional.linear(xd, wd, bias)
+        if _block_scaled_ok(x2, w):
+            aq, sa = mxfp8_quantize_packed(x2, "e4m3")
+            bq, sb = mxfp8_quantize_packed(w, "e4m3")
+            y = mxfp8_block_scaled_matmul(aq, sa, bq, sb, bias)
+        else:
+            _, _, xd = mxfp8_quantize(x2, "e4m3", True)
+            _, _, wd = mxfp8_quantize(w, "e4m3", True)
+            y = ops.gemm(xd, wd, bias=bias) if ops._fast(xd, wd) else torch.nn.functional.linear(xd, wd, bias)
         ctx.save_for_backward(x2, w)
         ctx.has_bias = bias is not None
         ctx.shape = x.shape
@@ -146,18 +233,30 @@ class _MXFP8LinearFn(torch.autograd.Function):
     def backward(ctx, dy):
         x2, w = ctx.saved_tensors
         dy2 = dy.reshape(-1, dy.shape[-1]).contiguous()
+        T, n_out = dy2.shape
         fast = ops._fast(dy2, w)
+        hw = _block_scaled_ok(x2, w) and dy2.dtype == torch.bfloat16
         dx = dw = db = None
         if ctx.needs_input_grad[0]:
             # dX = dY W : K runs over the output features -> quantise dY along its last dim, W along dim 0
-            _, _, gd = mxfp8_quantize(dy2, "e5m2", True)
-            _, _, wtd = mxfp8_quantize(w.t().contiguous(), "e4m3", True)          # [in, out], scales along out
-            dx = (ops.gemm(gd, wtd) if fast else gd @ wtd.t()).view(ctx.shape)
+            if hw and n_out % 32 == 0 and w.shape[1] % 8 == 0:
+                gq, gs = mxfp8_quantize_packed(dy2, "e5m2")
+                wq, ws = mxfp8_quantize_packed(w.t().contiguous(), "e4m3")              # [in, out], scales along out
+                dx = mxfp8_block_scaled_matmul(gq, gs, wq, ws, None, "e5m2", "e4m3").view(ctx.shape)
+            else:
+                _, _, gd = mxfp8_quantize(dy2, "e5m2", True)
+                _, _, wtd = mxfp8_quantize(w.t().contiguous(), "e4m3", True)
+                dx = (ops.gemm(gd, wtd) if fast else gd @ wtd.t()).view(ctx.shape)
         if ctx.needs_input_grad[1]:
             # dW = dY^T X : K runs over tokens -> both operands quantised along the token dimension
-            _, _, gtd = mxfp8_quantize(dy2.t().contiguous(), "e5m2", True)        # [out, T]
-            _, _, xtd = mxfp8_quantize(x2.t().contiguous(), "e4m3", True)         # [in, T]
-            dw = ops.gemm(gtd, xtd) if fast and gtd.shape[1] % 8 == 0 else (gtd.float() @ xtd.float().t()).to(w.dtype)
+            if hw and T % 32 == 0:
+                gq, gs = mxfp8_quantize_packed(dy2.t().contiguous(), "e5m2")            # [out, T]
+                xq, xs = mxfp8_quantize_packed(x2.t().contiguous(), "e4m3")             # [in, T]
+                dw = mxfp8_block_scaled_matmul(gq, gs, xq, xs, None, "e5m2", "e4m3")
+            else:
+                _, _, gtd = mxfp8_quantize(dy2.t().contiguous(), "e5m2", True)
+                _, _, xtd = mxfp8_quantize(x2.t().contiguous(), "e4m3", True)
+                dw = ops.gemm(gtd, xtd) if fast and gtd.shape[1] % 8 == 0 else (gtd.float() @ xtd.float().t()).to(w.dtype)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = ops.colsum(dy2)
         return dx, dw, db

@@ -319,6 +319,56 @@ def test_fp8_linear_module_runs_kernels_and_matches_reference():
     assert x.grad is not None and lin.weight.grad is not None and torch.isfinite(lin.weight.grad.float()).all()
 
 
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (200, 136, 160), (256, 384, 1024), (1024, 640, 4096)])
+@pytest.mark.parametrize("fmts", [("e4m3", "e4m3"), ("e5m2", "e4m3")])
+def test_block_scaled_mxfp8_gemm_matches_dequantised_fp32_product(M, N, K, fmts):
+    """``tcgen05.mma.kind::mxf8f6f4.block_scale``: fp8 bytes and packed e8m0 scales in, bf16 out, against
+    the fp32 product of the dequantised operands.  The scales vary by row and by 32-element block, so a wrong
+    lane / column / byte mapping of the scale atoms cannot pass; ragged M, N and K exercise the padding."""
+    from chronicals_b200.ops import ref
+    from chronicals_b200.utils import fp8_utils as F8
+    assert F8.block_scaled_available(), "block-scaled GEMM kernel missing from the extension"
+    g = torch.Generator(device="cuda").manual_seed(5)
+    fa = torch.float8_e5m2 if fmts[0] == "e5m2" else torch.float8_e4m3fn
+    a = torch.randn(M, K, device="cuda", generator=g).to(fa)
+    b = torch.randn(N, K, device="cuda", generator=g).to(torch.float8_e4m3fn)
+    sa = torch.randint(120, 134, (M, K // 32), device="cuda", generator=g, dtype=torch.uint8)
+    sb = torch.randint(120, 134, (N, K // 32), device="cuda", generator=g, dtype=torch.uint8)
+    bias = torch.randn(N, device="cuda", generator=g).to(torch.bfloat16)
+    y = F8.mxfp8_block_scaled_matmul(a.view(torch.uint8), F8.pack_mx_scales(sa), b.view(torch.uint8), F8.pack_mx_scales(sb),
+                                     bias, fmts[0], fmts[1]).float()
+    want = ref.mxfp8_dequantize(a, sa) @ ref.mxfp8_dequantize(b, sb).t() + bias.float()
+    assert (y - want).abs().max().item() < 6e-3 * want.abs().max().item()
+
+
+def test_mxfp8_packed_quantiser_writes_the_scale_atoms():
+    from chronicals_b200.ops import ref
+    from chronicals_b200.utils import fp8_utils as F8
+    x = torch.randn(200, 160, device="cuda", dtype=torch.bfloat16) * 3
+    q, sf = F8.mxfp8_quantize_packed(x)
+    q_ref, s_ref = ref.mxfp8_quantize(x.float())
+    assert torch.equal(sf, F8.pack_mx_scales(s_ref))
+    assert (q != q_ref.view(torch.uint8)).float().mean().item() < 1e-3
+
+
+def test_fp8_linear_gradients_on_block_scaled_tensor_cores():
+    """dX and dW of the MXFP8 linear (e5m2 gradients × e4m3 operands, block-scaled MMAs) against the bf16
+    autograd result: quantisation noise only."""
+    from chronicals_b200.utils.fp8_utils import FP8Linear
+    torch.manual_seed(1)
+    lin = FP8Linear(512, 384, bias=True).cuda().to(torch.bfloat16)
+    x = torch.randn(256, 512, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    gy = torch.randn(256, 384, device="cuda", dtype=torch.bfloat16)
+    lin(x).backward(gy)
+    xr = x.detach().float().requires_grad_(True)
+    wr = lin.weight.detach().float().requires_grad_(True)
+    (xr @ wr.t() + lin.bias.detach().float()).backward(gy.float())
+    for got, want in ((x.grad, xr.grad), (lin.weight.grad, wr.grad)):
+        rel = (got.float() - want).norm() / want.norm()
+        assert rel.item() < 0.08, rel.item()
+    assert (lin.bias.grad.float() - gy.float().sum(0)).abs().max().item() < 0.02 * gy.float().sum(0).abs().max().item()
+
+
 def test_fused_lora_projection_matches_reference_formula():
     """Frozen fused QKV projection with rank-16 adapters on every split: forward, dX, dA, dB against the
     plain PEFT formula in fp32 (the base weight must receive no gradient)."""

@@ -137,6 +137,30 @@ def test_mxfp8_quantization_is_exact_power_of_two_scaling():
     assert zq.float().abs().max() == 0
 
 
+def test_mx_scale_atoms_layout_and_block_scaled_product_oracle():
+    """The packed scale layout of the block-scaled tensor-core GEMM (512-byte atoms of 128 rows x 4 blocks,
+    byte (r % 32) * 16 + (r // 32 % 4) * 4 + kb % 4) round-trips, pads with scale 1.0, and the CPU path of
+    the block-scaled product equals the dequantise-then-multiply oracle."""
+    from chronicals_b200.utils import fp8_utils as F8
+    s = torch.randint(100, 140, (200, 5), dtype=torch.uint8)
+    p = F8.pack_mx_scales(s)
+    assert p.numel() == 2 * 2 * 512
+    assert torch.equal(F8.unpack_mx_scales(p, 200, 5), s)
+    for r, kb in [(0, 0), (33, 1), (130, 4), (199, 3)]:
+        idx = ((r // 128) * 2 + kb // 4) * 512 + (r % 32) * 16 + ((r // 32) % 4) * 4 + kb % 4
+        assert p[idx] == s[r, kb]
+    written = torch.zeros(p.numel(), dtype=torch.bool)
+    for r in range(200):
+        for kb in range(5):
+            written[((r // 128) * 2 + kb // 4) * 512 + (r % 32) * 16 + ((r // 32) % 4) * 4 + kb % 4] = True
+    assert (p[~written] == 127).all()
+    x, w = torch.randn(200, 160), torch.randn(136, 160)
+    aq, sa = F8.mxfp8_quantize_packed(x)
+    bq, sb = F8.mxfp8_quantize_packed(w)
+    y = F8.mxfp8_block_scaled_matmul(aq, sa, bq, sb)
+    assert torch.equal(y, ref.mxfp8_linear(x, w))
+
+
 def test_blockwise_8bit_roundtrip():
     x = torch.randn(1000)
     q, a = ref.quantize_blockwise_8bit(x)
