@@ -116,7 +116,7 @@ def run_gemm_fp8(results, peaks, iters, only=None):
 def run_gemm_mxfp8(results, peaks, iters, only=None):
     """Block-scaled MXFP8 GEMM (``tcgen05.mma.kind::mxf8f6f4.block_scale``, pre-quantised operands with packed
     e8m0 scales) against the bf16 GEMM of the same shape; also the cost of quantising the activation."""
-    from chronicals_b200.utils.fp8_utils import mxfp8_block_scaled_matmul, mxfp8_quantize_packed
+    from chronicals_b200.utils.fp8_utils import PAIR_TILE_ROWS, mxfp8_block_scaled_matmul, mxfp8_quantize_packed
     for name in ("small_2k", "gateup_fwd_0.5b", "down_fwd_0.5b", "gateup_fwd_7b", "down_fwd_7b", "square_8k"):
         if only and only != name:
             continue
@@ -124,13 +124,16 @@ def run_gemm_mxfp8(results, peaks, iters, only=None):
         a, b = bf(M, K), bf(N, K)
         aq, sa = mxfp8_quantize_packed(a)
         bq, sb = mxfp8_quantize_packed(b)
-        ms = timed(lambda: mxfp8_block_scaled_matmul(aq, sa, bq, sb), iters)
+        ms1 = timed(lambda: mxfp8_block_scaled_matmul(aq, sa, bq, sb), iters)
+        bq, sb = mxfp8_quantize_packed(b, tile_rows=PAIR_TILE_ROWS)
+        ms = timed(lambda: mxfp8_block_scaled_matmul(aq, sa, bq, sb, b_tile_rows=PAIR_TILE_ROWS), iters)
         ms_q = timed(lambda: mxfp8_quantize_packed(a), iters)
         out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
         ms_bf16 = timed(lambda: ops.gemm(a, b, out=out), iters)
         fl = 2.0 * M * N * K
-        results.append({"kernel": "mxgemm_block_scaled", "case": name, "shape": [M, N, K], "ms": ms, "tflops": fl / ms / 1e9,
-                        "frac_of_measured_bf16": fl / ms / 1e9 / peaks["bf16_tflops"], "bf16_gemm_ms": ms_bf16,
+        results.append({"kernel": "mxgemm2sm_block_scaled", "case": name, "shape": [M, N, K], "ms": ms, "tflops": fl / ms / 1e9,
+                        "frac_of_measured_bf16": fl / ms / 1e9 / peaks["bf16_tflops"], "single_cta_kernel_ms": ms1,
+                        "bf16_gemm_ms": ms_bf16,
                         "speedup_vs_bf16": ms_bf16 / ms, "activation_quant_ms": ms_q})
         _ext.check_status()
 
@@ -263,13 +266,14 @@ def main():
         _ext.check_status()
         print("ok")
         return
-    if args.one and args.one.startswith("mx:"):
-        from chronicals_b200.utils.fp8_utils import mxfp8_block_scaled_matmul, mxfp8_quantize_packed
-        M, N, K = GEMM_CASES[args.one[3:]][:3]
+    if args.one and args.one.startswith(("mx:", "mxp:")):
+        from chronicals_b200.utils.fp8_utils import PAIR_TILE_ROWS, mxfp8_block_scaled_matmul, mxfp8_quantize_packed
+        tile = PAIR_TILE_ROWS if args.one.startswith("mxp:") else 128          # mxp: the CTA-pair kernel
+        M, N, K = GEMM_CASES[args.one.split(":", 1)[1]][:3]
         aq, sa = mxfp8_quantize_packed(bf(M, K))
-        bq, sb = mxfp8_quantize_packed(bf(N, K))
+        bq, sb = mxfp8_quantize_packed(bf(N, K), tile_rows=tile)
         for _ in range(3):
-            mxfp8_block_scaled_matmul(aq, sa, bq, sb)
+            mxfp8_block_scaled_matmul(aq, sa, bq, sb, b_tile_rows=tile)
         torch.cuda.synchronize()
         _ext.check_status()
         print("ok")

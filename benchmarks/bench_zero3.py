@@ -33,7 +33,7 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-prefetch", action="store_true")
     ap.add_argument("--fp8", default="none", choices=["none", "rowwise", "mxfp8"],
-                    help="forward projections on FP8 operands (rowwise: e4m3 tensor-core GEMM; mxfp8: MX block scales, bf16 math)")
+                    help="forward projections on FP8 operands (rowwise: e4m3 tensor-core GEMM; mxfp8: MX block scales applied by the block-scaled tensor-core GEMM, also in backward)")
     a = ap.parse_args()
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     from chronicals_b200 import ChronicalsConfig, build_model

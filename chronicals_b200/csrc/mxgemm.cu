@@ -292,6 +292,303 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Args& g, cudaStre
   return static_cast<int>(cudaGetLastError());
 }
 
+
+// =====================================================================================================
+// CTA-pair variant: one 256 x 192 output tile per pair of CTAs (`tcgen05.mma.cta_group::2`).
+//
+// With one CTA per 128 x 128 tile every 128 elements of K cost 32 KB of operand traffic per 128 x 128 x 128
+// multiply-accumulates, and at FP8 rates the L2 -> shared-memory path, not the tensor core, sets the pace
+// (measured: tensor pipe 37 % active).  A pair shares B: each CTA loads its own 128 rows of A and only
+// 96 of the 192 rows of B (28 KB per 128 x 192 x 128), and the tensor cores of both SMs read both halves.
+// 192 columns (not 256) because tensor memory has 512 columns per SM: two accumulators of 192 leave room
+// for the scale columns (4 for A, 8 for B, four rotating sets).
+//
+// Each CTA needs the scales of its own 128 rows of A and of ALL 192 rows of B in its own tensor memory;
+// `tcgen05.cp.cta_group::2`, issued once by the leader, copies from each CTA's own shared memory (same
+// offsets) into each CTA's own tensor memory.  The B scales are packed for 192-row tiles: tile t owns two
+// 512-byte atoms per 128 elements of K (rows 0-127 and 128-191 of the tile; the rest of the second atom is
+// padding), addressed as ((2 t + j) * kb4 + kb) * 512.
+// Roles, barriers, bounded waits and the way the pair leaves together are those of gemm2sm.cu.
+constexpr int P_BN = 192;
+constexpr int P_BNH = 96;
+constexpr int P_STAGES = 6;
+constexpr int P_A_BYTES = BM * BKB;              // 16 KB
+constexpr int P_B_BYTES = P_BNH * BKB;           // 12 KB
+constexpr int P_TX_BYTES = P_A_BYTES + P_B_BYTES + 3 * SF_BYTES;
+constexpr int P_STAGE_BYTES = 30 * 1024;         // 30,208 used; padded so that every stage base stays 1024-aligned
+constexpr int P_STG_OFFSET = P_STAGES * P_STAGE_BYTES;
+constexpr int P_BAR_OFFSET = P_STG_OFFSET + 4 * 8192;
+constexpr int P_SMEM_TOTAL = P_BAR_OFFSET + 512 + 1024;
+constexpr uint32_t P_SF_COL0 = 2 * P_BN;         // 384
+constexpr uint32_t P_SF_SET = 12;                // columns per scale set: 4 (A) + 8 (B)
+
+struct PairArgs {
+  int M, N, K;
+  int num_m_pairs, num_n_tiles, num_tiles;
+  int sf_kb4;
+  const bf16* bias;
+  const unsigned char* sfa;   // atoms of A: [ceil(M/128)][sf_kb4][512]
+  const unsigned char* sfb;   // atoms of B for 192-row tiles: [n_tiles][2][sf_kb4][512]
+  int* status;
+};
+
+__device__ __forceinline__ void tmem_cp_sf_2cta(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+__device__ __forceinline__ void umma_mx_ss_2cta(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                uint32_t tsfa, uint32_t tsfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(tsfa), "r"(tsfb)
+      : "memory");
+}
+
+template <int AFMT, int BFMT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
+mxgemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmC, const PairArgs g) {
+  using namespace cb;
+  constexpr uint32_t IDESC = idesc_mx(2 * BM, P_BN, AFMT, BFMT);           // M = 256 across the pair
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + P_BAR_OFFSET);       // my stage landed
+  uint64_t* peer_full = full + P_STAGES;                                   // (leader) the peer's stage landed
+  uint64_t* empty = peer_full + P_STAGES;                                  // stage consumed (multicast commit)
+  uint64_t* tfull = empty + P_STAGES;                                      // accumulator complete (multicast commit)
+  uint64_t* tempty = tfull + 2;                                            // (leader) accumulator drained by both CTAs
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < P_STAGES; ++s) {
+      mbar_init(full + s, 1);
+      mbar_init(peer_full + s, 1);
+      mbar_init(empty + s, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull + a, 1);
+      mbar_init(tempty + a, 8);                                            // 4 epilogue warps in each CTA
+    }
+    mbar_fence_init();
+    *abort_flag = (g.status[0] != 0) ? 1 : 0;
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  __syncthreads();
+  cluster_sync_all();                                                      // barriers of both CTAs are initialised
+  // both CTAs take the LEADER's view of "poisoned by an earlier timeout", so the pair always decides alike
+  const uint32_t poisoned = ld_shared_cluster_u32(mapa_u32(smem_u32(const_cast<int*>(abort_flag)), 0));
+  cluster_sync_all();                                                      // nobody leaves while its flag is being read
+  if (poisoned != 0) return;
+  if (warp == 1) {
+    tmem_alloc_2cta(tmem_slot, TMEM_COLS);
+    tmem_relinquish_2cta();
+  }
+  tc_fence_before();
+  cluster_sync_all();                                                      // both halves of the pair hold their TMEM
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int num_kb = (g.K + BKB - 1) / BKB;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------- producer (each CTA: its A rows, its B half, scales)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = pair; t < g.num_tiles && ok; t += num_pairs) {
+        const int mp = t % g.num_m_pairs;
+        const int nt = t / g.num_m_pairs;
+        const int a_row = mp * 2 * BM + static_cast<int>(rank) * BM;
+        const int b_row = nt * P_BN + static_cast<int>(rank) * P_BNH;
+        const unsigned char* sfa_row = g.sfa + static_cast<size_t>(mp * 2 + static_cast<int>(rank)) * g.sf_kb4 * SF_BYTES;
+        const unsigned char* sfb0 = g.sfb + static_cast<size_t>(nt) * 2 * g.sf_kb4 * SF_BYTES;
+        const unsigned char* sfb1 = sfb0 + static_cast<size_t>(g.sf_kb4) * SF_BYTES;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(empty + stage, phase ^ 1, abort_flag, g.status, CB_ERR_WAIT_EMPTY)) {
+            ok = false;
+            break;
+          }
+          uint8_t* st = smem + stage * P_STAGE_BYTES;
+          uint8_t* sf = st + P_A_BYTES + P_B_BYTES;
+          mbar_expect_tx(full + stage, P_TX_BYTES);
+          tma_load_2d(st, &tmA, full + stage, kb * BKB, a_row);
+          tma_load_2d(st + P_A_BYTES, &tmB, full + stage, kb * BKB, b_row);
+          bulk_load(sf, sfa_row + static_cast<size_t>(kb) * SF_BYTES, SF_BYTES, full + stage);
+          bulk_load(sf + SF_BYTES, sfb0 + static_cast<size_t>(kb) * SF_BYTES, SF_BYTES, full + stage);
+          bulk_load(sf + 2 * SF_BYTES, sfb1 + static_cast<size_t>(kb) * SF_BYTES, SF_BYTES, full + stage);
+          if (++stage == P_STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      if (leader) {
+        // --------------------------------------------------------- scale copies + MMA issue for the pair
+        uint32_t tile_cnt = 0, it = 0;
+        for (int t = pair; t < g.num_tiles && ok; t += num_pairs, ++tile_cnt) {
+          const uint32_t acc = tile_cnt & 1u;
+          const uint32_t acc_phase = (tile_cnt >> 1) & 1u;
+          if (!mbar_wait(tempty + acc, acc_phase ^ 1, abort_flag, g.status, CB_ERR_WAIT_TMEM_EMPTY)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + acc * P_BN;
+          for (int kb = 0; kb < num_kb; ++kb, ++it) {
+            if (!mbar_wait(full + stage, phase, abort_flag, g.status, CB_ERR_WAIT_FULL) ||
+                !mbar_wait(peer_full + stage, phase, abort_flag, g.status, CB_ERR_WAIT_PEER)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            const uint32_t st = smem_u32(smem + stage * P_STAGE_BYTES);
+            const uint32_t a_base = st, b_base = st + P_A_BYTES, sf_base = st + P_A_BYTES + P_B_BYTES;
+            const uint32_t tsfa = tmem_base + P_SF_COL0 + (it & 3u) * P_SF_SET;
+            const uint32_t tsfb = tsfa + 4;
+            tmem_cp_sf_2cta(tsfa, sf_smem_desc(sf_base));
+            tmem_cp_sf_2cta(tsfb, sf_smem_desc(sf_base + SF_BYTES));
+            tmem_cp_sf_2cta(tsfb + 4, sf_smem_desc(sf_base + 2 * SF_BYTES));
+#pragma unroll
+            for (uint32_t k = 0; k < BKB / UMMA_K; ++k) {
+              const uint64_t adesc = umma_smem_desc(a_base + k * 32, 16, 1024);
+              const uint64_t bdesc = umma_smem_desc(b_base + k * 32, 16, 1024);
+              umma_mx_ss_2cta(d_tmem, adesc, bdesc, IDESC | (k << 4) | (k << 29), tsfa, tsfb,
+                              (kb != 0 || k != 0) ? 1u : 0u);
+            }
+            umma_commit_2cta(empty + stage);      // frees this stage in both CTAs once the copies and MMAs retire
+            if (++stage == P_STAGES) {
+              stage = 0;
+              phase ^= 1;
+            }
+          }
+          if (ok) umma_commit_2cta(tfull + acc);  // accumulator complete, visible to both epilogues
+        }
+      } else {
+        // --------------------------------------------------------- relay: tell the leader that my stage is full
+        const uint32_t remote0 = mapa_u32(smem_u32(peer_full), 0);
+        for (int t = pair; t < g.num_tiles && ok; t += num_pairs) {
+          for (int kb = 0; kb < num_kb; ++kb) {
+            if (!mbar_wait(full + stage, phase, abort_flag, g.status, CB_ERR_WAIT_FULL)) {
+              ok = false;
+              break;
+            }
+            mbar_arrive_remote(remote0 + stage * 8);
+            if (++stage == P_STAGES) {
+              stage = 0;
+              phase ^= 1;
+            }
+          }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------- epilogue (4 warps, one TMEM lane quarter each)
+    const int q = warp & 3;
+    const uint32_t tempty_leader = mapa_u32(smem_u32(tempty), 0);
+    uint8_t* stg = smem + P_STG_OFFSET + (warp - 2) * 8192;
+    uint32_t tile_cnt = 0;
+    for (int t = pair; t < g.num_tiles; t += num_pairs, ++tile_cnt) {
+      const int mp = t % g.num_m_pairs;
+      const int nt = t / g.num_m_pairs;
+      const uint32_t acc = tile_cnt & 1u;
+      const uint32_t acc_phase = (tile_cnt >> 1) & 1u;
+      bool w = mbar_wait(tfull + acc, acc_phase, abort_flag, g.status, CB_ERR_WAIT_TMEM_FULL);
+      w = __all_sync(0xffffffffu, w);
+      if (!w) break;
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * P_BN;
+      const int row0w = mp * 2 * BM + static_cast<int>(rank) * BM + q * 32;
+      int buf = 0;
+#pragma unroll 1
+      for (int c0 = 0; c0 < P_BN; c0 += 64) {
+        const int colbase = nt * P_BN + c0;
+        if (colbase >= g.N) break;                          // uniform across the warp
+        uint32_t r[64];
+        tmem_ld_32x32(t_row + c0, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+        tmem_ld_32x32(t_row + c0 + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+        tmem_ld_wait();
+        if (g.bias != nullptr) {
+#pragma unroll
+          for (int j = 0; j < 64; ++j)
+            if (colbase + j < g.N) r[j] = __float_as_uint(__uint_as_float(r[j]) + __bfloat162float(g.bias[colbase + j]));
+        }
+        if (lane == 0) tma_store_wait_read<1>();            // the buffer written two stores ago has been read out
+        __syncwarp();
+        uint8_t* dstrow = stg + buf * 4096 + lane * 128;
+#pragma unroll
+        for (int cc = 0; cc < 8; ++cc) {
+          uint4 u;
+          u.x = pack_bf16x2(__uint_as_float(r[8 * cc + 0]), __uint_as_float(r[8 * cc + 1]));
+          u.y = pack_bf16x2(__uint_as_float(r[8 * cc + 2]), __uint_as_float(r[8 * cc + 3]));
+          u.z = pack_bf16x2(__uint_as_float(r[8 * cc + 4]), __uint_as_float(r[8 * cc + 5]));
+          u.w = pack_bf16x2(__uint_as_float(r[8 * cc + 6]), __uint_as_float(r[8 * cc + 7]));
+          *reinterpret_cast<uint4*>(dstrow + ((cc ^ (lane & 7)) << 4)) = u;
+        }
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0 && row0w < g.M) {                      // a box that starts past the last row has nothing to write
+          tma_store_2d(&tmC, stg + buf * 4096, colbase, row0w);
+          tma_store_commit();
+        }
+        buf ^= 1;
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if (leader) mbar_arrive(tempty + acc);
+        else mbar_arrive_remote(tempty_leader + acc * 8);
+      }
+    }
+    if (lane == 0) tma_store_wait_all();
+  }
+
+  // ------------------------------------------------------------- teardown (the pair leaves together)
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  tc_fence_before();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_2cta(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int AFMT, int BFMT>
+int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const PairArgs& g, cudaStream_t s) {
+  auto kern = mxgemm2sm_kernel<AFMT, BFMT>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_TOTAL);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_set = true;
+  }
+  int pairs = cbhost::num_sms() / 2;
+  if (pairs > g.num_tiles) pairs = g.num_tiles;
+  kern<<<2 * pairs, THREADS, P_SMEM_TOTAL, s>>>(ta, tb, tc, g);
+  return static_cast<int>(cudaGetLastError());
+}
+
 }  // namespace cbmx
 
 extern "C" {
@@ -332,6 +629,51 @@ int cb_mxgemm(const void* Aq, const void* Bq, const void* sfa, const void* sfb, 
   if (a_e5m2) return cbmx::launch<1, 0>(ta, tb, g, s);
   if (b_e5m2) return cbmx::launch<0, 1>(ta, tb, g, s);
   return cbmx::launch<0, 0>(ta, tb, g, s);
+}
+
+// Rows per B tile of the CTA-pair kernel: the B scales handed to cb_mxgemm_pair must be packed for tiles of
+// this many rows (cb_mxfp8_quant_packed with tile_rows = this value).
+int cb_mxgemm_pair_tile_rows() { return cbmx::P_BN; }
+
+// Bytes of the packed scale buffer when the rows are grouped in tiles of `tile_rows` (each tile padded to a
+// multiple of 128 rows).
+long long cb_mxgemm_sf_bytes_tiled(long long rows, int K, int tile_rows) {
+  const long long tiles = (rows + tile_rows - 1) / tile_rows;
+  const long long atoms_per_tile = (tile_rows + 127) / 128;
+  const long long kb4 = (K + 127) / 128;
+  return tiles * atoms_per_tile * kb4 * 512;
+}
+
+// The same product on CTA pairs (256 x 192 tiles).  sfa as for cb_mxgemm; sfb packed for 192-row tiles.
+// C must be 16-byte aligned with a pitch that is a multiple of 8 elements (TMA-store epilogue).
+int cb_mxgemm_pair(const void* Aq, const void* Bq, const void* sfa, const void* sfb, void* C, const void* bias, int M,
+                   int N, int K, long long lda, long long ldb, long long ldc, int a_e5m2, int b_e5m2, int* status,
+                   void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || K % 32 != 0 || sfa == nullptr || sfb == nullptr) return -1;
+  if ((reinterpret_cast<uintptr_t>(sfa) & 15) != 0 || (reinterpret_cast<uintptr_t>(sfb) & 15) != 0) return -3;
+  if ((reinterpret_cast<uintptr_t>(C) & 15) != 0 || (ldc * 2) % 16 != 0) return -2;
+  if (a_e5m2 && b_e5m2) return -4;
+  CUtensorMap ta, tb, tc;
+  int e = cbhost::make_tmap(&ta, Aq, K, M, lda, cbmx::BKB, cbmx::BM, 1);
+  if (e) return e;
+  e = cbhost::make_tmap(&tb, Bq, K, N, ldb, cbmx::BKB, cbmx::P_BNH, 1);
+  if (e) return e;
+  e = cbhost::make_tmap(&tc, C, N, M, ldc, 64, 32, 2);
+  if (e) return e;
+  cbmx::PairArgs g = {};
+  g.M = M; g.N = N; g.K = K;
+  g.num_m_pairs = (M + 2 * cbmx::BM - 1) / (2 * cbmx::BM);
+  g.num_n_tiles = (N + cbmx::P_BN - 1) / cbmx::P_BN;
+  g.num_tiles = g.num_m_pairs * g.num_n_tiles;
+  g.sf_kb4 = (K + 127) / 128;
+  g.bias = static_cast<const cb::bf16*>(bias);
+  g.sfa = static_cast<const unsigned char*>(sfa);
+  g.sfb = static_cast<const unsigned char*>(sfb);
+  g.status = status;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (a_e5m2) return cbmx::launch_pair<1, 0>(ta, tb, tc, g, s);
+  if (b_e5m2) return cbmx::launch_pair<0, 1>(ta, tb, tc, g, s);
+  return cbmx::launch_pair<0, 0>(ta, tb, tc, g, s);
 }
 
 }  // extern "C"

@@ -222,8 +222,10 @@ def convert_model_to_fp8(model: nn.Module, exclude_patterns: Optional[List[str]]
                          mode: str = "mxfp8") -> nn.Module:
     """Replace eligible ``nn.Linear`` modules by ``FP8Linear`` (bf16 master weights are kept); fused
     projections of native models are switched to an FP8 forward: ``mode="mxfp8"`` = MX block-scaled operands
-    (32-element blocks, e8m0 scales) multiplied on the bf16 tensor path, ``mode="rowwise"`` = e4m3 operands
-    with per-token / per-channel scales multiplied by the FP8 tensor-core GEMM (``kind::f8f6f4``)."""
+    (32-element blocks, e8m0 scales) in forward, dX and dW, multiplied by the block-scaled tensor-core GEMM
+    (``kind::mxf8f6f4.block_scale``: the tensor core applies the scales), ``mode="rowwise"`` = e4m3 operands
+    with per-token / per-channel scales multiplied by the FP8 tensor-core GEMM (``kind::f8f6f4``) in the
+    forward only."""
     if mode not in ("mxfp8", "rowwise"):
         raise ValueError(f"unknown fp8 mode {mode!r}")
     n = 0

@@ -321,10 +321,12 @@ def test_fp8_linear_module_runs_kernels_and_matches_reference():
 
 @pytest.mark.parametrize("M,N,K", [(128, 128, 128), (200, 136, 160), (256, 384, 1024), (1024, 640, 4096)])
 @pytest.mark.parametrize("fmts", [("e4m3", "e4m3"), ("e5m2", "e4m3")])
-def test_block_scaled_mxfp8_gemm_matches_dequantised_fp32_product(M, N, K, fmts):
+@pytest.mark.parametrize("tile", [128, 192])
+def test_block_scaled_mxfp8_gemm_matches_dequantised_fp32_product(M, N, K, fmts, tile):
     """``tcgen05.mma.kind::mxf8f6f4.block_scale``: fp8 bytes and packed e8m0 scales in, bf16 out, against
     the fp32 product of the dequantised operands.  The scales vary by row and by 32-element block, so a wrong
-    lane / column / byte mapping of the scale atoms cannot pass; ragged M, N and K exercise the padding."""
+    lane / column / byte mapping of the scale atoms cannot pass; ragged M, N and K exercise the padding.
+    ``tile`` 128 runs the single-CTA kernel, 192 the CTA-pair kernel (B scales packed per 192-row tile)."""
     from chronicals_b200.ops import ref
     from chronicals_b200.utils import fp8_utils as F8
     assert F8.block_scaled_available(), "block-scaled GEMM kernel missing from the extension"
@@ -335,8 +337,8 @@ def test_block_scaled_mxfp8_gemm_matches_dequantised_fp32_product(M, N, K, fmts)
     sa = torch.randint(120, 134, (M, K // 32), device="cuda", generator=g, dtype=torch.uint8)
     sb = torch.randint(120, 134, (N, K // 32), device="cuda", generator=g, dtype=torch.uint8)
     bias = torch.randn(N, device="cuda", generator=g).to(torch.bfloat16)
-    y = F8.mxfp8_block_scaled_matmul(a.view(torch.uint8), F8.pack_mx_scales(sa), b.view(torch.uint8), F8.pack_mx_scales(sb),
-                                     bias, fmts[0], fmts[1]).float()
+    y = F8.mxfp8_block_scaled_matmul(a.view(torch.uint8), F8.pack_mx_scales(sa), b.view(torch.uint8),
+                                     F8.pack_mx_scales(sb, tile), bias, fmts[0], fmts[1], b_tile_rows=tile).float()
     want = ref.mxfp8_dequantize(a, sa) @ ref.mxfp8_dequantize(b, sb).t() + bias.float()
     assert (y - want).abs().max().item() < 6e-3 * want.abs().max().item()
 
@@ -345,10 +347,30 @@ def test_mxfp8_packed_quantiser_writes_the_scale_atoms():
     from chronicals_b200.ops import ref
     from chronicals_b200.utils import fp8_utils as F8
     x = torch.randn(200, 160, device="cuda", dtype=torch.bfloat16) * 3
-    q, sf = F8.mxfp8_quantize_packed(x)
     q_ref, s_ref = ref.mxfp8_quantize(x.float())
-    assert torch.equal(sf, F8.pack_mx_scales(s_ref))
-    assert (q != q_ref.view(torch.uint8)).float().mean().item() < 1e-3
+    for tile in (128, 192):
+        q, sf = F8.mxfp8_quantize_packed(x, tile_rows=tile)
+        assert torch.equal(sf, F8.pack_mx_scales(s_ref, tile))
+        assert (q != q_ref.view(torch.uint8)).float().mean().item() < 1e-3
+
+
+@pytest.mark.parametrize("fmt", ["e4m3", "e5m2"])
+@pytest.mark.parametrize("shape", [(64, 96), (512, 896), (1024, 4864)])
+def test_mxfp8_dual_quantiser_row_and_transposed_copies(fmt, shape):
+    """One read of x gives the copy with blocks along the last dimension and the transposed copy with blocks
+    along the first: both against the PyTorch quantiser (scales bit-exact, payload within one rounding)."""
+    from chronicals_b200.ops import ref
+    from chronicals_b200.utils import fp8_utils as F8
+    g = torch.Generator().manual_seed(3)
+    x = (torch.randn(*shape, generator=g) * torch.exp(torch.randn(shape[0], 1, generator=g))).to(torch.bfloat16).cuda()
+    q_row, sf_row, q_col, sf_col = F8.mxfp8_quantize_dual(x, fmt, 128, 192)
+    qr, sr = ref.mxfp8_quantize(x.float(), fmt)
+    qc, sc = ref.mxfp8_quantize(x.float().t().contiguous(), fmt)
+    assert torch.equal(sf_row, F8.pack_mx_scales(sr)) and torch.equal(sf_col, F8.pack_mx_scales(sc, 192))
+    assert (q_row != qr.view(torch.uint8)).float().mean().item() < 1e-3
+    assert (q_col != qc.view(torch.uint8)).float().mean().item() < 1e-3
+    only_col = F8.mxfp8_quantize_dual(x, fmt, 128, 192, want_row=False)
+    assert only_col[0] is None and torch.equal(only_col[2], q_col)
 
 
 def test_fp8_linear_gradients_on_block_scaled_tensor_cores():

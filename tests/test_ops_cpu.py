@@ -159,6 +159,16 @@ def test_mx_scale_atoms_layout_and_block_scaled_product_oracle():
     bq, sb = F8.mxfp8_quantize_packed(w)
     y = F8.mxfp8_block_scaled_matmul(aq, sa, bq, sb)
     assert torch.equal(y, ref.mxfp8_linear(x, w))
+    # tiles of 192 rows (the CTA-pair kernel's B operand): each tile padded to 256 rows = two atoms per 4 blocks
+    s2 = torch.randint(100, 140, (400, 5), dtype=torch.uint8)
+    p2 = F8.pack_mx_scales(s2, 192)
+    assert p2.numel() == 3 * 2 * 2 * 512 and torch.equal(F8.unpack_mx_scales(p2, 400, 5, 192), s2)
+    for r, kb in [(0, 0), (130, 1), (191, 4), (192, 0), (399, 3)]:
+        t, rr = divmod(r, 192)
+        atom = (2 * t + rr // 128) * 2 + kb // 4
+        assert p2[atom * 512 + (rr % 32) * 16 + ((rr // 32) % 4) * 4 + kb % 4] == s2[r, kb]
+    bq, sb = F8.mxfp8_quantize_packed(w, tile_rows=192)
+    assert torch.equal(F8.mxfp8_block_scaled_matmul(aq, sa, bq, sb, b_tile_rows=192), ref.mxfp8_linear(x, w))
 
 
 def test_blockwise_8bit_roundtrip():
