@@ -300,6 +300,8 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Args& g, cudaStre
 // multiply-accumulates, and at FP8 rates the L2 -> shared-memory path, not the tensor core, sets the pace
 // (measured: tensor pipe 37 % active).  A pair shares B: each CTA loads its own 128 rows of A and only
 // 96 of the 192 rows of B (28 KB per 128 x 192 x 128), and the tensor cores of both SMs read both halves.
+// The pipeline is bound by bytes in flight (shared-memory capacity over memory latency), so the ring is as deep
+// as 227 KB allow: seven stages, the scale atoms packed behind the operand ring, one staging buffer per warp.
 // 192 columns (not 256) because tensor memory has 512 columns per SM: two accumulators of 192 leave room
 // for the scale columns (4 for A, 8 for B, four rotating sets).
 //
@@ -311,14 +313,17 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Args& g, cudaStre
 // Roles, barriers, bounded waits and the way the pair leaves together are those of gemm2sm.cu.
 constexpr int P_BN = 192;
 constexpr int P_BNH = 96;
-constexpr int P_STAGES = 6;
+constexpr int P_STAGES = 7;
 constexpr int P_A_BYTES = BM * BKB;              // 16 KB
 constexpr int P_B_BYTES = P_BNH * BKB;           // 12 KB
-constexpr int P_TX_BYTES = P_A_BYTES + P_B_BYTES + 3 * SF_BYTES;
-constexpr int P_STAGE_BYTES = 30 * 1024;         // 30,208 used; padded so that every stage base stays 1024-aligned
-constexpr int P_STG_OFFSET = P_STAGES * P_STAGE_BYTES;
-constexpr int P_BAR_OFFSET = P_STG_OFFSET + 4 * 8192;
+constexpr int P_DATA_BYTES = P_A_BYTES + P_B_BYTES;            // 28 KB per stage, every stage base 1024-aligned
+constexpr int P_SF_STAGE = 3 * SF_BYTES;                       // scale atoms of a stage: A, B rows 0-127, B rows 128-191
+constexpr int P_TX_BYTES = P_DATA_BYTES + P_SF_STAGE;
+constexpr int P_SF_OFFSET = P_STAGES * P_DATA_BYTES;           // the scale atoms sit behind the operand ring
+constexpr int P_STG_OFFSET = (P_SF_OFFSET + P_STAGES * P_SF_STAGE + 1023) / 1024 * 1024;
+constexpr int P_BAR_OFFSET = P_STG_OFFSET + 4 * 4096;          // epilogue staging: one 4 KB buffer per warp
 constexpr int P_SMEM_TOTAL = P_BAR_OFFSET + 512 + 1024;
+static_assert(P_SMEM_TOTAL <= 232448, "shared memory per CTA");
 constexpr uint32_t P_SF_COL0 = 2 * P_BN;         // 384
 constexpr uint32_t P_SF_SET = 12;                // columns per scale set: 4 (A) + 8 (B)
 
@@ -419,8 +424,8 @@ mxgemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             ok = false;
             break;
           }
-          uint8_t* st = smem + stage * P_STAGE_BYTES;
-          uint8_t* sf = st + P_A_BYTES + P_B_BYTES;
+          uint8_t* st = smem + stage * P_DATA_BYTES;
+          uint8_t* sf = smem + P_SF_OFFSET + stage * P_SF_STAGE;
           mbar_expect_tx(full + stage, P_TX_BYTES);
           tma_load_2d(st, &tmA, full + stage, kb * BKB, a_row);
           tma_load_2d(st + P_A_BYTES, &tmB, full + stage, kb * BKB, b_row);
@@ -458,8 +463,8 @@ mxgemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               break;
             }
             tc_fence_after();
-            const uint32_t st = smem_u32(smem + stage * P_STAGE_BYTES);
-            const uint32_t a_base = st, b_base = st + P_A_BYTES, sf_base = st + P_A_BYTES + P_B_BYTES;
+            const uint32_t a_base = smem_u32(smem + stage * P_DATA_BYTES), b_base = a_base + P_A_BYTES;
+            const uint32_t sf_base = smem_u32(smem + P_SF_OFFSET + stage * P_SF_STAGE);
             const uint32_t tsfa = tmem_base + P_SF_COL0 + (it & 3u) * P_SF_SET;
             const uint32_t tsfb = tsfa + 4;
             tmem_cp_sf_2cta(tsfa, sf_smem_desc(sf_base));
@@ -502,7 +507,7 @@ mxgemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // ------------------------------------------------------------- epilogue (4 warps, one TMEM lane quarter each)
     const int q = warp & 3;
     const uint32_t tempty_leader = mapa_u32(smem_u32(tempty), 0);
-    uint8_t* stg = smem + P_STG_OFFSET + (warp - 2) * 8192;
+    uint8_t* stg = smem + P_STG_OFFSET + (warp - 2) * 4096;
     uint32_t tile_cnt = 0;
     for (int t = pair; t < g.num_tiles; t += num_pairs, ++tile_cnt) {
       const int mp = t % g.num_m_pairs;
@@ -515,7 +520,6 @@ mxgemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_after();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * P_BN;
       const int row0w = mp * 2 * BM + static_cast<int>(rank) * BM + q * 32;
-      int buf = 0;
 #pragma unroll 1
       for (int c0 = 0; c0 < P_BN; c0 += 64) {
         const int colbase = nt * P_BN + c0;
@@ -529,9 +533,9 @@ mxgemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           for (int j = 0; j < 64; ++j)
             if (colbase + j < g.N) r[j] = __float_as_uint(__uint_as_float(r[j]) + __bfloat162float(g.bias[colbase + j]));
         }
-        if (lane == 0) tma_store_wait_read<1>();            // the buffer written two stores ago has been read out
+        if (lane == 0) tma_store_wait_read<0>();            // the previous store has read the buffer out
         __syncwarp();
-        uint8_t* dstrow = stg + buf * 4096 + lane * 128;
+        uint8_t* dstrow = stg + lane * 128;
 #pragma unroll
         for (int cc = 0; cc < 8; ++cc) {
           uint4 u;
@@ -544,10 +548,9 @@ mxgemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         fence_async_smem();
         __syncwarp();
         if (lane == 0 && row0w < g.M) {                      // a box that starts past the last row has nothing to write
-          tma_store_2d(&tmC, stg + buf * 4096, colbase, row0w);
+          tma_store_2d(&tmC, stg, colbase, row0w);
           tma_store_commit();
         }
-        buf ^= 1;
       }
       tc_fence_before();
       __syncwarp();
