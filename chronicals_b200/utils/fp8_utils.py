@@ -205,6 +205,63 @@ def mxfp8_block_scaled_matmul(aq: torch.Tensor, sfa: torch.Tensor, bq: torch.Ten
     return y.to(torch.bfloat16 if aq.is_cuda else torch.float32)
 
 
+class FP8Handler:
+    """Quantise / dequantise with either MX block scaling or one delayed per-tensor scale, plus the
+    dynamic loss-scale bookkeeping the reference keeps next to it."""
+
+    def __init__(self, fmt: FP8Format = FP8Format.E4M3, block_size: int = 32, per_tensor: bool = False,
+                 amax_history_len: int = 32, margin: float = 1.0, init_loss_scale: float = 2.0 ** 15,
+                 growth_interval: int = 1000):
+        self.fmt, self.block_size, self.per_tensor, self.margin = fmt, block_size, per_tensor, margin
+        self.amax_history: Deque[float] = deque(maxlen=amax_history_len)
+        self.loss_scale, self.growth_interval = init_loss_scale, growth_interval
+        self._good_steps = 0
+        self.overflow_count = 0
+
+    # -- scaling -------------------------------------------------------------------------------------------
+    def update_amax(self, x: torch.Tensor) -> float:
+        a = float(x.detach().abs().max().item()) if x.numel() else 0.0
+        self.amax_history.append(a)
+        return a
+
+    def get_scale(self) -> float:
+        """Delayed scaling: the largest recent amax maps to the format's maximum."""
+        amax = max(self.amax_history) if self.amax_history else 0.0
+        return (self.fmt.max_value / self.margin) / amax if amax > 0 else 1.0
+
+    def quantize(self, x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        if self.per_tensor:
+            self.update_amax(x)
+            s = self.get_scale()
+            q = (x.float() * s).clamp(-self.fmt.max_value, self.fmt.max_value).to(self.fmt.torch_dtype)
+            return q, torch.tensor(1.0 / s, device=x.device)
+        return mxfp8_quantize(x, self.fmt.value)
+
+    def dequantize(self, q: torch.Tensor, scale: torch.Tensor, dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+        if scale.dtype == torch.uint8:
+            return mxfp8_dequantize(q, scale, dtype)
+        return (q.float() * scale).to(dtype)
+
+    # -- loss scaling --------------------------------------------------------------------------------------
+    def check_overflow(self, grads) -> bool:
+        for g in grads:
+            if g is not None and not torch.isfinite(g).all():
+                return True
+        return False
+
+    def update_loss_scale(self, overflow: bool) -> float:
+        if overflow:
+            self.loss_scale = max(1.0, self.loss_scale / 2)
+            self._good_steps = 0
+            self.overflow_count += 1
+        else:
+            self._good_steps += 1
+            if self._good_steps >= self.growth_interval:
+                self.loss_scale *= 2
+                self._good_steps = 0
+        return self.loss_scale
+
+
 def _block_scaled_ok(x2: torch.Tensor, w: torch.Tensor) -> bool:
     return (x2.is_cuda and x2.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and block_scaled_available()
             and x2.shape[1] % 32 == 0 and w.shape[0] % 8 == 0)
