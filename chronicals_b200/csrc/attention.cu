@@ -287,9 +287,38 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem, TMEM_COLS); }
 }
 
-// delta[h, t] = sum_d dO[t, h, d] * O[t, h, d]; one warp per (t, h)
-__global__ void attn_delta_kernel(const bf16* __restrict__ dO, const bf16* __restrict__ O, long long ld_do,
-                                  long long ld_o, int T, int hq, int D, float* __restrict__ delta) {
+// delta[h, t] = sum_d dO[t, h, d] * O[t, h, d].  LANES = D / 8 lanes share one (t, h): each loads 16 bytes
+// of dO and of O, so a warp reads 512 contiguous bytes of each tensor per instruction (32 / LANES heads of
+// one token, or of neighbouring tokens when the rows are dense) and the sum needs log2(LANES) shuffles.
+template <int LANES>
+__global__ void __launch_bounds__(256)
+attn_delta_kernel(const bf16* __restrict__ dO, const bf16* __restrict__ O, long long ld_do, long long ld_o, int T,
+                  int hq, float* __restrict__ delta) {
+  constexpr int D = LANES * 8;
+  const long long gid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  const long long pair = gid / LANES;                       // (t, h) index, h fastest
+  const int sub = static_cast<int>(gid % LANES);
+  const bool in = pair < static_cast<long long>(T) * hq;
+  float s = 0.f;
+  long long t = 0;
+  int h = 0;
+  if (in) {
+    t = pair / hq;
+    h = static_cast<int>(pair - t * hq);
+    const uint4 a = *reinterpret_cast<const uint4*>(dO + t * ld_do + static_cast<long long>(h) * D + sub * 8);
+    const uint4 b = *reinterpret_cast<const uint4*>(O + t * ld_o + static_cast<long long>(h) * D + sub * 8);
+    const float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), a2 = unpack_bf16x2(a.z), a3 = unpack_bf16x2(a.w);
+    const float2 b0 = unpack_bf16x2(b.x), b1 = unpack_bf16x2(b.y), b2 = unpack_bf16x2(b.z), b3 = unpack_bf16x2(b.w);
+    s = a0.x * b0.x + a0.y * b0.y + a1.x * b1.x + a1.y * b1.y + a2.x * b2.x + a2.y * b2.y + a3.x * b3.x + a3.y * b3.y;
+  }
+#pragma unroll
+  for (int o = LANES / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if (in && sub == 0) delta[static_cast<long long>(h) * T + t] = s;
+}
+
+// the same sum for head sizes the vector kernel does not cover: one warp per (t, h)
+__global__ void attn_delta_generic_kernel(const bf16* __restrict__ dO, const bf16* __restrict__ O, long long ld_do,
+                                          long long ld_o, int T, int hq, int D, float* __restrict__ delta) {
   const long long w = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (w >= static_cast<long long>(T) * hq) return;
@@ -659,9 +688,19 @@ int cb_attn_bwd(const void* q, const void* k, const void* v, const void* o, cons
   e = cbhost::make_tmap(&mdo, d_o, static_cast<unsigned long long>(hq) * D, T, ld_do, 64, 128);
   if (e) return e;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const long long warps = static_cast<long long>(T) * hq;
-  cb::attn_delta_kernel<<<static_cast<unsigned>((warps * 32 + 255) / 256), 256, 0, s>>>(
-      static_cast<const cb::bf16*>(d_o), static_cast<const cb::bf16*>(o), ld_do, ldo, T, hq, D, delta);
+  const long long pairs = static_cast<long long>(T) * hq;
+  const bool vec_ok = (reinterpret_cast<uintptr_t>(d_o) & 15) == 0 && (reinterpret_cast<uintptr_t>(o) & 15) == 0 &&
+                      ld_do % 8 == 0 && ldo % 8 == 0;
+  if (vec_ok && D == 64) {
+    cb::attn_delta_kernel<8><<<static_cast<unsigned>((pairs * 8 + 255) / 256), 256, 0, s>>>(
+        static_cast<const cb::bf16*>(d_o), static_cast<const cb::bf16*>(o), ld_do, ldo, T, hq, delta);
+  } else if (vec_ok && D == 128) {
+    cb::attn_delta_kernel<16><<<static_cast<unsigned>((pairs * 16 + 255) / 256), 256, 0, s>>>(
+        static_cast<const cb::bf16*>(d_o), static_cast<const cb::bf16*>(o), ld_do, ldo, T, hq, delta);
+  } else {
+    cb::attn_delta_generic_kernel<<<static_cast<unsigned>((pairs * 32 + 255) / 256), 256, 0, s>>>(
+        static_cast<const cb::bf16*>(d_o), static_cast<const cb::bf16*>(o), ld_do, ldo, T, hq, D, delta);
+  }
   CB_CHECK_CUDA(cudaMemsetAsync(dq_acc, 0, sizeof(float) * static_cast<size_t>(T) * hq * D, s));
   cb::AttnArgs a = {};
   a.T = T; a.hq = hq; a.hk = hk; a.n_docs = n_docs; a.cu = cu; a.scale = scale;
