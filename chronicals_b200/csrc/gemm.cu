@@ -426,7 +426,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             fence_async_smem();
             __syncwarp();
             if (lane == 0 && row0w < g.M) {          // a box that starts past the last row has nothing to write
-              tma_store_2d(&tmC, stg + buf * 4096, colbase, row0w);
+              if (g.items_per_ksplit > 0) tma_reduce_add_2d(&tmC, stg + buf * 4096, colbase, row0w);   // split K: sum the ranges
+              else tma_store_2d(&tmC, stg + buf * 4096, colbase, row0w);
               tma_store_commit();
             }
             }
@@ -825,6 +826,13 @@ int cb_gemm_bf16_splitk(const void* A, const void* B, float* C, int M, int N, in
   g.num_items = tiles * splits;
   g.C = C; g.ldc = ldc; g.out_fp32 = 1;
   g.tma_store = 0;
+  if ((reinterpret_cast<uintptr_t>(C) & 15) == 0 && (ldc * 4) % 16 == 0) {
+    // partial tiles go through the staging buffers and are added into C by TMA reduce (128-byte rows of 32 floats);
+    // otherwise each thread adds its elements one by one
+    e = cbhost::make_tmap(&tc, C, N, M, ldc, 32, 32, 4);
+    if (e) return e;
+    g.tma_store = 1;
+  }
   g.status = status;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   CB_CHECK_CUDA(cudaMemset2DAsync(C, sizeof(float) * ldc, 0, sizeof(float) * N, M, s));

@@ -117,6 +117,29 @@ def colsum(x: torch.Tensor) -> torch.Tensor:
     return x.float().sum(0).to(x.dtype)
 
 
+_SM_COUNT = {}
+
+
+def _sm_count(device: torch.device) -> int:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _SM_COUNT:
+        _SM_COUNT[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return _SM_COUNT[idx]
+
+
+def wgrad(dy2: torch.Tensor, x2: torch.Tensor) -> torch.Tensor:
+    """``dW = dYᵀ X`` (``[out, in]``) of a linear layer.  A small weight with many tokens gives fewer output
+    tiles than half the SMs and a long inner dimension (QKV and attention-output projections of a 0.5B model:
+    63 and 49 tiles of 128 × 128 over 8192 tokens), so the token range is split across CTAs, the partial tiles
+    are added in fp32 by TMA reduce and the sum is rounded once; everything else is one bf16-output GEMM."""
+    n_out, n_in, T = dy2.shape[1], x2.shape[1], dy2.shape[0]
+    if _fast(dy2, x2) and T >= 2048 and _gemm_ok(dy2) and _gemm_ok(x2):
+        tiles = ((n_out + 127) // 128) * ((n_in + 127) // 128)
+        if 2 * tiles <= _sm_count(dy2.device):
+            return gemm_splitk(dy2, x2, a_mn=True, b_mn=True).to(dy2.dtype)
+    return gemm(dy2, x2, a_mn=True, b_mn=True)
+
+
 class _LinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x2, w, bias, res2):
@@ -138,7 +161,7 @@ class _LinearFn(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = gemm(dy2, w, b_mn=True)                             # dX = dY @ W
         if ctx.needs_input_grad[1]:
-            dw = gemm(dy2, x2, a_mn=True, b_mn=True)                 # dW = dY^T @ X
+            dw = wgrad(dy2, x2)                                      # dW = dY^T @ X
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = colsum(dy2)
         dres = dy2 if ctx.has_res else None

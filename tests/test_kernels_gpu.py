@@ -391,6 +391,23 @@ def test_fp8_linear_gradients_on_block_scaled_tensor_cores():
     assert (lin.bias.grad.float() - gy.float().sum(0)).abs().max().item() < 0.02 * gy.float().sum(0).abs().max().item()
 
 
+def test_linear_weight_gradient_of_a_small_weight_uses_split_k_and_matches_fp32():
+    """out x in = 256 x 384 over 4096 tokens: 6 output tiles, so the token range is split across CTAs and the
+    partial tiles meet through TMA reduce-add; a ragged 200 x 136 output exercises the clipped boxes."""
+    from chronicals_b200 import ops
+    torch.manual_seed(0)
+    for n_out, n_in in ((256, 384), (200, 136)):
+        x = torch.randn(4096, n_in, device="cuda", dtype=torch.bfloat16)
+        dy = torch.randn(4096, n_out, device="cuda", dtype=torch.bfloat16)
+        dw = ops.wgrad(dy, x)
+        want = dy.float().t() @ x.float()
+        assert dw.dtype == torch.bfloat16 and dw.shape == (n_out, n_in)
+        assert (dw.float() - want).abs().max().item() < 8e-3 * want.abs().max().item()
+        w = torch.randn(n_out, n_in, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+        ops.linear(x, w).backward(dy)
+        assert (w.grad.float() - want).abs().max().item() < 8e-3 * want.abs().max().item()
+
+
 def test_fused_lora_projection_matches_reference_formula():
     """Frozen fused QKV projection with rank-16 adapters on every split: forward, dX, dA, dB against the
     plain PEFT formula in fp32 (the base weight must receive no gradient)."""
