@@ -61,3 +61,12 @@ def test_lora_example_trains_and_reloads(tmp_path):
 @pytest.mark.parametrize("script", ["examples/quickstart_lora.py"])
 def test_quickstart_runs(script):
     assert "done:" in _run([script])
+
+
+def test_fp8_mode_benchmark_runs_all_three_modes_on_cpu():
+    out = _run(["benchmarks/bench_fp8_modes.py", "--model", "tiny-qwen2", "--layers", "2", "--batch", "2", "--seq", "32",
+                "--steps", "2", "--warmup", "1"])
+    rows = [json.loads(l) for l in out.splitlines() if l.startswith("{")]
+    assert [r["mode"] for r in rows] == ["bf16", "rowwise", "mxfp8"]
+    base = rows[0]["loss"]
+    assert all(abs(r["loss"] - base) < 0.2 for r in rows), rows       # quantisation noise only
