@@ -81,6 +81,51 @@ __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t base, int kk) {     //
   return umma_smem_desc(base + kk * 2048, 16384, 1024);
 }
 
+// Forward softmax passes over my row of the score tile (fp32, TMEM columns [0, 128)), in two versions: the
+// diagonal block masks columns beyond the row, every other block of a causal document needs no mask at all
+// (7 of 8 blocks at 1024 tokens), so the common path carries no compare / select per element.
+template <bool DIAG>
+__device__ __forceinline__ float fwd_row_max(uint32_t t_row, int r) {
+  float mx = -INFINITY;
+#pragma unroll 1
+  for (int c = 0; c < 4; ++c) {
+    uint32_t s[32];
+    tmem_ld_32x32(t_row + c * 32, s);
+    tmem_ld_wait();
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const float v = __uint_as_float(s[i]);
+      if (!DIAG || c * 32 + i <= r) mx = fmaxf(mx, v);
+    }
+  }
+  return mx;
+}
+// P = 2^(S * sl2 - mb) written as bf16 pairs over the consumed S columns; returns the row sum
+template <bool DIAG>
+__device__ __forceinline__ float fwd_row_exp(uint32_t t_row, int r, float sl2, float mb) {
+  float rs = 0.f;
+#pragma unroll 1
+  for (int c = 0; c < 4; ++c) {
+    uint32_t s[32];
+    float p[32];
+    tmem_ld_32x32(t_row + c * 32, s);
+    tmem_ld_wait();
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const float e = ex2_approx(fmaf(__uint_as_float(s[i]), sl2, -mb));
+      p[i] = (!DIAG || c * 32 + i <= r) ? e : 0.f;
+      rs += p[i];
+    }
+    // 32 probabilities -> 16 bf16 pairs -> TMEM words [16c, 16c + 16) of my row: always behind the
+    // fp32 columns [32c, 32c + 32) just read, so S is consumed before it is overwritten
+    uint32_t pk[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) pk[i] = pack_bf16x2(p[2 * i], p[2 * i + 1]);
+    tmem_st_32x16(t_row + c * 16, pk);
+  }
+  return rs;
+}
+
 template <int D>
 struct FwdSmem {
   static constexpr int TILE = 128 * D * 2;            // one [128 x D] operand
@@ -180,18 +225,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     tc_fence_after();
     const bool diag = (j == qb);
     // pass 1: row maximum of the raw scores
-    float mx = -INFINITY;
-#pragma unroll 1
-    for (int c = 0; c < 4; ++c) {
-      uint32_t s[32];
-      tmem_ld_32x32(t_row + c * 32, s);
-      tmem_ld_wait();
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const float v = __uint_as_float(s[i]);
-        if (!diag || c * 32 + i <= r) mx = fmaxf(mx, v);
-      }
-    }
+    const float mx = diag ? fwd_row_max<true>(t_row, r) : fwd_row_max<false>(t_row, r);
     if (j > 0) {
       // previous P V product: fold into the running output before rescaling it
       ok &= mbar_wait(bar_o, (j - 1) & 1, abort_flag, a.status, CB_ERR_WAIT_TMEM_FULL);
@@ -207,28 +241,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (tid == 0 && ok && j + 1 < n_kv) load_kv(j + 1);   // stage (j+1)&1 was released by P V of block j-1
     }
     const float m_new = fmaxf(m_run, mx);
-    const float alpha = exp2f((m_run - m_new) * sl2);
+    const float alpha = ex2_approx((m_run - m_new) * sl2);
     const float mb = m_new * sl2;
-    float rs = 0.f;
-#pragma unroll 1
-    for (int c = 0; c < 4; ++c) {
-      uint32_t s[32];
-      float p[32];
-      tmem_ld_32x32(t_row + c * 32, s);
-      tmem_ld_wait();
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const float e = exp2f(fmaf(__uint_as_float(s[i]), sl2, -mb));
-        p[i] = (!diag || c * 32 + i <= r) ? e : 0.f;
-        rs += p[i];
-      }
-      // 32 probabilities -> 16 bf16 pairs -> TMEM words [16c, 16c + 16) of my row: always behind the
-      // fp32 columns [32c, 32c + 32) just read, so S is consumed before it is overwritten
-      uint32_t pk[16];
-#pragma unroll
-      for (int i = 0; i < 16; ++i) pk[i] = pack_bf16x2(p[2 * i], p[2 * i + 1]);
-      tmem_st_32x16(t_row + c * 16, pk);
-    }
+    const float rs = diag ? fwd_row_exp<true>(t_row, r, sl2, mb) : fwd_row_exp<false>(t_row, r, sl2, mb);
     tmem_st_wait();
     l_run = l_run * alpha + rs;
     m_run = m_new;
@@ -490,7 +505,7 @@ attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
       for (int k = 0; k < 32; ++k) {
         const bool keep = row_ok && (!diag || c * 32 + k <= r);
-        const float e = exp2f(fmaf(__uint_as_float(s[k]), sl2, -lse2));
+        const float e = ex2_approx(fmaf(__uint_as_float(s[k]), sl2, -lse2));
         p[k] = keep ? e : 0.f;
       }
       store_row_chunk32(sP, r, c, p);

@@ -285,6 +285,13 @@ __host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n, int a_major
 }
 
 // ---------------------------------------------------------------- small math helpers
+// 2^x on the special-function unit in one instruction (results below the normal range flush to zero, which is
+// what a softmax probability wants; exp2f() without fast-math wraps the same instruction in range scaling)
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
