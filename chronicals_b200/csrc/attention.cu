@@ -84,19 +84,22 @@ __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t base, int kk) {     //
 // Forward softmax passes over my row of the score tile (fp32, TMEM columns [0, 128)), in two versions: the
 // diagonal block masks columns beyond the row, every other block of a causal document needs no mask at all
 // (7 of 8 blocks at 1024 tokens), so the common path carries no compare / select per element.
+// Both passes keep the TMEM load of the next 32-column chunk in flight while they work on the current one.
 template <bool DIAG>
 __device__ __forceinline__ float fwd_row_max(uint32_t t_row, int r) {
   float mx = -INFINITY;
-#pragma unroll 1
+  uint32_t s[2][32];
+  tmem_ld_32x32(t_row, s[0]);
+  tmem_ld_wait();
+#pragma unroll
   for (int c = 0; c < 4; ++c) {
-    uint32_t s[32];
-    tmem_ld_32x32(t_row + c * 32, s);
-    tmem_ld_wait();
+    if (c + 1 < 4) tmem_ld_32x32(t_row + (c + 1) * 32, s[(c + 1) & 1]);
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
-      const float v = __uint_as_float(s[i]);
+      const float v = __uint_as_float(s[c & 1][i]);
       if (!DIAG || c * 32 + i <= r) mx = fmaxf(mx, v);
     }
+    if (c + 1 < 4) tmem_ld_wait();
   }
   return mx;
 }
@@ -104,23 +107,28 @@ __device__ __forceinline__ float fwd_row_max(uint32_t t_row, int r) {
 template <bool DIAG>
 __device__ __forceinline__ float fwd_row_exp(uint32_t t_row, int r, float sl2, float mb) {
   float rs = 0.f;
-#pragma unroll 1
-  for (int c = 0; c < 4; ++c) {
-    uint32_t s[32];
-    float p[32];
-    tmem_ld_32x32(t_row + c * 32, s);
-    tmem_ld_wait();
+  uint32_t s[2][32];
+  tmem_ld_32x32(t_row, s[0]);
+  tmem_ld_wait();
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      const float e = ex2_approx(fmaf(__uint_as_float(s[i]), sl2, -mb));
-      p[i] = (!DIAG || c * 32 + i <= r) ? e : 0.f;
-      rs += p[i];
-    }
-    // 32 probabilities -> 16 bf16 pairs -> TMEM words [16c, 16c + 16) of my row: always behind the
-    // fp32 columns [32c, 32c + 32) just read, so S is consumed before it is overwritten
+  for (int c = 0; c < 4; ++c) {
+    // the chunk fetched here ([32(c+1), 32(c+2))) lies above every word written below ([16c, 16c + 16))
+    if (c + 1 < 4) tmem_ld_32x32(t_row + (c + 1) * 32, s[(c + 1) & 1]);
     uint32_t pk[16];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) pk[i] = pack_bf16x2(p[2 * i], p[2 * i + 1]);
+    for (int i = 0; i < 16; ++i) {
+      float e0 = ex2_approx(fmaf(__uint_as_float(s[c & 1][2 * i]), sl2, -mb));
+      float e1 = ex2_approx(fmaf(__uint_as_float(s[c & 1][2 * i + 1]), sl2, -mb));
+      if (DIAG) {
+        e0 = (c * 32 + 2 * i <= r) ? e0 : 0.f;
+        e1 = (c * 32 + 2 * i + 1 <= r) ? e1 : 0.f;
+      }
+      rs += e0 + e1;
+      pk[i] = pack_bf16x2(e0, e1);
+    }
+    if (c + 1 < 4) tmem_ld_wait();
+    // 32 probabilities -> 16 bf16 pairs -> TMEM words [16c, 16c + 16) of my row: always behind the
+    // fp32 columns [32c, 32c + 32) already read, so S is consumed before it is overwritten
     tmem_st_32x16(t_row + c * 16, pk);
   }
   return rs;
@@ -247,8 +255,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     tmem_st_wait();
     l_run = l_run * alpha + rs;
     m_run = m_new;
+    if (__any_sync(0xffffffffu, alpha != 1.f)) {     // the row maximum rarely moves after the first blocks
 #pragma unroll
-    for (int i = 0; i < D; ++i) o[i] *= alpha;
+      for (int i = 0; i < D; ++i) o[i] *= alpha;
+    }
     tc_fence_before();
     if (__syncthreads_or(!ok)) { ok = false; break; }
     if (tid == 0) {
