@@ -133,7 +133,9 @@ def wgrad(dy2: torch.Tensor, x2: torch.Tensor) -> torch.Tensor:
     63 and 49 tiles of 128 × 128 over 8192 tokens), so the token range is split across CTAs, the partial tiles
     are added in fp32 by TMA reduce and the sum is rounded once; everything else is one bf16-output GEMM."""
     n_out, n_in, T = dy2.shape[1], x2.shape[1], dy2.shape[0]
-    if _fast(dy2, x2) and T >= 2048 and _gemm_ok(dy2) and _gemm_ok(x2):
+    if not _fast(dy2, x2):
+        return dy2.t() @ x2
+    if T >= 2048 and _gemm_ok(dy2) and _gemm_ok(x2):
         tiles = ((n_out + 127) // 128) * ((n_in + 127) // 128)
         if 2 * tiles <= _sm_count(dy2.device):
             return gemm_splitk(dy2, x2, a_mn=True, b_mn=True).to(dy2.dtype)

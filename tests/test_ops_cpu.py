@@ -171,6 +171,12 @@ def test_mx_scale_atoms_layout_and_block_scaled_product_oracle():
     assert torch.equal(F8.mxfp8_block_scaled_matmul(aq, sa, bq, sb, b_tile_rows=192), ref.mxfp8_linear(x, w))
 
 
+def test_wgrad_cpu_path_matches_matmul():
+    from chronicals_b200 import ops
+    dy, x = torch.randn(64, 24), torch.randn(64, 40)
+    assert torch.allclose(ops.wgrad(dy, x), dy.t() @ x, atol=1e-5)
+
+
 def test_blockwise_8bit_roundtrip():
     x = torch.randn(1000)
     q, a = ref.quantize_blockwise_8bit(x)
