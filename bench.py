@@ -428,6 +428,11 @@ def main():
     if args.impl == "reference":
         run_reference(args)
     else:
+        import torch
+        if not torch.cuda.is_available():
+            # the flagship step only exists as sm_100a kernels: no CPU stand-in is timed
+            print(json.dumps({"impl": "chronicals_b200", "unavailable": "no CUDA device"}), flush=True)
+            sys.exit(1)
         run_ours(args)
 
 
