@@ -199,6 +199,9 @@ def run_ours(args):
             from chronicals_b200.parallel.symm import peer_access_available
             comm = "fused" if peer_access_available() else "nccl"
     targs.parallel.comm_backend = comm
+    targs.parallel.overlap_grad_reduce = not args.no_overlap
+    if args.reduce_grid > 0:
+        targs.parallel.reduce_grid = args.reduce_grid
     pin = True
     batches = _host_batches(4, cfg.vocab_size, 1000 + rank, pin)
 
@@ -253,6 +256,9 @@ def run_ours(args):
                        "parallelism": f"dp{world}", "optimizer": "AdamW (fp32 moments) + global-norm clip",
                        "loss": "fused linear cross-entropy (no logits)", "cuda_graph": trainer.use_cuda_graphs,
                        "comm": comm if world > 1 else "none",
+                       "grad_reduce": ("per-bucket reduce-scatter from backward hooks on a side stream"
+                                       if (world > 1 and comm == "fused" and not args.no_overlap) else
+                                       "after backward" if world > 1 else "none"),
                        "l2": "per-step working set is several GB (>> 126 MB L2); no explicit flush"},
             "mfu_6N_vs_2250TF": 6.0 * n_params * value / (2250e12 * world),
             "clocks": clocks,
@@ -262,12 +268,31 @@ def run_ours(args):
             "gpu_launches": int(per_step_launches * args.steps),
             "final_loss": final_loss, "n_params": n_params,
         }
+        if hasattr(trainer.optimizer, "buckets"):
+            out["config"]["grad_buckets"] = len(trainer.optimizer.buckets)
+            out["config"]["reduce_grid"] = int(trainer.optimizer.rs_grid)
         print(json.dumps(out), flush=True)
+    import shutil
+    shutil.rmtree(targs.output_dir, ignore_errors=True)
     from chronicals_b200.parallel.bootstrap import shutdown
     shutdown()
 
 
 # ------------------------------------------------------------------------------------------- the reference
+def _clean_tmp_dirs():
+    """Removes benchmark output directories of processes that no longer exist (each arm of a back-to-back
+    series writes several GB of checkpoints; nothing else deletes them)."""
+    import glob
+    import shutil
+    for d in glob.glob("/tmp/ref_bench_*") + glob.glob("/tmp/cb_bench_*"):
+        try:
+            pid = int(d.rsplit("_", 1)[1])
+        except ValueError:
+            continue
+        if not os.path.exists(f"/proc/{pid}"):
+            shutil.rmtree(d, ignore_errors=True)
+
+
 def _unavailable(why: str):
     print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)
     sys.exit(0)
@@ -366,12 +391,26 @@ def run_reference(args):
         import contextlib
         import io
         sink = io.StringIO()
-        with contextlib.redirect_stdout(sink):
-            trainer = RefTrainer(model, cfg, loader)
-            trainer.train()
+        post_timing_error = None
+        _clean_tmp_dirs()                                   # checkpoints left by earlier arms on this box
+        trainer = None
+        try:
+            with contextlib.redirect_stdout(sink):
+                trainer = RefTrainer(model, cfg, loader)
+                trainer.train()
+        except Exception as e:
+            # The reference's train() writes two full checkpoints per rank (model + fp32 moments) after the
+            # last batch.  When that write fails (a full disk), the timed region has already been closed by the
+            # loader, so the measurement stands and the failure is reported beside it.
+            if loader.t1 <= 0.0:
+                raise
+            post_timing_error = f"{type(e).__name__}: {e}"[:300]
+        finally:
+            import shutil
+            shutil.rmtree(cfg.output_dir, ignore_errors=True)
         ms = _max_ms(loader.elapsed_ms(), world)
         clocks = sampler.stop() if (rank == 0 and dev.type == "cuda") else None
-        hist = getattr(trainer.state, "log_history", [])
+        hist = getattr(trainer.state, "log_history", []) if trainer is not None else []
     except SystemExit:
         raise
     except Exception as e:
@@ -400,6 +439,8 @@ def run_reference(args):
                     "d2h_bytes_per_step": 4},
             "n_params": n_params, "final_loss": (hist[-1].get("loss") if hist and isinstance(hist[-1], dict) else None),
         }
+        if post_timing_error:
+            out["post_timing_error"] = post_timing_error
         print(json.dumps(out), flush=True)
     from chronicals_b200.parallel.bootstrap import shutdown
     shutdown()
@@ -414,6 +455,9 @@ def main():
     ap.add_argument("--model", default=MODEL)
     ap.add_argument("--comm", default="auto", choices=["auto", "nccl", "fused"])
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-overlap", action="store_true",
+                    help="reduce-scatter the gradient buckets after the backward pass instead of from its hooks")
+    ap.add_argument("--reduce-grid", type=int, default=0, help="blocks per bucket reduce-scatter kernel (0: default)")
     ap.add_argument("--tiny", action="store_true", help="plumbing check of the reference arm on a tiny model")
     ap.add_argument("--ref-no-compile", action="store_true")
     args = ap.parse_args()

@@ -207,12 +207,74 @@ def save_training_state(out_dir: str, optimizer=None, scheduler=None, trainer_st
                 json.dump(history, f, default=float)
 
 
+def _state_kind(sd: Dict[str, Any]) -> str:
+    if "zero3" in sd:
+        return "zero3"
+    return str(sd.get("kind", "replicated"))
+
+
+def _optimizer_kind(optimizer) -> str:
+    name = type(optimizer).__name__
+    return {"Zero3Optimizer": "zero3", "ShardedFusedAdamW": "zero1"}.get(name, "replicated")
+
+
+def consolidate_optimizer_states(states: List[Dict[str, Any]]) -> Dict[str, Any]:
+    """Optimizer files of all saved ranks → per-parameter exchange form: ``exp_avg`` / ``exp_avg_sq`` as lists of
+    flat fp32 tensors in parameter order, ``step_count``, ``param_groups`` (hyper-parameters only)."""
+    kind = _state_kind(states[0])
+    if kind == "zero3":
+        from ..parallel.zero3 import consolidate_zero3_states
+        return consolidate_zero3_states(states)
+    if kind == "zero1":
+        from ..parallel.zero import consolidate_states
+        return consolidate_states(states)
+    sd = states[0]                                               # torch-style state dict, identical on every rank
+    ids = [i for g in sd["param_groups"] for i in g["params"]]
+    out: Dict[str, Any] = {"step_count": int(sd.get("step_count", 0)), "master": None,
+                           "param_groups": [{k: v for k, v in g.items() if k != "params"} for g in sd["param_groups"]]}
+    for name in ("exp_avg", "exp_avg_sq"):
+        out[name] = [sd["state"][i][name].reshape(-1).float() for i in ids if i in sd["state"]]
+    if not out["step_count"] and ids and ids[0] in sd["state"] and "step" in sd["state"][ids[0]]:
+        out["step_count"] = int(sd["state"][ids[0]]["step"])
+    return out
+
+
+def saved_world_size(ckpt_dir: str) -> int:
+    """Number of ranks that wrote the optimizer files of a checkpoint directory (0 when there are none)."""
+    if os.path.exists(os.path.join(ckpt_dir, "optimizer.pt")):
+        return 1
+    n = 0
+    while os.path.exists(os.path.join(ckpt_dir, f"optimizer.rank{n}.pt")):
+        n += 1
+    return n
+
+
 def load_training_state(ckpt_dir: str, optimizer=None, scheduler=None, rank: int = 0, world_size: int = 1,
                         restore_rng: bool = True) -> Dict[str, Any]:
     suffix = "" if world_size == 1 else f".rank{rank}"
-    p = os.path.join(ckpt_dir, f"optimizer{suffix}.pt")
-    if optimizer is not None and os.path.exists(p):
-        optimizer.load_state_dict(torch.load(p, map_location="cpu", weights_only=False))
+    saved_world = saved_world_size(ckpt_dir)
+    if optimizer is not None and saved_world:
+        mine = os.path.join(ckpt_dir, f"optimizer{suffix}.pt")
+        first = torch.load(mine if (saved_world == world_size and os.path.exists(mine)) else
+                           os.path.join(ckpt_dir, "optimizer.pt" if saved_world == 1 else "optimizer.rank0.pt"),
+                           map_location="cpu", weights_only=False)
+        if saved_world == world_size and _state_kind(first) == _optimizer_kind(optimizer):
+            optimizer.load_state_dict(first)
+        else:
+            # elastic restart (another number of ranks, or another sharding of the optimizer state): bring the
+            # saved state into the per-parameter exchange form and let the optimizer lay it out for itself
+            names = ["optimizer.pt"] if saved_world == 1 else [f"optimizer.rank{r}.pt" for r in range(saved_world)]
+            kind = _state_kind(first)
+            states = [first] if kind == "replicated" else [
+                torch.load(os.path.join(ckpt_dir, n), map_location="cpu", weights_only=False) for n in names]
+            if kind == _optimizer_kind(optimizer) and hasattr(optimizer, "load_resharded"):
+                optimizer.load_resharded(states)
+            elif hasattr(optimizer, "load_consolidated"):
+                optimizer.load_consolidated(consolidate_optimizer_states(states))
+            else:
+                optimizer.load_state_dict(first)
+            if saved_world != world_size:
+                suffix = "" if saved_world == 1 else ".rank0"       # RNG: every new rank continues rank 0's stream
     p = os.path.join(ckpt_dir, "scheduler.pt")
     if scheduler is not None and os.path.exists(p):
         scheduler.load_state_dict(torch.load(p, map_location="cpu", weights_only=False))

@@ -262,6 +262,12 @@ class ParallelConfig:
     bucket_mb: float = 32.0
     comm_backend: str = "nccl"
     wait_budget_us: int = 2_000_000
+    # sharded optimizer (zero_stage 1, or the fused data-parallel path): gradient buckets of about this size are
+    # reduce-scattered from backward hooks on a side stream; ``overlap_grad_reduce=False`` reduces after the
+    # backward pass instead
+    shard_bucket_mb: float = 24.0
+    overlap_grad_reduce: bool = True
+    reduce_grid: int = 24
 
     @property
     def world_size(self) -> int:

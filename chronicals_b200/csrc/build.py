@@ -68,8 +68,8 @@ def nvcc_path() -> str:
     return cand
 
 
-def _compile_one(nvcc: str, src: str, verbose: bool) -> str:
-    obj = os.path.join(OBJ_DIR, os.path.basename(src)[:-3] + ".o")
+def _compile_one(nvcc: str, src: str, verbose: bool, obj_dir: str = OBJ_DIR) -> str:
+    obj = os.path.join(obj_dir, os.path.basename(src)[:-3] + ".o")
     cmd = [nvcc, *_flags(), "-I", HERE, "-c", src, "-o", obj]
     if verbose:
         cmd.insert(1, "-Xptxas")
@@ -88,17 +88,33 @@ def build(force: bool = False, verbose: bool = False) -> str:
         return LIB_PATH
     nvcc = nvcc_path()
     os.makedirs(OBJ_DIR, exist_ok=True)
-    srcs = sources()
-    with cf.ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
-        objs = list(ex.map(lambda s: _compile_one(nvcc, s, verbose), srcs))
-    tmp = LIB_PATH + ".tmp"
-    cmd = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", tmp, *objs]
-    r = subprocess.run(cmd, capture_output=True, text=True)
-    if r.returncode != 0:
-        raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
-    os.replace(tmp, LIB_PATH)
-    with open(HASH_PATH, "w") as f:
-        f.write(source_hash())
+    # Several ranks of one job may find a stale library at the same time: one of them builds, the others wait for
+    # the lock and then see a current hash.  Objects and the linked library go to names private to this process
+    # and are moved into place atomically, so nobody ever loads a half-written file.
+    import fcntl
+    with open(os.path.join(OBJ_DIR, ".lock"), "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not force and is_current():
+                return LIB_PATH
+            obj_dir = os.path.join(OBJ_DIR, f"p{os.getpid()}")
+            os.makedirs(obj_dir, exist_ok=True)
+            srcs = sources()
+            with cf.ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
+                objs = list(ex.map(lambda s: _compile_one(nvcc, s, verbose, obj_dir), srcs))
+            tmp = f"{LIB_PATH}.{os.getpid()}.tmp"
+            cmd = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", tmp, *objs]
+            r = subprocess.run(cmd, capture_output=True, text=True)
+            if r.returncode != 0:
+                raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+            os.replace(tmp, LIB_PATH)
+            tmp_hash = f"{HASH_PATH}.{os.getpid()}.tmp"
+            with open(tmp_hash, "w") as f:
+                f.write(source_hash())
+            os.replace(tmp_hash, HASH_PATH)
+            shutil.rmtree(obj_dir, ignore_errors=True)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
     return LIB_PATH
 
 

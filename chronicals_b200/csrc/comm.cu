@@ -140,6 +140,66 @@ __global__ void sum_partials_kernel(const float* __restrict__ partials, int n, f
   }
 }
 
+// Per-bucket reduce-scatter that runs beside the backward pass on a second stream.  Same arithmetic as
+// rs_reduce_sqnorm_kernel, shaped to share SMs with the compute kernels: 128 threads per block and a
+// small grid (the host picks it), two 16-byte vectors per peer in flight per thread.  partials[block]
+// receives the block's sum of squares; the host sums all buckets' partials once after the last bucket.
+constexpr int RSB_THREADS = 128;
+__global__ void __launch_bounds__(RSB_THREADS)
+rs_bucket_kernel(PeerTable grads, int W, long long lo, long long hi, float* __restrict__ reduced,
+                 float* __restrict__ partials, int* status) {
+  __shared__ float sred[RSB_THREADS / 32];
+  float sq = 0.f;
+  if (status[0] == 0) {
+    const float inv = 1.f / static_cast<float>(W);
+    const long long nvec = (hi - lo) >> 3;
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long v = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; v < nvec; v += 2 * stride) {
+      const long long v2 = v + stride;
+      const bool two = v2 < nvec;
+      float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      float b[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int r = 0; r < W; r += 2) {
+        const bf16* g0 = static_cast<const bf16*>(grads.ptr[r]) + lo;
+        const bool r1 = r + 1 < W;
+        const bf16* g1 = r1 ? static_cast<const bf16*>(grads.ptr[r + 1]) + lo : g0;
+        const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+        const uint4 u00 = *reinterpret_cast<const uint4*>(g0 + (v << 3));
+        const uint4 u10 = r1 ? *reinterpret_cast<const uint4*>(g1 + (v << 3)) : z;
+        const uint4 u01 = two ? *reinterpret_cast<const uint4*>(g0 + (v2 << 3)) : z;
+        const uint4 u11 = (two && r1) ? *reinterpret_cast<const uint4*>(g1 + (v2 << 3)) : z;
+        acc_bf16x8(u00, a);
+        acc_bf16x8(u10, a);
+        acc_bf16x8(u01, b);
+        acc_bf16x8(u11, b);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        a[j] *= inv;
+        b[j] *= inv;
+        sq += a[j] * a[j] + b[j] * b[j];
+      }
+      float4* o = reinterpret_cast<float4*>(reduced + (v << 3));
+      o[0] = make_float4(a[0], a[1], a[2], a[3]);
+      o[1] = make_float4(a[4], a[5], a[6], a[7]);
+      if (two) {
+        float4* o2 = reinterpret_cast<float4*>(reduced + (v2 << 3));
+        o2[0] = make_float4(b[0], b[1], b[2], b[3]);
+        o2[1] = make_float4(b[4], b[5], b[6], b[7]);
+      }
+    }
+  }
+  sq = warp_sum(sq);
+  if ((threadIdx.x & 31) == 0) sred[threadIdx.x >> 5] = sq;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < RSB_THREADS / 32; ++i) t += sred[i];
+    partials[blockIdx.x] = t;
+  }
+}
+
 // AdamW on the owned slice [lo, hi) and fused all-gather.  `gathered` holds every rank's payload
 // (slot 0 = its share of the squared gradient norm); the clip coefficient is computed from their sum
 // in rank order, so all ranks get the same value.  chunk_group[(i - lo) / 1024] selects the
@@ -149,7 +209,8 @@ adamw_shard_allgather_kernel(PeerTable params, int W, int my_rank, long long lo,
                              const float* __restrict__ reduced, float* __restrict__ m, float* __restrict__ v,
                              float* __restrict__ master, const unsigned char* __restrict__ chunk_group,
                              const float* __restrict__ hyper, const float* __restrict__ gathered, float max_norm,
-                             float* __restrict__ norm_out, int W_store, int* status) {
+                             float* __restrict__ norm_out, int W_store, const long long* __restrict__ chunk_off,
+                             int* status) {
   if (status[0] != 0) return;
   float tot = 0.f;
   for (int r = 0; r < W; ++r) tot += gathered[r * PAYLOAD_FLOATS];
@@ -165,6 +226,9 @@ adamw_shard_allgather_kernel(PeerTable params, int W, int my_rank, long long lo,
   for (long long vi = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; vi < nvec;
        vi += static_cast<long long>(gridDim.x) * blockDim.x) {
     const long long e = vi << 3;
+    // bucketed layout: the owned slice is a concatenation of one piece per bucket; chunk_off[c] is where the
+    // c-th 1024-element chunk of the slice sits in the flat parameter buffer.  Without the table: lo + e.
+    const long long ge = chunk_off != nullptr ? chunk_off[e >> 10] + (e & 1023) : lo + e;
     const float* h = hyper + chunk_group[e >> 10] * 8;
     const float lr = h[0], wd = h[1], b1 = h[2], b2 = h[3], eps = h[4], bc1 = h[5], bc2 = h[6];
     const float step = lr / bc1, inv_bc2 = 1.f / bc2, decay = 1.f - lr * wd;
@@ -175,7 +239,7 @@ adamw_shard_allgather_kernel(PeerTable params, int W, int my_rank, long long lo,
       const float4 w0 = *reinterpret_cast<const float4*>(master + e), w1 = *reinterpret_cast<const float4*>(master + e + 4);
       w[0] = w0.x; w[1] = w0.y; w[2] = w0.z; w[3] = w0.w; w[4] = w1.x; w[5] = w1.y; w[6] = w1.z; w[7] = w1.w;
     } else {
-      const uint4 u = *reinterpret_cast<const uint4*>(mine + lo + e);
+      const uint4 u = *reinterpret_cast<const uint4*>(mine + ge);
       const float2 x0 = unpack_bf16x2(u.x), x1 = unpack_bf16x2(u.y), x2 = unpack_bf16x2(u.z), x3 = unpack_bf16x2(u.w);
       w[0] = x0.x; w[1] = x0.y; w[2] = x1.x; w[3] = x1.y; w[4] = x2.x; w[5] = x2.y; w[6] = x3.x; w[7] = x3.y;
     }
@@ -204,7 +268,7 @@ adamw_shard_allgather_kernel(PeerTable params, int W, int my_rank, long long lo,
     o.x = pack_bf16x2(w[0], w[1]); o.y = pack_bf16x2(w[2], w[3]);
     o.z = pack_bf16x2(w[4], w[5]); o.w = pack_bf16x2(w[6], w[7]);
     for (int r = 0; r < W_store; ++r)      // the all-gather: every rank receives the updated slice
-      *reinterpret_cast<uint4*>(static_cast<bf16*>(params.ptr[(my_rank + r) % W]) + lo + e) = o;
+      *reinterpret_cast<uint4*>(static_cast<bf16*>(params.ptr[(my_rank + r) % W]) + ge) = o;
   }
 }
 
@@ -488,7 +552,39 @@ int cb_adamw_shard_allgather(const unsigned long long* params, int W, int my_ran
   cb::PeerTable t;
   if (fill_table(&t, params, W) || lo % 8 != 0 || hi % 8 != 0 || hi < lo) return -1;
   cb::adamw_shard_allgather_kernel<<<cb_comm_grid(), cb::COMM_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
-      t, W, my_rank, lo, hi, reduced, m, v, master, chunk_group, hyper, gathered, max_norm, norm_out, W, status);
+      t, W, my_rank, lo, hi, reduced, m, v, master, chunk_group, hyper, gathered, max_norm, norm_out, W, nullptr, status);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// One bucket of the overlapped reduce-scatter: reduced[0 .. hi - lo) = mean over ranks of grads[r][lo .. hi),
+// partials[0 .. grid) = per-block sums of squares.  `grid` blocks of 128 threads (1..1024).
+int cb_rs_bucket(const unsigned long long* grads, int W, long long lo, long long hi, float* reduced, float* partials,
+                 int grid, int* status, void* stream) {
+  cb::PeerTable t;
+  if (fill_table(&t, grads, W) || lo % 8 != 0 || hi % 8 != 0 || hi < lo || grid < 1 || grid > 1024) return -1;
+  cb::rs_bucket_kernel<<<grid, cb::RSB_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(t, W, lo, hi, reduced, partials,
+                                                                                         status);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// payload[0] = sum(partials[0 .. n)), payload[1..3] = 0 (single block, fixed order).
+int cb_sum_partials(const float* partials, int n, float* payload, void* stream) {
+  if (n < 1) return -1;
+  cb::sum_partials_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(partials, n, payload);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// AdamW + all-gather for the bucketed layout: this rank's slice has shard_n elements (a multiple of 1024) made of
+// one piece per bucket; chunk_off[c] (device, shard_n / 1024 entries) is the offset of chunk c in the flat buffer.
+int cb_adamw_shard_allgather_table(const unsigned long long* params, int W, int my_rank, long long shard_n,
+                                   const long long* chunk_off, const float* reduced, float* m, float* v, float* master,
+                                   const unsigned char* chunk_group, const float* hyper, const float* gathered,
+                                   float max_norm, float* norm_out, int* status, void* stream) {
+  cb::PeerTable t;
+  if (fill_table(&t, params, W) || shard_n <= 0 || shard_n % 1024 != 0 || chunk_off == nullptr) return -1;
+  cb::adamw_shard_allgather_kernel<<<cb_comm_grid(), cb::COMM_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
+      t, W, my_rank, 0, shard_n, reduced, m, v, master, chunk_group, hyper, gathered, max_norm, norm_out, W, chunk_off,
+      status);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -503,7 +599,7 @@ int cb_adamw_shard_local(void* shard, int W, long long n, const float* reduced, 
   for (int i = 0; i < cb::MAX_RANKS; ++i) t.ptr[i] = nullptr;
   t.ptr[0] = shard;
   cb::adamw_shard_allgather_kernel<<<cb_comm_grid(), cb::COMM_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
-      t, W, 0, 0, n, reduced, m, v, master, chunk_group, hyper, gathered, max_norm, norm_out, 1, status);
+      t, W, 0, 0, n, reduced, m, v, master, chunk_group, hyper, gathered, max_norm, norm_out, 1, nullptr, status);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -134,7 +134,7 @@ rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ h, cons
                    const float* __restrict__ rstd_in, const bf16* __restrict__ dres_in, bf16* __restrict__ dx,
                    float* __restrict__ dw_part, int M, int N, float offset) {
   __shared__ float sred[EW_THREADS / 32];
-  extern __shared__ float sdw[];  // [N] block accumulator, used when several row groups share a block
+  extern __shared__ float sdw[];  // [RPB, N] per-group accumulators, used when several row groups share a block
   constexpr int RPB = EW_THREADS / TPR;
   const int group = threadIdx.x / TPR;
   const int t = threadIdx.x % TPR;
@@ -197,19 +197,26 @@ rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ h, cons
       }
     }
   }
-  // block-level reduction of dw over the row groups, then one partial row per block
+  // block-level reduction of dw over the row groups, then one partial row per block: every group parks its
+  // accumulators in its own [N] row of shared memory and the block sums the RPB rows column by column
+  // (fixed order, no atomics)
   if (RPB > 1) {
-    for (int i = threadIdx.x; i < N; i += EW_THREADS) sdw[i] = 0.f;
-    __syncthreads();
+    float* mine = sdw + static_cast<size_t>(group) * N;
 #pragma unroll
     for (int i = 0; i < VPL; ++i) {
       const int v = t + i * TPR;
-      if (v < nvec)
-#pragma unroll
-        for (int j = 0; j < 8; ++j) atomicAdd(&sdw[v * 8 + j], dwacc[i][j]);
+      if (v < nvec) {
+        reinterpret_cast<float4*>(mine + v * 8)[0] = make_float4(dwacc[i][0], dwacc[i][1], dwacc[i][2], dwacc[i][3]);
+        reinterpret_cast<float4*>(mine + v * 8)[1] = make_float4(dwacc[i][4], dwacc[i][5], dwacc[i][6], dwacc[i][7]);
+      }
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < N; i += EW_THREADS) dw_part[static_cast<long long>(blockIdx.x) * N + i] = sdw[i];
+    for (int i = threadIdx.x; i < N; i += EW_THREADS) {
+      float a = 0.f;
+#pragma unroll
+      for (int r = 0; r < RPB; ++r) a += sdw[static_cast<size_t>(r) * N + i];
+      dw_part[static_cast<long long>(blockIdx.x) * N + i] = a;
+    }
   } else {
 #pragma unroll
     for (int i = 0; i < VPL; ++i) {
@@ -609,7 +616,7 @@ int cb_rmsnorm_bwd(const void* dy, const void* h, const void* w, const float* rs
   const cb::bf16* rp = static_cast<const cb::bf16*>(dres_in);
   cb::bf16* dxp = static_cast<cb::bf16*>(dx);
   const int grid = cb_rmsnorm_bwd_blocks(M, N);
-  const size_t smem = static_cast<size_t>(N) * sizeof(float);
+  const size_t smem = tpr == 256 ? 0 : static_cast<size_t>(cb::EW_THREADS / tpr) * N * sizeof(float);   // <= 32 KB
   if (tpr == 32) cb::rmsnorm_bwd_kernel<32, 4><<<grid, cb::EW_THREADS, smem, s>>>(dyp, hp, wp, rstd, rp, dxp, dw_part, M, N, offset);
   else if (tpr == 128) cb::rmsnorm_bwd_kernel<128, 4><<<grid, cb::EW_THREADS, smem, s>>>(dyp, hp, wp, rstd, rp, dxp, dw_part, M, N, offset);
   else cb::rmsnorm_bwd_kernel<256, 4><<<grid, cb::EW_THREADS, smem, s>>>(dyp, hp, wp, rstd, rp, dxp, dw_part, M, N, offset);
@@ -773,7 +780,7 @@ int cb_rmsnorm_bwd_noalloc(const void* dy, const void* h, const void* w, const f
   const cb::bf16* wp = static_cast<const cb::bf16*>(w);
   const cb::bf16* rp = static_cast<const cb::bf16*>(dres_in);
   cb::bf16* dxp = static_cast<cb::bf16*>(dx);
-  const size_t smem = static_cast<size_t>(N) * sizeof(float);
+  const size_t smem = tpr == 256 ? 0 : static_cast<size_t>(cb::EW_THREADS / tpr) * N * sizeof(float);
   // every block writes all N entries of its own partial row before the reduction reads them, so
   // nothing left in the array by an earlier call can leak into this one
   if (tpr == 32) cb::rmsnorm_bwd_kernel<32, 4><<<grid, cb::EW_THREADS, smem, s>>>(dyp, hp, wp, rstd, rp, dxp, part, M, N, offset);

@@ -335,7 +335,8 @@ def create_packed_dataloader(dataset: Sequence[Dict[str, Any]], batch_size: int 
     """Tokenised samples → packed fixed-length rows → micro-batches of ``batch_size`` rows."""
     if not use_packing:
         coll = DataCollator(pad_token_id, max_length=max_length)
-        idx = list(range(len(dataset)))[rank::world_size]
+        # every rank gets the same number of samples (a rank with one batch more would start a step alone)
+        idx = list(range(len(dataset)))[rank::world_size][: len(dataset) // max(1, world_size)]
         sub = [dataset[i] for i in idx]
         return DataLoader(sub, batch_size=batch_size, shuffle=shuffle, collate_fn=coll, drop_last=True)
     packer = FixedShapeSequencePacker(max_seq_length=max_length, pad_token_id=pad_token_id, strategy=strategy,

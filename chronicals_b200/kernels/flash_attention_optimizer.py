@@ -223,6 +223,82 @@ def hadamard_transform(x: torch.Tensor) -> torch.Tensor:
     return (y / math.sqrt(n)).reshape(x.shape).to(x.dtype)
 
 
+_HADAMARD: Dict[Tuple[int, str], torch.Tensor] = {}
+
+
+def get_hadamard_matrix(n: int, device=None) -> torch.Tensor:
+    """Orthonormal ``n × n`` Hadamard matrix (Sylvester construction, ``n`` a power of two), cached per device
+    (reference flash_attention_optimizer.py:1035-1055)."""
+    if n < 1 or n & (n - 1):
+        raise ValueError(f"n must be a power of two, got {n}")
+    key = (n, str(device))
+    if key not in _HADAMARD:
+        h = torch.ones(1, 1, device=device)
+        core = torch.tensor([[1.0, 1.0], [1.0, -1.0]], device=device)
+        while h.shape[0] < n:
+            h = torch.kron(core, h)
+        _HADAMARD[key] = h / math.sqrt(n)
+    return _HADAMARD[key]
+
+
+def apply_hadamard_transform(x: torch.Tensor, normalize: bool = True) -> torch.Tensor:
+    """Walsh–Hadamard transform of the last dimension, zero-padded to the next power of two and cut back
+    (reference :1058-1115; the butterfly here is vectorised instead of looping over element pairs)."""
+    n = x.shape[-1]
+    m = 1 << max(0, (n - 1).bit_length())
+    xp = torch.nn.functional.pad(x, (0, m - n)) if m != n else x
+    y = hadamard_transform(xp)                       # orthonormal
+    if not normalize:
+        y = y * math.sqrt(m)
+    return y[..., :n]
+
+
+def apply_inverse_hadamard_transform(x: torch.Tensor) -> torch.Tensor:
+    """The orthonormal transform is its own inverse (exact when the last dimension is a power of two)."""
+    return apply_hadamard_transform(x, normalize=True)
+
+
+def get_fp8_max(format: str) -> float:
+    return {"e4m3": 448.0, "e5m2": 57344.0}[format.lower()]
+
+
+def compute_arithmetic_intensity(seq_len: int, head_dim: int, num_heads: int, batch_size: int = 1) -> Dict[str, float]:
+    """FLOPs per byte of attention with and without the materialised score matrix, against the ridge points of
+    A100 / H100 (as the reference reports, :455-502) and of B200 (measured bf16 GEMM rate over measured copy rate)."""
+    pairs = batch_size * num_heads * seq_len * seq_len
+    flops = 4 * pairs * head_dim + 5 * pairs
+    io = 4 * batch_size * seq_len * num_heads * head_dim * 2            # Q, K, V in, O out (bf16)
+    standard = io + pairs * 4
+    ridge_b200 = 1380.0e12 / 6.5e12
+    return {"standard_attention_ai": flops / standard, "flash_attention_ai": flops / io,
+            "ridge_point_a100": 153, "ridge_point_h100": 295, "ridge_point_b200": ridge_b200,
+            "is_memory_bound_standard": flops / standard < ridge_b200, "is_memory_bound_flash": flops / io < ridge_b200,
+            "memory_reduction_factor": standard / io}
+
+
+def estimate_tokens_per_second(num_params: int, batch_size: int = 1, seq_len: int = 1, gpu_tflops: float = 2250.0,
+                               mfu: float = 0.40) -> float:
+    """``peak · MFU / (6 · N)`` tokens per second (reference :505-542; the default peak here is B200 dense bf16)."""
+    return gpu_tflops * 1e12 * mfu / (6.0 * num_params)
+
+
+@dataclass
+class FlashAttnVarlenOutput:
+    """Output of a varlen attention call: ``[total_tokens, heads, head_dim]`` plus the per-row log-sum-exp."""
+    output: torch.Tensor
+    softmax_lse: Optional[torch.Tensor] = None
+
+
+@dataclass
+class OptimizationResult:
+    """What :func:`optimize_model_for_speed` did to a model (reference :2038-2045)."""
+    model: nn.Module
+    config: "FlashAttentionConfig"
+    is_compiled: bool = False
+    estimated_tokens_per_sec: float = 0.0
+    optimizations_applied: List[str] = field(default_factory=list)
+
+
 def quantize_to_fp8_block(x: torch.Tensor, config: Optional[FP8BlockQuantConfig] = None):
     cfg = config or FP8BlockQuantConfig()
     if cfg.use_hadamard:

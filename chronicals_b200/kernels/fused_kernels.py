@@ -61,6 +61,17 @@ def swiglu_pytorch(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return ref.swiglu(gate, up)
 
 
+def fused_swiglu_pytorch(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """Plain-PyTorch ``silu(gate) * up`` (the reference's fallback, triton_kernels.py:2115-2120)."""
+    return torch.nn.functional.silu(gate) * up
+
+
+def swiglu_with_grad(x: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+    """``gate * silu(x)`` with autograd through the fused forward / backward kernels (reference
+    triton_kernels.py:1217-1240: the FIRST argument goes through the activation)."""
+    return fused_swiglu(x, gate)
+
+
 def fused_geglu(gate: torch.Tensor, up: Optional[torch.Tensor] = None) -> torch.Tensor:
     if up is None:
         return ops.geglu(gate)
@@ -141,6 +152,19 @@ def fused_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, position_i
     return ref.apply_rope(x, cos, sin, position_ids, interleaved)
 
 
+def fused_rope_pytorch(q: torch.Tensor, k: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor
+                       ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Split-half rotation of ``q`` / ``k`` (``[batch, seq, heads, head_dim]``) with ``[seq, head_dim / 2]`` tables,
+    written with elementary tensor operations (the reference's fallback, triton_kernels.py:2123-2160)."""
+    S, d = q.shape[1], q.shape[-1]
+    c = torch.cat((cos[:S], cos[:S]), dim=-1)[None, :, None, :].to(q.dtype)
+    s = torch.cat((sin[:S], sin[:S]), dim=-1)[None, :, None, :].to(q.dtype)
+
+    def rot(x):
+        return torch.cat((-x[..., d // 2:], x[..., : d // 2]), dim=-1)
+    return q * c + rot(q) * s, k * c + rot(k) * s
+
+
 def rope_pytorch(q, k, cos, sin, position_ids=None):
     return fused_rope(q, cos, sin, position_ids), fused_rope(k, cos, sin, position_ids)
 
@@ -164,6 +188,22 @@ def fused_cross_entropy(*args, **kwargs) -> torch.Tensor:
 
 fused_cross_entropy_triton = fused_cross_entropy
 liger_cross_entropy = fused_cross_entropy
+
+
+def fused_cross_entropy_pytorch(logits: torch.Tensor, labels: torch.Tensor, label_smoothing: float = 0.0,
+                                z_loss_weight: float = 1e-4, ignore_index: int = -100
+                                ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``(loss, d loss / d logits)`` from ``torch.nn.functional`` only: mean cross-entropy over the valid labels
+    plus ``z_loss_weight * mean(logsumexp²)`` over ALL rows, as the reference's fallback computes it
+    (triton_kernels.py:2070-2100)."""
+    lg = logits.detach().float().requires_grad_(True)
+    with torch.enable_grad():
+        flat = lg.reshape(-1, lg.shape[-1])
+        loss = torch.nn.functional.cross_entropy(flat, labels.reshape(-1), ignore_index=ignore_index,
+                                                 label_smoothing=label_smoothing)
+        loss = loss + z_loss_weight * torch.logsumexp(flat, dim=-1).pow(2).mean()
+        (g,) = torch.autograd.grad(loss, (lg,))
+    return loss.detach(), g.to(logits.dtype)
 
 
 def cross_entropy_pytorch(logits, targets, ignore_index=-100, label_smoothing=0.0, z_loss_weight=0.0):
@@ -422,6 +462,15 @@ def liger_cross_entropy_forward(logits: torch.Tensor, labels: torch.Tensor, igno
         loss = ops.cross_entropy_logits(lg, labels, ignore_index, label_smoothing, z_loss_weight, "mean")
         (g,) = torch.autograd.grad(loss, (lg,))
     return loss.detach(), g
+
+
+def liger_cross_entropy_backward(logits: torch.Tensor, grad_out: torch.Tensor) -> torch.Tensor:
+    """Scale the gradient that the forward pass left in ``logits`` by the upstream gradient, in place
+    (reference triton_kernels.py:3070-3090); a unit upstream gradient is a no-op and is detected on the device
+    side-effect free, without reading it back."""
+    if grad_out.numel() == 1:
+        return logits.mul_(grad_out.reshape(()).to(logits.dtype))
+    return logits.mul_(grad_out.to(logits.dtype).reshape(-1, *([1] * (logits.dim() - 1))))
 
 
 class LigerCrossEntropyFunction(torch.autograd.Function):

@@ -65,6 +65,19 @@ class FusedLoRALinearFunction(torch.autograd.Function):
         return dx.view(ctx.shape), None, dA, dB, db, None
 
 
+def fused_lora_linear_with_grad(x: torch.Tensor, W: torch.Tensor, A: torch.Tensor, B: torch.Tensor,
+                                bias: Optional[torch.Tensor] = None, lora_alpha: float = 1.0, lora_dropout: float = 0.0,
+                                training: bool = True) -> torch.Tensor:
+    """``x Wᵀ + lora_alpha · (dropout(x) Aᵀ) Bᵀ + bias`` with gradients for ``x``, ``A``, ``B`` and ``bias`` and a
+    frozen ``W`` (reference fused_lora_kernels.py:775-789, where ``lora_alpha`` is the final scaling factor).
+    Dropout, when active, is applied to the adapter branch's input outside the fused function."""
+    if training and lora_dropout > 0.0:
+        base = ops.linear(x, W, bias)
+        h = ops.linear(torch.nn.functional.dropout(x, lora_dropout, True), A)
+        return base + lora_alpha * ops.linear(h, B)
+    return FusedLoRALinearFunction.apply(x, W, A, B, bias, lora_alpha)
+
+
 def lora_linear_pytorch(x, W, A, B, bias=None, lora_alpha: float = 16.0, lora_dropout: float = 0.0,
                         training: bool = True) -> torch.Tensor:
     xd = F.dropout(x, lora_dropout, training) if lora_dropout > 0 else x
@@ -159,5 +172,5 @@ def benchmark_lora(tokens: int = 8192, in_features: int = 896, out_features: int
     return res
 
 
-__all__ = ["fused_lora_down_dropout", "fused_lora_linear", "lora_linear_pytorch", "FusedLoRALinearFunction", "FusedLoRALinear",
+__all__ = ["fused_lora_down_dropout", "fused_lora_linear", "fused_lora_linear_with_grad", "lora_linear_pytorch", "FusedLoRALinearFunction", "FusedLoRALinear",
            "FusedLoRAAdapter", "apply_lora_to_model", "get_lora_params", "count_lora_params", "benchmark_lora"]

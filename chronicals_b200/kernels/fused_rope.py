@@ -30,6 +30,50 @@ def fused_q_rope_inplace(q: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
     return fused_rope(q, cos, sin, position_ids, interleaved)
 
 
+def fused_qk_rope_inplace(q: torch.Tensor, k: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
+                          position_ids: Optional[torch.Tensor] = None, interleaved: bool = True,
+                          long_context: Optional[bool] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Rotate ``q`` and ``k`` (``[batch, seq, heads, head_dim]``) and write the result back into the same
+    tensors (reference fused_rope.py:474-571, whose default pairing is interleaved).  ``long_context`` selected
+    64-bit indexing there; the kernel here always indexes with 64-bit offsets."""
+    with torch.no_grad():
+        rq, rk = fused_qk_rope(q, k, cos, sin, position_ids, interleaved)
+        if rq.data_ptr() != q.data_ptr():
+            q.copy_(rq)
+        if rk.data_ptr() != k.data_ptr():
+            k.copy_(rk)
+    return q, k
+
+
+def fused_qk_rope_inplace_backward(dq: torch.Tensor, dk: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
+                                   position_ids: Optional[torch.Tensor] = None, interleaved: bool = True,
+                                   long_context: Optional[bool] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Gradient of the in-place rotation: the rotation by the negated angle, again in place (reference :574-650)."""
+    return fused_qk_rope_inplace(dq, dk, cos, -sin, position_ids, interleaved, long_context)
+
+
+def precompute_rope_cache_extended(max_seq_len: int, head_dim: int, base: float = 10000.0, scaling_factor: float = 1.0,
+                                   low_freq_factor: float = 1.0, high_freq_factor: float = 4.0,
+                                   original_max_seq: int = 8192, device="cpu",
+                                   dtype: torch.dtype = torch.float32) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``[max_seq_len, head_dim / 2]`` cos / sin tables with Llama-3 style frequency interpolation: wavelengths
+    longer than ``original_max_seq / low_freq_factor`` are stretched by ``scaling_factor``, those shorter than
+    ``original_max_seq / high_freq_factor`` are kept, the band between is blended linearly in wavelength
+    (reference :957-1013, which blends in wavelength rather than in rotations per context as HuggingFace does)."""
+    import math
+    half = head_dim // 2
+    inv = 1.0 / (base ** (torch.arange(0, half, device=device, dtype=torch.float32) / half))
+    lo_len, hi_len = original_max_seq / low_freq_factor, original_max_seq / high_freq_factor
+    wavelen = 2 * math.pi / inv
+    if lo_len == hi_len:
+        smooth = (wavelen > lo_len).float()
+    else:
+        smooth = ((wavelen - hi_len) / (lo_len - hi_len)).clamp(0.0, 1.0)
+    inv = inv * (1 - smooth) + inv / scaling_factor * smooth
+    ang = torch.outer(torch.arange(max_seq_len, device=device, dtype=torch.float32), inv)
+    return ang.cos().to(dtype), ang.sin().to(dtype)
+
+
 def positions_from_cu_seqlens(cu_seqlens: torch.Tensor, total_tokens: int) -> torch.Tensor:
     """Per-token position inside its document (binary search in ``cu_seqlens``; padding → 0)."""
     from ..models.decoder import _positions_from_cu
@@ -86,6 +130,7 @@ def benchmark_rope(batch: int = 8, seq: int = 1024, hq: int = 14, hk: int = 2, d
 
 from .fused_kernels import FusedQKRoPEFunction  # noqa: E402
 
-__all__ = ["fused_qk_rope", "fused_q_rope_inplace", "fused_qk_rope_variable_length", "precompute_rope_cache",
+__all__ = ["fused_qk_rope", "fused_q_rope_inplace", "fused_qk_rope_inplace", "fused_qk_rope_inplace_backward",
+           "precompute_rope_cache_extended", "fused_qk_rope_variable_length", "precompute_rope_cache",
            "precompute_rope_cache_llama3", "FusedRotaryEmbedding", "positions_from_cu_seqlens", "benchmark_rope",
            "FusedQKRoPEFunction"]

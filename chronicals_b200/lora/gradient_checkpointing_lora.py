@@ -106,3 +106,27 @@ def estimate_checkpointing_savings(num_layers: int, activation_gb_per_layer: flo
     kept = (num_layers - k) * activation_gb_per_layer
     return {"checkpointed_layers": float(k), "full_gb": full, "with_checkpointing_gb": kept,
             "saved_gb": full - kept, "recompute_overhead": k / max(1, num_layers) / 3.0}
+
+
+class SelectiveCheckpoint:
+    """Callable that runs ``function(*args, **kwargs)`` under activation checkpointing according to a
+    :class:`LoRACheckpointConfig` (reference gradient_checkpointing_lora.py:149-300): ``standard`` and ``lora_fa``
+    recompute the block in backward, ``unsloth`` additionally parks the saved inputs in pinned host memory.
+    With ``enabled=False`` the function is simply called."""
+
+    def __init__(self, config: Optional[LoRACheckpointConfig] = None, enabled: bool = True):
+        self.config = config or LoRACheckpointConfig()
+        self.enabled = enabled
+        self._offload = None
+
+    def __call__(self, function, *args, use_reentrant: Optional[bool] = None, **kwargs):
+        if not self.enabled:
+            return function(*args, **kwargs)
+        reentrant = self.config.use_reentrant if use_reentrant is None else use_reentrant
+        if self.config.offload:
+            if self._offload is None:
+                from ..training.async_activation_offload import CheckpointWithOffload
+                self._offload = CheckpointWithOffload(use_reentrant=reentrant)
+            return self._offload(function, *args, **kwargs)
+        from torch.utils.checkpoint import checkpoint
+        return checkpoint(function, *args, use_reentrant=reentrant, **kwargs)

@@ -10,6 +10,7 @@ On a CUDA device the kernel library is mandatory; a missing library raises.
 from __future__ import annotations
 
 import math
+import weakref
 from typing import Optional, Tuple
 
 import torch
@@ -127,19 +128,32 @@ def _sm_count(device: torch.device) -> int:
     return _SM_COUNT[idx]
 
 
-def wgrad(dy2: torch.Tensor, x2: torch.Tensor) -> torch.Tensor:
+def wgrad(dy2: torch.Tensor, x2: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``dW = dYᵀ X`` (``[out, in]``) of a linear layer.  A small weight with many tokens gives fewer output
     tiles than half the SMs and a long inner dimension (QKV and attention-output projections of a 0.5B model:
     63 and 49 tiles of 128 × 128 over 8192 tokens), so the token range is split across CTAs, the partial tiles
-    are added in fp32 by TMA reduce and the sum is rounded once; everything else is one bf16-output GEMM."""
+    are added in fp32 by TMA reduce and the sum is rounded once; everything else is one bf16-output GEMM.
+    ``out`` (bf16 ``[out, in]``, contiguous) receives the result when given."""
     n_out, n_in, T = dy2.shape[1], x2.shape[1], dy2.shape[0]
     if not _fast(dy2, x2):
-        return dy2.t() @ x2
+        r = dy2.t() @ x2
+        return r if out is None else out.copy_(r)
     if T >= 2048 and _gemm_ok(dy2) and _gemm_ok(x2):
         tiles = ((n_out + 127) // 128) * ((n_in + 127) // 128)
         if 2 * tiles <= _sm_count(dy2.device):
-            return gemm_splitk(dy2, x2, a_mn=True, b_mn=True).to(dy2.dtype)
-    return gemm(dy2, x2, a_mn=True, b_mn=True)
+            r = gemm_splitk(dy2, x2, a_mn=True, b_mn=True)
+            return r.to(dy2.dtype) if out is None else out.copy_(r)
+    return gemm(dy2, x2, a_mn=True, b_mn=True, out=out)
+
+
+def grad_destination(param: torch.Tensor) -> Optional[torch.Tensor]:
+    """Where a weight-gradient kernel may write its result directly, or None.  An optimizer that keeps all
+    gradients in one flat buffer (``parallel.zero.ShardedFusedAdamW``) attaches ``_cb_grad_out`` to its
+    parameters: a callable that returns a fresh view of the parameter's slot while the slot holds nothing of the
+    current step yet.  The backward pass then returns that view as the gradient, autograd adopts it without a
+    copy, and no separate gradient tensor is ever allocated."""
+    fn = getattr(param, "_cb_grad_out", None)
+    return fn() if fn is not None else None
 
 
 class _LinearFn(torch.autograd.Function):
@@ -151,6 +165,9 @@ class _LinearFn(torch.autograd.Function):
         ctx.save_for_backward(x2, w)
         ctx.has_bias = bias is not None
         ctx.has_res = res2 is not None
+        # saved tensors come back as new Python objects; the parameter object itself carries the optimizer's
+        # gradient destination
+        ctx.weight_ref = weakref.ref(w) if hasattr(w, "_cb_grad_out") else None
         return y
 
     @staticmethod
@@ -163,7 +180,7 @@ class _LinearFn(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = gemm(dy2, w, b_mn=True)                             # dX = dY @ W
         if ctx.needs_input_grad[1]:
-            dw = wgrad(dy2, x2)                                      # dW = dY^T @ X
+            dw = wgrad(dy2, x2, out=grad_destination(ctx.weight_ref()) if ctx.weight_ref is not None else None)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = colsum(dy2)
         dres = dy2 if ctx.has_res else None

@@ -73,6 +73,47 @@ class FusedAdamW(torch.optim.Optimizer):
         state_dict = dict(state_dict)
         self.step_count = int(state_dict.pop("step_count", 0))
         super().load_state_dict(state_dict)
+        # torch casts every floating-point state tensor to the parameter dtype on load, which would round the fp32
+        # moments and master copy of bf16 parameters to bf16 (and halve the buffers the kernels index as fp32):
+        # put the saved tensors back unchanged
+        saved = state_dict["state"]
+        ids = [i for g in state_dict["param_groups"] for i in g["params"]]
+        params = [p for g in self.param_groups for p in g["params"]]
+        for pid, p in zip(ids, params):
+            src = saved.get(pid)
+            if src is None:
+                continue
+            for name in ("exp_avg", "exp_avg_sq", "master"):
+                t = src.get(name)
+                if torch.is_tensor(t):
+                    self.state[p][name] = t.detach().to(device=p.device, dtype=torch.float32).clone()
+        self._tables.clear()
+
+    def _trainable(self) -> List[torch.Tensor]:
+        return [p for g in self.param_groups for p in g["params"] if p.requires_grad]
+
+    def consolidated_state(self) -> Dict[str, Any]:
+        """World-size-independent form of the state: one flat fp32 tensor per parameter, in parameter order
+        (the exchange format between this optimizer and the sharded ones)."""
+        out: Dict[str, Any] = {"step_count": self.step_count, "exp_avg": [], "exp_avg_sq": [], "master": None,
+                               "param_groups": [{k: v for k, v in g.items() if k != "params"} for g in self.param_groups]}
+        for p in self._trainable():
+            st = self._init_state(p)
+            out["exp_avg"].append(st["exp_avg"].detach().reshape(-1).float().cpu())
+            out["exp_avg_sq"].append(st["exp_avg_sq"].detach().reshape(-1).float().cpu())
+        return out
+
+    def load_consolidated(self, cons: Dict[str, Any]) -> None:
+        self.step_count = int(cons["step_count"])
+        masters = cons.get("master")
+        for i, p in enumerate(self._trainable()):
+            st = self._init_state(p)
+            st["exp_avg"].copy_(cons["exp_avg"][i].view(p.shape))
+            st["exp_avg_sq"].copy_(cons["exp_avg_sq"][i].view(p.shape))
+            if masters is not None and "master" in st:
+                st["master"].copy_(masters[i].view(p.shape))
+        for g, saved in zip(self.param_groups, cons.get("param_groups") or []):
+            g.update({k: v for k, v in saved.items() if k in ("lr", "weight_decay", "betas", "eps")})
         self._tables.clear()
 
     # ------------------------------------------------------------------------------------------ CUDA path
@@ -96,9 +137,14 @@ class FusedAdamW(torch.optim.Optimizer):
         for n in numel:
             starts.append(starts[-1] + (n + chunk - 1) // chunk)
         has_master = any("master" in s for s in sts)
+        for p, st in zip(plist, sts):
+            for name in ("exp_avg", "exp_avg_sq", "master"):
+                t = st.get(name)
+                if t is not None and (t.dtype != torch.float32 or t.numel() != p.numel() or not t.is_contiguous()):
+                    raise RuntimeError(f"FusedAdamW state '{name}' must be contiguous float32 with {p.numel()} elements, "
+                                       f"got {t.dtype} x {t.numel()}")
         tab = {
             "params": plist,
-            "grads": [p.grad for p in plist],
             "p": ptrs(plist), "g": ptrs([p.grad for p in plist]),
             "m": ptrs([s["exp_avg"] for s in sts]), "v": ptrs([s["exp_avg_sq"] for s in sts]),
             "master": ptrs([s.get("master") for s in sts]) if has_master else None,
@@ -142,8 +188,17 @@ class FusedAdamW(torch.optim.Optimizer):
     def _step_cuda(self, key, plist, groups) -> None:
         L = _ext.lib()
         tab = self._tables.get(key)
-        if tab is None or tab["n"] != len(plist) or tab["grad_ptrs"] != [p.grad.data_ptr() for p in plist]:
+        if tab is None or tab["n"] != len(plist) or any(a is not b for a, b in zip(tab["params"], plist)):
             tab = self._build_table(key, plist, groups)
+        else:
+            gp = [p.grad.data_ptr() for p in plist]
+            if gp != tab["grad_ptrs"]:
+                # gradients were re-allocated (zero_grad(set_to_none=True)): only the pointer array changes.
+                # The table holds no reference to the gradient tensors, so last step's buffers are free by now.
+                host = torch.tensor(gp, dtype=torch.int64).pin_memory()
+                tab["_keep_g"] = host
+                tab["g"].copy_(host, non_blocking=True)
+                tab["grad_ptrs"] = gp
         tab["hyper"] = self._hyper_device(plist[0].device)
         out = self._clip_out.get(key)
         if out is None:

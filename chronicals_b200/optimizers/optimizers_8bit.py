@@ -119,6 +119,26 @@ class AdamW8bit(Optimizer):
                 self._store(st, "exp_avg_sq", v, False)
         return loss
 
+    def load_state_dict(self, state_dict: Dict[str, Any]) -> None:
+        """``torch.optim.Optimizer.load_state_dict`` casts every state tensor to the parameter dtype, which would
+        turn the int8 / uint8 codes and the fp32 block maxima into bf16.  The saved tensors are put back with
+        their own dtypes (on the parameter's device, or on the host for the paged variant)."""
+        super().load_state_dict(state_dict)
+        saved = state_dict["state"]
+        ids = [i for g in state_dict["param_groups"] for i in g["params"]]
+        params = [p for g in self.param_groups for p in g["params"]]
+        for pid, p in zip(ids, params):
+            src = saved.get(pid)
+            if src is None:
+                continue
+            st = self.state[p]
+            for name, val in src.items():
+                if torch.is_tensor(val):
+                    on_host = self.is_paged and val.dtype in (torch.int8, torch.uint8)
+                    st[name] = val.detach().clone().to("cpu" if on_host else p.device)
+                else:
+                    st[name] = val
+
     def state_bytes(self) -> int:
         n = 0
         for st in self.state.values():

@@ -44,6 +44,8 @@ def init_distributed(backend: Optional[str] = None, timeout_s: float = 600.0) ->
 
 def shutdown() -> None:
     if dist.is_available() and dist.is_initialized():
+        from .watchdog import stop_all
+        stop_all()                                 # heartbeat threads write to the store that goes away below
         try:
             dist.barrier()
         except Exception:

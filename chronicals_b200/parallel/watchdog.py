@@ -63,6 +63,18 @@ def _get(store, key: str) -> Optional[bytes]:
         return None
 
 
+_LIVE: "weakref.WeakSet[Heartbeat]" = None  # type: ignore[assignment]
+
+
+def stop_all() -> None:
+    """Stop every running heartbeat thread of this process.  Called before the process group (and with it the
+    store the threads write to) is destroyed: a thread caught inside a store call while the interpreter shuts
+    down would take the whole process with it."""
+    if _LIVE is not None:
+        for hb in list(_LIVE):
+            hb.stop()
+
+
 class Heartbeat:
     def __init__(self, store, rank: int, interval: float = 1.0, prefix: str = "cb/hb", clock: Callable[[], float] = time.time):
         self.store, self.rank, self.interval, self.prefix, self.clock = store, rank, interval, prefix, clock
@@ -88,14 +100,27 @@ class Heartbeat:
                 except Exception:
                     return
 
+        self._stop.clear()
         self._thread = threading.Thread(target=loop, daemon=True)
         self._thread.start()
+        global _LIVE
+        if _LIVE is None:
+            import atexit
+            import weakref
+            _LIVE = weakref.WeakSet()
+            atexit.register(stop_all)
+        _LIVE.add(self)
         return self
+
+    @property
+    def running(self) -> bool:
+        return self._thread is not None and self._thread.is_alive()
 
     def stop(self) -> None:
         self._stop.set()
         if self._thread is not None:
             self._thread.join(timeout=2 * self.interval + 1)
+            self._thread = None
 
 
 class Watchdog:

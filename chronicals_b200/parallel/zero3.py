@@ -310,20 +310,72 @@ class Zero3Engine:
             self._release(u)
         return sd
 
+    def _param_order(self) -> Dict[int, int]:
+        return {id(p): i for i, p in enumerate(p for p in self.model.parameters() if p.requires_grad)}
+
     def state_dict(self) -> Dict[str, Any]:
-        """This rank's optimizer shard."""
-        return {"step_count": self.step_count, "rank": self.rank, "world": self.world,
+        """This rank's optimizer shard.  ``layout`` lists, per unit, (offset in the unit's flat vector, numel,
+        index of the parameter in ``model.parameters()`` order) so that other layouts can re-assemble it."""
+        order = self._param_order()
+        return {"kind": "zero3", "step_count": self.step_count, "rank": self.rank, "world": self.world,
                 "units": [{"name": u.name, "exp_avg": u.exp_avg.cpu(), "exp_avg_sq": u.exp_avg_sq.cpu(),
-                           "shard": u.shard_t.detach().cpu()} for u in self.units]}
+                           "shard": u.shard_t.detach().cpu(),
+                           "layout": [(off, p.numel(), order[id(p)]) for p, off in zip(u.params, u.offsets)]}
+                          for u in self.units]}
+
+    def load_consolidated(self, cons: Dict[str, Any]) -> None:
+        """Load per-parameter state tensors (``model.parameters()`` order) written by any optimizer layout; the
+        weights themselves come from :meth:`load_full_state_dict`."""
+        order = self._param_order()
+        self.step_count = int(cons["step_count"])
+        for u in self.units:
+            for name, dst in (("exp_avg", u.exp_avg), ("exp_avg_sq", u.exp_avg_sq)):
+                flat = torch.zeros(u.n, dtype=torch.float32)
+                for p, off in zip(u.params, u.offsets):
+                    flat[off:off + p.numel()] = cons[name][order[id(p)]].reshape(-1).float()
+                dst.copy_(flat[self.rank * u.shard_n:(self.rank + 1) * u.shard_n])
 
     def load_state_dict(self, sd: Dict[str, Any]) -> None:
         if sd["world"] != self.world:
-            raise ValueError("ZeRO-3 state was written with a different world size; re-shard from a consolidated checkpoint")
+            raise ValueError("ZeRO-3 state was written with a different world size; pass the states of all saved "
+                             "ranks to load_resharded()")
         self.step_count = int(sd["step_count"])
         for u, s in zip(self.units, sd["units"]):
             u.exp_avg.copy_(s["exp_avg"])
             u.exp_avg_sq.copy_(s["exp_avg_sq"])
             u.shard_t.copy_(s["shard"])
+
+    def load_resharded(self, states: List[Dict[str, Any]]) -> None:
+        """Restart at a different number of ranks: ``states`` are the ``state_dict()`` of every rank of the run
+        that wrote the checkpoint.  Each unit's flat vectors are re-assembled in rank order and re-sliced for this
+        world size (the tail padding of a unit depends on the world size and holds zeros)."""
+        states = sorted(states, key=lambda s: s["rank"])
+        if len(states) != states[0]["world"]:
+            raise ValueError(f"need the state of all {states[0]['world']} saved ranks, got {len(states)}")
+        self.step_count = int(states[0]["step_count"])
+        lo = self.rank
+        for ui, u in enumerate(self.units):
+            for name, dst in (("exp_avg", u.exp_avg), ("exp_avg_sq", u.exp_avg_sq), ("shard", u.shard_t)):
+                flat = torch.cat([s["units"][ui][name].reshape(-1) for s in states])
+                if flat.numel() < u.n:
+                    flat = torch.cat((flat, torch.zeros(u.n - flat.numel(), dtype=flat.dtype)))
+                dst.copy_(flat[lo * u.shard_n:(lo + 1) * u.shard_n].to(dst.dtype))
+
+    @torch.no_grad()
+    def load_full_state_dict(self, hf_state: Dict[str, torch.Tensor]) -> None:
+        """Scatter full (HuggingFace-named) tensors into the shards: units are made resident, the model copies
+        the tensors into its parameter views, and every rank keeps its slice."""
+        for u in self.units:
+            self._gather(u, side=False)
+        if self.fused:
+            torch.cuda.synchronize()
+        self.model.load_hf_state_dict(hf_state, strict=False)
+        for u in self.units:
+            u.shard_t.copy_(u.full[self.rank * u.shard_n:(self.rank + 1) * u.shard_n])
+            self._release(u)
+        if self.fused:
+            torch.cuda.synchronize()
+        dist.barrier(group=self.group)
 
 
 class Zero3Optimizer(torch.optim.Optimizer):
@@ -357,3 +409,31 @@ class Zero3Optimizer(torch.optim.Optimizer):
     def load_state_dict(self, sd) -> None:
         self.engine.load_state_dict(sd["zero3"])
         self.param_groups[0]["lr"] = sd.get("lr", self.param_groups[0]["lr"])
+
+    def load_resharded(self, states) -> None:
+        self.engine.load_resharded([s["zero3"] for s in states])
+        self.param_groups[0]["lr"] = states[0].get("lr", self.param_groups[0]["lr"])
+
+    def load_consolidated(self, cons) -> None:
+        self.engine.load_consolidated(cons)
+        groups = cons.get("param_groups") or []
+        if groups and "lr" in groups[0]:
+            self.param_groups[0]["lr"] = groups[0]["lr"]
+
+
+def consolidate_zero3_states(states: List[Dict[str, Any]]) -> Dict[str, Any]:
+    """``Zero3Engine.state_dict()`` of every saved rank → one fp32 tensor per parameter (``model.parameters()``
+    order) for both moments: the exchange format shared with ``FusedAdamW`` and ``ShardedFusedAdamW``."""
+    states = sorted((s.get("zero3", s) for s in states), key=lambda s: s["rank"])
+    if len(states) != states[0]["world"]:
+        raise ValueError(f"need the state of all {states[0]['world']} saved ranks, got {len(states)}")
+    n_params = 1 + max(i for u in states[0]["units"] for _, _, i in u["layout"])
+    out: Dict[str, Any] = {"step_count": states[0]["step_count"], "master": None, "param_groups": None}
+    for name in ("exp_avg", "exp_avg_sq"):
+        vals: List[Optional[torch.Tensor]] = [None] * n_params
+        for ui, u in enumerate(states[0]["units"]):
+            flat = torch.cat([s["units"][ui][name].reshape(-1).float() for s in states])
+            for off, n, idx in u["layout"]:
+                vals[idx] = flat[off:off + n].clone()
+        out[name] = vals
+    return out

@@ -213,3 +213,34 @@ def estimate_offload_savings(activation_gb: float, offload_fraction: float = 0.8
 def should_offload(tensor: torch.Tensor, config: Optional[OffloadConfig] = None) -> bool:
     c = config or OffloadConfig()
     return bool(c.enabled and tensor.is_cuda and tensor.numel() >= c.min_tensor_numel)
+
+
+def estimate_offload_bandwidth(tensor_size_mb: float, pcie_bandwidth_gbps: float = 55.0) -> float:
+    """Milliseconds to move a tensor of ``tensor_size_mb`` MiB one way at ``pcie_bandwidth_gbps`` GB/s
+    (reference async_activation_offload.py:817-833; its default is PCIe 4 x16, a B200 sits on PCIe 5 x16)."""
+    return tensor_size_mb / 1024.0 / pcie_bandwidth_gbps * 1e3
+
+
+def estimate_activation_memory(batch_size: int, seq_len: int, hidden_size: int, intermediate_size: int, num_layers: int,
+                               dtype_bytes: int = 2) -> Dict[str, float]:
+    """Activation footprint (MiB) of a decoder stack without savings, with sqrt(L) checkpointing, and with
+    checkpointing plus host offload of the checkpointed inputs (reference :836-880)."""
+    import math
+    tok = batch_size * seq_len
+    per_layer = tok * dtype_bytes * (hidden_size + intermediate_size + 3 * hidden_size + hidden_size) / 2**20
+    every = max(1, int(math.sqrt(num_layers)))
+    baseline = num_layers * per_layer
+    checkpointed = (num_layers // every + every) * per_layer
+    offload = every * per_layer
+    return {"per_layer_mb": per_layer, "baseline_mb": baseline, "checkpointed_mb": checkpointed, "offload_mb": offload,
+            "checkpoint_every": every, "savings_vs_baseline": baseline / offload,
+            "savings_vs_checkpoint": checkpointed / offload}
+
+
+def create_offload_manager(num_layers: Optional[int] = None, use_checkpointing: bool = True, **offload_kwargs):
+    """``CheckpointWithOffload`` when checkpointing is wanted (and the layer count is known), else a bare
+    ``ActivationOffloadManager``; keyword arguments are ``OffloadConfig`` fields (reference :887-906)."""
+    config = OffloadConfig(**offload_kwargs)
+    if use_checkpointing and num_layers is not None:
+        return CheckpointWithOffload(config)
+    return ActivationOffloadManager(config)

@@ -47,7 +47,8 @@ class TrainerState:
     total_tokens: int = 0
     total_time: float = 0.0
     log_history: List[Dict[str, Any]] = field(default_factory=list)
-    micro_step: int = 0            # micro-batches consumed (the data cursor for resume)
+    micro_step: int = 0            # micro-batches consumed over all epochs
+    micro_in_epoch: int = 0        # micro-batches consumed in the current epoch (the data cursor for resume)
     real_tokens: int = 0           # tokens that carry a label (padding and masked positions excluded)
 
 
@@ -277,15 +278,20 @@ class ChronicalsTrainer:
                 betas=(a.adam_beta1, a.adam_beta2), eps=a.adam_epsilon, weight_decay=a.weight_decay,
                 max_grad_norm=a.max_grad_norm)
             self.use_external_grad_clip = False
-        elif (t == "fused_adamw" and a.use_fused_adamw and self.world_size > 1 and a.parallel.comm_backend == "fused"
-              and not getattr(self, "tp_model", False) and self.device.type == "cuda" and self._fused_comm_possible()):
-            # gradient reduce-scatter, clip, AdamW and parameter all-gather as peer-memory kernels
+        elif (t == "fused_adamw" and a.use_fused_adamw and self.world_size > 1 and not getattr(self, "tp_model", False)
+              and ((a.parallel.comm_backend == "fused" and self.device.type == "cuda" and self._fused_comm_possible())
+                   or (a.parallel.zero_stage == 1 and self.device.type != "cuda"))):
+            # optimizer state sharded over the ranks; on GPUs the gradient reduce-scatter (per bucket, from backward
+            # hooks), clip, AdamW and parameter all-gather are peer-memory kernels, on CPU ranks the same
+            # bookkeeping runs on process-group collectives
             from ..parallel.zero import ShardedFusedAdamW
             self.optimizer = ShardedFusedAdamW([p for p in self.model.parameters() if p.requires_grad],
                                                lr=a.learning_rate, betas=(a.adam_beta1, a.adam_beta2),
                                                eps=a.adam_epsilon, weight_decay=a.weight_decay,
                                                max_grad_norm=a.max_grad_norm,
-                                               wait_budget_us=a.parallel.wait_budget_us)
+                                               wait_budget_us=a.parallel.wait_budget_us,
+                                               bucket_mb=a.parallel.shard_bucket_mb,
+                                               overlap=a.parallel.overlap_grad_reduce, rs_grid=a.parallel.reduce_grid)
             self.use_external_grad_clip = False
             self._sharded_optimizer = True
         elif t == "fused_adamw" and a.use_fused_adamw:
@@ -354,6 +360,8 @@ class ChronicalsTrainer:
     def _backward_and_maybe_step(self, loss: torch.Tensor, do_step: bool) -> None:
         a = self.args
         scaled = loss / a.gradient_accumulation_steps if a.gradient_accumulation_steps > 1 else loss
+        if hasattr(self.optimizer, "begin_micro_step"):
+            self.optimizer.begin_micro_step(last=do_step)     # bucket reduce-scatters start from the last backward only
         scaled.backward()
         if not do_step:
             return
@@ -477,7 +485,7 @@ class ChronicalsTrainer:
         skip_micro = 0
         if resume_from_checkpoint:
             start_epoch = self.resume_from_checkpoint(resume_from_checkpoint)
-            skip_micro = self.state.micro_step
+            skip_micro = int(self.state.micro_in_epoch)       # cursor inside the epoch the checkpoint was taken in
         if self.rank == 0:
             print_chronicals_banner(self.world_size, type(self.model).__name__,
                                     {"params": f"{self.num_params / 1e6:.1f} M", "total steps": self.total_steps,
@@ -485,6 +493,8 @@ class ChronicalsTrainer:
         gc_was = gc.isenabled()
         if a.disable_gc_during_training:
             gc.disable()
+        if self.watchdog is not None and not self.watchdog.heartbeat.running:
+            self.watchdog.start()
         self.model.train()
         if isinstance(self.optimizer, ScheduleFreeAdamW):
             self.optimizer.train_mode()
@@ -507,6 +517,7 @@ class ChronicalsTrainer:
                         print(f"[epoch {epoch}] eval loss {ev:.4f}")
                     self.state.best_loss = min(self.state.best_loss, ev)
                 if a.save_steps and a.save_steps > 0:
+                    self.state.epoch, self.state.micro_in_epoch = epoch + 1, 0     # resume starts the next epoch
                     self.save_checkpoint(f"checkpoint-epoch-{epoch}")
         finally:
             if a.disable_gc_during_training and gc_was:
@@ -517,6 +528,8 @@ class ChronicalsTrainer:
                 except Exception:
                     pass
                 self._trace = None
+            if self.watchdog is not None:
+                self.watchdog.stop()              # no heartbeat thread outlives the loop it guards
         self.state.total_time += time.perf_counter() - t_start
         if a.save_steps is not None and a.save_steps >= 0 and self._get("save_final", True):
             self.save_checkpoint("final")
@@ -534,10 +547,13 @@ class ChronicalsTrainer:
         """Samples (dicts with ``input_ids``) → packed rows → micro-batches."""
         from ..data.data_loader import create_packed_dataloader
         a = self.args
+        # tensor-parallel ranks work on the same tokens (sequence parallelism and the vocabulary-parallel loss
+        # split one batch); only data-parallel ranks read different slices
+        dp_rank, dp_world = (0, 1) if self.tp_model else (self.rank, self.world_size)
         return create_packed_dataloader(dataset, batch_size=a.per_device_train_batch_size,
                                         max_length=a.max_seq_length, strategy=a.packing_strategy,
                                         use_packing=a.use_sequence_packing, seed=a.seed,
-                                        rank=self.rank, world_size=self.world_size)
+                                        rank=dp_rank, world_size=dp_world)
 
     def _train_epoch_fast(self, epoch: int, skip_micro: int = 0) -> float:
         a = self.args
@@ -551,12 +567,14 @@ class ChronicalsTrainer:
             torch.cuda.synchronize(self.device)
         t0 = time.perf_counter()
         micro_in_epoch = 0
+        self.state.micro_in_epoch = skip_micro
         for batch in self.train_dataloader:
             if a.max_steps > 0 and self.state.global_step >= a.max_steps:
                 break
             micro_in_epoch += 1
             if micro_in_epoch <= skip_micro:
                 continue
+            self.state.micro_in_epoch = micro_in_epoch
             do_step = (micro_in_epoch % accum) == 0
             if self.watchdog is not None:
                 try:
@@ -741,7 +759,11 @@ class ChronicalsTrainer:
         return out
 
     def load_checkpoint(self, checkpoint_dir: str, load_optimizer: bool = True) -> Dict[str, Any]:
-        ckpt_io.load_model_weights(self.model, checkpoint_dir, strict=False)
+        if self.zero3 is not None:
+            # parameter storage is released between uses; the engine scatters the full tensors into its shards
+            self.zero3.load_full_state_dict(ckpt_io.read_weights(checkpoint_dir))
+        else:
+            ckpt_io.load_model_weights(self.model, checkpoint_dir, strict=False)
         if os.path.exists(os.path.join(checkpoint_dir, "adapter_model.safetensors")):
             ckpt_io.load_lora_adapter(self.model, checkpoint_dir)
         st = ckpt_io.load_training_state(checkpoint_dir, self.optimizer if load_optimizer else None,

@@ -313,12 +313,55 @@ def replace_swiglu_with_smooth(model: nn.Module) -> int:
 
 
 # ------------------------------------------------------------------------------------------- attention in FP8
-def fp8_flash_attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = True) -> torch.Tensor:
-    """Attention with Q, K, V rounded through per-tensor e4m3 (dense ``[B, H, S, D]``)."""
-    sc = PerTensorDynamicScaler()
-    qd, kd, vd = (sc.dequantize(*sc.quantize(t), dtype=t.dtype) for t in (q, k, v))
-    return torch.nn.functional.scaled_dot_product_attention(qd, kd, vd, is_causal=causal,
-                                                            enable_gqa=qd.shape[1] != kd.shape[1])
+class FP8AttentionConfig:
+    """Options of the FP8 attention path (reference fp8_deepseek.py:1760-1787): which tensors are rounded to e4m3
+    and with which block size.  Scores and softmax always stay in fp32 inside the attention kernel."""
+
+    def __init__(self, use_fp8_qkv: bool = True, use_fp8_output: bool = True, qkv_block_size: int = MX_BLOCK_SIZE,
+                 compute_dtype: torch.dtype = torch.float32, output_dtype: torch.dtype = torch.bfloat16):
+        self.use_fp8_qkv, self.use_fp8_output, self.qkv_block_size = use_fp8_qkv, use_fp8_output, qkv_block_size
+        self.compute_dtype, self.output_dtype = compute_dtype, output_dtype
+
+
+def prepare_fp8_attention_inputs(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
+                                 config: Optional[FP8AttentionConfig] = None):
+    """Q, K, V → block-scaled e4m3 payloads plus their scales (``{"q_scales", "k_scales", "v_scales"}``)."""
+    cfg = config or FP8AttentionConfig()
+    if not cfg.use_fp8_qkv:
+        return query, key, value, {}
+    (q8, qs), (k8, ks), (v8, vs) = (quantize_block_e4m3(t, cfg.qkv_block_size) for t in (query, key, value))
+    return q8, k8, v8, {"q_scales": qs, "k_scales": ks, "v_scales": vs}
+
+
+def fp8_flash_attention_forward(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
+                                config: Optional[FP8AttentionConfig] = None, causal: bool = True,
+                                softmax_scale: Optional[float] = None) -> torch.Tensor:
+    """Attention on operands rounded through block-scaled e4m3 (``[batch, seq, heads, head_dim]`` in and out;
+    grouped-query K / V allowed).  The reference simulates FP8 the same way: quantise, dequantise, run the
+    ordinary attention (fp8_deepseek.py:1826-1910); here the attention itself is this framework's varlen
+    kernel on CUDA bf16 inputs and SDPA elsewhere."""
+    cfg = config or FP8AttentionConfig()
+    q8, k8, v8, sc = prepare_fp8_attention_inputs(query, key, value, cfg)
+    if sc:
+        q, k, v = (dequantize_block(t, sc[n], query.dtype) for t, n in
+                   ((q8, "q_scales"), (k8, "k_scales"), (v8, "v_scales")))
+    else:
+        q, k, v = query, key, value
+    B, S, H, D = q.shape
+    scale = softmax_scale if softmax_scale is not None else D ** -0.5
+    if q.is_cuda and q.dtype == torch.bfloat16 and causal and D in (64, 128):
+        from .. import ops
+        cu = torch.arange(0, (B + 1) * S, S, dtype=torch.int32, device=q.device)
+        out = ops.attention_varlen(q.reshape(B * S, H, D), k.reshape(B * S, -1, D), v.reshape(B * S, -1, D), cu, S,
+                                   softmax_scale=scale).view(B, S, H, D)
+    else:
+        out = torch.nn.functional.scaled_dot_product_attention(
+            q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=causal, scale=scale,
+            enable_gqa=q.shape[2] != k.shape[2]).transpose(1, 2)
+    if cfg.use_fp8_output:
+        o8, os_ = quantize_block_e4m3(out.contiguous(), cfg.qkv_block_size)
+        out = dequantize_block(o8, os_, cfg.output_dtype)
+    return out.to(cfg.output_dtype)
 
 
 # ------------------------------------------------------------------------------------------- trainer wrapper

@@ -23,6 +23,7 @@ def make_args(out):
 def main():
     out = sys.argv[1]
     zero3 = len(sys.argv) > 2 and sys.argv[2] == "zero3"
+    zero1 = len(sys.argv) > 2 and sys.argv[2] == "zero1"
     rank, _, world = init_distributed("gloo")
     cfg = ChronicalsConfig.from_model_name("tiny-qwen2")
     cfg.num_hidden_layers, cfg.vocab_size, cfg.dtype = 2, 2048, "float32"
@@ -36,6 +37,10 @@ def main():
     if zero3:
         a1.parallel.zero_stage = 3
         a1.max_grad_norm = 0.5
+    if zero1:
+        a1.parallel.zero_stage = 1
+        a1.parallel.shard_bucket_mb = 0.25           # several buckets, so bucket completion and slicing are exercised
+        a1.max_grad_norm = 0.5
     tr = ChronicalsTrainer(model, a1, mine)
     st = tr.train()
     trained = tr.zero3.gather_full_state_dict() if zero3 else None
@@ -46,7 +51,7 @@ def main():
         m2 = build_model(cfg, dtype=torch.float32, seed=0)
         a2 = make_args(out + ".single")
         a2.use_distributed = False
-        if zero3:
+        if zero3 or zero1:
             a2.max_grad_norm = 0.5
         t2 = ChronicalsTrainer(m2, a2, full)
         single = [h["loss"] for h in t2.train().log_history if "lr" in h]
@@ -56,7 +61,9 @@ def main():
         else:
             diff = max((p - q).abs().max().item() for p, q in zip(model.parameters(), m2.parameters()))
         with open(out, "w") as f:
-            json.dump({"dp_losses": dp_losses, "single_losses": single, "max_param_diff": diff}, f)
+            json.dump({"dp_losses": dp_losses, "single_losses": single, "max_param_diff": diff,
+                       "optimizer": type(tr.optimizer).__name__,
+                       "buckets": len(getattr(tr.optimizer, "buckets", []))}, f)
     dist.barrier()
     shutdown()
 

@@ -61,6 +61,72 @@ def main():
     # canary words behind every symmetric buffer are intact and the barrier epochs only ever grew
     res["canaries_ok"] = all(b.canary_ok() for b in (o_my.param_buf, o_my.grad_buf, o_my.ctx.pad, ctx.pad))
     res["epochs"] = [int(ctx.epoch_ctr.item()), int(o_my.ctx.epoch_ctr.item())]
+    res["buckets"] = len(o_my.buckets)
+
+    # ---- the same optimizer fed by a backward pass: several buckets, each reduce-scattered on the side stream from
+    # the gradient hooks while the backward pass continues; eager steps, then the step replayed from a CUDA graph
+    torch.manual_seed(1)
+    dims = [(256, 384), (384,), (384, 256), (256,), (512, 256)]
+    ref_q = [torch.nn.Parameter((torch.randn(*s2, device=dev) * 0.1).to(torch.bfloat16)) for s2 in dims]
+    my_q = [torch.nn.Parameter(p.detach().clone()) for p in ref_q]
+    o_ref2 = FusedAdamW(ref_q, lr=1e-2, betas=(0.9, 0.95), weight_decay=0.01, max_grad_norm=1.0)
+    o_my2 = ShardedFusedAdamW(my_q, lr=1e-2, betas=(0.9, 0.95), weight_decay=0.01, max_grad_norm=1.0, bucket_mb=0.1)
+    res["hook_buckets"] = len(o_my2.buckets)
+
+    def loss_fn(ps, x):
+        h = torch.tanh(x @ ps[0] + ps[1]) @ ps[2] + ps[3]
+        return (h @ ps[4].t()).float().pow(2).mean()
+
+    def batches(step):
+        return [torch.randn(64, 256, generator=torch.Generator().manual_seed(1000 * step + r)).to(torch.bfloat16).to(dev)
+                for r in range(world)]
+
+    def ref_step(step):
+        per_rank = []
+        for x in batches(step):
+            for p in ref_q:
+                p.grad = None
+            loss_fn(ref_q, x).backward()
+            per_rank.append([p.grad.float() for p in ref_q])       # each rank contributes its bf16 gradient
+        for i, p in enumerate(ref_q):
+            p.grad = (sum(g[i] for g in per_rank) / world).to(torch.bfloat16)
+        o_ref2.step()
+
+    for step in range(3):
+        ref_step(step)
+        loss_fn(my_q, batches(step)[rank]).backward()
+        o_my2.step()
+    torch.cuda.synchronize()
+    _ext.check_status(dev)
+    res["hook_max_err"] = max((p.float() - q.float()).abs().max().item() for p, q in zip(ref_q, my_q))
+    res["hook_norm"] = [o_ref2.last_grad_norm.item(), o_my2.last_grad_norm.item()]
+    # whole step (backward with hooks, side-stream reduce-scatters, update, all-gather) as one CUDA graph
+    static_x = batches(3)[rank].clone()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        loss_fn(my_q, static_x).backward()                          # warm-up backward that is not followed by a step
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    dist.barrier()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+        loss_fn(my_q, static_x).backward()
+        o_my2.launch_step()
+    for step in range(3, 6):
+        ref_step(step)
+        static_x.copy_(batches(step)[rank])
+        o_my2.prepare_step()
+        graph.replay()
+    torch.cuda.synchronize()
+    _ext.check_status(dev)
+    res["graph_max_err"] = max((p.float() - q.float()).abs().max().item() for p, q in zip(ref_q, my_q))
+    flat2 = torch.cat([q.detach().float().reshape(-1) for q in my_q])
+    lo2, hi2 = flat2.clone(), flat2.clone()
+    dist.all_reduce(lo2, op=dist.ReduceOp.MIN)
+    dist.all_reduce(hi2, op=dist.ReduceOp.MAX)
+    res["hook_ranks_identical"] = bool(torch.equal(lo2, hi2))
+    del graph
 
     # ---- bounded wait: a barrier nobody else joins gives up with an error status instead of hanging
     if os.environ.get("CB_TEST_TIMEOUT", "1") == "1":

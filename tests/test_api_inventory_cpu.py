@@ -84,13 +84,16 @@ INVENTORY = {
     "training.cuda_graph_manager": ["CUDAGraphConfig", "GraphStatistics", "CUDAGraphMemoryPool", "CapturedGraph",
                                     "CUDAGraphManager", "create_cuda_graph_training_step", "cuda_graph_capture"],
     "training.async_activation_offload": ["OffloadConfig", "OffloadStats", "CUDAStreamManager", "PinnedMemoryPool",
-                                          "ActivationOffloadManager", "OffloadActivations", "CheckpointWithOffload"],
+                                          "ActivationOffloadManager", "OffloadActivations", "CheckpointWithOffload",
+                                          "estimate_offload_bandwidth", "estimate_activation_memory",
+                                          "create_offload_manager"],
     "training": ["ChronicalsTrainer", "apply_gradient_checkpointing", "enable_gradient_checkpointing", "enable_cuda_graphs"],
     "utils.fp8_utils": ["FP8Format", "FP8Handler", "FP8Linear", "compute_fp8_memory_savings"],
     "utils.fp8_deepseek": ["FP8Spec", "FP8GradScaler", "FP8GradientAccumulator", "quantize_block_e4m3", "quantize_block_e5m2",
                            "dequantize_block", "AmaxHistory", "FP8LinearFunction", "FP8Linear", "DEFAULT_FP8_EXCLUDE_PATTERNS",
                            "should_convert_to_fp8", "convert_linear_to_fp8", "convert_model_to_fp8", "FP8Context",
-                           "compute_fp8_memory_savings", "apply_fp8_to_huggingface_model"],
+                           "compute_fp8_memory_savings", "apply_fp8_to_huggingface_model", "FP8AttentionConfig",
+                           "prepare_fp8_attention_inputs", "fp8_flash_attention_forward"],
     "utils.profiling_utils": ["GPU_SPECS", "detect_gpu_specs", "TimingBreakdown", "MemorySnapshot", "PerformanceMetrics",
                               "MFUTracker", "ThroughputMonitor", "PerformanceProfiler", "MixedPrecisionManager",
                               "generate_performance_report", "print_performance_report"],
@@ -102,9 +105,23 @@ INVENTORY = {
 }
 
 
+# names added after the first inventory pass (same modules as above)
+INVENTORY_ADDED = {
+    "kernels.flash_attention_optimizer": ["get_hadamard_matrix", "apply_hadamard_transform",
+                                          "apply_inverse_hadamard_transform", "get_fp8_max", "compute_arithmetic_intensity",
+                                          "estimate_tokens_per_second", "FlashAttnVarlenOutput", "OptimizationResult"],
+    "kernels.fused_rope": ["fused_qk_rope_inplace", "fused_qk_rope_inplace_backward", "precompute_rope_cache_extended"],
+    "kernels.fused_kernels": ["swiglu_with_grad", "fused_cross_entropy_pytorch", "fused_swiglu_pytorch",
+                              "fused_rope_pytorch", "liger_cross_entropy_backward"],
+    "kernels.triton_kernels": ["swiglu_with_grad", "fused_cross_entropy_pytorch", "liger_cross_entropy_backward"],
+    "kernels.fused_lora_kernels": ["fused_lora_linear_with_grad"],
+    "lora.gradient_checkpointing_lora": ["SelectiveCheckpoint"],
+}
+
+
 def _missing(root: str):
     out = []
-    for mod, names in INVENTORY.items():
+    for mod, names in list(INVENTORY.items()) + list(INVENTORY_ADDED.items()):
         m = importlib.import_module(root + ("." + mod if mod else ""))
         out += [f"{mod}.{n}" for n in names if not hasattr(m, n)]
     return out

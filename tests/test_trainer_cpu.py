@@ -179,3 +179,59 @@ def test_dp_gloo_matches_single_process(tmp_path, world):
     res = json.load(open(out))
     assert max(abs(a - b) for a, b in zip(res["dp_losses"], res["single_losses"])) < 1e-4
     assert res["max_param_diff"] < 1e-4
+
+
+def test_resume_in_the_middle_of_the_second_epoch_skips_only_that_epochs_batches(tmp_path):
+    """The data cursor of a checkpoint counts micro-batches inside its epoch: resuming from step 5 of a run with
+    3 batches per epoch continues with the third batch of epoch 1, not after a skip of five."""
+    cfg = _tiny_cfg(1)
+    data = _batches(3, cfg.vocab_size)
+    full = ChronicalsTrainer(build_model(cfg, dtype=torch.float32, seed=0),
+                             _args(tmp_path / "a", num_train_epochs=3, save_steps=5, save_total_limit=5), data)
+    full.train()
+    want = [h["loss"] for h in full.state.log_history if "lr" in h]
+    assert len(want) == 9
+    ck = os.path.join(str(tmp_path / "a"), "checkpoint-5")
+    st = json.load(open(os.path.join(ck, "trainer_state.json")))
+    assert st["epoch"] == 1 and st["micro_in_epoch"] == 2 and st["micro_step"] == 5
+    resumed = ChronicalsTrainer(build_model(cfg, dtype=torch.float32, seed=7),
+                                _args(tmp_path / "b", num_train_epochs=3), data)
+    resumed.train(resume_from_checkpoint=ck)
+    got = [h["loss"] for h in resumed.state.log_history if "lr" in h]
+    assert resumed.state.global_step == 9
+    assert len(got) == 9 and max(abs(a - b) for a, b in zip(got[5:], want[5:])) < 1e-6, (got, want)
+
+
+def test_fused_adamw_state_stays_fp32_after_loading_into_bf16_parameters():
+    """``torch.optim.Optimizer.load_state_dict`` casts floating-point state to the parameter dtype; the fused
+    optimizer's moments and master copy must come back as fp32 (the kernel reads them as such)."""
+    from chronicals_b200.optimizers import FusedAdamW
+    from chronicals_b200.optimizers.optimizers_8bit import AdamW8bit
+    p = torch.nn.Parameter(torch.randn(64, 96).to(torch.bfloat16))
+    opt = FusedAdamW([p], lr=1e-2, master_weights=True)
+    p.grad = torch.randn_like(p)
+    opt.step()
+    sd = opt.state_dict()
+    q = torch.nn.Parameter(p.detach().clone())
+    opt2 = FusedAdamW([q], lr=1e-2, master_weights=True)
+    opt2.load_state_dict(sd)
+    st = opt2.state[q]
+    assert st["exp_avg"].dtype == st["exp_avg_sq"].dtype == st["master"].dtype == torch.float32
+    assert torch.equal(st["exp_avg"], opt.state[p]["exp_avg"]) and opt2.step_count == 1
+    # continuing from the loaded state equals continuing the original
+    g = torch.randn_like(p)
+    p.grad, q.grad = g.clone(), g.clone()
+    opt.step()
+    opt2.step()
+    assert torch.equal(p, q)
+    # 8-bit moments keep their integer codes and fp32 block maxima
+    r = torch.nn.Parameter(torch.randn(8192).to(torch.bfloat16))
+    o8 = AdamW8bit([r], lr=1e-2)
+    r.grad = torch.randn_like(r)
+    o8.step()
+    r2 = torch.nn.Parameter(r.detach().clone())
+    o8b = AdamW8bit([r2], lr=1e-2)
+    o8b.load_state_dict(o8.state_dict())
+    s8 = o8b.state[r2]
+    assert s8["exp_avg"].dtype == torch.int8 and s8["exp_avg_sq"].dtype == torch.uint8
+    assert s8["exp_avg_absmax"].dtype == torch.float32 and torch.equal(s8["exp_avg_absmax"], o8.state[r]["exp_avg_absmax"])
