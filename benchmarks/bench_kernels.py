@@ -64,6 +64,7 @@ GEMM_CASES = {
     "gateup_fwd_0.5b": (8192, 9728, 896, 0, 0), "down_fwd_0.5b": (8192, 896, 4864, 0, 0),
     "gateup_dgrad_0.5b": (8192, 896, 9728, 0, 1), "down_dgrad_0.5b": (8192, 4864, 896, 0, 1),
     "gateup_wgrad_0.5b": (9728, 896, 8192, 1, 1), "down_wgrad_0.5b": (896, 4864, 8192, 1, 1),
+    "qkv_dgrad_0.5b": (8192, 896, 1152, 0, 1), "o_dgrad_0.5b": (8192, 896, 896, 0, 1),
     "gateup_fwd_7b": (8192, 37888, 3584, 0, 0), "down_fwd_7b": (8192, 3584, 18944, 0, 0),
     "square_8k": (8192, 8192, 8192, 0, 0),
 }
@@ -85,10 +86,14 @@ def run_gemm(results, peaks, iters, only=None):
         A = a.t() if a_mn else a
         B = b if b_mn else b.t()
         ms_lib = timed(lambda: torch.matmul(A, B, out=out), iters)
+        # the CTA-pair kernel alone, with tiles cut along K (stream-K) and restricted to whole tiles
+        ms_sk = timed(lambda: ops.gemm(a, b, a_mn=bool(a_mn), b_mn=bool(b_mn), out=out, pair_flags=2), iters)
+        ms_whole = timed(lambda: ops.gemm(a, b, a_mn=bool(a_mn), b_mn=bool(b_mn), out=out, pair_flags=1), iters)
         fl = 2.0 * M * N * K
         results.append({"kernel": "gemm_tcgen05", "case": name, "shape": [M, N, K], "ms": ms,
                         "tflops": fl / ms / 1e9, "frac_of_measured_bf16": fl / ms / 1e9 / peaks["bf16_tflops"],
-                        "cublas_ms": ms_lib, "cublas_tflops": fl / ms_lib / 1e9, "vs_cublas": ms_lib / ms})
+                        "cublas_ms": ms_lib, "cublas_tflops": fl / ms_lib / 1e9, "vs_cublas": ms_lib / ms,
+                        "pair_stream_k_ms": ms_sk, "pair_whole_tiles_ms": ms_whole})
         _ext.check_status()
 
 

@@ -657,6 +657,7 @@ __global__ void cce_finalize_kernel(const float* __restrict__ loss_rows, const l
 
 // =========================================================================================== host side
 extern "C" int cb_gemm2sm_supported(const void* C, long long ldc, int out_fp32);
+extern "C" int cb_gemm2sm_cost_milli(int M, int N, int K, int pairs_avail);
 extern "C" int cb_gemm2sm_bf16(const void* A, const void* B, void* C, const void* bias, const void* addend, int M, int N,
                                int K, long long lda, long long ldb, long long ldc, long long ld_add, int a_mn, int b_mn,
                                int out_fp32, int accumulate, int* status, void* stream);
@@ -720,18 +721,17 @@ int pick_block_n(int M, int N, int forced) {
   return best;
 }
 
-// Rounds of tiles, weighted by what one round costs relative to a round of the CTA-pair kernel (measured on
-// the 0.5B shapes: a 128x256 single-CTA round takes ~1.08 pair rounds, a 128x128 round ~0.9 because those tiles
-// are bound by operand bandwidth, not by the tensor pipe).  Short GEMMs stay on the single-CTA kernel, whose
-// fixed costs are lower.
+// Time of each kernel in units of one round of 256 x 256 CTA-pair tiles.  The pair kernel balances a partial last
+// round by cutting tiles along K (its own estimate, cb_gemm2sm_cost_milli); the single-CTA kernels run whole
+// tiles only (measured on the 0.5B shapes: a 128x256 round takes ~1.08 pair rounds, a 128x128 round ~0.9 because
+// those tiles are bound by operand bandwidth, not by the tensor pipe).  Short GEMMs stay on the single-CTA
+// kernel, whose fixed costs are lower.
 bool prefer_cta_pairs(int M, int N, int K) {
   if (K < 1024 && N < 1024) return false;
   const int sms = num_sms();
-  const long long t2 = static_cast<long long>((M + 255) / 256) * ((N + 255) / 256);
   const long long t256 = static_cast<long long>((M + 127) / 128) * ((N + 255) / 256);
   const long long t128 = static_cast<long long>((M + 127) / 128) * ((N + 127) / 128);
-  const int pairs = sms / 2;
-  const double c2 = static_cast<double>((t2 + pairs - 1) / pairs);
+  const double c2 = cb_gemm2sm_cost_milli(M, N, K, sms / 2) / 1000.0;
   const double c256 = 1.08 * static_cast<double>((t256 + sms - 1) / sms);
   const double c128 = 0.90 * static_cast<double>((t128 + sms - 1) / sms);
   return c2 <= (c256 < c128 ? c256 : c128);

@@ -189,6 +189,7 @@ class DecoderLayer(nn.Module):
         self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, norm_offset, dtype, device)
         self.mlp = MLP(cfg, dtype, device)
         self._use_checkpoint = False
+        self._offload = None            # an ActivationOffloadManager: checkpointed inputs wait in pinned host memory
 
     def _body(self, h, cos, sin, position_ids, cu_seqlens, max_seqlen, seqlens_host):
         # pre-norm residual blocks: the norm returns the stream itself as second value so that both gradient
@@ -200,6 +201,11 @@ class DecoderLayer(nn.Module):
 
     def forward(self, h, cos, sin, position_ids, cu_seqlens, max_seqlen, seqlens_host=None):
         if self._use_checkpoint and self.training and torch.is_grad_enabled():
+            if self._offload is not None:
+                from ..training.async_activation_offload import OffloadActivations
+                with OffloadActivations(manager=self._offload):
+                    return _checkpoint(self._body, h, cos, sin, position_ids, cu_seqlens, max_seqlen, seqlens_host,
+                                       use_reentrant=False)
             return _checkpoint(self._body, h, cos, sin, position_ids, cu_seqlens, max_seqlen, seqlens_host,
                                use_reentrant=False)
         return self._body(h, cos, sin, position_ids, cu_seqlens, max_seqlen, seqlens_host)
@@ -269,16 +275,25 @@ class CausalLM(nn.Module):
     def num_parameters(self, only_trainable: bool = False) -> int:
         return sum(p.numel() for p in self.parameters() if p.requires_grad or not only_trainable)
 
-    def gradient_checkpointing_enable(self, ratio: float = 1.0, **_) -> None:
+    def gradient_checkpointing_enable(self, ratio: float = 1.0, offload: bool = False, offload_config=None, **_) -> None:
+        """Recompute the chosen layers in the backward pass; with ``offload`` the tensors those layers keep for
+        it (their inputs) are moved to pinned host memory by one shared ``ActivationOffloadManager``."""
         n = len(self.model.layers)
         k = n if ratio >= 1.0 else max(1, int(round(n * ratio)))
         chosen = set(int(round(i * n / k)) for i in range(k)) if k < n else set(range(n))
+        manager = None
+        if offload:
+            from ..training.async_activation_offload import ActivationOffloadManager
+            manager = ActivationOffloadManager(offload_config)
+        self.activation_offload = manager
         for i, layer in enumerate(self.model.layers):
             layer._use_checkpoint = i in chosen
+            layer._offload = manager if i in chosen else None
 
     def gradient_checkpointing_disable(self) -> None:
         for layer in self.model.layers:
             layer._use_checkpoint = False
+            layer._offload = None
 
     # -- rope ------------------------------------------------------------------------------------------------
     def _rope(self, need: int, device) -> Tuple[torch.Tensor, torch.Tensor]:

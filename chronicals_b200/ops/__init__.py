@@ -48,7 +48,7 @@ def _gemm_ok(t: torch.Tensor) -> bool:
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
          bias: Optional[torch.Tensor] = None, addend: Optional[torch.Tensor] = None,
          out: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16,
-         accumulate: bool = False, block_n: int = 0) -> torch.Tensor:
+         accumulate: bool = False, block_n: int = 0, pair_flags: Optional[int] = None) -> torch.Tensor:
     """``C[M,N] = op(A) @ op(B)^T (+bias) (+addend) (+C)`` on the tcgen05 kernel.
 
     ``a_mn=False``: ``a`` is ``[M, K]``; ``a_mn=True``: ``a`` is ``[K, M]``
@@ -77,6 +77,17 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         return out
     if addend is not None:
         assert addend.stride(1) == 1 and addend.dtype == torch.bfloat16
+    if pair_flags is not None:
+        # the CTA-pair kernel with explicit options (tests, benchmarks): bit 0 = whole tiles only, bit 1 = always
+        # split a partial last round along K,
+        # bits 8.. = tile width 256 / 224 / 192
+        code = _ext.lib().cb_gemm2sm_bf16_ex(
+            a.data_ptr(), b.data_ptr(), out.data_ptr(), _ext.ptr(bias), _ext.ptr(addend), M, N, K,
+            a.stride(0), b.stride(0), out.stride(0), addend.stride(0) if addend is not None else 0,
+            int(a_mn), int(b_mn), int(out.dtype == torch.float32), int(accumulate), int(pair_flags),
+            _ext.status_buffer(a.device).data_ptr(), _ext.stream_ptr())
+        _ext.check(code, "gemm2sm_bf16_ex")
+        return out
     code = _ext.lib().cb_gemm_bf16(
         a.data_ptr(), b.data_ptr(), out.data_ptr(), _ext.ptr(bias), _ext.ptr(addend), M, N, K,
         a.stride(0), b.stride(0), out.stride(0), addend.stride(0) if addend is not None else 0,

@@ -51,6 +51,8 @@ _PROTOTYPES = {
     "cb_attn_bwd": [P, P, P, P, P, P, P, I, I, I, I, I, L, L, L, L, L, F, P, P, P, P, P, L, P, P],
     "cb_gemm2sm_bf16": [P, P, P, P, P, I, I, I, L, L, L, L, I, I, I, I, P, P],
     "cb_gemm2sm_supported": [P, L, I],
+    "cb_gemm2sm_bf16_ex": [P, P, P, P, P, I, I, I, L, L, L, L, I, I, I, I, I, P, P],
+    "cb_gemm2sm_cost_milli": [I, I, I, I],
     "cb_gemm2sm_fp8": [P, P, P, P, P, P, I, I, I, L, L, L, P, P],
     "cb_rowquant_e4m3": [P, P, P, L, I, L, L, P],
     "cb_gemm_bf16_splitk": [P, P, P, I, I, I, L, L, L, I, I, P, P],
@@ -123,7 +125,7 @@ def lib() -> ctypes.CDLL:
 
 
 # device kernels launched by one call of each entry point (0: host-only query)
-_KERNELS_PER_CALL = {"cb_cce_num_splits": 0, "cb_rmsnorm_max_n": 0, "cb_rmsnorm_bwd_blocks": 0, "cb_opt_chunk": 0,
+_KERNELS_PER_CALL = {"cb_gemm2sm_supported": 0, "cb_gemm2sm_cost_milli": 0, "cb_cce_num_splits": 0, "cb_rmsnorm_max_n": 0, "cb_rmsnorm_bwd_blocks": 0, "cb_opt_chunk": 0,
                      "cb_cce_combine": 2, "cb_rmsnorm_bwd": 2, "cb_grad_clip_coef": 2, "cb_attn_bwd": 3}
 LAUNCH_COUNT = [0]
 
@@ -183,7 +185,31 @@ def status_buffer(device: Optional[torch.device] = None) -> torch.Tensor:
     if buf is None:
         buf = torch.zeros(16, dtype=torch.int32, device=torch.device("cuda", key))
         _STATUS[key] = buf
+        _register_gemm_workspace(key)
     return buf
+
+
+_GEMM_WS = {}
+
+
+def _register_gemm_workspace(index: int) -> None:
+    """Zero-filled scratch for the CTA-pair GEMM's split tiles (fp32 tile slots + arrival counters, about 41 MB per
+    GPU), allocated together with the device's status words on first use and kept for the life of the process.
+    The kernels leave it zero-filled.  ``CHRONICALS_GEMM_STREAMK=0`` runs whole tiles only."""
+    if os.environ.get("CHRONICALS_GEMM_STREAMK", "1") == "0" or not has_symbol("cb_gemm2sm_set_workspace"):
+        return
+    L_ = lib()
+    fn_bytes = L_.cb_gemm2sm_workspace_bytes
+    fn_bytes.restype, fn_bytes.argtypes = ctypes.c_ulonglong, []
+    fn_set = L_.cb_gemm2sm_set_workspace
+    fn_set.restype, fn_set.argtypes = c_int, [c_int, c_void_p, ctypes.c_ulonglong]
+    n = int(fn_bytes())
+    ws = torch.zeros(n + 1024, dtype=torch.uint8, device=torch.device("cuda", index))
+    off = (-ws.data_ptr()) % 1024
+    _GEMM_WS[index] = ws
+    code = fn_set(index, ws.data_ptr() + off, n)
+    if code != 0:
+        raise KernelError(f"cb_gemm2sm_set_workspace failed with code {code}")
 
 
 _STATUS_NAMES = {101: "TMA stage never filled", 102: "smem stage never drained", 103: "accumulator never completed",

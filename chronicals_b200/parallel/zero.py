@@ -384,9 +384,12 @@ class ShardedFusedAdamW(torch.optim.Optimizer):
         return loss
 
     def zero_grad(self, set_to_none: bool = True) -> None:
-        """Gradients live in the flat buffer and are overwritten by the next backward pass."""
+        """Gradients live in the flat buffer: discarding them means that the next backward pass overwrites its
+        slots instead of adding to them (as ``step()`` arranges by itself for the gradients it consumed)."""
         for e in self.entries:
             e["p"].grad = None
+            e["filled"] = False
+        self._reset_pending()
 
     # ------------------------------------------------------------------------------------------ state
     def state_dict(self) -> Dict[str, Any]:

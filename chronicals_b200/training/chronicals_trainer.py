@@ -163,13 +163,16 @@ class ChronicalsTrainer:
         if a.use_gradient_checkpointing:
             if hasattr(self.model, "gradient_checkpointing_enable"):
                 try:
-                    self.model.gradient_checkpointing_enable(ratio=1.0)
+                    self.model.gradient_checkpointing_enable(ratio=1.0, offload=bool(a.use_activation_offloading))
                 except TypeError:
                     self.model.gradient_checkpointing_enable()
             else:
                 from .gradient_checkpointing import apply_gradient_checkpointing
                 apply_gradient_checkpointing(self.model, a.checkpoint_ratio)
         self._active_optimizations["gradient_checkpointing"] = bool(a.use_gradient_checkpointing)
+        self._active_optimizations["activation_offloading"] = bool(a.use_gradient_checkpointing
+                                                                   and a.use_activation_offloading
+                                                                   and getattr(self.model, "activation_offload", None))
 
         # packer for raw (un-packed) sample lists handed to train(dataset)
         self.packer = None

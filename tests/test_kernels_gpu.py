@@ -525,6 +525,67 @@ def test_gemm_cta_pair_kernel_epilogues():
     _ext.check_status()
 
 
+def _rel_l2(got, want):
+    return ((got.float() - want).norm() / want.norm().clamp_min(1e-30)).item()
+
+
+@pytest.mark.parametrize("a_mn,b_mn,M,N,K,bn", [
+    (False, False, 8192, 896, 4864, 0),      # down projection forward: 128 tiles of 256 x 224 on 74 pairs
+    (False, True, 8192, 896, 1152, 0),       # dgrad layout, tile width 224 with the B halves in two 64-column atoms
+    (True, True, 4864, 896, 8192, 0),        # wgrad layout: 76 tiles, every pair continues its neighbour's tile
+    (True, True, 896, 4864, 8192, 0),
+    (False, False, 8192, 1152, 896, 192),    # QKV: tile width 192
+    (False, False, 4000, 1000, 520, 256),    # ragged M, N and K, runs of a few k-blocks
+    (False, False, 2304, 640, 2048, 224),    # tile width that does not divide N
+])
+def test_gemm_cta_pair_stream_k_matches_fp32_and_whole_tiles(a_mn, b_mn, M, N, K, bn):
+    """Tiles cut along K across CTA pairs (fp32 partial sums added in the workspace, last arrival runs the epilogue)
+    against the fp32 product and against the same kernel restricted to whole tiles; the workspace is clean again
+    afterwards (a second launch gives the same bits)."""
+    from chronicals_b200 import ops
+    g = torch.Generator().manual_seed(11)
+    a = (torch.randn((K, M) if a_mn else (M, K), generator=g) * 0.5).to(torch.bfloat16).cuda()
+    b = (torch.randn((K, N) if b_mn else (N, K), generator=g) * 0.5).to(torch.bfloat16).cuda()
+    A = a.float().t() if a_mn else a.float()
+    B = b.float() if b_mn else b.float().t()
+    want = A @ B
+    split = ops.gemm(a, b, a_mn=a_mn, b_mn=b_mn, pair_flags=(bn << 8) | 2)
+    whole = ops.gemm(a, b, a_mn=a_mn, b_mn=b_mn, pair_flags=(bn << 8) | 1)
+    again = ops.gemm(a, b, a_mn=a_mn, b_mn=b_mn, pair_flags=(bn << 8) | 2)
+    _ext.check_status()
+    assert _rel_l2(split, want) < 4e-3 and _rel_l2(whole, want) < 4e-3
+    assert (split.float() - want).abs().max().item() < 1.5e-2 * want.abs().max().item()
+    # split tiles are summed in fp32 before the single rounding, like whole tiles: at most an ulp apart
+    assert (split.float() - whole.float()).abs().max().item() <= 2.0 ** -7 * want.abs().max().item()
+    assert torch.equal(split, again)
+
+
+def test_gemm_cta_pair_stream_k_epilogues():
+    """Bias, residual, accumulate (bf16 and fp32 outputs) on a shape whose tiles are split along K."""
+    from chronicals_b200 import ops
+    g = torch.Generator().manual_seed(12)
+    M, N, K = 8192, 896, 2048
+    a = (torch.randn(M, K, generator=g) * 0.3).to(torch.bfloat16).cuda()
+    w = (torch.randn(N, K, generator=g) * 0.3).to(torch.bfloat16).cuda()
+    bias = torch.randn(N, generator=g).to(torch.bfloat16).cuda()
+    res = torch.randn(M, N, generator=g).to(torch.bfloat16).cuda()
+    prod = a.float() @ w.float().t()
+    out = ops.gemm(a, w, bias=bias, addend=res, pair_flags=2)
+    want = prod + bias.float() + res.float()
+    assert _rel_l2(out, want) < 4e-3
+    acc32 = torch.randn(M, N, generator=g).cuda()
+    want2 = acc32 + prod
+    ops.gemm(a, w, out=acc32, accumulate=True, pair_flags=2)
+    assert _rel_l2(acc32, want2) < 1e-3
+    acc16 = torch.randn(M, N, generator=g).to(torch.bfloat16).cuda()
+    want3 = acc16.float() + prod
+    ops.gemm(a, w, out=acc16, accumulate=True, pair_flags=2)
+    assert _rel_l2(acc16, want3) < 4e-3
+    o32 = ops.gemm(a, w, out_dtype=torch.float32, pair_flags=2)
+    assert _rel_l2(o32, prod) < 1e-3
+    _ext.check_status()
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 def test_adamw8bit_kernel_matches_python_path(dtype):
     """Fused 8-bit AdamW (block-wise quantised moments) against the same optimizer run through the PyTorch
