@@ -240,6 +240,15 @@ def run_ours(args):
     e2e_ms = _max_ms(loader.elapsed_ms(), world)
     _ext.check_status(dev)
 
+    dp_profile = None
+    if args.dp_profile and hasattr(trainer.optimizer, "profile_report"):
+        trainer.use_cuda_graphs = False                   # events cannot be read back from inside a replayed graph
+        trainer.optimizer.profile = True
+        for i in range(3):
+            trainer.training_step(dev_batches[i % len(dev_batches)])
+        dp_profile = trainer.optimizer.profile_report()
+        trainer.optimizer.profile = False
+        _barrier_sync(world)
     tokens_per_step = MICRO_BATCH * SEQ_LEN * world
     value = tokens_per_step * args.steps / (ms / 1e3)
     e2e = tokens_per_step * args.steps / (e2e_ms / 1e3)
@@ -271,6 +280,8 @@ def run_ours(args):
         if hasattr(trainer.optimizer, "buckets"):
             out["config"]["grad_buckets"] = len(trainer.optimizer.buckets)
             out["config"]["reduce_grid"] = int(trainer.optimizer.rs_grid)
+            if dp_profile is not None:
+                out["dp_profile"] = dp_profile
         print(json.dumps(out), flush=True)
     import shutil
     shutil.rmtree(targs.output_dir, ignore_errors=True)
@@ -458,6 +469,9 @@ def main():
     ap.add_argument("--no-overlap", action="store_true",
                     help="reduce-scatter the gradient buckets after the backward pass instead of from its hooks")
     ap.add_argument("--reduce-grid", type=int, default=0, help="blocks per bucket reduce-scatter kernel (0: default)")
+    ap.add_argument("--dp-profile", action="store_true",
+                    help="after the timed regions, run three eager steps with CUDA events around every gradient bucket's "
+                         "reduce-scatter and add their hidden / exposed times to the JSON line (diagnostic)")
     ap.add_argument("--tiny", action="store_true", help="plumbing check of the reference arm on a tiny model")
     ap.add_argument("--ref-no-compile", action="store_true")
     args = ap.parse_args()

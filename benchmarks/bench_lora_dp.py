@@ -43,6 +43,9 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--rank-r", type=int, default=16)
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--no-graph", action="store_true", help="launch the step kernel by kernel instead of replaying a CUDA graph")
+    ap.add_argument("--max-docs", type=int, default=0, help="documents per batch the captured graph is sized for "
+                                                            "(0: the largest count among the generated batches)")
     a = ap.parse_args()
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     from chronicals_b200 import ChronicalsConfig, ChronicalsTrainer, TrainingConfig, build_model
@@ -63,7 +66,8 @@ def main() -> int:
                            max_seq_length=a.row_len, gradient_accumulation_steps=1, learning_rate=2e-4, weight_decay=0.0,
                            max_grad_norm=1.0, lr_scheduler_type="constant", warmup_ratio=0.0, bf16=cuda, fp8=False,
                            use_gradient_checkpointing=False, use_sequence_packing=True, logging_steps=10 ** 9, save_steps=0,
-                           visual_reporting=False, optimizer_type="lora_plus", seed=1234)
+                           visual_reporting=False, optimizer_type="lora_plus", seed=1234,
+                           use_cuda_graphs=cuda and not a.no_graph and a.comm == "fused")
     targs.lora_plus_ratio = 16.0
     targs.save_final = False
     targs.log_jsonl = False
@@ -78,6 +82,11 @@ def main() -> int:
     batches = [b for _, b in zip(range(n_steps), loader)]
     if len(batches) < n_steps:
         batches = (batches * (n_steps // max(1, len(batches)) + 1))[:n_steps]
+    targs.cuda_graph_max_documents = a.max_docs or max(int(b["cu_seqlens"].numel()) - 1 for b in batches)
+    if world > 1:
+        t = torch.tensor([targs.cuda_graph_max_documents], device=dev)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        targs.cuda_graph_max_documents = int(t.item())
     trainer = ChronicalsTrainer(model, targs, None)
     real = sum(int((b["labels"] != -100).sum()) for b in batches[a.warmup:])
     for b in batches[: a.warmup]:
@@ -113,7 +122,10 @@ def main() -> int:
                           "ms_per_step": ms, "tokens_per_sec": tokens / (ms / 1e3),
                           "non_masked_token_fraction_rank0": real / (a.steps * a.rows * a.row_len),
                           "vs_published_lora_a100": tokens / (ms / 1e3) / 11699.0, "comm": a.comm if world > 1 else "none",
-                          "cuda_graph": bool(trainer.use_cuda_graphs), "kernel_launches_per_step": (_ext.launches() - l0) // a.steps,
+                          "cuda_graph": bool(trainer.use_cuda_graphs),
+                          "kernel_launches_per_step": (trainer.graph_kernel_launches if trainer.use_cuda_graphs
+                                                       else (_ext.launches() - l0) // a.steps),
+                          "documents_per_batch_max": int(targs.cuda_graph_max_documents),
                           "loss": float(loss), "dtype": "bf16", "data": "synthetic lognormal-length documents, random-init weights"}),
               flush=True)
     shutdown()

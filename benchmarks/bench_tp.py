@@ -89,6 +89,7 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--single-cta", action="store_true", help="keep the fused GEMMs on the single-CTA kernel (no CTA pairs)")
     a = ap.parse_args()
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     from chronicals_b200 import ChronicalsConfig
@@ -105,11 +106,13 @@ def main() -> int:
     if a.layers:
         cfg.num_hidden_layers = a.layers
     tp = TPState(backend=a.comm)
+    tp.pair_gemm = not a.single_cta
     if a.micro:
         res = micro(tp, cfg, a.batch * a.seq, dev)
         _ext.check_status(dev)
         if rank == 0:
-            print(json.dumps({"bench": "tensor_parallel_micro", "model": a.model, "tp": world, **res}), flush=True)
+            print(json.dumps({"bench": "tensor_parallel_micro", "model": a.model, "tp": world, "pair_gemm": not a.single_cta,
+                              **res}), flush=True)
         shutdown()
         return 0
     model = TensorParallelCausalLM.from_config(cfg, tp, dtype=torch.bfloat16, device=dev, seed=0)
@@ -145,7 +148,7 @@ def main() -> int:
     mem = torch.cuda.max_memory_allocated() / 2 ** 30
     if rank == 0:
         print(json.dumps({"bench": "tensor_parallel_step", "model": a.model, "layers": cfg.num_hidden_layers, "tp": world,
-                          "comm": a.comm, "tokens_per_step": tokens, "ms_per_step": ms, "tokens_per_sec": tokens / (ms / 1e3),
+                          "comm": a.comm, "pair_gemm": not a.single_cta, "tokens_per_step": tokens, "ms_per_step": ms, "tokens_per_sec": tokens / (ms / 1e3),
                           "params_per_rank": n_local, "peak_mem_gb": mem, "loss": float(loss),
                           "kernel_launches_per_step": (_ext.launches() - l0) // a.steps, "dtype": "bf16",
                           "data": "synthetic token ids, random-init shards"}), flush=True)

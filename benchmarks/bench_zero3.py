@@ -32,6 +32,9 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-prefetch", action="store_true")
+    ap.add_argument("--comm", default="fused", choices=["fused", "nccl"],
+                    help="fused: gathers / reduce-scatters by peer-memory kernels; nccl: all_gather_into_tensor and "
+                         "reduce_scatter_tensor on the same schedule (comparison arm)")
     ap.add_argument("--fp8", default="none", choices=["none", "rowwise", "mxfp8"],
                     help="forward projections on FP8 operands (rowwise: e4m3 tensor-core GEMM; mxfp8: MX block scales applied by the block-scaled tensor-core GEMM, also in backward)")
     a = ap.parse_args()
@@ -53,7 +56,7 @@ def main() -> int:
     if a.fp8 != "none":
         from chronicals_b200.utils.fp8_deepseek import convert_model_to_fp8
         convert_model_to_fp8(model, exclude_patterns=[], mode=a.fp8)
-    eng = Zero3Engine(model, lr=1e-5, weight_decay=0.01, max_grad_norm=1.0, prefetch=not a.no_prefetch)
+    eng = Zero3Engine(model, lr=1e-5, weight_decay=0.01, max_grad_norm=1.0, prefetch=not a.no_prefetch, backend=a.comm)
     torch.cuda.empty_cache()
     g = torch.Generator().manual_seed(100 + rank)
     batches = [torch.randint(0, cfg.vocab_size, (a.batch, a.seq), generator=g).to(dev) for _ in range(4)]
@@ -84,7 +87,7 @@ def main() -> int:
                           "tokens_per_step": tokens, "ms_per_step": ms, "tokens_per_sec": tokens / (ms / 1e3),
                           "n_params": n_params, "peak_mem_gb": torch.cuda.max_memory_allocated() / 2 ** 30,
                           "mfu_6N_vs_2250TF": 6.0 * n_params * tokens / (ms / 1e3) / (2250e12 * world),
-                          "prefetch": not a.no_prefetch, "fp8": a.fp8, "loss": float(loss), "dtype": "bf16",
+                          "prefetch": not a.no_prefetch, "fp8": a.fp8, "comm": a.comm, "batch": a.batch, "seq": a.seq, "loss": float(loss), "dtype": "bf16",
                           "data": "synthetic token ids, random-init weights"}), flush=True)
     shutdown()
     return 0

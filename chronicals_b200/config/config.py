@@ -267,7 +267,7 @@ class ParallelConfig:
     # backward pass instead
     shard_bucket_mb: float = 24.0
     overlap_grad_reduce: bool = True
-    reduce_grid: int = 24
+    reduce_grid: int = 64
 
     @property
     def world_size(self) -> int:

@@ -19,6 +19,7 @@
 // Replaces the reference's calls into flash-attn / SDPA (chronicals/kernels/
 // flash_attention_optimizer.py:845-994) and its forward-only Triton kernels
 // (:2460-3209); the reference has no attention backward of its own.
+#include <cstdlib>
 #include "common.cuh"
 
 namespace cb {
@@ -312,6 +313,216 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem, TMEM_COLS); }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Forward, second form: two threads per score row and one pass over S.
+// 256 threads: warps w and w + 4 own the same 32 TMEM lanes (score rows) and split the 128 columns of S (and
+// the D columns of O) in halves.  Each thread reads its 64 scores once, the two halves of a row exchange their
+// maxima through shared memory (a 64-thread named barrier per lane quarter), and the probabilities go back to
+// TMEM as bf16 over the S columns both halves have finished reading.  O is never held in registers: the P V
+// products accumulate in TMEM across kv blocks, and a warp rescales its slice of O in place only when one of its
+// rows saw a larger maximum (rare after the first blocks of a causal row).  Per kv block a thread therefore runs
+// 64 instead of 256 score visits and the per-block O read-back disappears.
+__device__ __forceinline__ void pair_bar_sync(int id) { asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory"); }
+
+template <int D>
+__global__ void __launch_bounds__(BWD2_THREADS, (D == 64 ? 2 : 1))
+attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const AttnArgs a) {
+  using L = FwdSmem<D>;
+  constexpr int PANELS = D / 64;
+  constexpr int DH = D / 2;                            // O columns per thread
+  constexpr uint32_t TMEM_COLS = 256;                  // S / P at [0, 128), O at [128, 128 + D)
+  constexpr uint32_t IDESC_S = umma_idesc_bf16(128, 128, 0, 0);
+  constexpr uint32_t IDESC_PV = umma_idesc_bf16(128, D, 0, 1);
+
+  int start, len, qb, nblk;
+  if (!locate_block(a.cu, a.n_docs, blockIdx.x, start, len, qb, nblk)) return;
+  qb = nblk - 1 - qb;                                  // heaviest (most kv blocks) first
+  const int h = blockIdx.y;
+  const int hkv = h / (a.hq / a.hk);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem + L::OFF_Q;
+  uint8_t* sK = smem + L::OFF_K;
+  uint8_t* sV = smem + L::OFF_V;
+  uint64_t* kv_full = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);   // [2]
+  uint64_t* bar_q = kv_full + 2;
+  uint64_t* bar_s = kv_full + 3;
+  uint64_t* bar_o = kv_full + 4;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(kv_full + 5);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  __shared__ float s_x[2][128];                        // per-row exchange between the two column halves
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int q4 = warp & 3, half = warp >> 2;
+  if (tid == 0) {
+    mbar_init(kv_full, 1); mbar_init(kv_full + 1, 1);
+    mbar_init(bar_q, 1); mbar_init(bar_s, 1); mbar_init(bar_o, 1);
+    mbar_fence_init();
+    *abort_flag = a.status[0] != 0 ? 1 : 0;
+  }
+  __syncthreads();
+  if (*abort_flag) return;
+  if (warp == 0) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t t_row = tmem + (static_cast<uint32_t>(q4 * 32) << 16);
+
+  const int n_kv = qb + 1;
+  const int q_row0 = start + qb * 128;
+  auto load_kv = [&](int j) {
+    const int st = j & 1;
+    mbar_expect_tx(kv_full + st, 2 * L::TILE);
+#pragma unroll
+    for (int p = 0; p < PANELS; ++p) {
+      tma_load_2d(sK + st * L::TILE + p * 16384, &tmK, kv_full + st, hkv * D + p * 64, start + j * 128);
+      tma_load_2d(sV + st * L::TILE + p * 16384, &tmV, kv_full + st, hkv * D + p * 64, start + j * 128);
+    }
+  };
+  auto issue_s = [&](int j) {
+    const uint32_t qa = smem_u32(sQ), kb = smem_u32(sK + (j & 1) * L::TILE);
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk)
+      umma_f16_ss(tmem, desc_kmajor(qa, kk), desc_kmajor(kb, kk), IDESC_S, kk != 0);
+    umma_commit(bar_s);
+  };
+
+  bool ok = true;
+  if (tid == 0) {
+    mbar_expect_tx(bar_q, L::TILE);
+#pragma unroll
+    for (int p = 0; p < PANELS; ++p) tma_load_2d(sQ + p * 16384, &tmQ, bar_q, h * D + p * 64, q_row0);
+    load_kv(0);
+    if (n_kv > 1) load_kv(1);
+    ok &= mbar_wait(bar_q, 0, abort_flag, a.status, CB_ERR_WAIT_FULL);
+    ok &= mbar_wait(kv_full, 0, abort_flag, a.status, CB_ERR_WAIT_FULL);
+    if (ok) { tc_fence_after(); issue_s(0); }
+  }
+
+  const int r = q4 * 32 + (tid & 31);                  // my row of the tile
+  const int c0 = half * 64;                            // my first score column
+  const float sl2 = a.scale * LOG2E;
+  float m_run = -INFINITY, l_run = 0.f;                // l_run: this half's share of the row sum
+
+  for (int j = 0; j < n_kv; ++j) {
+    ok &= mbar_wait(bar_s, j & 1, abort_flag, a.status, CB_ERR_WAIT_TMEM_FULL);
+    tc_fence_after();
+    const bool diag = (j == qb);
+    uint32_t s[64];
+    tmem_ld_32x32(t_row + c0, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+    tmem_ld_32x32(t_row + c0 + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+    tmem_ld_wait();
+    float mx = -INFINITY;
+    if (diag) {
+#pragma unroll
+      for (int i = 0; i < 64; ++i)
+        if (c0 + i <= r) mx = fmaxf(mx, __uint_as_float(s[i]));
+    } else {
+#pragma unroll
+      for (int i = 0; i < 64; ++i) mx = fmaxf(mx, __uint_as_float(s[i]));
+    }
+    s_x[half][r] = mx;
+    pair_bar_sync(1 + q4);                             // both halves have read their scores and posted their maxima
+    mx = fmaxf(mx, s_x[half ^ 1][r]);
+    const float m_new = fmaxf(m_run, mx);
+    const float alpha = ex2_approx((m_run - m_new) * sl2);
+    const float mb = m_new * sl2;
+    float rs = 0.f;
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      uint32_t pk[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        float e0 = ex2_approx(fmaf(__uint_as_float(s[32 * c + 2 * i]), sl2, -mb));
+        float e1 = ex2_approx(fmaf(__uint_as_float(s[32 * c + 2 * i + 1]), sl2, -mb));
+        if (diag) {
+          e0 = (c0 + 32 * c + 2 * i <= r) ? e0 : 0.f;
+          e1 = (c0 + 32 * c + 2 * i + 1 <= r) ? e1 : 0.f;
+        }
+        rs += e0 + e1;
+        pk[i] = pack_bf16x2(e0, e1);
+      }
+      // bf16 pairs of columns [c0 + 32c, c0 + 32c + 32) -> TMEM words [c0 / 2 + 16c, + 16) of my row
+      tmem_st_32x16(t_row + (c0 >> 1) + 16 * c, pk);
+    }
+    l_run = l_run * alpha + rs;
+    m_run = m_new;
+    if (j > 0) {
+      // the previous P V product has landed in O (and released its K / V stage)
+      ok &= mbar_wait(bar_o, (j - 1) & 1, abort_flag, a.status, CB_ERR_WAIT_TMEM_FULL);
+      tc_fence_after();
+      if (tid == 0 && ok && j + 1 < n_kv) load_kv(j + 1);
+      if (__any_sync(0xffffffffu, alpha != 1.f)) {     // a row of this warp has a new maximum: rescale my slice of O
+#pragma unroll
+        for (int c = 0; c < DH / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld_32x32(t_row + 128 + half * DH + c * 32, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st_32x32(t_row + 128 + half * DH + c * 32, o);
+        }
+      }
+    }
+    tmem_st_wait();
+    tc_fence_before();
+    if (__syncthreads_or(!ok)) { ok = false; break; }
+    if (tid == 0) {
+      tc_fence_after();
+      const uint32_t vb = smem_u32(sV + (j & 1) * L::TILE);
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk)      // A = P from TMEM: 16 bf16 of K per step = 8 words; O accumulates across blocks
+        umma_f16_ts(tmem + 128, tmem + kk * 8, desc_mnmajor(vb, kk), IDESC_PV, (j | kk) != 0);
+      umma_commit(bar_o);
+      if (j + 1 < n_kv) {
+        ok &= mbar_wait(kv_full + ((j + 1) & 1), ((j + 1) >> 1) & 1, abort_flag, a.status, CB_ERR_WAIT_FULL);
+        if (ok) { tc_fence_after(); issue_s(j + 1); }
+      }
+    }
+  }
+  if (ok) ok &= mbar_wait(bar_o, (n_kv - 1) & 1, abort_flag, a.status, CB_ERR_WAIT_TMEM_FULL);
+  s_x[half][r] = l_run;
+  pair_bar_sync(1 + q4);                                 // reached by every thread, whatever its waits returned
+  if (ok) {
+    tc_fence_after();
+    const float l_tot = l_run + s_x[half ^ 1][r];
+    const int rg = qb * 128 + r;
+    const bool row_ok = ok && rg < len;
+    const float inv = 1.f / l_tot;
+    const long long t = start + rg;
+#pragma unroll
+    for (int c = 0; c < DH / 32; ++c) {
+      uint32_t o[32];
+      tmem_ld_32x32(t_row + 128 + half * DH + c * 32, o);
+      tmem_ld_wait();
+      if (row_ok) {
+        uint4* op = reinterpret_cast<uint4*>(a.O + t * a.ldo + static_cast<long long>(h) * D + half * DH + c * 32);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          uint4 u;
+          u.x = pack_bf16x2(__uint_as_float(o[8 * k + 0]) * inv, __uint_as_float(o[8 * k + 1]) * inv);
+          u.y = pack_bf16x2(__uint_as_float(o[8 * k + 2]) * inv, __uint_as_float(o[8 * k + 3]) * inv);
+          u.z = pack_bf16x2(__uint_as_float(o[8 * k + 4]) * inv, __uint_as_float(o[8 * k + 5]) * inv);
+          u.w = pack_bf16x2(__uint_as_float(o[8 * k + 6]) * inv, __uint_as_float(o[8 * k + 7]) * inv);
+          op[k] = u;
+        }
+      }
+    }
+    if (row_ok && half == 0) a.lse[static_cast<long long>(h) * a.T + t] = m_run * a.scale + __logf(l_tot);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem, TMEM_COLS); }
+}
+
 // delta[h, t] = sum_d dO[t, h, d] * O[t, h, d].  LANES = D / 8 lanes share one (t, h): each loads 16 bytes
 // of dO and of O, so a warp reads 512 contiguous bytes of each tensor per instruction (32 / LANES heads of
 // one token, or of neighbouring tokens when the rows are dense) and the sum needs log2(LANES) shuffles.
@@ -410,7 +621,8 @@ __device__ __forceinline__ void load_row_chunk32(const uint8_t* base, int r, int
 template <int D>
 __global__ void __launch_bounds__(BWD2_THREADS, 2)
 attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO, const AttnArgs a) {
+                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                 const __grid_constant__ CUtensorMap tmdQ, const AttnArgs a) {
   using L = Bwd2Smem<D>;
   constexpr int PANELS = D / 64;
   constexpr uint32_t TMEM_COLS = (128 + 2 * D) <= 256 ? 256 : 512;
@@ -488,6 +700,7 @@ attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   for (int it = 0; it < n_it; ++it) {
     const int i = jb + it;
     if (tid == 0) {
+      if (D == 64) tma_store_wait_read<0>();          // the dQ tile of the last iteration has left the P / dS buffer
       ok &= mbar_wait(q_full, it & 1, abort_flag, a.status, CB_ERR_WAIT_FULL);
       if (ok) {
         tc_fence_after();
@@ -564,22 +777,44 @@ attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     ok &= mbar_wait(bar_dq, it & 1, abort_flag, a.status, CB_ERR_WAIT_TMEM_FULL);
     tc_fence_after();
     if (tid == 0 && ok && it + 1 < n_it) load_q(it + 1);                // Q / dO of this iteration are consumed
-#pragma unroll
-    for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
+    if (D == 64) {
+      // dQ tile (fp32) -> the P / dS buffer, which nobody reads any more, as two [128 x 32] boxes in the layout
+      // of the dq_acc tensor map -> one TMA reduce-add per box instead of eight red.global.add per thread.
+      // Rows past the end of the document carry exact zeros (their P was masked), rows past T are clipped.
       uint32_t dq[32];
-      tmem_ld_32x32(t_row + C_S + c * 32, dq);
+      tmem_ld_32x32(t_row + C_S + half * 32, dq);
       tmem_ld_wait();
-      if (row_ok && ok) {
-        float* dst = a.dq_acc + (tq * a.hq + h) * D + c * 32;
+      uint8_t* dstrow = sP + half * 16384 + r * 128;
 #pragma unroll
-        for (int k = 0; k < 32; k += 4)
-          red_add_v4(dst + k, __uint_as_float(dq[k]), __uint_as_float(dq[k + 1]), __uint_as_float(dq[k + 2]),
-                     __uint_as_float(dq[k + 3]));
+      for (int cc = 0; cc < 8; ++cc)
+        *reinterpret_cast<uint4*>(dstrow + ((cc ^ (r & 7)) << 4)) = make_uint4(dq[4 * cc], dq[4 * cc + 1], dq[4 * cc + 2], dq[4 * cc + 3]);
+      fence_async_smem();
+      tc_fence_before();
+      if (__syncthreads_or(!ok)) { ok = false; break; }
+      if (tid == 0) {
+        tma_reduce_add_2d(&tmdQ, sP, h * D, start + i * 128);
+        tma_reduce_add_2d(&tmdQ, sP + 16384, h * D + 32, start + i * 128);
+        tma_store_commit();
       }
+    } else {
+#pragma unroll
+      for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
+        uint32_t dq[32];
+        tmem_ld_32x32(t_row + C_S + c * 32, dq);
+        tmem_ld_wait();
+        if (row_ok && ok) {
+          float* dst = a.dq_acc + (tq * a.hq + h) * D + c * 32;
+#pragma unroll
+          for (int k = 0; k < 32; k += 4)
+            red_add_v4(dst + k, __uint_as_float(dq[k]), __uint_as_float(dq[k + 1]), __uint_as_float(dq[k + 2]),
+                       __uint_as_float(dq[k + 3]));
+        }
+      }
+      tc_fence_before();
+      if (__syncthreads_or(!ok)) { ok = false; break; }
     }
-    tc_fence_before();
-    if (__syncthreads_or(!ok)) { ok = false; break; }
   }
+  if (D == 64 && tid == 0) tma_store_wait_all();
   if (ok) {
     tc_fence_after();
     const int kg = jb * 128 + r;                      // my kv row within the document
@@ -688,6 +923,20 @@ int cb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse
   a.O = static_cast<cb::bf16*>(o); a.ldo = ldo; a.lse = lse; a.status = status;
   dim3 grid((T + 127) / 128 + n_docs, hq);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // CB_ATTN_FWD=1 in the environment selects the one-thread-per-row kernel (kept for comparison)
+  static const bool one_thread_rows = [] { const char* v = getenv("CB_ATTN_FWD"); return v != nullptr && v[0] == '1'; }();
+  if (!one_thread_rows) {
+    if (D == 64) {
+      static bool cfg = false;
+      if (!cfg) { e = set_smem(cb::attn_fwd2_kernel<64>, cb::FwdSmem<64>::TOTAL); if (e) return e; cfg = true; }
+      cb::attn_fwd2_kernel<64><<<grid, cb::BWD2_THREADS, cb::FwdSmem<64>::TOTAL, s>>>(mq, mk, mv, a);
+    } else {
+      static bool cfg = false;
+      if (!cfg) { e = set_smem(cb::attn_fwd2_kernel<128>, cb::FwdSmem<128>::TOTAL); if (e) return e; cfg = true; }
+      cb::attn_fwd2_kernel<128><<<grid, cb::BWD2_THREADS, cb::FwdSmem<128>::TOTAL, s>>>(mq, mk, mv, a);
+    }
+    return static_cast<int>(cudaGetLastError());
+  }
   if (D == 64) {
     static bool cfg = false;
     if (!cfg) { e = set_smem(cb::attn_fwd_kernel<64>, cb::FwdSmem<64>::TOTAL); if (e) return e; cfg = true; }
@@ -711,6 +960,10 @@ int cb_attn_bwd(const void* q, const void* k, const void* v, const void* o, cons
   int e = attn_maps(&mq, &mk, &mv, q, k, v, T, hq, hk, D, ldq, ldk, ldv);
   if (e) return e;
   e = cbhost::make_tmap(&mdo, d_o, static_cast<unsigned long long>(hq) * D, T, ld_do, 64, 128);
+  if (e) return e;
+  CUtensorMap mdq;                                      // fp32 dQ accumulator [T, hq * D], boxes of 128 rows x 32 columns
+  e = cbhost::make_tmap(&mdq, dq_acc, static_cast<unsigned long long>(hq) * D, T, static_cast<unsigned long long>(hq) * D,
+                        32, 128, 4);
   if (e) return e;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const long long pairs = static_cast<long long>(T) * hq;
@@ -740,11 +993,11 @@ int cb_attn_bwd(const void* q, const void* k, const void* v, const void* o, cons
   if (D == 64) {
     static bool cfg = false;
     if (!cfg) { e = set_smem(cb::attn_bwd2_kernel<64>, cb::Bwd2Smem<64>::TOTAL); if (e) return e; cfg = true; }
-    cb::attn_bwd2_kernel<64><<<grid, cb::BWD2_THREADS, cb::Bwd2Smem<64>::TOTAL, s>>>(mq, mk, mv, mdo, a);
+    cb::attn_bwd2_kernel<64><<<grid, cb::BWD2_THREADS, cb::Bwd2Smem<64>::TOTAL, s>>>(mq, mk, mv, mdo, mdq, a);
   } else {
     static bool cfg = false;
     if (!cfg) { e = set_smem(cb::attn_bwd2_kernel<128>, cb::Bwd2Smem<128>::TOTAL); if (e) return e; cfg = true; }
-    cb::attn_bwd2_kernel<128><<<grid, cb::BWD2_THREADS, cb::Bwd2Smem<128>::TOTAL, s>>>(mq, mk, mv, mdo, a);
+    cb::attn_bwd2_kernel<128><<<grid, cb::BWD2_THREADS, cb::Bwd2Smem<128>::TOTAL, s>>>(mq, mk, mv, mdo, mdq, a);
   }
   cb::attn_bwd_finalize_kernel<<<T, 128, 0, s>>>(dq_acc, dk_part, dv_part, static_cast<cb::bf16*>(dqkv), ld_dqkv, T,
                                                   hq, hk, D, cu, n_docs, part_heads);

@@ -65,6 +65,19 @@ struct Args {
   const float* row_scale;  // fp8 operands: C = (A_q B_q^T) * row_scale[m] * col_scale[n]; null for bf16 operands
   const float* col_scale;
   int* status;
+  // ---- tensor-parallel fusion (TP = 1 instantiations only; same contract as cb_gemm_bf16_tp in gemm.cu)
+  // all-gather -> GEMM: the rows of A arrive in panels of `panel_pairs` 256-row tiles, one panel per source rank,
+  // pushed into local memory by the peers; flag[src] reaches *panel_epoch once panel src is complete
+  const unsigned long long* panel_flags;
+  const unsigned long long* panel_epoch;
+  int panel_pairs;
+  int panel_self;                 // the panel this rank produced itself (never waited for)
+  int rot_pairs;                  // row tiles are visited starting here, so every rank begins with its own panel
+  unsigned long long peer_wait_ns;
+  // GEMM -> reduce-scatter: output rows belong to `push_rows` rows per owner rank; the epilogue stores each tile
+  // through push_c[owner] (a peer mapping, pre-offset so that the global row indexes it with pitch ldc)
+  unsigned long long push_c[16];
+  int push_rows;
 };
 
 __device__ __forceinline__ void umma_f16_ss_2cta(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
@@ -145,7 +158,7 @@ __device__ __forceinline__ int pair_of_unit(const Args& g, long long u) {
 // k-block, K-major only).  Either way a k-block row is 128 bytes and one MMA consumes 32 bytes of it, so the
 // shared-memory layout, the descriptors and the pipeline are identical.
 // BN: columns of the pair's tile (256, 224 or 192); each CTA loads BN / 2 rows of B.
-template <int BN, int A_MN, int B_MN, int KIND>
+template <int BN, int A_MN, int B_MN, int KIND, int TP = 0>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmW, const Args g) {
@@ -216,10 +229,37 @@ gemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       Segments seg(g, pair, num_pairs);
       int t, kb0, kb1;
       while (ok && seg.next(g, t, kb0, kb1)) {
-        const int mp = t % g.num_m_pairs;
+        int mp = t % g.num_m_pairs;
+        if (TP) {
+          mp += g.rot_pairs;
+          if (mp >= g.num_m_pairs) mp -= g.num_m_pairs;
+        }
         const int nt = t / g.num_m_pairs;
         const int a_row = mp * 2 * BM + static_cast<int>(rank) * BM;
         const int b_row = nt * BN + static_cast<int>(rank) * BNH;
+        if (TP && g.panel_pairs > 0) {
+          // rows of this tile come from rank `src`: wait (bounded) until its push kernel has signalled
+          const int src = mp / g.panel_pairs;
+          if (src != g.panel_self) {
+            const unsigned long long want = *g.panel_epoch;
+            const uint64_t t0 = globaltimer_ns();
+            while (ld_acquire_sys_u64(g.panel_flags + src) < want) {
+              if (*abort_flag) { ok = false; break; }
+              if (globaltimer_ns() - t0 > g.peer_wait_ns) {
+                *abort_flag = 1;
+                atomicCAS(g.status, 0, CB_ERR_WAIT_PEER);
+                g.status[1] = src;
+                g.status[2] = blockIdx.x;
+                __threadfence();
+                ok = false;
+                break;
+              }
+              __nanosleep(128);
+            }
+            if (!ok) break;
+            fence_proxy_async_all();   // the peer's generic-proxy stores are read by TMA (async proxy) below
+          }
+        }
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(empty + stage, phase ^ 1, abort_flag, g.status, CB_ERR_WAIT_EMPTY)) {
             ok = false;
@@ -409,6 +449,25 @@ gemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       if (g.out_fp32) {
         stage_fp32(r);
         flush(&tmC, colbase, row0w, false, row0w < g.M);
+      } else if (ncol == 64 && TP && g.push_rows > 0) {
+        // reduce-scatter epilogue: these 32 rows live on rank row0w / push_rows; plain 16-byte stores to the peer
+        // from the staged tile, 8 lanes per 128-byte row segment (full lines on the wire)
+        stage_bf16(r);
+        __syncwarp();
+        bf16* push_base = reinterpret_cast<bf16*>(g.push_c[row0w / g.push_rows]);
+        const int chunk = lane & 7;
+        const int ccol = colbase + chunk * 8;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int rr = (lane >> 3) + 4 * i;
+          const int grow = row0w + rr;
+          if (grow < g.M && ccol < g.N) {
+            const uint4 u = *reinterpret_cast<const uint4*>(stg + buf * 4096 + rr * 128 + ((chunk ^ (rr & 7)) << 4));
+            *reinterpret_cast<uint4*>(push_base + static_cast<long long>(grow) * g.ldc + ccol) = u;
+          }
+        }
+        __syncwarp();
+        buf ^= 1;
       } else if (ncol == 64) {
         stage_bf16(r);
         flush(&tmC, colbase, row0w, false, row0w < g.M);
@@ -436,7 +495,11 @@ gemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     };
 
     while (ok && seg.next(g, t, kb0, kb1)) {
-      const int mp = t % g.num_m_pairs;
+      int mp = t % g.num_m_pairs;
+      if (TP) {
+        mp += g.rot_pairs;
+        if (mp >= g.num_m_pairs) mp -= g.num_m_pairs;
+      }
       const int nt = t / g.num_m_pairs;
       const uint32_t acc = seg_cnt & 1u;
       const uint32_t acc_phase = (seg_cnt >> 1) & 1u;
@@ -566,10 +629,10 @@ constexpr int MAX_DEVICES = 64;
 void* g_ws_ptr[MAX_DEVICES] = {};
 unsigned long long g_ws_bytes[MAX_DEVICES] = {};
 
-template <int BN, int A_MN, int B_MN, int KIND = 0>
+template <int BN, int A_MN, int B_MN, int KIND = 0, int TP = 0>
 int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tw, const cb2::Args& g,
             int pairs, cudaStream_t s) {
-  auto kern = cb2::gemm2sm_kernel<BN, A_MN, B_MN, KIND>;
+  auto kern = cb2::gemm2sm_kernel<BN, A_MN, B_MN, KIND, TP>;
   static bool configured = false;
   if (!configured) {
     CB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, cb2::SMEM_TOTAL));
@@ -734,6 +797,66 @@ int cb_gemm2sm_bf16(const void* A, const void* B, void* C, const void* bias, con
                     int accumulate, int* status, void* stream) {
   return cb_gemm2sm_bf16_ex(A, B, C, bias, addend, M, N, K, lda, ldb, ldc, ld_add, a_mn, b_mn, out_fp32, accumulate, 0,
                             status, stream);
+}
+
+// Tensor-parallel variants on CTA pairs (bf16 output, A stored [M, K]; same contract as cb_gemm_bf16_tp in gemm.cu):
+//  * panel_rows > 0 (all-gather -> GEMM): A's rows arrive in W panels of panel_rows rows pushed by the peers;
+//    panel_flags[src] (local, u64) reaches *panel_epoch when panel src is complete.  The kernel starts with this
+//    rank's own panel and waits (bounded by wait_ns) per panel while the others are still in flight.
+//  * push_rows > 0 (GEMM -> reduce-scatter): output rows [o * push_rows, (o + 1) * push_rows) are stored through
+//    push_ptrs[o] (peer mappings, pre-offset so that the global row number indexes them with pitch ldc).
+// panel_rows must be a multiple of 256 and push_rows of 32; N a multiple of 64 with push.  Returns -5 when the
+// shape does not fit these tiles (the caller then uses the single-CTA kernel).
+int cb_gemm2sm_bf16_tp(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, long long lda,
+                       long long ldb, long long ldc, int b_mn, const unsigned long long* panel_flags,
+                       const unsigned long long* panel_epoch, int panel_rows, const unsigned long long* push_ptrs,
+                       int push_rows, int W, int my_rank, unsigned long long wait_ns, int* status, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || W < 1 || W > 16 || my_rank < 0 || my_rank >= W) return -1;
+  if (panel_rows < 0 || push_rows < 0 || panel_rows % 256 != 0 || push_rows % 32 != 0) return -5;
+  if (panel_rows > 0 && (panel_flags == nullptr || panel_epoch == nullptr || static_cast<long long>(panel_rows) * W < M)) return -3;
+  if (push_rows > 0 && (push_ptrs == nullptr || static_cast<long long>(push_rows) * W < M || N % 64 != 0 || ldc % 8 != 0)) return -5;
+  if (push_rows == 0 && !cb_gemm2sm_supported(C, ldc, 0)) return -5;
+  if (b_mn && (ldb * 2) % 16 != 0) return -5;
+  CUtensorMap ta, tb, tc, tw;
+  int e = cbhost::make_tmap(&ta, A, K, M, lda, 64, cb2::BM);
+  if (e) return e;
+  if (!b_mn) e = cbhost::make_tmap(&tb, B, K, N, ldb, 64, 128);
+  else e = cbhost::make_tmap(&tb, B, N, K, ldb, 64, 64);
+  if (e) return e;
+  memset(&tc, 0, sizeof(tc));
+  memset(&tw, 0, sizeof(tw));
+  if (push_rows == 0) {
+    e = cbhost::make_tmap(&tc, C, N, M, ldc, 64, 32, 2);
+    if (e) return e;
+  }
+  cb2::Args g = {};
+  g.M = M; g.N = N; g.K = K;
+  g.num_m_pairs = (M + 2 * cb2::BM - 1) / (2 * cb2::BM);
+  g.num_n_tiles = (N + 255) / 256;
+  g.num_tiles = g.num_m_pairs * g.num_n_tiles;
+  g.num_kb = (K + cb2::BK - 1) / cb2::BK;
+  g.C = C; g.ldc = ldc;
+  g.bias = static_cast<const cb::bf16*>(bias);
+  g.status = status;
+  g.peer_wait_ns = wait_ns;
+  if (panel_rows > 0) {
+    g.panel_flags = panel_flags;
+    g.panel_epoch = panel_epoch;
+    g.panel_pairs = panel_rows / 256;
+    g.panel_self = my_rank;
+    g.rot_pairs = (my_rank * g.panel_pairs) % g.num_m_pairs;
+  }
+  if (push_rows > 0) {
+    g.push_rows = push_rows;
+    for (int i = 0; i < W; ++i) g.push_c[i] = push_ptrs[i];
+    g.rot_pairs = static_cast<int>((static_cast<long long>(my_rank) * push_rows / 256) % g.num_m_pairs);
+    g.C = nullptr;
+  }
+  int pairs = cbhost::num_sms() / 2;
+  if (pairs > g.num_tiles) pairs = g.num_tiles;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (!b_mn) return launch2<256, 0, 0, 0, 1>(ta, tb, tc, tw, g, pairs, s);
+  return launch2<256, 0, 1, 0, 1>(ta, tb, tc, tw, g, pairs, s);
 }
 
 // FP8 (e4m3) GEMM on the tensor cores: C[M,N] (bf16) = (Aq[M,K] * Bq[N,K]^T) * row_scale[m] * col_scale[n] (+bias).

@@ -32,6 +32,7 @@ from . import symm
 _P, _I, _L, _F, _U = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_ulonglong
 _PROTOS = {
     "cb_gemm_bf16_tp": [_P, _P, _P, _P, _I, _I, _I, _L, _L, _L, _I, _I, _I, _P, _P, _I, _P, _I, _I, _I, _U, _P, _P],
+    "cb_gemm2sm_bf16_tp": [_P, _P, _P, _P, _I, _I, _I, _L, _L, _L, _I, _P, _P, _I, _P, _I, _I, _I, _U, _P, _P],
     "cb_rmsnorm_push": [_P, _P, _P, _P, _I, _I, _I, _I, _L, _F, _F, _P, _P, _P, _P, _P],
     "cb_reduce_partials": [_P, _P, _P, _I, _L, _P, _P],
     "cb_vp_combine": [_P, _I, _I, _P, _P, _P, _P],
@@ -73,6 +74,11 @@ class FusedTP:
         self.xf = [None, None]
         self.stage = None
         self.ex = None
+        # CTA-pair kernels for the two fused GEMMs where the shape fits their tiles (rows per rank a multiple of
+        # 256 for the panel wait, N a multiple of 64 for the push epilogue); ``pair_gemm = False`` keeps the
+        # single-CTA kernel everywhere
+        self.pair_gemm = bool(getattr(tp, "pair_gemm", True))
+        self.pair_min_dim = int(getattr(tp, "pair_min_dim", 1024))      # below this K and N the single-CTA kernel is quicker
         self.ensure(tokens, hidden)
 
     def ensure(self, tokens: int, hidden: int) -> None:
@@ -116,6 +122,16 @@ class FusedTP:
         M, K = a_full.shape
         N = b.shape[1] if b_mn else b.shape[0]
         out = torch.empty(M, N, dtype=torch.bfloat16, device=a_full.device)
+        if self.pair_gemm and (M // self.world) % 256 == 0 and max(K, N) >= self.pair_min_dim:
+            code = _lib().cb_gemm2sm_bf16_tp(a_full.data_ptr(), b.data_ptr(), out.data_ptr(), _ext.ptr(bias), M, N, K,
+                                             a_full.stride(0), b.stride(0), out.stride(0), int(b_mn),
+                                             self.flags[channel].local.data_ptr(), self.epoch[channel].data_ptr(),
+                                             M // self.world, None, 0, self.world, self.rank, self.wait_ns,
+                                             self.status.data_ptr(), _ext.stream_ptr())
+            if code != -5:
+                _ext.check(code, "gemm2sm_tp(wait)")
+                _ext.count_launch()
+                return out
         code = _lib().cb_gemm_bf16_tp(a_full.data_ptr(), b.data_ptr(), out.data_ptr(), _ext.ptr(bias), M, N, K,
                                       a_full.stride(0), b.stride(0), out.stride(0), 0, int(b_mn), 0,
                                       self.flags[channel].local.data_ptr(), self.epoch[channel].data_ptr(),
@@ -139,9 +155,17 @@ class FusedTP:
         for o in range(self.world):
             off_rows = self.rank * rows - o * rows
             ptrs[o] = (self.stage.ptrs[o] + off_rows * N * 2) & 0xFFFFFFFFFFFFFFFF
-        code = _lib().cb_gemm_bf16_tp(a.data_ptr(), b.data_ptr(), None, None, M, N, K, a.stride(0), b.stride(0), N, 0,
-                                      int(b_mn), 0, None, None, 0, ptrs, rows, self.world, self.rank, self.wait_ns,
-                                      self.status.data_ptr(), _ext.stream_ptr())
+        code = -5
+        if self.pair_gemm and N % 64 == 0 and max(K, N) >= self.pair_min_dim:
+            code = _lib().cb_gemm2sm_bf16_tp(a.data_ptr(), b.data_ptr(), None, None, M, N, K, a.stride(0), b.stride(0), N,
+                                             int(b_mn), None, None, 0, ptrs, rows, self.world, self.rank, self.wait_ns,
+                                             self.status.data_ptr(), _ext.stream_ptr())
+            if code != -5:
+                _ext.count_launch()
+        if code == -5:
+            code = _lib().cb_gemm_bf16_tp(a.data_ptr(), b.data_ptr(), None, None, M, N, K, a.stride(0), b.stride(0), N, 0,
+                                          int(b_mn), 0, None, None, 0, ptrs, rows, self.world, self.rank, self.wait_ns,
+                                          self.status.data_ptr(), _ext.stream_ptr())
         _ext.check(code, "gemm_tp(push)")
         self.ctx.barrier()                                   # all ranks' tiles have landed in my staging buffer
         out = torch.empty(rows, N, dtype=torch.bfloat16, device=a.device)

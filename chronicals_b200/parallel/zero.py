@@ -55,7 +55,7 @@ class _Bucket:
 class ShardedFusedAdamW(torch.optim.Optimizer):
     def __init__(self, params, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.01,
                  max_grad_norm: float = 1.0, group=None, master_weights: bool = False, wait_budget_us: int = 2_000_000,
-                 bucket_mb: float = 24.0, overlap: bool = True, rs_grid: int = 24):
+                 bucket_mb: float = 24.0, overlap: bool = True, rs_grid: int = 64):
         defaults = dict(lr=lr, betas=tuple(betas), eps=eps, weight_decay=weight_decay)
         super().__init__(params, defaults)
         if not (dist.is_available() and dist.is_initialized()):
@@ -82,6 +82,10 @@ class ShardedFusedAdamW(torch.optim.Optimizer):
         self.last_grad_norm: Optional[torch.Tensor] = None
         self.accumulating = False          # True on micro-steps that only accumulate (no reduce, no update)
         self.direct_writes = 0             # gradients that arrived already inside the buffer (diagnostic counter)
+        # with ``profile = True`` (eager steps only) CUDA events bracket every bucket's reduce-scatter and the tail
+        # of the step; ``profile_report()`` turns the last step's events into hidden / exposed times
+        self.profile = False
+        self._events: Dict[str, Any] = {}
 
     # ------------------------------------------------------------------------------------------ layout
     def _layout(self) -> None:
@@ -273,13 +277,24 @@ class ShardedFusedAdamW(torch.optim.Optimizer):
             self.side.wait_event(ev)                     # the bucket's gradients are complete on the main stream
             self._forked = True
         grid = self.rs_grid if overlapped else self.full_grid
+        prof = self.profile and not torch.cuda.is_current_stream_capturing()
+        if prof:
+            ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True), overlapped)
+            self._events.setdefault("buckets", {})[b.index] = ev
+            ready = torch.cuda.Event(enable_timing=True)
+            ready.record(main)
+            self._events.setdefault("ready", {})[b.index] = ready
         with torch.cuda.stream(stream):
+            if prof:
+                ev[0].record(stream)
             self.ctx.barrier()                           # every rank holds this bucket's gradients
             code = self.lib.cb_rs_bucket(self.grad_buf.ptrs, self.world, lo, hi, out.data_ptr(),
                                          self.partials[b.index * self.full_grid:].data_ptr(), grid,
                                          self.ctx.status.data_ptr(), stream.cuda_stream)
             _ext.check(code, "rs_bucket")
             _ext.count_launch(2)
+            if prof:
+                ev[1].record(stream)
 
     # ------------------------------------------------------------------------------------------ step
     def ensure_state(self) -> None:
@@ -315,10 +330,17 @@ class ShardedFusedAdamW(torch.optim.Optimizer):
                 self._reduce_bucket(b, overlapped=False)
         if self.fused:
             main = torch.cuda.current_stream(self.device)
+            prof = self.profile and not torch.cuda.is_current_stream_capturing()
+            if prof:
+                for name in ("bwd_end", "joined", "step_end"):
+                    self._events[name] = torch.cuda.Event(enable_timing=True)
+                self._events["bwd_end"].record(main)
             if self._forked:
                 ev = torch.cuda.Event()
                 ev.record(self.side)
                 main.wait_event(ev)                      # join: every bucket's reduce-scatter has finished
+            if prof:
+                self._events["joined"].record(main)
             s = main.cuda_stream
             st = self.ctx.status.data_ptr()
             _ext.check(self.lib.cb_sum_partials(self.partials.data_ptr(), self.partials.numel(), self.payload.data_ptr(), s),
@@ -334,6 +356,8 @@ class ShardedFusedAdamW(torch.optim.Optimizer):
             _ext.count_launch(2)
             self.ctx.barrier()
             self.last_grad_norm = self.norm_out[1]
+            if prof:
+                self._events["step_end"].record(main)
         else:
             self._step_reference()
         self._reset_pending()
@@ -382,6 +406,25 @@ class ShardedFusedAdamW(torch.optim.Optimizer):
         self.prepare_step()
         self.launch_step()
         return loss
+
+    def profile_report(self) -> Dict[str, Any]:
+        """Timings of the last profiled step (synchronises): per bucket the reduce-scatter's duration and how
+        long after the bucket's last gradient it finished; for the step the time the main stream spent waiting
+        for the side stream after the backward pass (exposed reduce-scatter) and the norm exchange + update +
+        all-gather tail."""
+        if not self._events or "bwd_end" not in self._events:
+            return {}
+        torch.cuda.synchronize(self.device)
+        e = self._events
+        rows = []
+        for i, (a, b, overlapped) in sorted(e.get("buckets", {}).items()):
+            rows.append({"bucket": i, "mb": round((self.buckets[i].hi - self.buckets[i].lo) * 2 / 2**20, 1),
+                         "overlapped": bool(overlapped), "rs_ms": round(a.elapsed_time(b), 4),
+                         "ready_to_done_ms": round(e["ready"][i].elapsed_time(b), 4),
+                         "done_before_bwd_end_ms": round(b.elapsed_time(e["bwd_end"]), 4)})
+        return {"buckets": rows, "exposed_wait_ms": round(e["bwd_end"].elapsed_time(e["joined"]), 4),
+                "tail_ms": round(e["joined"].elapsed_time(e["step_end"]), 4),
+                "hidden_rs_ms": round(sum(r["rs_ms"] for r in rows if r["done_before_bwd_end_ms"] >= 0), 4)}
 
     def zero_grad(self, set_to_none: bool = True) -> None:
         """Gradients live in the flat buffer: discarding them means that the next backward pass overwrites its

@@ -64,7 +64,8 @@ class Zero3Engine:
     """
 
     def __init__(self, model: nn.Module, lr: float = 1e-5, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.01,
-                 max_grad_norm: float = 1.0, group=None, wait_budget_us: int = 2_000_000, prefetch: bool = True):
+                 max_grad_norm: float = 1.0, group=None, wait_budget_us: int = 2_000_000, prefetch: bool = True,
+                 backend: str = "fused"):
         if not (dist.is_available() and dist.is_initialized()):
             raise RuntimeError("ZeRO-3 needs an initialised process group")
         self.model = model
@@ -74,10 +75,13 @@ class Zero3Engine:
         self.step_count = 0
         p0 = next(model.parameters())
         self.device, self.dtype = p0.device, p0.dtype
-        self.fused = self.device.type == "cuda"
-        if self.fused and self.dtype != torch.bfloat16:
-            raise ValueError("the fused ZeRO-3 path handles bf16 parameters")
-        self.prefetch = prefetch and self.fused
+        # "fused": gathers and reduce-scatters are peer-memory kernels; "nccl": the same schedule on
+        # all_gather_into_tensor / reduce_scatter_tensor (the comparison arm; the compute kernels are the same)
+        self.fused = self.device.type == "cuda" and backend == "fused"
+        self.nccl = self.device.type == "cuda" and backend != "fused"
+        if self.device.type == "cuda" and self.dtype != torch.bfloat16:
+            raise ValueError("the GPU ZeRO-3 paths handle bf16 parameters")
+        self.prefetch = prefetch and self.device.type == "cuda"
         layers = list(model.model.layers)
         outer = [p for n, p in model.named_parameters() if not n.startswith("model.layers.")]
         self.units: List[_Unit] = [_Unit("outer", outer, self.world)]
@@ -102,6 +106,15 @@ class Zero3Engine:
                                 + [ctypes.c_float, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p])):
                 fn = getattr(self.lib, name)
                 fn.argtypes, fn.restype = args, ctypes.c_int
+            self.side = torch.cuda.Stream(device=dev)
+        elif self.nccl:
+            from . import symm
+            self.lib = symm._lib()
+            fn = self.lib.cb_adamw_shard_local
+            fn.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong] + [ctypes.c_void_p] * 7 + [
+                ctypes.c_float, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
+            fn.restype = ctypes.c_int
+            self.status = _ext.status_buffer(dev)
             self.side = torch.cuda.Stream(device=dev)
         max_layer_n = max((u.n for u in self.layer_units), default=ALIGN * W)
         for u in self.units:
@@ -137,6 +150,11 @@ class Zero3Engine:
         else:
             self.gslot_t = [torch.zeros(max_layer_n, dtype=self.dtype, device=dev) for _ in range(2)]
             self.gouter_t = torch.zeros(self.units[0].n, dtype=self.dtype, device=dev)
+            if self.nccl:
+                self.hyper = torch.zeros(8, dtype=torch.float32, device=dev)
+                self.norm_out = torch.zeros(3, dtype=torch.float32, device=dev)
+                self.gathered = torch.zeros(self.world * 4, dtype=torch.float32, device=dev)
+                self.rs_out = torch.zeros(max(u.shard_n for u in self.units), dtype=self.dtype, device=dev)
         self.sq_total = torch.zeros(1, dtype=torch.float32, device=dev)
         if self.fused:
             torch.cuda.synchronize()
@@ -169,6 +187,16 @@ class Zero3Engine:
                 code = self.lib.cb_allgather_pull(u.shard.ptrs, self.world, u.shard_n, u.full.data_ptr(),
                                                   self.status.data_ptr(), stream.cuda_stream)
                 _ext.check(code, "allgather_pull")
+                if stream is not main:
+                    u.gather_event = torch.cuda.Event()
+                    u.gather_event.record(stream)
+        elif self.nccl:
+            main = torch.cuda.current_stream()
+            stream = self.side if (side and self.prefetch) else main
+            if stream is not main:
+                stream.wait_stream(main)
+            with torch.cuda.stream(stream):
+                dist.all_gather_into_tensor(u.full, u.shard_t, group=self.group)
                 if stream is not main:
                     u.gather_event = torch.cuda.Event()
                     u.gather_event.record(stream)
@@ -224,6 +252,12 @@ class Zero3Engine:
                                                 self.payload.data_ptr(), self.status.data_ptr(), _ext.stream_ptr())
             _ext.check(code, "rs_reduce_sqnorm")
             self.sq_total += self.payload[0]
+        elif self.nccl:
+            buf_t = self.gouter_t if u is self.units[0] else self.gslot_t[u.grad_slot]
+            out = self.rs_out[: u.shard_n]
+            dist.reduce_scatter_tensor(out, buf_t[: u.n], op=dist.ReduceOp.AVG, group=self.group)
+            u.reduced.copy_(out)
+            self.sq_total += u.reduced.pow(2).sum()
         else:
             buf_t = self.gouter_t if u is self.units[0] else self.gslot_t[u.grad_slot]
             g = buf_t[: u.n].float()
@@ -285,6 +319,21 @@ class Zero3Engine:
             return
         tot = self.sq_total.clone()
         dist.all_reduce(tot, group=self.group)
+        if self.nccl:
+            # the update kernel of the fused path, fed with the all-reduced squared norm in slot 0
+            self.hyper.copy_(torch.tensor([self.lr, self.weight_decay, b1, b2, self.eps, 1.0 - b1 ** t, 1.0 - b2 ** t, 0.0],
+                                          dtype=torch.float32), non_blocking=True)
+            self.gathered.zero_()
+            self.gathered[0:1].copy_(tot)
+            for u in self.units:
+                code = self.lib.cb_adamw_shard_local(u.shard_t.data_ptr(), self.world, u.shard_n, u.reduced.data_ptr(),
+                                                     u.exp_avg.data_ptr(), u.exp_avg_sq.data_ptr(), None,
+                                                     u.chunk_group.data_ptr(), self.hyper.data_ptr(),
+                                                     self.gathered.data_ptr(), float(self.max_grad_norm or 0.0),
+                                                     self.norm_out.data_ptr(), self.status.data_ptr(), _ext.stream_ptr())
+                _ext.check(code, "adamw_shard_local")
+            self.last_grad_norm = self.norm_out[1]
+            return
         norm = tot.sqrt()
         clip = (self.max_grad_norm / (norm + 1e-6)).clamp(max=1.0) if self.max_grad_norm else torch.ones_like(norm)
         for u in self.units:

@@ -220,8 +220,11 @@ class ChronicalsTrainer:
         self.num_params = sum(p.numel() for p in self.model.parameters())
         self.flops_per_token = 6 * self.num_params
         # with several ranks the step is captured only when it contains no NCCL call (sharded fused optimizer)
+        # (sharded fused optimizer, or adapter buckets reduced by the peer-memory all-reduce)
+        no_nccl_in_step = self.world_size == 1 or self._sharded_optimizer or (
+            self.dp is not None and getattr(self.dp, "_fused", None) is not None)
         self.use_cuda_graphs = bool(a.use_cuda_graphs) and on_gpu and self.is_native_model \
-            and a.gradient_accumulation_steps == 1 and (self.world_size == 1 or self._sharded_optimizer) \
+            and a.gradient_accumulation_steps == 1 and no_nccl_in_step \
             and not self.tp_model and self.zero3 is None
         self._active_optimizations["cuda_graphs"] = self.use_cuda_graphs
         # host-side failure detection: heartbeat over the process-group store, checked before each step
@@ -417,6 +420,17 @@ class ChronicalsTrainer:
     def _graphed_step(self, batch: Any) -> torch.Tensor:
         f = _batch_fields(batch)
         ids = f["input_ids"]
+        max_docs = int(self._get("cuda_graph_max_documents", 0) or 0)
+        if max_docs > 0 and isinstance(f.get("cu_seqlens"), torch.Tensor):
+            # packed batches hold a varying number of documents: pad the boundary list to a fixed length with
+            # empty documents (the attention kernels skip them) so that one captured graph serves every batch
+            cu = f["cu_seqlens"]
+            if cu.numel() - 1 > max_docs:
+                raise ValueError(f"batch holds {cu.numel() - 1} documents, cuda_graph_max_documents is {max_docs}")
+            f = dict(f)
+            f["cu_seqlens"] = torch.cat((cu, cu[-1:].expand(max_docs + 1 - cu.numel())))
+            f["max_seqlen"] = int(self.args.max_seq_length)
+            f["seqlens_host"] = None
         key = (tuple(ids.shape), tuple(f["cu_seqlens"].shape) if isinstance(f.get("cu_seqlens"), torch.Tensor) else None,
                f.get("max_seqlen"), tuple(f["seqlens_host"]) if f.get("seqlens_host") is not None and
                not isinstance(f.get("cu_seqlens"), torch.Tensor) else None)

@@ -32,7 +32,11 @@ def main():
         for n, p in full.named_parameters():
             if p.dim() == 1:
                 p.add_((0.1 * torch.randn(p.shape, generator=g)).to(p.dtype).to(dev))
-    tp = TPState(backend="fused" if backend == "fused" else "nccl")
+    tp = TPState(backend="fused" if backend.startswith("fused") else "nccl")
+    if backend == "fused_pair":
+        tp.pair_min_dim = 0                        # the CTA-pair kernels also on these small projections
+    elif backend == "fused":
+        tp.pair_gemm = False
     model = TensorParallelCausalLM.from_full(full, tp)
     g = torch.Generator().manual_seed(2)
     ids = torch.randint(0, cfg.vocab_size, (B, S), generator=g).to(dev)

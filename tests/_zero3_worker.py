@@ -26,7 +26,7 @@ def main():
     model = build_model(cfg, dtype=dtype, device=dev, seed=0)
     ref = build_model(cfg, dtype=dtype, device=dev, seed=0)
     hyper = dict(lr=1e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.01)
-    eng = Zero3Engine(model, max_grad_norm=1.0, **hyper)
+    eng = Zero3Engine(model, max_grad_norm=1.0, backend="nccl" if backend == "nccl" else "fused", **hyper)
     if use_cuda:
         from chronicals_b200.optimizers import FusedAdamW
         opt = FusedAdamW(ref.parameters(), max_grad_norm=1.0, **hyper)

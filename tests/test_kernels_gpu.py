@@ -16,11 +16,22 @@ def _rand(*shape, scale=1.0, dtype=torch.bfloat16, seed=0):
     return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
 
 
-def _close(a, b, rtol=2e-2, atol=2e-2, what=""):
+def _close(a, b, rtol=2e-2, atol=2e-2, what="", l2=1e-2):
+    """Three bounds: the largest error against the largest magnitude, the relative L2 error of the whole tensor,
+    and an element-wise bound on a random sample that scales with each element's own row (so rows or columns of
+    small magnitude cannot hide behind large ones)."""
     a, b = a.float(), b.float()
     err = (a - b).abs().max().item()
     ref_mag = b.abs().max().item()
     assert err <= atol + rtol * ref_mag, f"{what}: max err {err:.4g} vs magnitude {ref_mag:.4g}"
+    rel = ((a - b).norm() / b.norm().clamp_min(1e-30)).item()
+    assert rel <= l2 or (a - b).abs().max().item() <= atol, f"{what}: relative L2 error {rel:.4g}"
+    if b.dim() == 2 and b.numel() > 0:
+        g = torch.Generator(device="cpu").manual_seed(1234)
+        rows = torch.randint(0, b.shape[0], (min(64, b.shape[0]),), generator=g).to(b.device)
+        row_mag = b[rows].abs().amax(dim=1, keepdim=True)
+        bad = ((a[rows] - b[rows]).abs() > atol + 4 * rtol * row_mag).sum().item()
+        assert bad == 0, f"{what}: {bad} sampled elements beyond their row's tolerance"
 
 
 def test_library_loaded_and_status_clean():
@@ -180,6 +191,30 @@ def test_linear_cross_entropy_fwd_bwd(T, H, V, smoothing, z):
     assert abs(loss.item() - lr_.item()) < 2e-3 * max(1.0, abs(lr_.item())), (loss.item(), lr_.item())
     _close(h.grad, hr.grad, rtol=3e-2, atol=1e-5, what="cce dh")
     _close(w.grad, wr.grad, rtol=3e-2, atol=1e-5, what="cce dw")
+    _ext.check_status()
+
+
+@pytest.mark.parametrize("V", [32000, 151936])
+def test_linear_cross_entropy_full_vocabularies_against_fp32(V):
+    """The vocabulary sizes of the benchmark configurations (4 and 38 splits of the forward, 4 and 19 chunks of the
+    backward), a token count that is not a multiple of the tile, labels in the first and last vocabulary rows."""
+    T, H = 200, 256
+    h = _rand(T, H).requires_grad_()
+    w = _rand(V, H, scale=0.05, seed=1).requires_grad_()
+    y = torch.randint(0, V, (T,), device=DEV)
+    y[0], y[1], y[2] = 0, V - 1, -100
+    loss = ops.linear_cross_entropy(h, w, y, None, -100, 0.0, 1e-4)
+    loss.backward()
+    hr, wr = h.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    want = ref.linear_cross_entropy_dense(hr, wr, y, None, -100, 0.0, 1e-4)
+    want.backward()
+    assert abs(loss.item() - want.item()) < 2e-3 * max(1.0, abs(want.item())), (loss.item(), want.item())
+    _close(h.grad, hr.grad, rtol=3e-2, atol=1e-5, what="cce dh", l2=2e-2)
+    rel = ((w.grad.float() - wr.grad).norm() / wr.grad.norm()).item()
+    assert rel < 2e-2, rel
+    # the label rows carry the largest weight gradients: check them element by element
+    rows = y[y >= 0].unique()
+    _close(w.grad[rows], wr.grad[rows], rtol=3e-2, atol=1e-6, what="cce dw label rows", l2=2e-2)
     _ext.check_status()
 
 

@@ -40,10 +40,11 @@ def test_symmetric_barrier_sharded_adamw_and_bounded_wait(tmp_path):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("backend,port", [("nccl", 29543), ("fused", 29544)])
+@pytest.mark.parametrize("backend,port", [("nccl", 29543), ("fused", 29544), ("fused_pair", 29545)])
 def test_tensor_parallel_matches_single_gpu(tmp_path, backend, port):
     """TP=2 with sequence parallelism and the vocab-parallel loss against the unsharded model on one GPU;
-    ``fused`` runs the push all-gather, the panel-waiting GEMM and the GEMM with the reduce-scatter epilogue."""
+    ``fused`` runs the push all-gather, the panel-waiting GEMM and the GEMM with the reduce-scatter epilogue on
+    the single-CTA kernel, ``fused_pair`` the same two GEMMs on CTA pairs."""
     res = _run_worker(tmp_path, 2, "_tp_worker.py", port, extra=(backend, "untied"))
     assert max(abs(a - b) for a, b in zip(res["loss_tp"], res["loss_full"])) < 3e-2, res
     assert res["grad_rel_err_max"] < 6e-2, res
@@ -51,9 +52,11 @@ def test_tensor_parallel_matches_single_gpu(tmp_path, backend, port):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_zero3_fused_matches_unsharded_optimizer(tmp_path):
-    """ZeRO-3 with the pull all-gather, pull reduce-scatter and sharded AdamW kernels against the
-    unsharded fused AdamW on the joint batch (bf16 parameters, so a few ulps of drift are allowed)."""
-    res = _run_worker(tmp_path, 2, "_zero3_worker.py", 29548, extra=("fused",))
+@pytest.mark.parametrize("backend,port", [("fused", 29548), ("nccl", 29549)])
+def test_zero3_fused_matches_unsharded_optimizer(tmp_path, backend, port):
+    """ZeRO-3 with the pull all-gather, pull reduce-scatter and sharded AdamW kernels (``fused``), and the same
+    schedule on NCCL collectives (``nccl``, the comparison arm), against the unsharded fused AdamW on the joint
+    batch (bf16 parameters, so a few ulps of drift are allowed)."""
+    res = _run_worker(tmp_path, 2, "_zero3_worker.py", port, extra=(backend,))
     assert max(abs(a - b) for a, b in zip(res["zero3_losses"], res["ref_losses"])) < 3e-2, res
     assert res["max_param_diff"] < 2e-2, res
