@@ -309,6 +309,70 @@ def benchmark_huggingface(a) -> BenchmarkResult:
     return _finish("huggingface", a, n_params, n_params, t, transformers=transformers.__version__)
 
 
+class _PlainLoRALinear(torch.nn.Module):
+    """``nn.Linear`` with a frozen weight and a rank-r adapter, written with stock PyTorch operators only
+    (what PEFT's ``LoraLayer`` computes): ``y = W x + (alpha / r) * B (A x)``."""
+
+    def __init__(self, base: torch.nn.Linear, rank: int, alpha: float):
+        super().__init__()
+        self.base = base
+        for p in self.base.parameters():
+            p.requires_grad_(False)
+        dev, dt = base.weight.device, base.weight.dtype
+        self.lora_A = torch.nn.Parameter(torch.empty(rank, base.in_features, device=dev, dtype=dt))
+        self.lora_B = torch.nn.Parameter(torch.zeros(base.out_features, rank, device=dev, dtype=dt))
+        torch.nn.init.kaiming_uniform_(self.lora_A, a=math.sqrt(5))
+        self.scaling = alpha / rank
+
+    def forward(self, x):
+        return self.base(x) + torch.nn.functional.linear(torch.nn.functional.linear(x, self.lora_A), self.lora_B) * self.scaling
+
+
+def benchmark_huggingface_lora(a) -> BenchmarkResult:
+    """The library baseline of the LoRA comparison that runs offline: transformers' implementation of the same
+    architecture (random init, SDPA attention) with plain PyTorch LoRA modules (rank / alpha as in the other LoRA
+    methods, all seven projections), frozen base, torch fused AdamW on the adapters.  It stands where the
+    reference's suite puts Unsloth / PEFT, which need a model hub."""
+    try:
+        import transformers
+        from chronicals_b200 import ChronicalsConfig
+    except Exception as e:                               # pragma: no cover
+        return BenchmarkResult("huggingface_lora", status="skipped", reason=f"transformers not importable: {e}")
+    dev = _device()
+    cfg = ChronicalsConfig.from_model_name(a.model)
+    hf_cfg = transformers.Qwen2Config(
+        vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size, intermediate_size=cfg.intermediate_size,
+        num_hidden_layers=cfg.num_hidden_layers, num_attention_heads=cfg.num_attention_heads,
+        num_key_value_heads=cfg.num_key_value_heads, max_position_embeddings=max(cfg.max_position_embeddings, a.seq_length),
+        rms_norm_eps=cfg.rms_norm_eps, rope_theta=cfg.rope_theta, tie_word_embeddings=cfg.tie_word_embeddings,
+        attn_implementation="sdpa")
+    torch.manual_seed(0)
+    model = transformers.AutoModelForCausalLM.from_config(hf_cfg).to(dev, torch.bfloat16 if dev.type == "cuda" else torch.float32)
+    for p in model.parameters():
+        p.requires_grad_(False)
+    targets = ("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj")
+    for module in list(model.modules()):
+        for name, child in list(module.named_children()):
+            if name in targets and isinstance(child, torch.nn.Linear):
+                setattr(module, name, _PlainLoRALinear(child, a.lora_rank, 2.0 * a.lora_rank))
+    n_params = sum(p.numel() for p in model.parameters())
+    adapters = [p for p in model.parameters() if p.requires_grad]
+    opt = torch.optim.AdamW(adapters, lr=2e-4, weight_decay=0.0, fused=dev.type == "cuda")
+    data = load_alpaca_dataloader(cfg.vocab_size, a.batch_size, a.seq_length, 4, seed=0)
+    data = [{k: v.to(dev) for k, v in b.items()} for b in data]
+
+    def step(i):
+        loss = model(**data[i % len(data)]).loss
+        loss.backward()
+        torch.nn.utils.clip_grad_norm_(adapters, 1.0)
+        opt.step()
+        opt.zero_grad(set_to_none=True)
+        return loss
+    t = _time_steps(step, a, a.batch_size * a.seq_length)
+    return _finish("huggingface_lora", a, n_params, sum(p.numel() for p in adapters), t, lora_rank=a.lora_rank,
+                   transformers=transformers.__version__)
+
+
 def _skipped(name: str, package: str) -> Callable[[Any], BenchmarkResult]:
     def run(a) -> BenchmarkResult:
         try:
@@ -325,6 +389,7 @@ METHODS: Dict[str, Callable[[Any], BenchmarkResult]] = {
     "chronicals_packed": lambda a: benchmark_chronicals(a, packed=True),
     "chronicals_lora": benchmark_chronicals_lora,
     "huggingface": benchmark_huggingface,
+    "huggingface_lora": benchmark_huggingface_lora,
     "native_pytorch": benchmark_native_pytorch,
     "unsloth": _skipped("unsloth", "unsloth"),
     "liger": _skipped("liger", "liger_kernel"),

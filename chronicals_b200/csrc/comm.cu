@@ -94,6 +94,7 @@ rs_reduce_sqnorm_kernel(PeerTable grads, int W, long long lo, long long hi, floa
                         float* __restrict__ partials, int* status) {
   __shared__ float sred[COMM_THREADS / 32];
   float sq = 0.f;
+  CB_DEBUG_CHECK_ST(status, ((lo | hi) & 7) == 0 && hi >= lo, CB_DBG_COMM_SLICE, lo);
   if (status[0] == 0) {
     const float inv = 1.f / static_cast<float>(W);
     const long long nvec = (hi - lo) >> 3;
@@ -150,6 +151,7 @@ rs_bucket_kernel(PeerTable grads, int W, long long lo, long long hi, float* __re
                  float* __restrict__ partials, int* status) {
   __shared__ float sred[RSB_THREADS / 32];
   float sq = 0.f;
+  CB_DEBUG_CHECK_ST(status, ((lo | hi) & 7) == 0 && hi >= lo, CB_DBG_COMM_SLICE, lo);
   if (status[0] == 0) {
     const float inv = 1.f / static_cast<float>(W);
     const long long nvec = (hi - lo) >> 3;

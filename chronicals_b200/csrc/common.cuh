@@ -29,6 +29,24 @@ enum : int {
   CB_ERR_WAIT_MISC = 301,
 };
 
+// Optional index checks (build with -DCHRONICALS_DEBUG_BOUNDS, i.e. CHRONICALS_DEBUG_BOUNDS=1 in the environment
+// of csrc/build.py) for the kernels that receive the status words: the first violated check leaves its code in
+// status[8] and the offending value in status[9]; nothing traps and the kernel carries on.  Codes:
+//   411  a TMA store / reduce coordinate is negative or its x is not on a 16-byte boundary
+//   412  a peer store of the reduce-scatter epilogue falls outside the owner's row range
+//   421  an attention output row lies outside [0, T)
+//   431  a reduce-scatter / all-gather slice is not a multiple of 8 elements or is reversed
+enum : int { CB_DBG_TMA_COORD = 411, CB_DBG_PUSH_ROW = 412, CB_DBG_ATTN_ROW = 421, CB_DBG_COMM_SLICE = 431 };
+#ifdef CHRONICALS_DEBUG_BOUNDS
+#define CB_DEBUG_CHECK_ST(status, cond, code, value)                                       \
+  do {                                                                                     \
+    if (!(cond) && atomicCAS((status) + 8, 0, static_cast<int>(code)) == 0)                \
+      (status)[9] = static_cast<int>(value);                                               \
+  } while (0)
+#else
+#define CB_DEBUG_CHECK_ST(status, cond, code, value) do { } while (0)
+#endif
+
 #ifndef CB_WAIT_LIMIT_NS
 #define CB_WAIT_LIMIT_NS 1000000000ull   // 1 s: far above any legitimate in-kernel wait
 #endif

@@ -425,6 +425,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             } else {
             fence_async_smem();
             __syncwarp();
+            CB_DEBUG_CHECK_ST(g.status, colbase >= 0 && row0w >= 0 && (colbase * (g.out_fp32 ? 4 : 2)) % 16 == 0,
+                              CB_DBG_TMA_COORD, colbase);
             if (lane == 0 && row0w < g.M) {          // a box that starts past the last row has nothing to write
               if (g.items_per_ksplit > 0) tma_reduce_add_2d(&tmC, stg + buf * 4096, colbase, row0w);   // split K: sum the ranges
               else tma_store_2d(&tmC, stg + buf * 4096, colbase, row0w);

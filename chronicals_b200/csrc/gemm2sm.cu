@@ -409,6 +409,8 @@ gemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     };
     // one staging buffer -> global memory through `map` (store, or fp32 add for partial tiles)
     auto flush = [&](const CUtensorMap* map, int x, int y, bool add, bool active) {
+      CB_DEBUG_CHECK_ST(g.status, !active || (x >= 0 && y >= 0 && (x * ((add || g.out_fp32) ? 4 : 2)) % 16 == 0),
+                        CB_DBG_TMA_COORD, x);
       fence_async_smem();
       __syncwarp();
       if (lane == 0 && active) {
@@ -461,6 +463,7 @@ gemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         for (int i = 0; i < 8; ++i) {
           const int rr = (lane >> 3) + 4 * i;
           const int grow = row0w + rr;
+          CB_DEBUG_CHECK_ST(g.status, grow / g.push_rows == row0w / g.push_rows || grow >= g.M, CB_DBG_PUSH_ROW, grow);
           if (grow < g.M && ccol < g.N) {
             const uint4 u = *reinterpret_cast<const uint4*>(stg + buf * 4096 + rr * 128 + ((chunk ^ (rr & 7)) << 4));
             *reinterpret_cast<uint4*>(push_base + static_cast<long long>(grow) * g.ldc + ccol) = u;

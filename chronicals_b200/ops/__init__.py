@@ -24,6 +24,10 @@ __all__ = [
 ]
 
 
+# how often an op left the hand-written kernels for a library routine on a CUDA device (by reason)
+FALLBACKS: dict = {}
+
+
 def _fast(*tensors: torch.Tensor) -> bool:
     """True when the CUDA kernels handle these tensors (all CUDA + bf16)."""
     if _ext.reference_forced():
@@ -63,7 +67,13 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         assert not accumulate
         out = torch.empty(M, N, dtype=out_dtype, device=a.device)
     if not (_gemm_ok(a) and _gemm_ok(b) and out.stride(1) == 1):
-        # shapes the TMA path cannot address (row pitch not a multiple of 16 bytes): library fallback
+        # shapes the TMA path cannot address (row pitch not a multiple of 16 bytes): library fallback, counted
+        # and reported once so that it never happens unnoticed
+        FALLBACKS["gemm_unaligned"] = FALLBACKS.get("gemm_unaligned", 0) + 1
+        if FALLBACKS["gemm_unaligned"] == 1 and a.is_cuda:
+            import warnings
+            warnings.warn(f"ops.gemm: operand pitch not 16-byte aligned (shapes {tuple(a.shape)} x {tuple(b.shape)}); "
+                          "this product runs as an fp32 library matmul (see ops.FALLBACKS)", RuntimeWarning, stacklevel=2)
         A = a.t() if a_mn else a
         B = b if b_mn else b.t()
         r = (A.float() @ B.float())

@@ -92,7 +92,17 @@ def debug_word():
     code 401 = token id, 402 = rotary position, 403 = label out of range; reading clears the word."""
     buf = (ctypes.c_longlong * 2)()
     rc = lib().cb_debug_word(buf)
-    return rc == 1, int(buf[0]), int(buf[1])
+    code, value = int(buf[0]), int(buf[1])
+    if code == 0:
+        # checks of the kernels that carry the status words (GEMM epilogues, attention, collectives: codes 411-431)
+        # leave their finding in status[8:10] of the device they ran on
+        for st in _STATUS.values():
+            vals = st[8:10].tolist()
+            if vals[0] != 0:
+                code, value = int(vals[0]), int(vals[1])
+                st[8:10].zero_()
+                break
+    return rc == 1, code, value
 
 
 def reference_forced() -> bool:

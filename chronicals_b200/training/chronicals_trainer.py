@@ -444,6 +444,9 @@ class ChronicalsTrainer:
         if hasattr(self.optimizer, "prepare_step"):
             self.optimizer.prepare_step()
         g["graph"].replay()
+        # the update ran inside the graph: tell torch's scheduler bookkeeping that an optimizer step happened
+        # (it otherwise warns that lr_scheduler.step() came first)
+        self.optimizer._opt_called = True
         return g["loss"]
 
     def _capture_graph(self, f: Dict[str, Any], key) -> None:

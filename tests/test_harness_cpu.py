@@ -70,3 +70,14 @@ def test_fp8_mode_benchmark_runs_all_three_modes_on_cpu():
     assert [r["mode"] for r in rows] == ["bf16", "rowwise", "mxfp8"]
     base = rows[0]["loss"]
     assert all(abs(r["loss"] - base) < 0.2 for r in rows), rows       # quantisation noise only
+
+
+def test_lora_comparison_runs_both_arms_offline():
+    out = _run(["benchmarks/unsloth_max_benchmark.py", "--model", "tiny-qwen2", "--steps", "2", "--warmup_steps", "1",
+                "--batch_size", "2", "--seq_length", "64", "--lora_rank", "4"])
+    rows = [json.loads(l) for l in out.splitlines() if l.startswith("{")]
+    by = {r["method"]: r for r in rows}
+    assert by["chronicals_lora_packed"]["status"] == "ok" and by["huggingface_lora"]["status"] == "ok"
+    assert by["huggingface_lora"]["trainable_params"] < by["huggingface_lora"]["n_params"]
+    assert by["unsloth_max"]["status"] == "skipped"
+    assert abs(by["chronicals_lora_packed"]["final_loss"] - by["huggingface_lora"]["final_loss"]) < 0.5

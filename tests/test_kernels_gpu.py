@@ -595,6 +595,32 @@ def test_gemm_cta_pair_stream_k_matches_fp32_and_whole_tiles(a_mn, b_mn, M, N, K
     assert torch.equal(split, again)
 
 
+@pytest.mark.parametrize("M,N,K,a_mn,b_mn", [(2048, 896, 1536, False, False), (1024, 1152, 2048, False, True),
+                                              (896, 640, 4096, True, True)])
+def test_gemm_result_does_not_depend_on_tiling_stage_count_or_work_order(M, N, K, a_mn, b_mn):
+    """The same product through every schedule the dispatcher can pick: single-CTA tiles of 128 and 256 columns
+    (6 and 4 pipeline stages), CTA-pair tiles of 256 / 224 / 192 columns, whole tiles and tiles cut along K.  All
+    of them accumulate each output element over the full K in fp32 and round once, so they agree with the fp32
+    product and, element by element, with each other to one bf16 rounding step."""
+    g = torch.Generator().manual_seed(21)
+    a = (torch.randn((K, M) if a_mn else (M, K), generator=g) * 0.5).to(torch.bfloat16).cuda()
+    b = (torch.randn((K, N) if b_mn else (N, K), generator=g) * 0.5).to(torch.bfloat16).cuda()
+    A = a.float().t() if a_mn else a.float()
+    B = b.float() if b_mn else b.float().t()
+    want = A @ B
+    outs = {"single128": ops.gemm(a, b, a_mn=a_mn, b_mn=b_mn, block_n=128),
+            "single256": ops.gemm(a, b, a_mn=a_mn, b_mn=b_mn, block_n=256)}
+    for bn in (256, 224, 192):
+        outs[f"pair{bn}"] = ops.gemm(a, b, a_mn=a_mn, b_mn=b_mn, pair_flags=(bn << 8) | 1)
+        outs[f"pair{bn}_split"] = ops.gemm(a, b, a_mn=a_mn, b_mn=b_mn, pair_flags=(bn << 8) | 2)
+    _ext.check_status()
+    mag = want.abs().max().item()
+    base = outs["single128"].float()
+    for name, o in outs.items():
+        assert _rel_l2(o, want) < 4e-3, name
+        assert (o.float() - base).abs().max().item() <= 2.0 ** -7 * mag, name
+
+
 def test_gemm_cta_pair_stream_k_epilogues():
     """Bias, residual, accumulate (bf16 and fp32 outputs) on a shape whose tiles are split along K."""
     from chronicals_b200 import ops

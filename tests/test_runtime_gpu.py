@@ -146,3 +146,22 @@ def test_training_step_is_run_to_run_deterministic_where_the_kernels_promise_it(
     for a, b in zip(runs[0][1], runs[1][1]):
         assert (a - b).abs().max().item() <= 2.0 ** -6 * max(a.abs().max().item(), 1e-12)
     _ext.check_status()
+
+
+def test_index_checks_stay_silent_over_a_training_step():
+    """After a full step (GEMM epilogues, attention, fused loss, optimizer) no bounds / alignment check has fired.
+    In the default build the checks are compiled out and the word is always clear; a library built with
+    CHRONICALS_DEBUG_BOUNDS=1 evaluates them in every kernel that carries the status words."""
+    from chronicals_b200 import ChronicalsTrainer, TrainingConfig
+    cfg = _tiny(2)
+    model = build_model(cfg, dtype=torch.bfloat16, device=DEV, seed=0)
+    a = TrainingConfig(output_dir="/tmp/cb_dbg", gradient_accumulation_steps=1, save_steps=0, visual_reporting=False,
+                       use_gradient_checkpointing=False, fp8=False, use_cuda_graphs=False, use_sequence_packing=False)
+    a.save_final = a.log_jsonl = False
+    tr = ChronicalsTrainer(model, a, None)
+    ids = torch.randint(0, cfg.vocab_size, (3, 200), device=DEV)         # token count that is not a tile multiple
+    tr.training_step({"input_ids": ids, "labels": ids})
+    torch.cuda.synchronize()
+    _ext.check_status()
+    compiled, code, value = _ext.debug_word()
+    assert code == 0, (compiled, code, value)
