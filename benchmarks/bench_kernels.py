@@ -283,12 +283,27 @@ def main():
         _ext.check_status()
         print("ok")
         return
+    if args.one and args.one.startswith("fp8:"):
+        from chronicals_b200.utils.fp8_utils import fp8_rowwise_matmul, rowwise_quantize_e4m3
+        M, N, K = GEMM_CASES[args.one.split(":", 1)[1]][:3]
+        aq, asc = rowwise_quantize_e4m3(bf(M, K))
+        bq, bsc = rowwise_quantize_e4m3(bf(N, K))
+        for _ in range(3):
+            fp8_rowwise_matmul(aq, asc, bq, bsc)
+        torch.cuda.synchronize()
+        _ext.check_status()
+        print("ok")
+        return
     if args.one:
-        M, N, K, a_mn, b_mn = GEMM_CASES[args.one]
+        # "<case>": the dispatcher's choice; "single:<case>": the single-CTA kernel; "pair:<case>": CTA pairs, whole
+        # tiles; "split:<case>": CTA pairs with the last round cut along K
+        mode, _, case = args.one.rpartition(":")
+        M, N, K, a_mn, b_mn = GEMM_CASES[case]
         a, b = gemm_inputs(M, N, K, a_mn, b_mn)
         out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+        kw = {"single": {"block_n": 256}, "pair": {"pair_flags": 1}, "split": {"pair_flags": 2}}.get(mode, {})
         for _ in range(3):
-            ops.gemm(a, b, a_mn=bool(a_mn), b_mn=bool(b_mn), out=out)
+            ops.gemm(a, b, a_mn=bool(a_mn), b_mn=bool(b_mn), out=out, **kw)
         torch.cuda.synchronize()
         _ext.check_status()
         print("ok")

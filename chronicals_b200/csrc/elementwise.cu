@@ -129,7 +129,7 @@ rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ res, con
 // dw[n] = sum_rows dy*xhat, accumulated per block in registers and written as one
 // [gridDim.x, N] fp32 partial (reduced by rmsnorm_dw_reduce_kernel).
 template <int TPR, int VPL>
-__global__ void __launch_bounds__(EW_THREADS)
+__global__ void __launch_bounds__(EW_THREADS, 2)
 rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ h, const bf16* __restrict__ w,
                    const float* __restrict__ rstd_in, const bf16* __restrict__ dres_in, bf16* __restrict__ dx,
                    float* __restrict__ dw_part, int M, int N, float offset) {
@@ -148,28 +148,39 @@ rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ h, cons
   for (int base = blockIdx.x * RPB; base < M; base += gridDim.x * RPB) {
     const int row = base + group;
     const bool active = row < M;
-    float g[VPL][8], xh[VPL][8];
+    // One memory round trip per row: dy, h and the pass-through gradient are all requested before anything is
+    // consumed, and stay packed (bf16) in registers until the second pass converts them again.
+    uint4 dyr[VPL], hr[VPL], rr[VPL];
     float dot = 0.f;
     float rstd = 0.f;
+    const uint4* wp = reinterpret_cast<const uint4*>(w);
     if (active) {
       rstd = rstd_in[row];
       const uint4* dyp = reinterpret_cast<const uint4*>(dy + static_cast<long long>(row) * N);
       const uint4* hp = reinterpret_cast<const uint4*>(h + static_cast<long long>(row) * N);
-      const uint4* wp = reinterpret_cast<const uint4*>(w);
+      const uint4* rp = dres_in ? reinterpret_cast<const uint4*>(dres_in + static_cast<long long>(row) * N) : nullptr;
 #pragma unroll
       for (int i = 0; i < VPL; ++i) {
         const int v = t + i * TPR;
         if (v < nvec) {
-          float d[8], wf[8];
-          unpack8(dyp[v], d);
-          unpack8(hp[v], xh[i]);
+          dyr[i] = dyp[v];
+          hr[i] = hp[v];
+          if (rp) rr[i] = rp[v];
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) {
+        const int v = t + i * TPR;
+        if (v < nvec) {
+          float d[8], x[8], wf[8];
+          unpack8(dyr[i], d);
+          unpack8(hr[i], x);
           unpack8(wp[v], wf);
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
-            xh[i][j] *= rstd;
-            g[i][j] = d[j] * (wf[j] + offset);
-            dot += g[i][j] * xh[i][j];
-            dwacc[i][j] += d[j] * xh[i][j];
+            const float xh = x[j] * rstd;
+            dot += d[j] * (wf[j] + offset) * xh;
+            dwacc[i][j] += d[j] * xh;
           }
         }
       }
@@ -177,18 +188,20 @@ rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ h, cons
     dot = group_sum<TPR>(dot, sred);
     if (active) {
       const float mean = dot / static_cast<float>(N);
-      const uint4* rp = dres_in ? reinterpret_cast<const uint4*>(dres_in + static_cast<long long>(row) * N) : nullptr;
       uint4* dxp = reinterpret_cast<uint4*>(dx + static_cast<long long>(row) * N);
 #pragma unroll
       for (int i = 0; i < VPL; ++i) {
         const int v = t + i * TPR;
         if (v < nvec) {
-          float o[8];
+          float d[8], x[8], wf[8], o[8];
+          unpack8(dyr[i], d);
+          unpack8(hr[i], x);
+          unpack8(wp[v], wf);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] = rstd * (g[i][j] - xh[i][j] * mean);
-          if (rp) {
+          for (int j = 0; j < 8; ++j) o[j] = rstd * (d[j] * (wf[j] + offset) - x[j] * rstd * mean);
+          if (dres_in) {
             float r[8];
-            unpack8(rp[v], r);
+            unpack8(rr[i], r);
 #pragma unroll
             for (int j = 0; j < 8; ++j) o[j] += r[j];
           }
@@ -628,8 +641,8 @@ int cb_rmsnorm_bwd(const void* dy, const void* h, const void* w, const float* rs
 // out[n] (bf16) = sum over rows of x[row, n]; x bf16 [M, N] with pitch ld (N and ld multiples of 8);
 // part: fp32 scratch of cb_colsum_blocks(M) * N elements.
 int cb_colsum_blocks(long long M) {
-  long long b = (M + 63) / 64;
-  const long long cap = static_cast<long long>(sm_count()) * 2;
+  long long b = (M + 15) / 16;
+  const long long cap = static_cast<long long>(sm_count()) * 4;
   if (b > cap) b = cap;
   return static_cast<int>(b < 1 ? 1 : b);
 }

@@ -50,6 +50,10 @@ constexpr int MAX_SK_TILES = 2 * 74 + 8;         // slots the counters are sized
 struct Args {
   int M, N, K;
   int num_m_pairs, num_n_tiles, num_tiles, num_kb;
+  // Second operand pair: C = A B^T + A2 B2^T.  Its k-blocks follow the num_kb1 k-blocks of the first pair in the
+  // same accumulator (num_kb counts both), which is how a low-rank adapter's  (x A^T) B^T  joins the frozen
+  // projection without a second pass over the output.  num_kb1 == num_kb: no second pair.
+  int num_kb1;
   // stream-K region: tiles [0, sk_tiles) are cut along K; pair p owns sk_q (+1 if p < sk_r) consecutive
   // k-blocks of the region's tile-major list.  sk_tiles == 0: whole tiles only.
   int sk_tiles, sk_q, sk_r;
@@ -161,7 +165,8 @@ __device__ __forceinline__ int pair_of_unit(const Args& g, long long u) {
 template <int BN, int A_MN, int B_MN, int KIND, int TP = 0>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-               const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmW, const Args g) {
+               const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmW,
+               const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2, const Args g) {
   constexpr int BNH = BN / 2;
   constexpr uint32_t TMEM_COLS = 512;                                    // two accumulators, 256 columns apart
   constexpr uint32_t IDESC = KIND ? umma_idesc_fp8(2 * BM, BN, 0, 0)
@@ -269,17 +274,21 @@ gemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const uint32_t bar = full_leader + stage * 8;
           uint8_t* a_dst = sA + stage * A_BYTES;
           uint8_t* b_dst = sB + stage * B_BYTES;
+          const bool second = kb >= g.num_kb1;                 // k-blocks of the second operand pair
+          const CUtensorMap* ma = second ? &tmA2 : &tmA;
+          const CUtensorMap* mb = second ? &tmB2 : &tmB;
+          const int kk = second ? kb - g.num_kb1 : kb;
           if (A_MN == 0) {
-            tma_load_2d_pair(a_dst, &tmA, bar, kb * BKE, a_row);
+            tma_load_2d_pair(a_dst, ma, bar, kk * BKE, a_row);
           } else {
 #pragma unroll
-            for (int j = 0; j < BM / 64; ++j) tma_load_2d_pair(a_dst + j * 8192, &tmA, bar, a_row + j * 64, kb * BK);
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d_pair(a_dst + j * 8192, ma, bar, a_row + j * 64, kk * BK);
           }
           if (B_MN == 0) {
-            tma_load_2d_pair(b_dst, &tmB, bar, kb * BKE, b_row);
+            tma_load_2d_pair(b_dst, mb, bar, kk * BKE, b_row);
           } else {
 #pragma unroll
-            for (int j = 0; j < (BNH + 63) / 64; ++j) tma_load_2d_pair(b_dst + j * 8192, &tmB, bar, b_row + j * 64, kb * BK);
+            for (int j = 0; j < (BNH + 63) / 64; ++j) tma_load_2d_pair(b_dst + j * 8192, mb, bar, b_row + j * 64, kk * BK);
           }
           if (++stage == STAGES) {
             stage = 0;
@@ -634,24 +643,25 @@ unsigned long long g_ws_bytes[MAX_DEVICES] = {};
 
 template <int BN, int A_MN, int B_MN, int KIND = 0, int TP = 0>
 int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tw, const cb2::Args& g,
-            int pairs, cudaStream_t s) {
+            int pairs, cudaStream_t s, const CUtensorMap* ta2 = nullptr, const CUtensorMap* tb2 = nullptr) {
   auto kern = cb2::gemm2sm_kernel<BN, A_MN, B_MN, KIND, TP>;
   static bool configured = false;
   if (!configured) {
     CB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, cb2::SMEM_TOTAL));
     configured = true;
   }
-  kern<<<2 * pairs, cb2::THREADS, cb2::SMEM_TOTAL, s>>>(ta, tb, tc, tw, g);
+  kern<<<2 * pairs, cb2::THREADS, cb2::SMEM_TOTAL, s>>>(ta, tb, tc, tw, ta2 ? *ta2 : ta, tb2 ? *tb2 : tb, g);
   return static_cast<int>(cudaGetLastError());
 }
 
 template <int BN>
 int dispatch_layout(int a_mn, int b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
-                    const CUtensorMap& tw, const cb2::Args& g, int pairs, cudaStream_t s) {
-  if (!a_mn && !b_mn) return launch2<BN, 0, 0>(ta, tb, tc, tw, g, pairs, s);
-  if (!a_mn && b_mn) return launch2<BN, 0, 1>(ta, tb, tc, tw, g, pairs, s);
-  if (a_mn && b_mn) return launch2<BN, 1, 1>(ta, tb, tc, tw, g, pairs, s);
-  return launch2<BN, 1, 0>(ta, tb, tc, tw, g, pairs, s);
+                    const CUtensorMap& tw, const cb2::Args& g, int pairs, cudaStream_t s,
+                    const CUtensorMap* ta2 = nullptr, const CUtensorMap* tb2 = nullptr) {
+  if (!a_mn && !b_mn) return launch2<BN, 0, 0>(ta, tb, tc, tw, g, pairs, s, ta2, tb2);
+  if (!a_mn && b_mn) return launch2<BN, 0, 1>(ta, tb, tc, tw, g, pairs, s, ta2, tb2);
+  if (a_mn && b_mn) return launch2<BN, 1, 1>(ta, tb, tc, tw, g, pairs, s, ta2, tb2);
+  return launch2<BN, 1, 0>(ta, tb, tc, tw, g, pairs, s, ta2, tb2);
 }
 
 // Whole tiles take ceil(T / pairs) rounds; cut along K the work takes T / pairs rounds plus the fixups (partial
@@ -774,6 +784,7 @@ int cb_gemm2sm_bf16_ex(const void* A, const void* B, void* C, const void* bias, 
   g.num_n_tiles = (N + bn - 1) / bn;
   g.num_tiles = g.num_m_pairs * g.num_n_tiles;
   g.num_kb = (K + cb2::BK - 1) / cb2::BK;
+  g.num_kb1 = g.num_kb;
   g.C = C; g.ldc = ldc; g.out_fp32 = out_fp32; g.accumulate = accumulate;
   g.bias = static_cast<const cb::bf16*>(bias);
   g.addend = static_cast<const cb::bf16*>(addend);
@@ -793,6 +804,61 @@ int cb_gemm2sm_bf16_ex(const void* A, const void* B, void* C, const void* bias, 
   if (bn == 256) return dispatch_layout<256>(a_mn, b_mn, ta, tb, tc, tw, g, pairs, s);
   if (bn == 224) return dispatch_layout<224>(a_mn, b_mn, ta, tb, tc, tw, g, pairs, s);
   return dispatch_layout<192>(a_mn, b_mn, ta, tb, tc, tw, g, pairs, s);
+}
+
+// C[M,N] = A B^T + A2 B2^T (+bias) (+addend): the second product (inner dimension K2, small) is accumulated in the
+// same tiles after the first (a low-rank adapter joining its frozen projection).  A / A2 are stored [M, K] / [M, K2];
+// B / B2 share one layout: b_mn = 0 for [N, K] / [N, K2], 1 for [K, N] / [K2, N].  bf16 output.
+int cb_gemm2sm_bf16_dual(const void* A, const void* B, const void* A2, const void* B2, void* C, const void* bias,
+                         const void* addend, int M, int N, int K, int K2, long long lda, long long ldb, long long lda2,
+                         long long ldb2, long long ldc, long long ld_add, int b_mn, int* status, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || K2 <= 0) return -1;
+  if (!cb_gemm2sm_supported(C, ldc, 0)) return -2;
+  const int bn = pick_bn(N);
+  if (b_mn && ((ldb * 2) % 16 != 0 || (ldb2 * 2) % 16 != 0)) return -3;
+  CUtensorMap ta, tb, ta2, tb2, tc, tw;
+  int e = cbhost::make_tmap(&ta, A, K, M, lda, 64, cb2::BM);
+  if (e) return e;
+  e = cbhost::make_tmap(&ta2, A2, K2, M, lda2, 64, cb2::BM);
+  if (e) return e;
+  if (!b_mn) {
+    e = cbhost::make_tmap(&tb, B, K, N, ldb, 64, bn / 2);
+    if (e) return e;
+    e = cbhost::make_tmap(&tb2, B2, K2, N, ldb2, 64, bn / 2);
+  } else {
+    e = cbhost::make_tmap(&tb, B, N, K, ldb, 64, 64);
+    if (e) return e;
+    e = cbhost::make_tmap(&tb2, B2, N, K2, ldb2, 64, 64);
+  }
+  if (e) return e;
+  e = cbhost::make_tmap(&tc, C, N, M, ldc, 64, 32, 2);
+  if (e) return e;
+  memset(&tw, 0, sizeof(tw));
+  cb2::Args g = {};
+  g.M = M; g.N = N; g.K = K;
+  g.num_m_pairs = (M + 2 * cb2::BM - 1) / (2 * cb2::BM);
+  g.num_n_tiles = (N + bn - 1) / bn;
+  g.num_tiles = g.num_m_pairs * g.num_n_tiles;
+  g.num_kb1 = (K + cb2::BK - 1) / cb2::BK;
+  g.num_kb = g.num_kb1 + (K2 + cb2::BK - 1) / cb2::BK;
+  g.C = C; g.ldc = ldc;
+  g.bias = static_cast<const cb::bf16*>(bias);
+  g.addend = static_cast<const cb::bf16*>(addend);
+  g.ld_add = ld_add;
+  g.status = status;
+  int pairs = cbhost::num_sms() / 2;
+  if (pairs > g.num_tiles) pairs = g.num_tiles;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const int slots = plan_stream_k(&g, pairs, bn, dev, 1);
+  if (slots > 0) {
+    e = cbhost::make_tmap(&tw, g.ws, bn, static_cast<unsigned long long>(slots) * 256ull, bn, 32, 32, 4);
+    if (e) return e;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (bn == 256) return dispatch_layout<256>(0, b_mn, ta, tb, tc, tw, g, pairs, s, &ta2, &tb2);
+  if (bn == 224) return dispatch_layout<224>(0, b_mn, ta, tb, tc, tw, g, pairs, s, &ta2, &tb2);
+  return dispatch_layout<192>(0, b_mn, ta, tb, tc, tw, g, pairs, s, &ta2, &tb2);
 }
 
 int cb_gemm2sm_bf16(const void* A, const void* B, void* C, const void* bias, const void* addend, int M, int N, int K,
@@ -838,6 +904,7 @@ int cb_gemm2sm_bf16_tp(const void* A, const void* B, void* C, const void* bias, 
   g.num_n_tiles = (N + 255) / 256;
   g.num_tiles = g.num_m_pairs * g.num_n_tiles;
   g.num_kb = (K + cb2::BK - 1) / cb2::BK;
+  g.num_kb1 = g.num_kb;
   g.C = C; g.ldc = ldc;
   g.bias = static_cast<const cb::bf16*>(bias);
   g.status = status;
@@ -883,6 +950,7 @@ int cb_gemm2sm_fp8(const void* Aq, const void* Bq, void* C, const float* row_sca
   g.num_n_tiles = (N + 255) / 256;
   g.num_tiles = g.num_m_pairs * g.num_n_tiles;
   g.num_kb = (K + 2 * cb2::BK - 1) / (2 * cb2::BK);
+  g.num_kb1 = g.num_kb;
   g.C = C; g.ldc = ldc;
   g.bias = static_cast<const cb::bf16*>(bias);
   g.row_scale = row_scale;

@@ -39,15 +39,15 @@ class _FusedLoRAFn(torch.autograd.Function):
 
     With ``A_cat = [s_1 A_1; s_2 A_2; …]`` (``[R, in]``) and the block-diagonal ``B_big`` (``[out, R]``):
 
-    forward : ``hs = x A_catᵀ``; ``y = x Wᵀ + b (+ res)``; ``y += hs B_bigᵀ`` (K = R, accumulated in place);
-    backward: ``dhs = dy B_big``; ``dx = dy W + dhs A_cat``; ``dA_cat = dhsᵀ x`` and ``dB_big = dyᵀ hs`` by the
+    forward : ``hs = x A_catᵀ``; ``y = x Wᵀ + hs B_bigᵀ + b (+ res)`` in one dual-product GEMM;
+    backward: ``dhs = dy B_big``; ``dx = dy W + dhs A_cat`` (again one dual-product GEMM); ``dA_cat = dhsᵀ x`` and ``dB_big = dyᵀ hs`` by the
               split-K GEMM (skinny outputs, K = tokens); the frozen ``W`` gets no weight-gradient GEMM.
     ``ab`` is ``A_1, B_1, A_2, B_2, …`` in split order; ``meta`` carries the output slices and scalings.
     """
 
     @staticmethod
     def forward(ctx, x2, w, bias, res2, meta, *ab):
-        slices, scalings = meta
+        slices, scalings, drop_p = meta
         As, Bs = ab[0::2], ab[1::2]
         a_cat = torch.cat([a * sc for a, sc in zip(As, scalings)], dim=0) if len(As) > 1 else As[0] * scalings[0]
         R = a_cat.shape[0]
@@ -61,16 +61,24 @@ class _FusedLoRAFn(torch.autograd.Function):
             for b, sl in zip(Bs, slices):
                 b_big[sl, r0:r0 + b.shape[1]] = b
                 r0 += b.shape[1]
-        hs = ops.gemm(x2, a_cat)                                      # [T, R], already scaled
-        y = ops.gemm(x2, w, bias=bias, addend=res2)
-        ops.gemm(hs, b_big, out=y, accumulate=True)
-        ctx.save_for_backward(x2, w, a_cat, hs, b_big)
+        # adapter-branch dropout (reference fused_lora_kernels.py:63-155 draws it inside its down-projection
+        # kernel): the keep mask, scaled by 1 / (1 - p), multiplies the adapter's input only
+        keep = None
+        xa = x2
+        if drop_p > 0.0:
+            keep = (torch.rand_like(x2, dtype=torch.float32) >= drop_p).to(x2.dtype) * (1.0 / (1.0 - drop_p))
+            xa = x2 * keep
+        hs = ops.gemm(xa, a_cat)                                      # [T, R], already scaled
+        # one kernel for  x Wᵀ + hs B_bigᵀ + b (+ res): the adapter's k-block follows the projection's in the
+        # same accumulators, so the output is written once
+        y = ops.gemm_dual(x2, w, hs, b_big, bias=bias, addend=res2)
+        ctx.save_for_backward(x2, w, a_cat, hs, b_big, keep)
         ctx.meta = (slices, scalings, [b.shape[1] for b in Bs], bias is not None, res2 is not None)
         return y
 
     @staticmethod
     def backward(ctx, dy):
-        x2, w, a_cat, hs, b_big = ctx.saved_tensors
+        x2, w, a_cat, hs, b_big, keep = ctx.saved_tensors
         slices, scalings, ranks, has_bias, has_res = ctx.meta
         dy2 = dy.reshape(-1, dy.shape[-1])
         if not dy2.is_contiguous():
@@ -78,9 +86,13 @@ class _FusedLoRAFn(torch.autograd.Function):
         dhs = ops.gemm(dy2, b_big, b_mn=True)                               # [T, R]
         dx = None
         if ctx.needs_input_grad[0]:
-            dx = ops.gemm(dy2, w, b_mn=True)                                # frozen base: dX only
-            ops.gemm(dhs, a_cat, b_mn=True, out=dx, accumulate=True)
-        da_cat = ops.gemm_splitk(dhs, x2, a_mn=True, b_mn=True)            # [R, in]  fp32
+            if keep is None:
+                dx = ops.gemm_dual(dy2, w, dhs, a_cat, b_mn=True)           # dX = dY W + dhs A_cat, one kernel
+            else:
+                dx = ops.gemm(dy2, w, b_mn=True)
+                dx.addcmul_(ops.gemm(dhs, a_cat, b_mn=True), keep)          # the adapter's share passes the same mask
+        xa = x2 if keep is None else x2 * keep
+        da_cat = ops.gemm_splitk(dhs, xa, a_mn=True, b_mn=True)            # [R, in]  fp32
         db_big = ops.gemm_splitk(dy2, hs, a_mn=True, b_mn=True)            # [out, R] fp32
         grads = []
         r0 = 0
@@ -96,7 +108,7 @@ class _FusedLoRAFn(torch.autograd.Function):
 
 
 def _fused_path_ok(fl, x: torch.Tensor) -> bool:
-    if not ops._fast(x, fl.weight) or fl.lora_dropout_p > 0:
+    if not ops._fast(x, fl.weight):
         return False
     sl = fl.split_slices()
     for s in fl.lora_A:
@@ -114,7 +126,8 @@ def fused_lora_forward(fl, x: torch.Tensor, residual: Optional[torch.Tensor] = N
             x2 = x2.contiguous()
         res2 = residual.reshape(-1, fl.out_features) if residual is not None else None
         sl = fl.split_slices()
-        meta = ([sl[s] for s in names], [float(fl.lora_scaling[s]) for s in names])
+        drop_p = float(fl.lora_dropout_p) if (fl.training and fl.lora_dropout_p > 0) else 0.0
+        meta = ([sl[s] for s in names], [float(fl.lora_scaling[s]) for s in names], drop_p)
         ab = [t for s in names for t in (fl.lora_A[s], fl.lora_B[s])]
         y = _FusedLoRAFn.apply(x2, fl.weight, fl.bias, res2, meta, *ab)
         return y if x.dim() == 2 else y.view(*x.shape[:-1], fl.out_features)

@@ -19,7 +19,7 @@ from . import ref
 from . import _ext
 
 __all__ = [
-    "linear", "gemm", "gemm_splitk", "colsum", "rmsnorm", "rmsnorm_residual", "add_rmsnorm", "swiglu", "geglu", "qk_rope_", "embedding",
+    "linear", "gemm", "gemm_dual", "gemm_splitk", "colsum", "rmsnorm", "rmsnorm_residual", "add_rmsnorm", "swiglu", "geglu", "qk_rope_", "embedding",
     "attention_varlen", "attention_qkv_packed", "linear_cross_entropy", "cross_entropy_logits", "kernels_active",
 ]
 
@@ -105,6 +105,32 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         _ext.status_buffer(a.device).data_ptr(), _ext.stream_ptr())
     _ext.check(code, "gemm_bf16")
     return out
+
+
+def gemm_dual(a: torch.Tensor, b: torch.Tensor, a2: torch.Tensor, b2: torch.Tensor, *, b_mn: bool = False,
+              bias: Optional[torch.Tensor] = None, addend: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``A op(B)ᵀ + A2 op(B2)ᵀ (+bias) (+addend)`` in one kernel: the k-blocks of the second, low-rank product follow
+    those of the first in the same tensor-core accumulators (``a [M, K]``, ``a2 [M, K2]``; ``b [N, K]`` and
+    ``b2 [N, K2]``, or ``[K, N]`` / ``[K2, N]`` with ``b_mn``).  A frozen projection and its LoRA branch meet
+    without a second pass over the output."""
+    M, K = a.shape
+    N = b.shape[1] if b_mn else b.shape[0]
+    K2 = a2.shape[1]
+    ok = (_fast(a, b, a2, b2) and all(_gemm_ok(t) for t in (a, b, a2, b2))
+          and (addend is None or (addend.stride(1) == 1 and addend.dtype == torch.bfloat16)))
+    if ok:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+        code = _ext.lib().cb_gemm2sm_bf16_dual(
+            a.data_ptr(), b.data_ptr(), a2.data_ptr(), b2.data_ptr(), out.data_ptr(), _ext.ptr(bias), _ext.ptr(addend),
+            M, N, K, K2, a.stride(0), b.stride(0), a2.stride(0), b2.stride(0), out.stride(0),
+            addend.stride(0) if addend is not None else 0, int(b_mn), _ext.status_buffer(a.device).data_ptr(),
+            _ext.stream_ptr())
+        if code == 0:
+            return out
+        if code > 0:
+            _ext.check(code, "gemm2sm_bf16_dual")
+    out = gemm(a, b, b_mn=b_mn, bias=bias, addend=addend)
+    return gemm(a2, b2, b_mn=b_mn, out=out, accumulate=True)
 
 
 def gemm_splitk(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False) -> torch.Tensor:

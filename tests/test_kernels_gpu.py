@@ -443,6 +443,47 @@ def test_linear_weight_gradient_of_a_small_weight_uses_split_k_and_matches_fp32(
         assert (w.grad.float() - want).abs().max().item() < 8e-3 * want.abs().max().item()
 
 
+def test_fused_lora_projection_with_dropout_stays_on_the_fused_path():
+    """Adapter dropout keeps the single fused autograd node (dual-product forward, split-K adapter gradients): with
+    the random stream fixed, output and gradients equal the plain formula evaluated with the same keep mask."""
+    from collections import OrderedDict
+    from chronicals_b200.lora import functional as lf
+    from chronicals_b200.models.decoder import FusedLinear
+    torch.manual_seed(0)
+    T, K, p = 256, 256, 0.25
+    fl = FusedLinear(K, OrderedDict(gate_proj=384, up_proj=384), bias=False, dtype=torch.bfloat16, device="cuda")
+    with torch.no_grad():
+        fl.weight.normal_(0, 0.05)
+    fl.weight.requires_grad_(False)
+    for s in fl.splits:
+        fl.add_lora(s, 16, 32.0)
+        with torch.no_grad():
+            fl.lora_B[s].normal_(0, 0.05)
+    fl.lora_dropout_p = p
+    fl.train()
+    x = torch.randn(T, K, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    assert lf._fused_path_ok(fl, x)
+    torch.manual_seed(123)
+    y = fl(x)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    torch.manual_seed(123)
+    keep = (torch.rand_like(x, dtype=torch.float32) >= p).float() / (1 - p)
+    xf = x.detach().float().requires_grad_(True)
+    A = {s: fl.lora_A[s].detach().float().requires_grad_(True) for s in fl.splits}
+    B = {s: fl.lora_B[s].detach().float().requires_grad_(True) for s in fl.splits}
+    want = xf @ fl.weight.float().t() + torch.cat([fl.lora_scaling[s] * ((xf * keep) @ A[s].t()) @ B[s].t()
+                                                   for s in fl.splits], dim=1)
+    want.backward(gy.float())
+    _close(y, want, rtol=2e-2, atol=2e-2, what="lora dropout fwd")
+    _close(x.grad, xf.grad, rtol=2e-2, atol=2e-2, what="lora dropout dx")
+    for s in fl.splits:
+        _close(fl.lora_A[s].grad, A[s].grad, rtol=3e-2, atol=3e-2, what="dA")
+        _close(fl.lora_B[s].grad, B[s].grad, rtol=3e-2, atol=3e-2, what="dB")
+    assert fl.weight.grad is None
+    _ext.check_status()
+
+
 def test_fused_lora_projection_matches_reference_formula():
     """Frozen fused QKV projection with rank-16 adapters on every split: forward, dX, dA, dB against the
     plain PEFT formula in fp32 (the base weight must receive no gradient)."""
