@@ -37,7 +37,8 @@ def lora_cat_matrices(fl):
 class _FusedLoRAFn(torch.autograd.Function):
     """One autograd node for a frozen fused projection with per-split adapters (CUDA bf16 path).
 
-    With ``A_cat = [s_1 A_1; s_2 A_2; …]`` (``[R, in]``) and the block-diagonal ``B_big`` (``[out, R]``):
+    With ``A_cat = [A_1; A_2; …]`` (``[R, in]``) and the block-diagonal ``B_big = diag(s_1 B_1, s_2 B_2, …)``
+    (``[out, R]``):
 
     forward : ``hs = x A_catᵀ``; ``y = x Wᵀ + hs B_bigᵀ + b (+ res)`` in one dual-product GEMM;
     backward: ``dhs = dy B_big``; ``dx = dy W + dhs A_cat`` (again one dual-product GEMM); ``dA_cat = dhsᵀ x`` and ``dB_big = dyᵀ hs`` by the
@@ -47,20 +48,27 @@ class _FusedLoRAFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x2, w, bias, res2, meta, *ab):
-        slices, scalings, drop_p = meta
+        slices, scalings, drop_p, bufs = meta
         As, Bs = ab[0::2], ab[1::2]
-        a_cat = torch.cat([a * sc for a, sc in zip(As, scalings)], dim=0) if len(As) > 1 else As[0] * scalings[0]
-        R = a_cat.shape[0]
-        contiguous_cover = slices[0].start == 0 and slices[-1].stop == w.shape[0] and all(
-            slices[i].stop == slices[i + 1].start for i in range(len(slices) - 1))
-        if contiguous_cover:
-            b_big = torch.block_diag(*Bs) if len(Bs) > 1 else Bs[0]
-        else:
-            b_big = torch.zeros(w.shape[0], R, dtype=w.dtype, device=w.device)
+        ranks = [b.shape[1] for b in Bs]
+        R = sum(ranks)
+        # A_cat: one concatenation, unscaled.  B_big: the adapters' B matrices copied (one multi-tensor copy) onto
+        # the diagonal blocks of a persistent zero matrix, times the per-column scaling vector - the scalings live
+        # on the B side, so hs = x A_catᵀ needs no scaling pass and dA no rescaling.
+        a_cat = torch.cat(As, dim=0) if len(As) > 1 else As[0]
+        if ("b_zero" not in bufs or bufs["b_zero"].shape != (w.shape[0], R) or bufs["b_zero"].device != w.device
+                or bufs.get("scalings") != tuple(scalings)):
+            bufs["scalings"] = tuple(scalings)
+            bufs["b_zero"] = torch.zeros(w.shape[0], R, dtype=w.dtype, device=w.device)
+            bufs["colscale"] = torch.cat([torch.full((r,), float(sc)) for r, sc in zip(ranks, scalings)]).to(
+                device=w.device, dtype=w.dtype)
             r0 = 0
-            for b, sl in zip(Bs, slices):
-                b_big[sl, r0:r0 + b.shape[1]] = b
-                r0 += b.shape[1]
+            bufs["views"] = []
+            for sl, r in zip(slices, ranks):
+                bufs["views"].append(bufs["b_zero"][sl, r0:r0 + r])
+                r0 += r
+        torch._foreach_copy_(bufs["views"], [b.detach() for b in Bs])
+        b_big = bufs["b_zero"] * bufs["colscale"]                     # [out, R], scaled; off-diagonal blocks stay zero
         # adapter-branch dropout (reference fused_lora_kernels.py:63-155 draws it inside its down-projection
         # kernel): the keep mask, scaled by 1 / (1 - p), multiplies the adapter's input only
         keep = None
@@ -68,22 +76,22 @@ class _FusedLoRAFn(torch.autograd.Function):
         if drop_p > 0.0:
             keep = (torch.rand_like(x2, dtype=torch.float32) >= drop_p).to(x2.dtype) * (1.0 / (1.0 - drop_p))
             xa = x2 * keep
-        hs = ops.gemm(xa, a_cat)                                      # [T, R], already scaled
+        hs = ops.gemm(xa, a_cat)                                      # [T, R]
         # one kernel for  x Wᵀ + hs B_bigᵀ + b (+ res): the adapter's k-block follows the projection's in the
         # same accumulators, so the output is written once
         y = ops.gemm_dual(x2, w, hs, b_big, bias=bias, addend=res2)
-        ctx.save_for_backward(x2, w, a_cat, hs, b_big, keep)
-        ctx.meta = (slices, scalings, [b.shape[1] for b in Bs], bias is not None, res2 is not None)
+        ctx.save_for_backward(x2, w, a_cat, hs, b_big, keep, bufs["colscale"])
+        ctx.meta = (slices, ranks, bias is not None, res2 is not None)
         return y
 
     @staticmethod
     def backward(ctx, dy):
-        x2, w, a_cat, hs, b_big, keep = ctx.saved_tensors
-        slices, scalings, ranks, has_bias, has_res = ctx.meta
+        x2, w, a_cat, hs, b_big, keep, colscale = ctx.saved_tensors
+        slices, ranks, has_bias, has_res = ctx.meta
         dy2 = dy.reshape(-1, dy.shape[-1])
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
-        dhs = ops.gemm(dy2, b_big, b_mn=True)                               # [T, R]
+        dhs = ops.gemm(dy2, b_big, b_mn=True)                               # [T, R], carries the scalings
         dx = None
         if ctx.needs_input_grad[0]:
             if keep is None:
@@ -92,13 +100,13 @@ class _FusedLoRAFn(torch.autograd.Function):
                 dx = ops.gemm(dy2, w, b_mn=True)
                 dx.addcmul_(ops.gemm(dhs, a_cat, b_mn=True), keep)          # the adapter's share passes the same mask
         xa = x2 if keep is None else x2 * keep
-        da_cat = ops.gemm_splitk(dhs, xa, a_mn=True, b_mn=True)            # [R, in]  fp32
-        db_big = ops.gemm_splitk(dy2, hs, a_mn=True, b_mn=True)            # [out, R] fp32
+        da_cat = ops.gemm_splitk(dhs, xa, a_mn=True, b_mn=True).to(dy2.dtype)            # [R, in]
+        db_big = (ops.gemm_splitk(dy2, hs, a_mn=True, b_mn=True) * colscale.float()).to(dy2.dtype)   # [out, R]
         grads = []
         r0 = 0
-        for sl, sc, r in zip(slices, scalings, ranks):
-            grads.append((da_cat[r0:r0 + r] * sc).to(dy2.dtype))
-            grads.append(db_big[sl, r0:r0 + r].to(dy2.dtype))
+        for sl, r in zip(slices, ranks):
+            grads.append(da_cat[r0:r0 + r])                                 # row blocks: contiguous views
+            grads.append(db_big[sl, r0:r0 + r])
             r0 += r
         db = ops.colsum(dy2) if (has_bias and ctx.needs_input_grad[2]) else None
         dw = None
@@ -127,7 +135,9 @@ def fused_lora_forward(fl, x: torch.Tensor, residual: Optional[torch.Tensor] = N
         res2 = residual.reshape(-1, fl.out_features) if residual is not None else None
         sl = fl.split_slices()
         drop_p = float(fl.lora_dropout_p) if (fl.training and fl.lora_dropout_p > 0) else 0.0
-        meta = ([sl[s] for s in names], [float(fl.lora_scaling[s]) for s in names], drop_p)
+        if not hasattr(fl, "_lora_bufs"):
+            fl._lora_bufs = {}                      # persistent block-diagonal B buffer and column scalings
+        meta = ([sl[s] for s in names], [float(fl.lora_scaling[s]) for s in names], drop_p, fl._lora_bufs)
         ab = [t for s in names for t in (fl.lora_A[s], fl.lora_B[s])]
         y = _FusedLoRAFn.apply(x2, fl.weight, fl.bias, res2, meta, *ab)
         return y if x.dim() == 2 else y.view(*x.shape[:-1], fl.out_features)
