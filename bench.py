@@ -388,7 +388,7 @@ def run_reference(args):
         cfg.max_seq_length = SEQ_LEN
         cfg.logging_steps = 1
         cfg.save_steps = 0
-        cfg.output_dir = os.path.join("/tmp", f"ref_bench_{os.getpid()}")
+        cfg.output_dir = os.path.join(args.ref_output_root, f"ref_bench_{os.getpid()}")
         cfg.visual_reporting = False
         cfg.bf16 = True
         cfg.learning_rate = 2e-5
@@ -399,6 +399,10 @@ def run_reference(args):
         sampler = ClockSampler(local_rank)
         if rank == 0 and dev.type == "cuda":
             loader.on_start = sampler.start
+        if args.ref_fail_after_timing:
+            def _injected():
+                raise RuntimeError("injected failure after the timed region")
+            loader.on_end = _injected
         import contextlib
         import io
         sink = io.StringIO()
@@ -474,6 +478,10 @@ def main():
                          "reduce-scatter and add their hidden / exposed times to the JSON line (diagnostic)")
     ap.add_argument("--tiny", action="store_true", help="plumbing check of the reference arm on a tiny model")
     ap.add_argument("--ref-no-compile", action="store_true")
+    ap.add_argument("--ref-fail-after-timing", action="store_true",
+                    help="harness self-test: raise inside the reference's loop right after the timed region closed")
+    ap.add_argument("--ref-output-root", default="/tmp",
+                    help="where the reference trainer writes its (mandatory) checkpoints; removed afterwards")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -466,6 +466,11 @@ class ChronicalsTrainer:
         if not hasattr(self.optimizer, "launch_step"):
             raise RuntimeError("CUDA-graph capture of the step needs an optimizer with a capturable device half "
                                "(FusedAdamW / LoRAPlusAdamW)")
+        # warm-up and capture run on streams of their own, so the gradient-accumulation nodes see another stream
+        # than the one the parameters were created on: intended here, torch's notice about it is switched off
+        quiet = getattr(torch.autograd.graph, "set_warn_on_accumulate_grad_stream_mismatch", None)
+        if quiet is not None:
+            quiet(False)
         side = torch.cuda.Stream(self.device)
         side.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(side):

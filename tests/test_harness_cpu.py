@@ -81,3 +81,18 @@ def test_lora_comparison_runs_both_arms_offline():
     assert by["huggingface_lora"]["trainable_params"] < by["huggingface_lora"]["n_params"]
     assert by["unsloth_max"]["status"] == "skipped"
     assert abs(by["chronicals_lora_packed"]["final_loss"] - by["huggingface_lora"]["final_loss"]) < 0.5
+
+
+def test_reference_arm_keeps_its_number_when_the_reference_fails_after_the_timed_region(tmp_path):
+    """The reference's train() writes checkpoints after the last batch.  When something fails there (a full disk in
+    practice; an injected exception here) the timed region is already closed: the arm still prints its
+    measurement, with the failure noted beside it, and leaves no checkpoint directory behind."""
+    if not os.path.isdir(os.path.join(ROOT, "baseline", "_ref", "chronicals")):
+        pytest.skip("reference not installed under baseline/_ref")
+    out = _run(["bench.py", "--impl", "reference", "--tiny", "--steps", "2", "--warmup", "3", "--ref-output-root", str(tmp_path),
+                "--ref-fail-after-timing"], timeout=900)
+    rec = json.loads([l for l in out.splitlines() if l.startswith("{")][-1])
+    assert rec["impl"] == "reference" and "unavailable" not in rec, rec
+    assert rec["value"] > 0 and rec["steps"] == 2
+    assert "injected failure" in rec.get("post_timing_error", ""), rec
+    assert not [d for d in os.listdir(tmp_path) if d.startswith("ref_bench_")]
