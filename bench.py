@@ -241,6 +241,7 @@ def run_ours(args):
     _ext.check_status(dev)
 
     dp_profile = None
+    graph_used = bool(trainer.use_cuda_graphs)            # as the timed steps ran
     if args.dp_profile and hasattr(trainer.optimizer, "profile_report"):
         trainer.use_cuda_graphs = False                   # events cannot be read back from inside a replayed graph
         trainer.optimizer.profile = True
@@ -263,7 +264,7 @@ def run_ours(args):
             "config": {"model": "Qwen2.5-0.5B architecture (24L, H896, 14q/2kv, d64, I4864, V151936, tied)",
                        "global_batch": MICRO_BATCH * world, "micro_batch_per_gpu": MICRO_BATCH, "seq_len": SEQ_LEN,
                        "parallelism": f"dp{world}", "optimizer": "AdamW (fp32 moments) + global-norm clip",
-                       "loss": "fused linear cross-entropy (no logits)", "cuda_graph": trainer.use_cuda_graphs,
+                       "loss": "fused linear cross-entropy (no logits)", "cuda_graph": graph_used,
                        "comm": comm if world > 1 else "none",
                        "grad_reduce": ("per-bucket reduce-scatter from backward hooks on a side stream"
                                        if (world > 1 and comm == "fused" and not args.no_overlap) else

@@ -183,7 +183,15 @@ def run_attn(results, peaks, iters, only=None):
             def lib():
                 o = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
                 o.backward(torch.ones_like(o))
+
+            def lib_fwd():
+                with torch.no_grad():
+                    torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
+            # torch's SDPA (its flash / cuDNN back end) on the same box, same run: forward, and forward + backward
+            results[-2]["sdpa_fwd_ms"] = timed(lib_fwd, iters)
+            results[-2]["ours_vs_sdpa"] = results[-2]["sdpa_fwd_ms"] / ms_f
             results[-1]["sdpa_fwd_bwd_ms"] = timed(lib, iters)
+            results[-1]["ours_vs_sdpa"] = results[-1]["sdpa_fwd_bwd_ms"] / ms_fb
         _ext.check_status()
 
 

@@ -43,16 +43,56 @@ struct AttnArgs {
   int* status;
 };
 
-// which (document, block) a CTA owns; blocks of one document are handed out heaviest first
-__device__ __forceinline__ bool locate_block(const int* cu, int n_docs, int b, int& start, int& len, int& blk, int& nblk) {
-  for (int i = 0; i < n_docs; ++i) {
-    const int s = cu[i], e = cu[i + 1];
-    const int nb = (e - s + 127) >> 7;
-    if (b < nb) {
-      start = s; len = e - s; nblk = nb; blk = b;
-      return true;
+// Phase timers (compiled in with -DCB_ATTN_PHASE_TIMERS only): two threads of every CTA - the MMA-issuing thread
+// and one thread of another warp - add the SM clock cycles they spend between consecutive marks to a global
+// table, which cb_attn_phase_read() copies out.  The default build contains none of this.
+#ifdef CB_ATTN_PHASE_TIMERS
+__device__ unsigned long long cb_attn_phase[2][16];
+#define CB_PHASE_DECL_T(ta, tb) const int ph_who = (threadIdx.x == (ta)) ? 0 : ((threadIdx.x == (tb)) ? 1 : -1); \
+                      long long ph_t = clock64(); unsigned long long ph_acc[13] = {}
+#define CB_PHASE(n) do { if (ph_who >= 0) { const long long t_ = clock64(); ph_acc[n] += t_ - ph_t; ph_t = t_; } } while (0)
+#define CB_PHASE_FLUSH do { if (ph_who >= 0) { for (int i_ = 0; i_ < 13; ++i_) atomicAdd(&cb_attn_phase[ph_who][i_], ph_acc[i_]); \
+                                               atomicAdd(&cb_attn_phase[ph_who][15], 1ull); } } while (0)
+#define CB_PHASE_DECL CB_PHASE_DECL_T(0, 96)
+#else
+#define CB_PHASE_DECL
+#define CB_PHASE_DECL_T(ta, tb)
+#define CB_PHASE(n)
+#define CB_PHASE_FLUSH
+#endif
+
+// Which tile a CTA owns.  A tile is one 128-row block of one document; its weight is the number of 128-row
+// blocks its main loop visits (forward: kv blocks up to the diagonal; backward: query blocks from the diagonal
+// on), so a document of nb blocks has exactly one tile of every weight 1..nb.  Tiles are handed out by
+// descending weight over ALL documents (ties in document order): the heaviest tiles of the batch start first and
+// the last wave consists of single-block tiles, whatever the mix of document lengths.  Every warp runs this by
+// itself with warp-wide votes (no shared memory, so it can precede the CTA's set-up); cost is one pass over the
+// document lengths per weight level.
+__device__ __forceinline__ bool locate_tile(const int* cu, int n_docs, int b, int& start, int& len, int& weight, int& nblk) {
+  const int lane = threadIdx.x & 31;
+  int maxnb = 0;
+  for (int d = lane; d < n_docs; d += 32) maxnb = max(maxnb, (cu[d + 1] - cu[d] + 127) >> 7);
+  maxnb = __reduce_max_sync(0xffffffffu, maxnb);
+  for (int L = maxnb; L >= 1; --L) {
+    int cnt = 0;
+    for (int d = lane; d < n_docs; d += 32) cnt += (((cu[d + 1] - cu[d] + 127) >> 7) >= L) ? 1 : 0;
+    const int tot = __reduce_add_sync(0xffffffffu, cnt);
+    if (b < tot) {
+      for (int d0 = 0; d0 < n_docs; d0 += 32) {        // the b-th document, in document order, with >= L blocks
+        const int d = d0 + lane;
+        const bool has = d < n_docs && (((cu[d + 1] - cu[d] + 127) >> 7) >= L);
+        const unsigned m = __ballot_sync(0xffffffffu, has);
+        const int c = __popc(m);
+        if (b < c) {
+          const int pos = d0 + __fns(m, 0, b + 1);
+          start = cu[pos]; len = cu[pos + 1] - start; nblk = (len + 127) >> 7; weight = L;
+          return true;
+        }
+        b -= c;
+      }
+      return false;
     }
-    b -= nb;
+    b -= tot;
   }
   return false;
 }
@@ -158,9 +198,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   constexpr uint32_t IDESC_PV = umma_idesc_bf16(128, D, 0, 1);
 
   int start, len, qb, nblk;
-  if (!locate_block(a.cu, a.n_docs, blockIdx.x, start, len, qb, nblk)) return;
-  qb = nblk - 1 - qb;                                  // heaviest (most kv blocks) first
-  const int h = blockIdx.y;
+  if (!locate_tile(a.cu, a.n_docs, blockIdx.y, start, len, qb, nblk)) return;
+  qb -= 1;                                             // weight = kv blocks up to the diagonal = qb + 1
+  const int h = blockIdx.x;
   const int hkv = h / (a.hq / a.hk);
 
   extern __shared__ uint8_t smem_raw[];
@@ -337,9 +377,9 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   constexpr uint32_t IDESC_PV = umma_idesc_bf16(128, D, 0, 1);
 
   int start, len, qb, nblk;
-  if (!locate_block(a.cu, a.n_docs, blockIdx.x, start, len, qb, nblk)) return;
-  qb = nblk - 1 - qb;                                  // heaviest (most kv blocks) first
-  const int h = blockIdx.y;
+  if (!locate_tile(a.cu, a.n_docs, blockIdx.y, start, len, qb, nblk)) return;
+  qb -= 1;                                             // weight = kv blocks up to the diagonal = qb + 1
+  const int h = blockIdx.x;
   const int hkv = h / (a.hq / a.hk);
 
   extern __shared__ uint8_t smem_raw[];
@@ -573,6 +613,322 @@ __global__ void attn_delta_generic_kernel(const bf16* __restrict__ dO, const bf1
   if (lane == 0) delta[static_cast<long long>(h) * T + t] = s;
 }
 
+
+// ---------------------------------------------------------------------------------------------------
+// Forward, pipelined form (the default, see cb_attn_fwd).
+//
+// The two forms above run S-MMA -> softmax -> PV-MMA -> S-MMA of one CTA strictly one after the other and rely on
+// a second resident CTA to fill the gaps.  Here the tensor core works in the shadow of the softmax inside ONE CTA:
+//   * kv blocks are 64 rows, so a score tile [128 x 64] fp32 takes 64 TMEM columns and two of them plus the
+//     output accumulator [128 x D] fit in 256 columns for D = 64 and D = 128 alike (two CTAs per SM);
+//   * S(j+1) is computed while the softmax threads work on S(j) (the scores are double-buffered); P(j) (bf16)
+//     overwrites the first 32 columns of S(j) and is consumed from TMEM by the P V product, which accumulates O in
+//     TMEM over the whole kv loop, so the output never travels through registers inside the loop;
+//   * a fifth warp owns the TMA ring (K and V blocks, separate rings) and issues every MMA; the four softmax warps
+//     never meet at a CTA barrier: they signal "P(j) written, S(j) consumed" on an mbarrier and move straight on to
+//     S(j+1), which is already complete in the other buffer;
+//   * one pass over the scores: a thread keeps its 64 scores of the block in registers, takes their maximum, and
+//     exponentiates against a reference maximum that is only raised when the block's maximum exceeds it by more
+//     than 2^8 (the probabilities then stay below 256, exact in fp32 sums and harmless in bf16); raising it
+//     rescales the thread's own O row in TMEM, which after the first blocks of a causal row is rare.
+// Per kv block a softmax thread issues about 64 x (max, fma, ex2, add, half a cvt) instructions and nothing else;
+// the exp2 unit (16 results per clock and SM) is the bound: 1024 cycles per [128 x 128] of scores.
+constexpr int FWD3_THREADS = 160;                      // 4 softmax warps + 1 warp for TMA and MMA issue
+constexpr float FWD3_RAISE_LOG2 = 8.f;                 // raise the reference maximum only beyond 2^8
+
+template <int D>
+struct Fwd3Smem {
+  static constexpr int NS = (D == 64) ? 4 : 2;         // depth of the K ring and of the V ring (64-row blocks)
+  static constexpr int QT = 128 * D * 2;               // Q tile [128 x D]: D/64 panels of 16 KB
+  static constexpr int KT = 64 * D * 2;                // one K or V block [64 x D]: D/64 panels of 8 KB
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_K = QT;
+  static constexpr int OFF_V = QT + NS * KT;
+  static constexpr int OFF_BAR = QT + 2 * NS * KT;
+  static constexpr int TOTAL = OFF_BAR + 256 + 1024;
+};
+
+template <int D>
+__global__ void __launch_bounds__(FWD3_THREADS, 2)
+attn_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const AttnArgs a) {
+  using L = Fwd3Smem<D>;
+  constexpr int NS = L::NS;
+  constexpr int PANELS = D / 64;
+  constexpr uint32_t TMEM_COLS = 256;                  // S0 [0, 64)  S1 [64, 128)  O [128, 128 + D)
+  constexpr uint32_t C_O = 128;
+  constexpr uint32_t IDESC_S = umma_idesc_bf16(128, 64, 0, 0);
+  constexpr uint32_t IDESC_PV = umma_idesc_bf16(128, D, 0, 1);
+
+  int start, len, qb, nblk;
+  if (!locate_tile(a.cu, a.n_docs, blockIdx.y, start, len, qb, nblk)) return;
+  qb -= 1;
+  const int h = blockIdx.x;
+  const int hkv = h / (a.hq / a.hk);
+  const int n_kv = min(2 * qb + 2, (len + 63) >> 6);   // 64-row kv blocks up to and including the diagonal
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem + L::OFF_Q;
+  uint8_t* sK = smem + L::OFF_K;
+  uint8_t* sV = smem + L::OFF_V;
+  uint64_t* k_full = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);    // [NS]
+  uint64_t* v_full = k_full + NS;                                       // [NS]
+  uint64_t* bar_s = v_full + NS;                                        // [2]  S(j) complete in buffer j & 1
+  uint64_t* p_ready = bar_s + 2;                                        // [2]  128 arrivals: P(j) written, S(j) consumed
+  uint64_t* bar_o = p_ready + 2;                                        //      P V product of block j complete (phase j)
+  uint64_t* bar_q = bar_o + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_q + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  if (tid == 0) {
+    for (int i = 0; i < NS; ++i) { mbar_init(k_full + i, 1); mbar_init(v_full + i, 1); }
+    mbar_init(bar_s, 1); mbar_init(bar_s + 1, 1);
+    mbar_init(p_ready, 128); mbar_init(p_ready + 1, 128);
+    mbar_init(bar_o, 1); mbar_init(bar_q, 1);
+    mbar_fence_init();
+    *abort_flag = a.status[0] != 0 ? 1 : 0;
+  }
+  __syncthreads();
+  if (*abort_flag) return;
+  if (warp == 0) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  bool ok = true;
+  CB_PHASE_DECL_T(128, 64);            // slot 0: the MMA / TMA thread, slot 1: a softmax thread
+
+  if (warp == 4) {
+    // ------------------------------------------------------------------ TMA ring + MMA issue
+    // The whole warp walks this path with warp-uniform control flow and one elected lane issues; the values that
+    // feed addresses and descriptors are broadcast from lane 0 so that they are uniform for the compiler too.
+    const int u_start = __shfl_sync(0xffffffffu, start, 0);
+    const int u_qb = __shfl_sync(0xffffffffu, qb, 0);
+    const int u_nkv = __shfl_sync(0xffffffffu, n_kv, 0);
+    const uint32_t u_tmem = __shfl_sync(0xffffffffu, tmem, 0);
+    const uint32_t qa = smem_u32(sQ);
+    auto wait_w = [&](uint64_t* bar, uint32_t parity, int code) {
+      ok = __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, a.status, code) && ok);
+    };
+    auto load_k = [&](int j) {
+      const int st = j % NS;
+      if (elect_one()) {
+        mbar_expect_tx(k_full + st, L::KT);
+#pragma unroll
+        for (int p = 0; p < PANELS; ++p)
+          tma_load_2d(sK + st * L::KT + p * 8192, &tmK, k_full + st, hkv * D + p * 64, u_start + j * 64);
+      }
+    };
+    auto load_v = [&](int j) {
+      const int st = j % NS;
+      if (elect_one()) {
+        mbar_expect_tx(v_full + st, L::KT);
+#pragma unroll
+        for (int p = 0; p < PANELS; ++p)
+          tma_load_2d(sV + st * L::KT + p * 8192, &tmV, v_full + st, hkv * D + p * 64, u_start + j * 64);
+      }
+    };
+    auto issue_s = [&](int j) {                         // S(j) = Q K(j)^T into buffer j & 1
+      const uint32_t kb = smem_u32(sK + (j % NS) * L::KT);
+      tc_fence_after();
+      if (elect_one()) {
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          umma_f16_ss(u_tmem + (j & 1) * 64, umma_smem_desc(qa + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024),
+                      umma_smem_desc(kb + (kk >> 2) * 8192 + (kk & 3) * 32, 16, 1024), IDESC_S, kk != 0);
+        umma_commit(bar_s + (j & 1));
+      }
+    };
+    if (elect_one()) {
+      mbar_expect_tx(bar_q, L::QT);
+#pragma unroll
+      for (int p = 0; p < PANELS; ++p) tma_load_2d(sQ + p * 16384, &tmQ, bar_q, h * D + p * 64, u_start + u_qb * 128);
+    }
+    int next_k = 0;
+    for (; next_k < NS && next_k < u_nkv; ++next_k) { load_k(next_k); load_v(next_k); }
+    wait_w(bar_q, 0, CB_ERR_WAIT_FULL);
+    wait_w(k_full, 0, CB_ERR_WAIT_FULL);
+    if (ok) issue_s(0);
+    if (ok && u_nkv > 1) {
+      wait_w(k_full + (1 % NS), 0, CB_ERR_WAIT_FULL);
+      if (ok) issue_s(1);
+    }
+    CB_PHASE(0);
+    for (int j = 0; j < u_nkv && ok; ++j) {
+      wait_w(p_ready + (j & 1), (j >> 1) & 1, CB_ERR_WAIT_TMEM_EMPTY);
+      CB_PHASE(1);
+      wait_w(v_full + (j % NS), (j / NS) & 1, CB_ERR_WAIT_FULL);
+      CB_PHASE(2);
+      if (j >= 1) {
+        // phase j - 1 of bar_o has to be observed before this iteration's commit can complete phase j
+        wait_w(bar_o, (j - 1) & 1, CB_ERR_WAIT_TMEM_FULL);
+        if (ok && j - 1 + NS < u_nkv) load_v(j - 1 + NS);              // V stage of block j - 1 is free
+      }
+      CB_PHASE(3);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t vb = smem_u32(sV + (j % NS) * L::KT);
+      if (elect_one()) {
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)                  // O += P(j) V(j): A = P from TMEM, 16 bf16 = 8 words per step
+          umma_f16_ts(u_tmem + C_O, u_tmem + (j & 1) * 64 + kk * 8, umma_smem_desc(vb + kk * 2048, 8192, 1024), IDESC_PV,
+                      (j | kk) != 0);
+        umma_commit(bar_o);
+      }
+      CB_PHASE(4);
+      // S(j) was consumed (p_ready), so its K stage is free; S(j+1) finished while the softmax of block j ran
+      if (j + 1 < u_nkv) wait_w(bar_s + ((j + 1) & 1), ((j + 1) >> 1) & 1, CB_ERR_WAIT_TMEM_FULL);
+      CB_PHASE(5);
+      while (ok && next_k < u_nkv && next_k - NS <= j + 1) { load_k(next_k); ++next_k; }
+      CB_PHASE(6);
+      if (ok && j + 2 < u_nkv) {
+        wait_w(k_full + ((j + 2) % NS), ((j + 2) / NS) & 1, CB_ERR_WAIT_FULL);
+        CB_PHASE(7);
+        if (ok) issue_s(j + 2);
+        CB_PHASE(8);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ softmax: thread r owns score row r
+    const int r = tid;
+    const uint32_t t_row = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+    const float sl2 = a.scale * LOG2E;
+    const float raise = FWD3_RAISE_LOG2 / sl2;          // in raw score units
+    float m_ref = -INFINITY, l_run = 0.f;
+    // every wait ends in a warp-wide vote, so that the lanes of a warp leave the loop together (the TMEM loads
+    // and stores and the votes below want the whole warp)
+    auto wait_all = [&](uint64_t* bar, uint32_t parity, int code) {
+      ok = __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, a.status, code) && ok);
+    };
+    CB_PHASE(0);
+    for (int j = 0; j < n_kv; ++j) {
+      const uint32_t t_s = t_row + (j & 1) * 64;
+      wait_all(bar_s + (j & 1), (j >> 1) & 1, CB_ERR_WAIT_TMEM_FULL);
+      CB_PHASE(1);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t s0[32], s1[32];
+      tmem_ld_32x32(t_s, s0);
+      tmem_ld_32x32(t_s + 32, s1);
+      tmem_ld_wait();
+      CB_PHASE(2);
+      // columns j*64 + c <= qb*128 + r are visible; only the blocks that touch the diagonal need the test
+      const int lim = qb * 128 + r - j * 64;
+      if (j >= 2 * qb) {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          if (c > lim) s0[c] = 0xff800000u;             // -inf
+          if (c + 32 > lim) s1[c] = 0xff800000u;
+        }
+      }
+      float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        mx0 = fmaxf(mx0, __uint_as_float(s0[c]));
+        mx1 = fmaxf(mx1, __uint_as_float(s1[c]));
+      }
+      const float mx = fmaxf(mx0, mx1);
+      CB_PHASE(3);
+      const bool up = mx > m_ref + raise;               // also true for the first block (m_ref = -inf)
+      bool o_seen = false;
+      if (__any_sync(0xffffffffu, up)) {
+        if (j > 0) {
+          // my O row is rescaled in TMEM: P V of block j - 1 has to be complete, and that of block j cannot start
+          // before this thread has signalled p_ready
+          wait_all(bar_o, (j - 1) & 1, CB_ERR_WAIT_TMEM_FULL);
+          o_seen = true;
+          if (!ok) break;
+          tc_fence_after();
+          const float alpha = up ? ex2_approx((m_ref - mx) * sl2) : 1.f;
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld_32x32(t_row + C_O + c * 32, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st_32x32(t_row + C_O + c * 32, o);
+          }
+          l_run *= alpha;
+        }
+        if (up) m_ref = mx;
+      }
+      CB_PHASE(4);
+      const float mb = m_ref * sl2;
+      uint32_t pk[32];
+      float rs0 = 0.f, rs1 = 0.f;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float e0 = ex2_approx(fmaf(__uint_as_float(s0[2 * i]), sl2, -mb));
+        const float e1 = ex2_approx(fmaf(__uint_as_float(s0[2 * i + 1]), sl2, -mb));
+        const float e2 = ex2_approx(fmaf(__uint_as_float(s1[2 * i]), sl2, -mb));
+        const float e3 = ex2_approx(fmaf(__uint_as_float(s1[2 * i + 1]), sl2, -mb));
+        rs0 += e0 + e1;
+        rs1 += e2 + e3;
+        pk[i] = pack_bf16x2(e0, e1);
+        pk[16 + i] = pack_bf16x2(e2, e3);
+      }
+      l_run += rs0 + rs1;
+      CB_PHASE(5);
+      tmem_st_32x32(t_s, pk);                           // P(j): 64 bf16 = 32 words over the scores just read
+      tmem_st_wait();
+      CB_PHASE(6);
+      if (j > 0 && !o_seen) {
+        // keep pace with bar_o: a parity wait can only tell the current phase from the one before it
+        wait_all(bar_o, (j - 1) & 1, CB_ERR_WAIT_TMEM_FULL);
+        if (!ok) break;
+      }
+      CB_PHASE(7);
+      tc_fence_before();
+      mbar_arrive(p_ready + (j & 1));
+      CB_PHASE(8);
+    }
+    if (ok) {
+      wait_all(bar_o, (n_kv - 1) & 1, CB_ERR_WAIT_TMEM_FULL);
+      tc_fence_after();
+      const int rg = qb * 128 + r;
+      const bool row_ok = rg < len;                     // the TMEM loads below are warp-wide; only the stores are per row
+      const float inv = 1.f / l_run;
+      const long long t = start + (row_ok ? rg : 0);
+      CB_DEBUG_CHECK_ST(a.status, t >= 0 && t < a.T, CB_DBG_ATTN_ROW, t);
+      uint4* op = reinterpret_cast<uint4*>(a.O + t * a.ldo + static_cast<long long>(h) * D);
+      if (ok) {
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld_32x32(t_row + C_O + c * 32, o);
+          tmem_ld_wait();
+          if (row_ok) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 u;
+              u.x = pack_bf16x2(__uint_as_float(o[8 * q + 0]) * inv, __uint_as_float(o[8 * q + 1]) * inv);
+              u.y = pack_bf16x2(__uint_as_float(o[8 * q + 2]) * inv, __uint_as_float(o[8 * q + 3]) * inv);
+              u.z = pack_bf16x2(__uint_as_float(o[8 * q + 4]) * inv, __uint_as_float(o[8 * q + 5]) * inv);
+              u.w = pack_bf16x2(__uint_as_float(o[8 * q + 6]) * inv, __uint_as_float(o[8 * q + 7]) * inv);
+              op[c * 4 + q] = u;
+            }
+          }
+        }
+        if (row_ok) a.lse[static_cast<long long>(h) * a.T + t] = m_ref * a.scale + __logf(l_run);
+      }
+    }
+  }
+  CB_PHASE(9);
+  CB_PHASE_FLUSH;
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem, TMEM_COLS); }
+}
+
 }  // namespace cb
 
 // =========================================================================================== backward
@@ -596,11 +952,13 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
 template <int D>
 struct Bwd2Smem {
   static constexpr int TILE = 128 * D * 2;
+  static constexpr int NQ = (D == 128) ? 2 : 1;       // Q / dO stages: D = 128 runs one CTA per SM and has the room to
+                                                      // fetch the next query block while this one is worked on
   static constexpr int OFF_K = 0;
   static constexpr int OFF_V = TILE;
-  static constexpr int OFF_Q = 2 * TILE;
-  static constexpr int OFF_DO = 3 * TILE;
-  static constexpr int OFF_P = 4 * TILE;              // P, then dS (bf16 [128 x 128] operand image)
+  static constexpr int OFF_Q = 2 * TILE;              // NQ stages
+  static constexpr int OFF_DO = (2 + NQ) * TILE;      // NQ stages
+  static constexpr int OFF_P = (2 + 2 * NQ) * TILE;   // P, then dS (bf16 [128 x 128] operand image)
   static constexpr int OFF_BAR = OFF_P + 32768;
   static constexpr int TOTAL = OFF_BAR + 128 + 1024;
 };
@@ -633,8 +991,9 @@ attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   constexpr uint32_t IDESC_DQ = umma_idesc_bf16(128, D, 0, 1);           // dS K
 
   int start, len, jb, nblk;
-  if (!locate_block(a.cu, a.n_docs, blockIdx.x, start, len, jb, nblk)) return;   // jb = 0 is the heaviest
-  const int h = blockIdx.y;
+  if (!locate_tile(a.cu, a.n_docs, blockIdx.y, start, len, jb, nblk)) return;
+  jb = nblk - jb;                                      // weight = query blocks from the diagonal on = nblk - jb
+  const int h = blockIdx.x;
   const int hkv = h / (a.hq / a.hk);
 
   extern __shared__ uint8_t smem_raw[];
@@ -644,12 +1003,13 @@ attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint8_t* sQ = smem + L::OFF_Q;
   uint8_t* sdO = smem + L::OFF_DO;
   uint8_t* sP = smem + L::OFF_P;
-  uint64_t* q_full = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
-  uint64_t* bar_kv = q_full + 1;
-  uint64_t* bar_s = q_full + 2;
-  uint64_t* bar_dp = q_full + 3;
-  uint64_t* bar_dq = q_full + 4;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_full + 5);
+  constexpr int NQ = L::NQ;
+  uint64_t* q_full = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);   // [2]
+  uint64_t* bar_kv = q_full + 2;
+  uint64_t* bar_s = q_full + 3;
+  uint64_t* bar_dp = q_full + 4;
+  uint64_t* bar_dq = q_full + 5;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_full + 6);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   // 8 warps: warps w and w + 4 own the same 32 TMEM lanes (score rows) and split the columns in halves,
@@ -657,7 +1017,7 @@ attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int tid = threadIdx.x, warp = tid >> 5;
   const int q4 = warp & 3, half = warp >> 2;
   if (tid == 0) {
-    mbar_init(q_full, 1); mbar_init(bar_kv, 1); mbar_init(bar_s, 1); mbar_init(bar_dp, 1); mbar_init(bar_dq, 1);
+    mbar_init(q_full, 1); mbar_init(q_full + 1, 1); mbar_init(bar_kv, 1); mbar_init(bar_s, 1); mbar_init(bar_dp, 1); mbar_init(bar_dq, 1);
     mbar_fence_init();
     *abort_flag = a.status[0] != 0 ? 1 : 0;
   }
@@ -670,56 +1030,84 @@ attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const uint32_t tmem = *tmem_slot;
   const uint32_t t_row = tmem + (static_cast<uint32_t>(q4 * 32) << 16);
 
-  const int kv_row0 = start + jb * 128;
   const int n_it = nblk - jb;
-  auto load_q = [&](int it) {
-    const int row0 = start + (jb + it) * 128;
-    mbar_expect_tx(q_full, 2 * L::TILE);
+  // Warp 0 issues every TMA load and MMA: the whole warp follows the issuing path with warp-uniform control flow
+  // and one elected lane issues, with the values that feed coordinates and descriptors broadcast from lane 0, so
+  // that the compiler can keep them in uniform registers.
+  const bool w0 = __shfl_sync(0xffffffffu, warp, 0) == 0;
+  const int u_start = __shfl_sync(0xffffffffu, start, 0);
+  const int u_jb = __shfl_sync(0xffffffffu, jb, 0);
+  const int kv_row0 = u_start + u_jb * 128;
+  auto load_q = [&](int it) {                          // Q / dO of query block jb + it into stage it % NQ
+    const int row0 = u_start + (u_jb + it) * 128;
+    const int st = it % NQ;
+    mbar_expect_tx(q_full + st, 2 * L::TILE);
 #pragma unroll
     for (int p = 0; p < PANELS; ++p) {
-      tma_load_2d(sQ + p * 16384, &tmQ, q_full, h * D + p * 64, row0);
-      tma_load_2d(sdO + p * 16384, &tmdO, q_full, h * D + p * 64, row0);
+      tma_load_2d(sQ + st * L::TILE + p * 16384, &tmQ, q_full + st, h * D + p * 64, row0);
+      tma_load_2d(sdO + st * L::TILE + p * 16384, &tmdO, q_full + st, h * D + p * 64, row0);
     }
   };
 
   bool ok = true;
-  if (tid == 0) {
-    mbar_expect_tx(bar_kv, 2 * L::TILE);
+  if (w0) {
+    if (elect_one()) {
+      mbar_expect_tx(bar_kv, 2 * L::TILE);
 #pragma unroll
-    for (int p = 0; p < PANELS; ++p) {
-      tma_load_2d(sK + p * 16384, &tmK, bar_kv, hkv * D + p * 64, kv_row0);
-      tma_load_2d(sV + p * 16384, &tmV, bar_kv, hkv * D + p * 64, kv_row0);
+      for (int p = 0; p < PANELS; ++p) {
+        tma_load_2d(sK + p * 16384, &tmK, bar_kv, hkv * D + p * 64, kv_row0);
+        tma_load_2d(sV + p * 16384, &tmV, bar_kv, hkv * D + p * 64, kv_row0);
+      }
+      load_q(0);
     }
-    load_q(0);
-    ok &= mbar_wait(bar_kv, 0, abort_flag, a.status, CB_ERR_WAIT_FULL);
+    ok = __all_sync(0xffffffffu, mbar_wait(bar_kv, 0, abort_flag, a.status, CB_ERR_WAIT_FULL));
   }
 
   const int r = q4 * 32 + (tid & 31);
   const float sl2 = a.scale * LOG2E;
-  const uint32_t kA = smem_u32(sK), vA = smem_u32(sV), pA = smem_u32(sP), qA = smem_u32(sQ), doA = smem_u32(sdO);
+  const uint32_t kA = smem_u32(sK), vA = smem_u32(sV), pA = smem_u32(sP);
+  const uint32_t u_tmem = __shfl_sync(0xffffffffu, tmem, 0);
+  // lse and delta of my query row: fetched one iteration ahead, the loads fly while this iteration works
+  auto row_stats = [&](int it, float& lse2_o, float& dlt_o) {
+    const int rg_ = (jb + it) * 128 + r;
+    const bool in = it < n_it && rg_ < len;
+    const long long at = static_cast<long long>(h) * a.T + start + rg_;
+    lse2_o = in ? a.lse[at] * LOG2E : 0.f;
+    dlt_o = in ? a.delta[at] : 0.f;
+  };
+  float lse2_n, dlt_n;
+  row_stats(0, lse2_n, dlt_n);
 
+  CB_PHASE_DECL;
   for (int it = 0; it < n_it; ++it) {
     const int i = jb + it;
-    if (tid == 0) {
-      if (D == 64) tma_store_wait_read<0>();          // the dQ tile of the last iteration has left the P / dS buffer
-      ok &= mbar_wait(q_full, it & 1, abort_flag, a.status, CB_ERR_WAIT_FULL);
-      if (ok) {
-        tc_fence_after();
+    CB_PHASE(0);
+    const uint32_t qA = smem_u32(sQ + (it % NQ) * L::TILE), doA = smem_u32(sdO + (it % NQ) * L::TILE);
+    if (w0) {
+      if (elect_one()) {
+        if (D == 64) tma_store_wait_read<0>();        // the dQ tile of the last iteration has left the P / dS buffer
+        if (NQ == 2 && it + 1 < n_it) load_q(it + 1); // the other stage was released by the last iteration's MMAs
+      }
+      ok = __all_sync(0xffffffffu, mbar_wait(q_full + (it % NQ), (it / NQ) & 1, abort_flag, a.status, CB_ERR_WAIT_FULL) && ok);
+      tc_fence_after();
+      if (ok && elect_one()) {
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
-          umma_f16_ss(tmem + C_S, desc_kmajor(qA, kk), desc_kmajor(kA, kk), IDESC_S, kk != 0);
+          umma_f16_ss(u_tmem + C_S, desc_kmajor(qA, kk), desc_kmajor(kA, kk), IDESC_S, kk != 0);
         umma_commit(bar_s);
       }
     }
     const int rg = i * 128 + r;                      // my query row within the document
     const bool row_ok = rg < len;
     const long long tq = start + rg;
-    const float lse2 = row_ok ? a.lse[static_cast<long long>(h) * a.T + tq] * LOG2E : 0.f;
-    const float dlt = row_ok ? a.delta[static_cast<long long>(h) * a.T + tq] : 0.f;
+    const float lse2 = lse2_n, dlt = dlt_n;
+    row_stats(it + 1, lse2_n, dlt_n);
     const bool diag = (it == 0);
+    CB_PHASE(1);
     // ---- phase 1: P = exp(S - lse), masked, to shared memory
     ok &= mbar_wait(bar_s, it & 1, abort_flag, a.status, CB_ERR_WAIT_TMEM_FULL);
     tc_fence_after();
+    CB_PHASE(2);
 #pragma unroll 1
     for (int c = half * 2; c < half * 2 + 2; ++c) {
       uint32_t s[32];
@@ -734,22 +1122,28 @@ attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       store_row_chunk32(sP, r, c, p);
     }
+    CB_PHASE(3);
     tc_fence_before();
     fence_async_smem();
     if (__syncthreads_or(!ok)) { ok = false; break; }
-    if (tid == 0) {
+    CB_PHASE(4);
+    if (w0) {
       tc_fence_after();
+      if (elect_one()) {
 #pragma unroll
-      for (int kk = 0; kk < 8; ++kk)                  // dV += P^T dO     (K = the 128 query rows)
-        umma_f16_ss(tmem + C_DV, desc_mnmajor(pA, kk), desc_mnmajor(doA, kk), IDESC_T, (it | kk) != 0);
+        for (int kk = 0; kk < 8; ++kk)                // dV += P^T dO     (K = the 128 query rows)
+          umma_f16_ss(u_tmem + C_DV, desc_mnmajor(pA, kk), desc_mnmajor(doA, kk), IDESC_T, (it | kk) != 0);
 #pragma unroll
-      for (int kk = 0; kk < D / 16; ++kk)             // dP = dO V^T      (over the columns S occupied)
-        umma_f16_ss(tmem + C_S, desc_kmajor(doA, kk), desc_kmajor(vA, kk), IDESC_S, kk != 0);
-      umma_commit(bar_dp);
+        for (int kk = 0; kk < D / 16; ++kk)           // dP = dO V^T      (over the columns S occupied)
+          umma_f16_ss(u_tmem + C_S, desc_kmajor(doA, kk), desc_kmajor(vA, kk), IDESC_S, kk != 0);
+        umma_commit(bar_dp);
+      }
     }
     // ---- phase 2: dS = P (dP - delta) scale, overwriting P in shared memory
+    CB_PHASE(5);
     ok &= mbar_wait(bar_dp, it & 1, abort_flag, a.status, CB_ERR_WAIT_TMEM_FULL);
     tc_fence_after();
+    CB_PHASE(6);
 #pragma unroll 1
     for (int c = half * 2; c < half * 2 + 2; ++c) {
       uint32_t dp[32];
@@ -761,23 +1155,31 @@ attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       for (int k = 0; k < 32; ++k) p[k] = p[k] * (__uint_as_float(dp[k]) - dlt) * a.scale;
       store_row_chunk32(sP, r, c, p);
     }
+    CB_PHASE(7);
     tc_fence_before();
     fence_async_smem();
     if (__syncthreads_or(!ok)) { ok = false; break; }
-    if (tid == 0) {
+    CB_PHASE(8);
+    if (w0) {
       tc_fence_after();
+      if (elect_one()) {
 #pragma unroll
-      for (int kk = 0; kk < 8; ++kk)                  // dK += dS^T Q
-        umma_f16_ss(tmem + C_DK, desc_mnmajor(pA, kk), desc_mnmajor(qA, kk), IDESC_T, (it | kk) != 0);
+        for (int kk = 0; kk < 8; ++kk)                // dK += dS^T Q
+          umma_f16_ss(u_tmem + C_DK, desc_mnmajor(pA, kk), desc_mnmajor(qA, kk), IDESC_T, (it | kk) != 0);
 #pragma unroll
-      for (int kk = 0; kk < 8; ++kk)                  // dQ = dS K        (K = the 128 kv rows)
-        umma_f16_ss(tmem + C_S, desc_kmajor(pA, kk), desc_mnmajor(kA, kk), IDESC_DQ, kk != 0);
-      umma_commit(bar_dq);
+        for (int kk = 0; kk < 8; ++kk)                // dQ = dS K        (K = the 128 kv rows)
+          umma_f16_ss(u_tmem + C_S, desc_kmajor(pA, kk), desc_mnmajor(kA, kk), IDESC_DQ, kk != 0);
+        umma_commit(bar_dq);
+      }
     }
     // ---- phase 3: dQ out
+    CB_PHASE(9);
     ok &= mbar_wait(bar_dq, it & 1, abort_flag, a.status, CB_ERR_WAIT_TMEM_FULL);
     tc_fence_after();
-    if (tid == 0 && ok && it + 1 < n_it) load_q(it + 1);                // Q / dO of this iteration are consumed
+    CB_PHASE(10);
+    if (NQ == 1 && w0 && ok && it + 1 < n_it) {                         // Q / dO of this iteration are consumed
+      if (elect_one()) load_q(it + 1);
+    }
     if (D == 64) {
       // dQ tile (fp32) -> the P / dS buffer, which nobody reads any more, as two [128 x 32] boxes in the layout
       // of the dq_acc tensor map -> one TMA reduce-add per box instead of eight red.global.add per thread.
@@ -789,13 +1191,15 @@ attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
       for (int cc = 0; cc < 8; ++cc)
         *reinterpret_cast<uint4*>(dstrow + ((cc ^ (r & 7)) << 4)) = make_uint4(dq[4 * cc], dq[4 * cc + 1], dq[4 * cc + 2], dq[4 * cc + 3]);
+      CB_PHASE(11);
       fence_async_smem();
       tc_fence_before();
       if (__syncthreads_or(!ok)) { ok = false; break; }
-      if (tid == 0) {
+      CB_PHASE(12);
+      if (w0 && elect_one()) {
         CB_DEBUG_CHECK_ST(a.status, start + i * 128 >= 0 && ((h * D) * 4) % 16 == 0, CB_DBG_TMA_COORD, start + i * 128);
-        tma_reduce_add_2d(&tmdQ, sP, h * D, start + i * 128);
-        tma_reduce_add_2d(&tmdQ, sP + 16384, h * D + 32, start + i * 128);
+        tma_reduce_add_2d(&tmdQ, sP, h * D, u_start + (u_jb + it) * 128);
+        tma_reduce_add_2d(&tmdQ, sP + 16384, h * D + 32, u_start + (u_jb + it) * 128);
         tma_store_commit();
       }
     } else {
@@ -816,7 +1220,10 @@ attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (__syncthreads_or(!ok)) { ok = false; break; }
     }
   }
-  if (D == 64 && tid == 0) tma_store_wait_all();
+  CB_PHASE_FLUSH;
+  if (D == 64 && w0) {
+    if (elect_one()) tma_store_wait_all();
+  }
   if (ok) {
     tc_fence_after();
     const int kg = jb * 128 + r;                      // my kv row within the document
@@ -923,13 +1330,30 @@ int cb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse
   cb::AttnArgs a = {};
   a.T = T; a.hq = hq; a.hk = hk; a.n_docs = n_docs; a.cu = cu; a.scale = scale;
   a.O = static_cast<cb::bf16*>(o); a.ldo = ldo; a.lse = lse; a.status = status;
-  dim3 grid((T + 127) / 128 + n_docs, hq);
+  dim3 grid(hq, (T + 127) / 128 + n_docs);            // x: query head (fastest, the heads of a group share K/V in L2); y: tile by descending weight
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  // CB_ATTN_FWD=2 in the environment selects the two-threads-per-row kernel.  Measured on the 0.5B shape
-  // (8 x 1024 tokens, 14 heads): 68.7 us against 61.0 us for the one-thread-per-row kernel below, which therefore
-  // stays the default: a kv block costs a chain of dependent hops (MMA commit -> TMEM load -> exchange -> TMEM
-  // store -> CTA barrier -> MMA), and halving the arithmetic per thread does not shorten that chain.
-  static const bool two_thread_rows = [] { const char* v = getenv("CB_ATTN_FWD"); return v != nullptr && v[0] == '2'; }();
+  // Default: the pipelined kernel (64-row kv blocks, double-buffered scores, O accumulated in TMEM).
+  // CB_ATTN_FWD=1 in the environment selects the first form (one thread per row, 128-row kv blocks, O in
+  // registers), CB_ATTN_FWD=2 the two-threads-per-row form; both are kept for comparison.
+  static const int form = [] { const char* v = getenv("CB_ATTN_FWD"); return (v != nullptr && v[0] >= '1' && v[0] <= '3') ? v[0] - '0' : 3; }();
+  if (form == 3) {
+    CUtensorMap mk64, mv64;                             // K / V in boxes of 64 rows
+    e = cbhost::make_tmap(&mk64, k, static_cast<unsigned long long>(hk) * D, T, ldk, 64, 64);
+    if (e) return e;
+    e = cbhost::make_tmap(&mv64, v, static_cast<unsigned long long>(hk) * D, T, ldv, 64, 64);
+    if (e) return e;
+    if (D == 64) {
+      static bool cfg = false;
+      if (!cfg) { e = set_smem(cb::attn_fwd3_kernel<64>, cb::Fwd3Smem<64>::TOTAL); if (e) return e; cfg = true; }
+      cb::attn_fwd3_kernel<64><<<grid, cb::FWD3_THREADS, cb::Fwd3Smem<64>::TOTAL, s>>>(mq, mk64, mv64, a);
+    } else {
+      static bool cfg = false;
+      if (!cfg) { e = set_smem(cb::attn_fwd3_kernel<128>, cb::Fwd3Smem<128>::TOTAL); if (e) return e; cfg = true; }
+      cb::attn_fwd3_kernel<128><<<grid, cb::FWD3_THREADS, cb::Fwd3Smem<128>::TOTAL, s>>>(mq, mk64, mv64, a);
+    }
+    return static_cast<int>(cudaGetLastError());
+  }
+  const bool two_thread_rows = form == 2;
   if (two_thread_rows) {
     if (D == 64) {
       static bool cfg = false;
@@ -989,7 +1413,7 @@ int cb_attn_bwd(const void* q, const void* k, const void* v, const void* o, cons
   a.T = T; a.hq = hq; a.hk = hk; a.n_docs = n_docs; a.cu = cu; a.scale = scale;
   a.lse = const_cast<float*>(lse); a.delta = delta; a.dq_acc = dq_acc; a.dk_part = dk_part; a.dv_part = dv_part;
   a.status = status;
-  dim3 grid((T + 127) / 128 + n_docs, hq);
+  dim3 grid(hq, (T + 127) / 128 + n_docs);            // x: query head (fastest, the heads of a group share K/V in L2); y: tile by descending weight
   // Two threads per score row, S / dP / dQ sharing TMEM columns, dK / dV accumulated per kv head with red.add
   // (so those buffers start from zero).  D = 64 additionally fits two CTAs per SM.
   const int part_heads = hk;
@@ -1008,5 +1432,16 @@ int cb_attn_bwd(const void* q, const void* k, const void* v, const void* o, cons
                                                   hq, hk, D, cu, n_docs, part_heads);
   return static_cast<int>(cudaGetLastError());
 }
+
+#ifdef CB_ATTN_PHASE_TIMERS
+// out[2][16] cycles per phase (see CB_PHASE in attn_bwd2_kernel), slot 15 = number of CTAs; clears the table
+int cb_attn_phase_read(unsigned long long* out) {
+  CB_CHECK_CUDA(cudaDeviceSynchronize());
+  CB_CHECK_CUDA(cudaMemcpyFromSymbol(out, cb::cb_attn_phase, sizeof(unsigned long long) * 32));
+  unsigned long long zero[32] = {};
+  CB_CHECK_CUDA(cudaMemcpyToSymbol(cb::cb_attn_phase, zero, sizeof(zero)));
+  return 0;
+}
+#endif
 
 }  // extern "C"

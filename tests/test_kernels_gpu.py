@@ -257,6 +257,33 @@ def test_attention_packed_fwd_bwd(hq, hk, d, bounds, T):
     _ext.check_status()
 
 
+def test_attention_many_documents_and_large_scores():
+    """More than 32 documents of mixed lengths (the tile schedule votes over the documents 32 at a time) and
+    scores with a large spread (the running reference maximum of the forward has to be raised and the output
+    accumulator rescaled several times along a row)."""
+    g = torch.Generator().manual_seed(3)
+    lens = torch.randint(1, 300, (41,), generator=g).tolist() + [700, 129, 128, 64, 65]
+    T = sum(lens) + 37
+    hq, hk, d = 6, 2, 64
+    nq, nk = hq * d, hk * d
+    qkv = (_rand(T, nq + 2 * nk) * 3.0).requires_grad_()
+    cu = torch.tensor([0] + torch.tensor(lens).cumsum(0).tolist(), dtype=torch.int32, device=DEV)
+    valid = int(cu[-1].item())
+    o = ops.attention_qkv_packed(qkv, cu, hq, hk, d)
+    gr = _rand(T, nq, seed=9)
+    o.backward(gr)
+    xr = qkv.detach().float().requires_grad_()
+    q = xr[:, :nq].reshape(T, hq, d)
+    k = xr[:, nq:nq + nk].reshape(T, hk, d)
+    v = xr[:, nq + nk:].reshape(T, hk, d)
+    want = ref.attention_varlen(q, k, v, cu, None).reshape(T, nq)
+    want.backward(gr.float())
+    _close(o[:valid], want[:valid], rtol=3e-2, atol=3e-2, what="attention fwd (41+5 documents, large scores)")
+    assert o[valid:].abs().max().item() == 0
+    _close(qkv.grad[:valid], xr.grad[:valid], rtol=5e-2, atol=5e-2, what="attention dqkv (large scores)")
+    _ext.check_status()
+
+
 def test_attention_varlen_separate_tensors():
     T, hq, hk, d = 700, 14, 2, 64
     q, k, v = _rand(T, hq, d), _rand(T, hk, d, seed=1), _rand(T, hk, d, seed=2)
