@@ -195,6 +195,23 @@ def run_attn(results, peaks, iters, only=None):
         _ext.check_status()
 
 
+def run_glu(results, peaks, iters, only=None):
+    """Gate | up projection + SwiGLU: one GEMM with the activation in its epilogue against GEMM + activation kernel."""
+    for name, (M, K, I) in {"mlp_0.5b": (8192, 896, 4864), "mlp_7b": (8192, 3584, 18944)}.items():
+        if only and only != name:
+            continue
+        x, w = bf(M, K), bf(2 * I, K)
+        ms_fused = timed(lambda: ops.linear_swiglu(x, w), iters)
+        gu = torch.empty(M, 2 * I, dtype=torch.bfloat16, device=DEV)
+        ms_gemm = timed(lambda: ops.gemm(x, w, out=gu), iters)
+        ms_two = timed(lambda: ops.swiglu(ops.gemm(x, w, out=gu)), iters)
+        fl = 2.0 * M * 2 * I * K
+        results.append({"kernel": "gateup_gemm+swiglu_epilogue", "case": name, "ms": ms_fused, "tflops": fl / ms_fused / 1e9,
+                        "frac_of_measured_bf16": fl / ms_fused / 1e9 / peaks["bf16_tflops"], "gemm_alone_ms": ms_gemm,
+                        "gemm_then_activation_ms": ms_two})
+        _ext.check_status()
+
+
 def run_elementwise(results, peaks, iters, only=None):
     T, H, I = 8192, 896, 4864
     bw = peaks["hbm_gbs"]
@@ -279,6 +296,15 @@ def main():
         _ext.check_status()
         print("ok")
         return
+    if args.one and args.one.startswith("glu:"):                  # glu:mlp_0.5b - the GEMM with the SwiGLU epilogue
+        M, K, I = {"mlp_0.5b": (8192, 896, 4864), "mlp_7b": (8192, 3584, 18944)}[args.one.split(":", 1)[1]]
+        x, w = bf(M, K), bf(2 * I, K)
+        for _ in range(3):
+            ops.linear_swiglu(x, w)
+        torch.cuda.synchronize()
+        _ext.check_status()
+        print("ok")
+        return
     if args.one and args.one.startswith(("mx:", "mxp:")):
         from chronicals_b200.utils.fp8_utils import PAIR_TILE_ROWS, mxfp8_block_scaled_matmul, mxfp8_quantize_packed
         tile = PAIR_TILE_ROWS if args.one.startswith("mxp:") else 128          # mxp: the CTA-pair kernel
@@ -325,7 +351,7 @@ def main():
 
     print(f"peaks ({peaks['source']}): bf16 {peaks['bf16_tflops']} TFLOP/s, HBM {peaks['hbm_gbs']} GB/s", flush=True)
     results = _Live()
-    groups = {"gemm": run_gemm, "gemm_fp8": run_gemm_fp8, "gemm_mxfp8": run_gemm_mxfp8, "attn": run_attn, "elementwise": run_elementwise, "cce": run_cce, "optim": run_optim}
+    groups = {"gemm": run_gemm, "gemm_fp8": run_gemm_fp8, "gemm_mxfp8": run_gemm_mxfp8, "attn": run_attn, "glu": run_glu, "elementwise": run_elementwise, "cce": run_cce, "optim": run_optim}
     for name, fn in groups.items():
         if args.only and args.only != name:
             continue

@@ -41,6 +41,7 @@ struct AttnArgs {
   float* dk_part;       // [T, hk, D] fp32, zero-initialised; accumulated with red.add over the group's query heads
   float* dv_part;
   int* status;
+  int o_tma;            // forward: a tensor map over O exists, whole blocks may leave by TMA store
 };
 
 // Phase timers (compiled in with -DCB_ATTN_PHASE_TIMERS only): two threads of every CTA - the MMA-issuing thread
@@ -111,6 +112,17 @@ __device__ __forceinline__ void store_row_chunk32(uint8_t* base, int r, int c32,
     u.z = pack_bf16x2(v[8 * q + 4], v[8 * q + 5]);
     u.w = pack_bf16x2(v[8 * q + 6], v[8 * q + 7]);
     *reinterpret_cast<uint4*>(row + ((cc ^ (r & 7)) << 4)) = u;
+  }
+}
+
+// the same for 32 values already packed as bf16 pairs
+__device__ __forceinline__ void store_row_chunk32_packed(uint8_t* base, int r, int c32, const uint32_t (&v)[16]) {
+  const int panel = c32 >> 1;
+  uint8_t* row = base + panel * 16384 + r * 128;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const int cc = (c32 & 1) * 4 + q;
+    *reinterpret_cast<uint4*>(row + ((cc ^ (r & 7)) << 4)) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
   }
 }
 
@@ -624,7 +636,8 @@ __global__ void attn_delta_generic_kernel(const bf16* __restrict__ dO, const bf1
 //   * S(j+1) is computed while the softmax threads work on S(j) (the scores are double-buffered); P(j) (bf16)
 //     overwrites the first 32 columns of S(j) and is consumed from TMEM by the P V product, which accumulates O in
 //     TMEM over the whole kv loop, so the output never travels through registers inside the loop;
-//   * a fifth warp owns the TMA ring (K and V blocks, separate rings) and issues every MMA; the four softmax warps
+//   * a fifth warp issues every MMA and a sixth owns the TMA rings (K and V blocks, separate rings, stages handed
+//     back by tcgen05.commit); the four softmax warps
 //     never meet at a CTA barrier: they signal "P(j) written, S(j) consumed" on an mbarrier and move straight on to
 //     S(j+1), which is already complete in the other buffer;
 //   * one pass over the scores: a thread keeps its 64 scores of the block in registers, takes their maximum, and
@@ -633,7 +646,7 @@ __global__ void attn_delta_generic_kernel(const bf16* __restrict__ dO, const bf1
 //     rescales the thread's own O row in TMEM, which after the first blocks of a causal row is rare.
 // Per kv block a softmax thread issues about 64 x (max, fma, ex2, add, half a cvt) instructions and nothing else;
 // the exp2 unit (16 results per clock and SM) is the bound: 1024 cycles per [128 x 128] of scores.
-constexpr int FWD3_THREADS = 160;                      // 4 softmax warps + 1 warp for TMA and MMA issue
+constexpr int FWD3_THREADS = 192;                      // 4 softmax warps + the MMA-issuing warp + the TMA warp
 constexpr float FWD3_RAISE_LOG2 = 8.f;                 // raise the reference maximum only beyond 2^8
 
 template <int D>
@@ -651,12 +664,17 @@ struct Fwd3Smem {
 template <int D>
 __global__ void __launch_bounds__(FWD3_THREADS, 2)
 attn_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                 const __grid_constant__ CUtensorMap tmV, const AttnArgs a) {
+                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, const AttnArgs a) {
   using L = Fwd3Smem<D>;
   constexpr int NS = L::NS;
   constexpr int PANELS = D / 64;
   constexpr uint32_t TMEM_COLS = 256;                  // S0 [0, 64)  S1 [64, 128)  O [128, 128 + D)
   constexpr uint32_t C_O = 128;
+  // D = 64 leaves 64 columns: P(j) goes to its own 32 columns (P0 [192, 224), P1 [224, 256)) instead of over S(j),
+  // so S(j+2) may overwrite S(j) as soon as the softmax threads hold the scores in registers - a whole
+  // exponentiation pass earlier than "P(j) written".  D = 128 fills all 256 columns and keeps P over S.
+  constexpr bool P_APART = (D == 64);
+  constexpr uint32_t C_P = 192;
   constexpr uint32_t IDESC_S = umma_idesc_bf16(128, 64, 0, 0);
   constexpr uint32_t IDESC_PV = umma_idesc_bf16(128, D, 0, 1);
 
@@ -674,19 +692,26 @@ attn_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint8_t* sV = smem + L::OFF_V;
   uint64_t* k_full = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);    // [NS]
   uint64_t* v_full = k_full + NS;                                       // [NS]
-  uint64_t* bar_s = v_full + NS;                                        // [2]  S(j) complete in buffer j & 1
+  uint64_t* k_empty = v_full + NS;                                      // [NS] S of the stage's block complete
+  uint64_t* v_empty = k_empty + NS;                                     // [NS] P V of the stage's block complete
+  uint64_t* bar_s = v_empty + NS;                                       // [2]  S(j) complete in buffer j & 1
   uint64_t* p_ready = bar_s + 2;                                        // [2]  128 arrivals: P(j) written, S(j) consumed
   uint64_t* bar_o = p_ready + 2;                                        //      P V product of block j complete (phase j)
   uint64_t* bar_q = bar_o + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_q + 1);
+  uint64_t* s_free = bar_q + 1;                                         // [2]  128 arrivals: S(j) is in registers
+  uint64_t* o_staged = s_free + 2;                                      //      128 arrivals: output rows are in shared memory
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_staged + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5;
   if (tid == 0) {
-    for (int i = 0; i < NS; ++i) { mbar_init(k_full + i, 1); mbar_init(v_full + i, 1); }
+    for (int i = 0; i < NS; ++i) {
+      mbar_init(k_full + i, 1); mbar_init(v_full + i, 1); mbar_init(k_empty + i, 1); mbar_init(v_empty + i, 1);
+    }
     mbar_init(bar_s, 1); mbar_init(bar_s + 1, 1);
     mbar_init(p_ready, 128); mbar_init(p_ready + 1, 128);
     mbar_init(bar_o, 1); mbar_init(bar_q, 1);
+    mbar_init(s_free, 128); mbar_init(s_free + 1, 128); mbar_init(o_staged, 128);
     mbar_fence_init();
     *abort_flag = a.status[0] != 0 ? 1 : 0;
   }
@@ -700,95 +725,94 @@ attn_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   bool ok = true;
   CB_PHASE_DECL_T(128, 64);            // slot 0: the MMA / TMA thread, slot 1: a softmax thread
 
-  if (warp == 4) {
-    // ------------------------------------------------------------------ TMA ring + MMA issue
-    // The whole warp walks this path with warp-uniform control flow and one elected lane issues; the values that
-    // feed addresses and descriptors are broadcast from lane 0 so that they are uniform for the compiler too.
+  if (warp == 5) {
+    // ------------------------------------------------------------------ TMA producer: Q once, then the K and V rings
+    // (whole warp, warp-uniform control flow, one elected lane issues; see elect_one)
     const int u_start = __shfl_sync(0xffffffffu, start, 0);
     const int u_qb = __shfl_sync(0xffffffffu, qb, 0);
     const int u_nkv = __shfl_sync(0xffffffffu, n_kv, 0);
-    const uint32_t u_tmem = __shfl_sync(0xffffffffu, tmem, 0);
-    const uint32_t qa = smem_u32(sQ);
-    auto wait_w = [&](uint64_t* bar, uint32_t parity, int code) {
-      ok = __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, a.status, code) && ok);
-    };
-    auto load_k = [&](int j) {
+    if (elect_one()) {
+      mbar_expect_tx(bar_q, L::QT);
+#pragma unroll
+      for (int p = 0; p < PANELS; ++p) tma_load_2d(sQ + p * 16384, &tmQ, bar_q, h * D + p * 64, u_start + u_qb * 128);
+    }
+    for (int j = 0; j < u_nkv && ok; ++j) {
       const int st = j % NS;
+      if (j >= NS) {                                    // the stage's previous block: S(j - NS) complete
+        ok = __all_sync(0xffffffffu, mbar_wait(k_empty + st, ((j / NS) - 1) & 1, abort_flag, a.status, CB_ERR_WAIT_EMPTY) && ok);
+        if (!ok) break;
+      }
       if (elect_one()) {
         mbar_expect_tx(k_full + st, L::KT);
 #pragma unroll
         for (int p = 0; p < PANELS; ++p)
           tma_load_2d(sK + st * L::KT + p * 8192, &tmK, k_full + st, hkv * D + p * 64, u_start + j * 64);
       }
-    };
-    auto load_v = [&](int j) {
-      const int st = j % NS;
+      if (j >= NS) {                                    // P V of block j - NS complete
+        ok = __all_sync(0xffffffffu, mbar_wait(v_empty + st, ((j / NS) - 1) & 1, abort_flag, a.status, CB_ERR_WAIT_EMPTY) && ok);
+        if (!ok) break;
+      }
       if (elect_one()) {
         mbar_expect_tx(v_full + st, L::KT);
 #pragma unroll
         for (int p = 0; p < PANELS; ++p)
           tma_load_2d(sV + st * L::KT + p * 8192, &tmV, v_full + st, hkv * D + p * 64, u_start + j * 64);
       }
+    }
+    __syncwarp();
+  } else if (warp == 4) {
+    // ------------------------------------------------------------------ MMA issue
+    // Per kv block: wait for P(j), issue O += P(j) V(j), then S(j+2) into the score buffer P(j) has just left.
+    // Every tcgen05.commit arrives on the consumers' barrier and on the ring's "stage free" barrier.
+    const int u_nkv = __shfl_sync(0xffffffffu, n_kv, 0);
+    const uint32_t u_tmem = __shfl_sync(0xffffffffu, tmem, 0);
+    const uint32_t qa = smem_u32(sQ);
+    auto wait_w = [&](uint64_t* bar, uint32_t parity, int code) {
+      ok = __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, a.status, code) && ok);
     };
     auto issue_s = [&](int j) {                         // S(j) = Q K(j)^T into buffer j & 1
-      const uint32_t kb = smem_u32(sK + (j % NS) * L::KT);
+      const int st = j % NS;
+      wait_w(k_full + st, (j / NS) & 1, CB_ERR_WAIT_FULL);
+      const uint32_t kb = smem_u32(sK + st * L::KT);
       tc_fence_after();
-      if (elect_one()) {
+      if (ok && elect_one()) {
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
           umma_f16_ss(u_tmem + (j & 1) * 64, umma_smem_desc(qa + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024),
                       umma_smem_desc(kb + (kk >> 2) * 8192 + (kk & 3) * 32, 16, 1024), IDESC_S, kk != 0);
         umma_commit(bar_s + (j & 1));
+        umma_commit(k_empty + st);
       }
     };
-    if (elect_one()) {
-      mbar_expect_tx(bar_q, L::QT);
-#pragma unroll
-      for (int p = 0; p < PANELS; ++p) tma_load_2d(sQ + p * 16384, &tmQ, bar_q, h * D + p * 64, u_start + u_qb * 128);
-    }
-    int next_k = 0;
-    for (; next_k < NS && next_k < u_nkv; ++next_k) { load_k(next_k); load_v(next_k); }
     wait_w(bar_q, 0, CB_ERR_WAIT_FULL);
-    wait_w(k_full, 0, CB_ERR_WAIT_FULL);
     if (ok) issue_s(0);
-    if (ok && u_nkv > 1) {
-      wait_w(k_full + (1 % NS), 0, CB_ERR_WAIT_FULL);
-      if (ok) issue_s(1);
-    }
+    if (ok && u_nkv > 1) issue_s(1);
     CB_PHASE(0);
     for (int j = 0; j < u_nkv && ok; ++j) {
-      wait_w(p_ready + (j & 1), (j >> 1) & 1, CB_ERR_WAIT_TMEM_EMPTY);
-      CB_PHASE(1);
-      wait_w(v_full + (j % NS), (j / NS) & 1, CB_ERR_WAIT_FULL);
-      CB_PHASE(2);
-      if (j >= 1) {
-        // phase j - 1 of bar_o has to be observed before this iteration's commit can complete phase j
-        wait_w(bar_o, (j - 1) & 1, CB_ERR_WAIT_TMEM_FULL);
-        if (ok && j - 1 + NS < u_nkv) load_v(j - 1 + NS);              // V stage of block j - 1 is free
+      const int st = j % NS;
+      if (P_APART && j + 2 < u_nkv) {
+        wait_w(s_free + (j & 1), (j >> 1) & 1, CB_ERR_WAIT_TMEM_EMPTY);
+        if (ok) issue_s(j + 2);
       }
       CB_PHASE(3);
+      wait_w(p_ready + (j & 1), (j >> 1) & 1, CB_ERR_WAIT_TMEM_EMPTY);
+      CB_PHASE(1);
+      wait_w(v_full + st, (j / NS) & 1, CB_ERR_WAIT_FULL);
+      CB_PHASE(2);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t vb = smem_u32(sV + (j % NS) * L::KT);
+      const uint32_t vb = smem_u32(sV + st * L::KT);
       if (elect_one()) {
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)                  // O += P(j) V(j): A = P from TMEM, 16 bf16 = 8 words per step
-          umma_f16_ts(u_tmem + C_O, u_tmem + (j & 1) * 64 + kk * 8, umma_smem_desc(vb + kk * 2048, 8192, 1024), IDESC_PV,
-                      (j | kk) != 0);
+          umma_f16_ts(u_tmem + C_O, u_tmem + (P_APART ? C_P + (j & 1) * 32 : (j & 1) * 64) + kk * 8,
+                      umma_smem_desc(vb + kk * 2048, 8192, 1024), IDESC_PV, (j | kk) != 0);
         umma_commit(bar_o);
+        umma_commit(v_empty + st);
       }
       CB_PHASE(4);
-      // S(j) was consumed (p_ready), so its K stage is free; S(j+1) finished while the softmax of block j ran
-      if (j + 1 < u_nkv) wait_w(bar_s + ((j + 1) & 1), ((j + 1) >> 1) & 1, CB_ERR_WAIT_TMEM_FULL);
-      CB_PHASE(5);
-      while (ok && next_k < u_nkv && next_k - NS <= j + 1) { load_k(next_k); ++next_k; }
-      CB_PHASE(6);
-      if (ok && j + 2 < u_nkv) {
-        wait_w(k_full + ((j + 2) % NS), ((j + 2) / NS) & 1, CB_ERR_WAIT_FULL);
-        CB_PHASE(7);
-        if (ok) issue_s(j + 2);
-        CB_PHASE(8);
-      }
+      if (!P_APART && j + 2 < u_nkv) issue_s(j + 2);
+      CB_PHASE(8);
     }
     __syncwarp();
   } else {
@@ -814,6 +838,10 @@ attn_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tmem_ld_32x32(t_s, s0);
       tmem_ld_32x32(t_s + 32, s1);
       tmem_ld_wait();
+      if (P_APART) {                                    // the scores are in registers: their buffer may take S(j+2)
+        tc_fence_before();
+        mbar_arrive(s_free + (j & 1));
+      }
       CB_PHASE(2);
       // columns j*64 + c <= qb*128 + r are visible; only the blocks that touch the diagonal need the test
       const int lim = qb * 128 + r - j * 64;
@@ -824,13 +852,21 @@ attn_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           if (c + 32 > lim) s1[c] = 0xff800000u;
         }
       }
-      float mx0 = -INFINITY, mx1 = -INFINITY;
+      float mxc[8];                                     // eight independent chains: the maximum is latency-, not issue-bound
 #pragma unroll
-      for (int c = 0; c < 32; ++c) {
-        mx0 = fmaxf(mx0, __uint_as_float(s0[c]));
-        mx1 = fmaxf(mx1, __uint_as_float(s1[c]));
+      for (int q = 0; q < 4; ++q) {
+        mxc[q] = fmaxf(__uint_as_float(s0[q]), __uint_as_float(s0[q + 4]));
+        mxc[q + 4] = fmaxf(__uint_as_float(s1[q]), __uint_as_float(s1[q + 4]));
       }
-      const float mx = fmaxf(mx0, mx1);
+#pragma unroll
+      for (int c = 8; c < 32; c += 4) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          mxc[q] = fmaxf(mxc[q], __uint_as_float(s0[c + q]));
+          mxc[q + 4] = fmaxf(mxc[q + 4], __uint_as_float(s1[c + q]));
+        }
+      }
+      const float mx = fmaxf(fmaxf(fmaxf(mxc[0], mxc[1]), fmaxf(mxc[2], mxc[3])), fmaxf(fmaxf(mxc[4], mxc[5]), fmaxf(mxc[6], mxc[7])));
       CB_PHASE(3);
       const bool up = mx > m_ref + raise;               // also true for the first block (m_ref = -inf)
       bool o_seen = false;
@@ -865,7 +901,8 @@ attn_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const float e0 = ex2_approx(fmaf(__uint_as_float(s0[2 * i]), sl2, -mb));
         const float e1 = ex2_approx(fmaf(__uint_as_float(s0[2 * i + 1]), sl2, -mb));
         const float e2 = ex2_approx(fmaf(__uint_as_float(s1[2 * i]), sl2, -mb));
-        const float e3 = ex2_approx(fmaf(__uint_as_float(s1[2 * i + 1]), sl2, -mb));
+        // one exponential in four runs on the FMA pipe: the exp2 unit is this loop's bound
+        const float e3 = ex2_fma(fmaf(__uint_as_float(s1[2 * i + 1]), sl2, -mb));
         rs0 += e0 + e1;
         rs1 += e2 + e3;
         pk[i] = pack_bf16x2(e0, e1);
@@ -873,19 +910,23 @@ attn_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       l_run += rs0 + rs1;
       CB_PHASE(5);
-      tmem_st_32x32(t_s, pk);                           // P(j): 64 bf16 = 32 words over the scores just read
+      // P(j): 64 bf16 = 32 words, over the scores just read or (D = 64) in its own columns, which P V of block
+      // j - 2 has left: its completion was observed before the arrival of the last iteration
+      tmem_st_32x32(P_APART ? t_row + C_P + (j & 1) * 32 : t_s, pk);
       tmem_st_wait();
       CB_PHASE(6);
       if (j > 0 && !o_seen) {
-        // keep pace with bar_o: a parity wait can only tell the current phase from the one before it
-        wait_all(bar_o, (j - 1) & 1, CB_ERR_WAIT_TMEM_FULL);
-        if (!ok) break;
+        // keep pace with bar_o: a parity wait can only tell the current phase from the one before it (a lane
+        // that gives up here is caught by the vote of the next wait)
+        ok &= mbar_wait(bar_o, (j - 1) & 1, abort_flag, a.status, CB_ERR_WAIT_TMEM_FULL);
       }
       CB_PHASE(7);
       tc_fence_before();
       mbar_arrive(p_ready + (j & 1));
       CB_PHASE(8);
     }
+    // A block that lies wholly inside its document leaves through shared memory and a TMA store (below)
+    const bool whole = a.o_tma != 0 && (qb + 1) * 128 <= len;          // CTA-uniform
     if (ok) {
       wait_all(bar_o, (n_kv - 1) & 1, CB_ERR_WAIT_TMEM_FULL);
       tc_fence_after();
@@ -894,6 +935,10 @@ attn_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const float inv = 1.f / l_run;
       const long long t = start + (row_ok ? rg : 0);
       CB_DEBUG_CHECK_ST(a.status, t >= 0 && t < a.T, CB_DBG_ATTN_ROW, t);
+      // A block that lies wholly inside its document leaves through shared memory (the Q tile, which the last
+      // S product has finished with) and one TMA store per 64-column panel: row-contiguous 128-byte writes
+      // instead of 32 scattered 16-byte sectors per store instruction.  The last, partial block of a document
+      // stores row by row, because a TMA box cannot skip the rows that belong to the next document.
       uint4* op = reinterpret_cast<uint4*>(a.O + t * a.ldo + static_cast<long long>(h) * D);
       if (ok) {
 #pragma unroll
@@ -901,7 +946,12 @@ attn_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           uint32_t o[32];
           tmem_ld_32x32(t_row + C_O + c * 32, o);
           tmem_ld_wait();
-          if (row_ok) {
+          if (whole) {
+            float v[32];
+#pragma unroll
+            for (int q = 0; q < 32; ++q) v[q] = __uint_as_float(o[q]) * inv;
+            store_row_chunk32(sQ, r, c, v);
+          } else if (row_ok) {
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
               uint4 u;
@@ -914,6 +964,21 @@ attn_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           }
         }
         if (row_ok) a.lse[static_cast<long long>(h) * a.T + t] = m_ref * a.scale + __logf(l_run);
+      }
+    }
+    if (whole) {
+      // every softmax thread reports its rows staged (also one that gave up, so that nobody waits without a
+      // limit); warp 0 then stores the tile
+      fence_async_smem();
+      mbar_arrive(o_staged);
+      if (warp == 0) {
+        wait_all(o_staged, 0, CB_ERR_WAIT_MISC);
+        if (ok && elect_one()) {
+#pragma unroll
+          for (int p = 0; p < PANELS; ++p) tma_store_2d(&tmO, sQ + p * 16384, h * D + p * 64, start + qb * 128);
+          tma_store_commit();
+          tma_store_wait_all();                         // shared memory is released when the CTA exits
+        }
       }
     }
   }
@@ -1009,7 +1074,8 @@ attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint64_t* bar_s = q_full + 3;
   uint64_t* bar_dp = q_full + 4;
   uint64_t* bar_dq = q_full + 5;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_full + 6);
+  uint64_t* stg_free = q_full + 6;                   // the dQ tile of the last iteration has left shared memory
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_full + 7);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   // 8 warps: warps w and w + 4 own the same 32 TMEM lanes (score rows) and split the columns in halves,
@@ -1018,6 +1084,7 @@ attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int q4 = warp & 3, half = warp >> 2;
   if (tid == 0) {
     mbar_init(q_full, 1); mbar_init(q_full + 1, 1); mbar_init(bar_kv, 1); mbar_init(bar_s, 1); mbar_init(bar_dp, 1); mbar_init(bar_dq, 1);
+    mbar_init(stg_free, 1);
     mbar_fence_init();
     *abort_flag = a.status[0] != 0 ? 1 : 0;
   }
@@ -1068,15 +1135,19 @@ attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const uint32_t kA = smem_u32(sK), vA = smem_u32(sV), pA = smem_u32(sP);
   const uint32_t u_tmem = __shfl_sync(0xffffffffu, tmem, 0);
   // lse and delta of my query row: fetched one iteration ahead, the loads fly while this iteration works
-  auto row_stats = [&](int it, float& lse2_o, float& dlt_o) {
+  // (the loaded values are not touched before the next iteration, so nothing waits for the loads here)
+  auto row_stats = [&](int it, float& lse_o, float& dlt_o) {
     const int rg_ = (jb + it) * 128 + r;
-    const bool in = it < n_it && rg_ < len;
     const long long at = static_cast<long long>(h) * a.T + start + rg_;
-    lse2_o = in ? a.lse[at] * LOG2E : 0.f;
-    dlt_o = in ? a.delta[at] : 0.f;
+    lse_o = 0.f;
+    dlt_o = 0.f;
+    if (it < n_it && rg_ < len) {
+      lse_o = __ldg(a.lse + at);
+      dlt_o = __ldg(a.delta + at);
+    }
   };
-  float lse2_n, dlt_n;
-  row_stats(0, lse2_n, dlt_n);
+  float lse_n, dlt_n;
+  row_stats(0, lse_n, dlt_n);
 
   CB_PHASE_DECL;
   for (int it = 0; it < n_it; ++it) {
@@ -1084,43 +1155,58 @@ attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     CB_PHASE(0);
     const uint32_t qA = smem_u32(sQ + (it % NQ) * L::TILE), doA = smem_u32(sdO + (it % NQ) * L::TILE);
     if (w0) {
-      if (elect_one()) {
-        if (D == 64) tma_store_wait_read<0>();        // the dQ tile of the last iteration has left the P / dS buffer
-        if (NQ == 2 && it + 1 < n_it) load_q(it + 1); // the other stage was released by the last iteration's MMAs
-      }
       ok = __all_sync(0xffffffffu, mbar_wait(q_full + (it % NQ), (it / NQ) & 1, abort_flag, a.status, CB_ERR_WAIT_FULL) && ok);
       tc_fence_after();
-      if (ok && elect_one()) {
+      if (elect_one()) {
+        if (ok) {
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk)
-          umma_f16_ss(u_tmem + C_S, desc_kmajor(qA, kk), desc_kmajor(kA, kk), IDESC_S, kk != 0);
-        umma_commit(bar_s);
+          for (int kk = 0; kk < D / 16; ++kk)
+            umma_f16_ss(u_tmem + C_S, desc_kmajor(qA, kk), desc_kmajor(kA, kk), IDESC_S, kk != 0);
+          umma_commit(bar_s);
+        }
+        // While S is computed, the TMA reduce of the last iteration's dQ tile finishes reading the P / dS buffer
+        // (and, D = 128, the dO stage the next load goes to); everybody waits for `stg_free` before writing P.
+        tma_store_wait_read<0>();
+        if (NQ == 2 && ok && it + 1 < n_it) load_q(it + 1);
+        mbar_arrive(stg_free);
       }
     }
     const int rg = i * 128 + r;                      // my query row within the document
     const bool row_ok = rg < len;
-    const long long tq = start + rg;
-    const float lse2 = lse2_n, dlt = dlt_n;
-    row_stats(it + 1, lse2_n, dlt_n);
+    const float lse2 = row_ok ? lse_n * LOG2E : INFINITY, dlt = dlt_n;
+    row_stats(it + 1, lse_n, dlt_n);
     const bool diag = (it == 0);
     CB_PHASE(1);
     // ---- phase 1: P = exp(S - lse), masked, to shared memory
     ok &= mbar_wait(bar_s, it & 1, abort_flag, a.status, CB_ERR_WAIT_TMEM_FULL);
+    ok &= mbar_wait(stg_free, it & 1, abort_flag, a.status, CB_ERR_WAIT_MISC);
     tc_fence_after();
     CB_PHASE(2);
-#pragma unroll 1
-    for (int c = half * 2; c < half * 2 + 2; ++c) {
+    // my 64 probabilities stay in registers as bf16 pairs (pk) for phase 2; rows past the end of the document
+    // carry lse = +inf and so exponentiate to exact zeros, only the diagonal block tests columns against rows
+    uint32_t pk[2][16];
+#pragma unroll
+    for (int cl = 0; cl < 2; ++cl) {
+      const int c = half * 2 + cl;
       uint32_t s[32];
-      float p[32];
       tmem_ld_32x32(t_row + C_S + c * 32, s);
       tmem_ld_wait();
+      if (diag) {
 #pragma unroll
-      for (int k = 0; k < 32; ++k) {
-        const bool keep = row_ok && (!diag || c * 32 + k <= r);
-        const float e = ex2_approx(fmaf(__uint_as_float(s[k]), sl2, -lse2));
-        p[k] = keep ? e : 0.f;
+        for (int k = 0; k < 16; ++k) {
+          float e0 = ex2_approx(fmaf(__uint_as_float(s[2 * k]), sl2, -lse2));
+          float e1 = ex2_approx(fmaf(__uint_as_float(s[2 * k + 1]), sl2, -lse2));
+          e0 = (c * 32 + 2 * k <= r) ? e0 : 0.f;
+          e1 = (c * 32 + 2 * k + 1 <= r) ? e1 : 0.f;
+          pk[cl][k] = pack_bf16x2(e0, e1);
+        }
+      } else {
+#pragma unroll
+        for (int k = 0; k < 16; ++k)
+          pk[cl][k] = pack_bf16x2(ex2_approx(fmaf(__uint_as_float(s[2 * k]), sl2, -lse2)),
+                                  ex2_approx(fmaf(__uint_as_float(s[2 * k + 1]), sl2, -lse2)));
       }
-      store_row_chunk32(sP, r, c, p);
+      store_row_chunk32_packed(sP, r, c, pk[cl]);
     }
     CB_PHASE(3);
     tc_fence_before();
@@ -1144,16 +1230,20 @@ attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     ok &= mbar_wait(bar_dp, it & 1, abort_flag, a.status, CB_ERR_WAIT_TMEM_FULL);
     tc_fence_after();
     CB_PHASE(6);
-#pragma unroll 1
-    for (int c = half * 2; c < half * 2 + 2; ++c) {
-      uint32_t dp[32];
-      float p[32];
-      tmem_ld_32x32(t_row + C_S + c * 32, dp);
-      load_row_chunk32(sP, r, c, p);
-      tmem_ld_wait();
 #pragma unroll
-      for (int k = 0; k < 32; ++k) p[k] = p[k] * (__uint_as_float(dp[k]) - dlt) * a.scale;
-      store_row_chunk32(sP, r, c, p);
+    for (int cl = 0; cl < 2; ++cl) {
+      const int c = half * 2 + cl;
+      uint32_t dp[32];
+      tmem_ld_32x32(t_row + C_S + c * 32, dp);
+      tmem_ld_wait();
+      uint32_t ds[16];
+#pragma unroll
+      for (int k = 0; k < 16; ++k) {
+        const float2 pp = unpack_bf16x2(pk[cl][k]);
+        ds[k] = pack_bf16x2(pp.x * (__uint_as_float(dp[2 * k]) - dlt) * a.scale,
+                            pp.y * (__uint_as_float(dp[2 * k + 1]) - dlt) * a.scale);
+      }
+      store_row_chunk32_packed(sP, r, c, ds);
     }
     CB_PHASE(7);
     tc_fence_before();
@@ -1180,17 +1270,23 @@ attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     if (NQ == 1 && w0 && ok && it + 1 < n_it) {                         // Q / dO of this iteration are consumed
       if (elect_one()) load_q(it + 1);
     }
-    if (D == 64) {
-      // dQ tile (fp32) -> the P / dS buffer, which nobody reads any more, as two [128 x 32] boxes in the layout
-      // of the dq_acc tensor map -> one TMA reduce-add per box instead of eight red.global.add per thread.
+    {
+      // dQ tile (fp32) -> shared memory as [128 x 32] boxes in the layout of the dq_acc tensor map -> one TMA
+      // reduce-add per box instead of eight red.global.add per thread and box.  The first two boxes go to the
+      // P / dS buffer, which nobody reads any more; D = 128 has two more, which go to this iteration's dO stage
+      // (dV and dP have consumed it; the next load into that stage waits for the reduce's reads, see the loop top).
       // Rows past the end of the document carry exact zeros (their P was masked), rows past T are clipped.
-      uint32_t dq[32];
-      tmem_ld_32x32(t_row + C_S + half * 32, dq);
-      tmem_ld_wait();
-      uint8_t* dstrow = sP + half * 16384 + r * 128;
+      uint8_t* sdO_it = sdO + (it % NQ) * L::TILE;
 #pragma unroll
-      for (int cc = 0; cc < 8; ++cc)
-        *reinterpret_cast<uint4*>(dstrow + ((cc ^ (r & 7)) << 4)) = make_uint4(dq[4 * cc], dq[4 * cc + 1], dq[4 * cc + 2], dq[4 * cc + 3]);
+      for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
+        uint32_t dq[32];
+        tmem_ld_32x32(t_row + C_S + c * 32, dq);
+        tmem_ld_wait();
+        uint8_t* dstrow = (c < 2 ? sP + c * 16384 : sdO_it + (c - 2) * 16384) + r * 128;
+#pragma unroll
+        for (int cc = 0; cc < 8; ++cc)
+          *reinterpret_cast<uint4*>(dstrow + ((cc ^ (r & 7)) << 4)) = make_uint4(dq[4 * cc], dq[4 * cc + 1], dq[4 * cc + 2], dq[4 * cc + 3]);
+      }
       CB_PHASE(11);
       fence_async_smem();
       tc_fence_before();
@@ -1198,30 +1294,16 @@ attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       CB_PHASE(12);
       if (w0 && elect_one()) {
         CB_DEBUG_CHECK_ST(a.status, start + i * 128 >= 0 && ((h * D) * 4) % 16 == 0, CB_DBG_TMA_COORD, start + i * 128);
-        tma_reduce_add_2d(&tmdQ, sP, h * D, u_start + (u_jb + it) * 128);
-        tma_reduce_add_2d(&tmdQ, sP + 16384, h * D + 32, u_start + (u_jb + it) * 128);
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c)
+          tma_reduce_add_2d(&tmdQ, c < 2 ? sP + c * 16384 : sdO_it + (c - 2) * 16384, h * D + c * 32,
+                            u_start + (u_jb + it) * 128);
         tma_store_commit();
       }
-    } else {
-#pragma unroll
-      for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
-        uint32_t dq[32];
-        tmem_ld_32x32(t_row + C_S + c * 32, dq);
-        tmem_ld_wait();
-        if (row_ok && ok) {
-          float* dst = a.dq_acc + (tq * a.hq + h) * D + c * 32;
-#pragma unroll
-          for (int k = 0; k < 32; k += 4)
-            red_add_v4(dst + k, __uint_as_float(dq[k]), __uint_as_float(dq[k + 1]), __uint_as_float(dq[k + 2]),
-                       __uint_as_float(dq[k + 3]));
-        }
-      }
-      tc_fence_before();
-      if (__syncthreads_or(!ok)) { ok = false; break; }
     }
   }
   CB_PHASE_FLUSH;
-  if (D == 64 && w0) {
+  if (w0) {
     if (elect_one()) tma_store_wait_all();
   }
   if (ok) {
@@ -1342,14 +1424,17 @@ int cb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse
     if (e) return e;
     e = cbhost::make_tmap(&mv64, v, static_cast<unsigned long long>(hk) * D, T, ldv, 64, 64);
     if (e) return e;
+    CUtensorMap mo;                                     // O in boxes of 128 rows x 64 columns, for the tile stores
+    a.o_tma = cbhost::make_tmap(&mo, o, static_cast<unsigned long long>(hq) * D, T, ldo, 64, 128) == 0 ? 1 : 0;
+    if (!a.o_tma) mo = mq;                              // O is not TMA-addressable: every block stores row by row
     if (D == 64) {
       static bool cfg = false;
       if (!cfg) { e = set_smem(cb::attn_fwd3_kernel<64>, cb::Fwd3Smem<64>::TOTAL); if (e) return e; cfg = true; }
-      cb::attn_fwd3_kernel<64><<<grid, cb::FWD3_THREADS, cb::Fwd3Smem<64>::TOTAL, s>>>(mq, mk64, mv64, a);
+      cb::attn_fwd3_kernel<64><<<grid, cb::FWD3_THREADS, cb::Fwd3Smem<64>::TOTAL, s>>>(mq, mk64, mv64, mo, a);
     } else {
       static bool cfg = false;
       if (!cfg) { e = set_smem(cb::attn_fwd3_kernel<128>, cb::Fwd3Smem<128>::TOTAL); if (e) return e; cfg = true; }
-      cb::attn_fwd3_kernel<128><<<grid, cb::FWD3_THREADS, cb::Fwd3Smem<128>::TOTAL, s>>>(mq, mk64, mv64, a);
+      cb::attn_fwd3_kernel<128><<<grid, cb::FWD3_THREADS, cb::Fwd3Smem<128>::TOTAL, s>>>(mq, mk64, mv64, mo, a);
     }
     return static_cast<int>(cudaGetLastError());
   }

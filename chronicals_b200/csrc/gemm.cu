@@ -110,7 +110,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
-  const int warp = threadIdx.x >> 5;
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);   // warp-uniform for the compiler too
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
@@ -211,7 +211,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+    // The whole warp walks the schedule with warp-uniform control flow and one elected lane issues, so stage
+    // addresses and descriptors live in uniform registers (see elect_one).
+    {
       int stage = 0;
       uint32_t phase = 0;
       uint32_t tile_cnt = 0;
@@ -227,35 +229,33 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         for (int nt = nt0; nt < nt1 && ok; ++nt, ++tile_cnt) {
           const uint32_t acc = tile_cnt & 1u;
           const uint32_t acc_phase = (tile_cnt >> 1) & 1u;
-          if (!mbar_wait(tempty + acc, acc_phase ^ 1, abort_flag, g.status, CB_ERR_WAIT_TMEM_EMPTY)) {
-            ok = false;
-            break;
-          }
+          ok = __all_sync(0xffffffffu, mbar_wait(tempty + acc, acc_phase ^ 1, abort_flag, g.status, CB_ERR_WAIT_TMEM_EMPTY));
+          if (!ok) break;
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
           for (int kb = kb0; kb < kb1; ++kb) {
-            if (!mbar_wait(full + stage, phase, abort_flag, g.status, CB_ERR_WAIT_FULL)) {
-              ok = false;
-              break;
-            }
+            ok = __all_sync(0xffffffffu, mbar_wait(full + stage, phase, abort_flag, g.status, CB_ERR_WAIT_FULL));
+            if (!ok) break;
             tc_fence_after();
             const uint32_t a_base = smem_u32(sA + stage * A_BYTES);
             const uint32_t b_base = smem_u32(sB + stage * B_BYTES);
+            if (elect_one()) {
 #pragma unroll
-            for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
-              const uint64_t adesc = A_MN ? umma_smem_desc(a_base + k * 2048, 8192, 1024)
-                                          : umma_smem_desc(a_base + k * 32, 16, 1024);
-              const uint64_t bdesc = B_MN ? umma_smem_desc(b_base + k * 2048, 8192, 1024)
-                                          : umma_smem_desc(b_base + k * 32, 16, 1024);
-              umma_f16_ss(d_tmem, adesc, bdesc, IDESC, (kb != kb0 || k != 0) ? 1u : 0u);
+              for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+                const uint64_t adesc = A_MN ? umma_smem_desc(a_base + k * 2048, 8192, 1024)
+                                            : umma_smem_desc(a_base + k * 32, 16, 1024);
+                const uint64_t bdesc = B_MN ? umma_smem_desc(b_base + k * 2048, 8192, 1024)
+                                            : umma_smem_desc(b_base + k * 32, 16, 1024);
+                umma_f16_ss(d_tmem, adesc, bdesc, IDESC, (kb != kb0 || k != 0) ? 1u : 0u);
+              }
+              umma_commit(empty + stage);  // frees the smem stage once these MMAs retire
             }
-            umma_commit(empty + stage);  // frees the smem stage once these MMAs retire
             if (++stage == STAGES) {
               stage = 0;
               phase ^= 1;
             }
           }
-          if (ok) umma_commit(tfull + acc);  // accumulator complete
+          if (ok && elect_one()) umma_commit(tfull + acc);  // accumulator complete
         }
       }
     }

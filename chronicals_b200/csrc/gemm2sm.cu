@@ -82,6 +82,8 @@ struct Args {
   // through push_c[owner] (a peer mapping, pre-offset so that the global row indexes it with pitch ldc)
   unsigned long long push_c[16];
   int push_rows;
+  // ---- gated-activation epilogue (GLU = 1 instantiation only): B is the fused gate | up weight [2 * glu_i, K]
+  int glu_i;
 };
 
 __device__ __forceinline__ void umma_f16_ss_2cta(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
@@ -162,7 +164,7 @@ __device__ __forceinline__ int pair_of_unit(const Args& g, long long u) {
 // k-block, K-major only).  Either way a k-block row is 128 bytes and one MMA consumes 32 bytes of it, so the
 // shared-memory layout, the descriptors and the pipeline are identical.
 // BN: columns of the pair's tile (256, 224 or 192); each CTA loads BN / 2 rows of B.
-template <int BN, int A_MN, int B_MN, int KIND, int TP = 0>
+template <int BN, int A_MN, int B_MN, int KIND, int TP = 0, int GLU = 0>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmW,
@@ -187,7 +189,7 @@ gemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
-  const int warp = threadIdx.x >> 5;
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);   // warp-uniform for the compiler too
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
@@ -241,7 +243,9 @@ gemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         const int nt = t / g.num_m_pairs;
         const int a_row = mp * 2 * BM + static_cast<int>(rank) * BM;
-        const int b_row = nt * BN + static_cast<int>(rank) * BNH;
+        // GLU: the leader's half of B holds the gate rows of activation columns [nt * BNH, +BNH), the peer's half
+        // the up rows of the same columns (glu_i rows further down in the fused gate|up weight)
+        const int b_row = GLU ? nt * BNH + static_cast<int>(rank) * g.glu_i : nt * BN + static_cast<int>(rank) * BNH;
         if (TP && g.panel_pairs > 0) {
           // rows of this tile come from rank `src`: wait (bounded) until its push kernel has signalled
           const int src = mp / g.panel_pairs;
@@ -298,8 +302,10 @@ gemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
     }
   } else if (warp == 1) {
-    if (lane == 0 && leader) {
+    if (leader) {
       // --------------------------------------------------------- MMA issuer for the pair
+      // The whole warp walks the schedule with warp-uniform control flow and one elected lane issues, so stage
+      // addresses and descriptors live in uniform registers (see elect_one).
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -310,37 +316,35 @@ gemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const uint32_t acc = seg_cnt & 1u;
         const uint32_t acc_phase = (seg_cnt >> 1) & 1u;
         ++seg_cnt;
-        if (!mbar_wait(tempty + acc, acc_phase ^ 1, abort_flag, g.status, CB_ERR_WAIT_TMEM_EMPTY)) {
-          ok = false;
-          break;
-        }
+        ok = __all_sync(0xffffffffu, mbar_wait(tempty + acc, acc_phase ^ 1, abort_flag, g.status, CB_ERR_WAIT_TMEM_EMPTY));
+        if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * 256;
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait(full + stage, phase, abort_flag, g.status, CB_ERR_WAIT_FULL)) {
-            ok = false;
-            break;
-          }
+          ok = __all_sync(0xffffffffu, mbar_wait(full + stage, phase, abort_flag, g.status, CB_ERR_WAIT_FULL));
+          if (!ok) break;
           tc_fence_after();
           const uint32_t a_base = smem_u32(sA + stage * A_BYTES);
           const uint32_t b_base = smem_u32(sB + stage * B_BYTES);
+          if (elect_one()) {
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k) {
-            const uint64_t adesc = A_MN ? umma_smem_desc(a_base + k * 2048, 8192, 1024)
-                                        : umma_smem_desc(a_base + k * 32, 16, 1024);
-            const uint64_t bdesc = B_MN ? umma_smem_desc(b_base + k * 2048, 8192, 1024)
-                                        : umma_smem_desc(b_base + k * 32, 16, 1024);
-            const uint32_t accum = (kb != kb0 || k != 0) ? 1u : 0u;
-            if (KIND) umma_f8_ss_2cta(d_tmem, adesc, bdesc, IDESC, accum);
-            else umma_f16_ss_2cta(d_tmem, adesc, bdesc, IDESC, accum);
+            for (int k = 0; k < BK / 16; ++k) {
+              const uint64_t adesc = A_MN ? umma_smem_desc(a_base + k * 2048, 8192, 1024)
+                                          : umma_smem_desc(a_base + k * 32, 16, 1024);
+              const uint64_t bdesc = B_MN ? umma_smem_desc(b_base + k * 2048, 8192, 1024)
+                                          : umma_smem_desc(b_base + k * 32, 16, 1024);
+              const uint32_t accum = (kb != kb0 || k != 0) ? 1u : 0u;
+              if (KIND) umma_f8_ss_2cta(d_tmem, adesc, bdesc, IDESC, accum);
+              else umma_f16_ss_2cta(d_tmem, adesc, bdesc, IDESC, accum);
+            }
+            umma_commit_2cta(empty + stage);    // frees this stage in both CTAs once the MMAs retire
           }
-          umma_commit_2cta(empty + stage);      // frees this stage in both CTAs once the MMAs retire
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1;
           }
         }
-        if (ok) umma_commit_2cta(tfull + acc);  // accumulator complete, visible to both epilogues
+        if (ok && elect_one()) umma_commit_2cta(tfull + acc);  // accumulator complete, visible to both epilogues
       }
     }
   } else {
@@ -529,7 +533,49 @@ gemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const bool row_ok = row < g.M;
       const bool whole = (kb0 == 0 && kb1 == g.num_kb);
 
-      if (whole) {
+      if (GLU) {
+        // Accumulator columns [0, BNH) are the gate, [BNH, BN) the up projection of activation columns
+        // nt * BNH ...  Per 64 columns: gate -> C (kept as bf16 pairs), up -> C, silu(gate) * up -> the activation
+        // tensor (map tmW), all three through the staging buffers and TMA stores.  The product uses the values as
+        // rounded to bf16 for C, so it equals the stand-alone kernel applied to the stored gate | up.
+#pragma unroll 1
+        for (int c0 = 0; c0 < BNH; c0 += 64) {
+          const int acol = nt * BNH + c0;
+          if (acol >= g.glu_i) break;                         // uniform across the warp
+          uint32_t r[64], gp[32];
+          tmem_ld_32x32(t_row + c0, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+          tmem_ld_32x32(t_row + c0 + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+          tmem_ld_wait();
+          fuse32(reinterpret_cast<float*>(r), row, row_ok, acol);
+          fuse32(reinterpret_cast<float*>(r + 32), row, row_ok, acol + 32);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) gp[j] = pack_bf16x2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+          stage_bf16(r);
+          flush(&tmC, acol, row0w, false, row0w < g.M);
+          tmem_ld_32x32(t_row + BNH + c0, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+          tmem_ld_32x32(t_row + BNH + c0 + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+          tmem_ld_wait();
+          fuse32(reinterpret_cast<float*>(r), row, row_ok, g.glu_i + acol);
+          fuse32(reinterpret_cast<float*>(r + 32), row, row_ok, g.glu_i + acol + 32);
+          stage_bf16(r);
+          flush(&tmC, g.glu_i + acol, row0w, false, row0w < g.M);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float2 gt = unpack_bf16x2(gp[j]);
+            const float2 up = unpack_bf16x2(pack_bf16x2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1])));
+            r[2 * j] = __float_as_uint(gt.x * (1.f / (1.f + __expf(-gt.x))) * up.x);
+            r[2 * j + 1] = __float_as_uint(gt.y * (1.f / (1.f + __expf(-gt.y))) * up.y);
+          }
+          stage_bf16(r);
+          flush(&tmW, acol, row0w, false, row0w < g.M);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          if (leader) mbar_arrive(tempty + acc);
+          else mbar_arrive_remote(tempty_leader + acc * 8);
+        }
+      } else if (whole) {
         const int step = g.out_fp32 ? 32 : 64;
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += step) {
@@ -641,10 +687,10 @@ constexpr int MAX_DEVICES = 64;
 void* g_ws_ptr[MAX_DEVICES] = {};
 unsigned long long g_ws_bytes[MAX_DEVICES] = {};
 
-template <int BN, int A_MN, int B_MN, int KIND = 0, int TP = 0>
+template <int BN, int A_MN, int B_MN, int KIND = 0, int TP = 0, int GLU = 0>
 int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tw, const cb2::Args& g,
             int pairs, cudaStream_t s, const CUtensorMap* ta2 = nullptr, const CUtensorMap* tb2 = nullptr) {
-  auto kern = cb2::gemm2sm_kernel<BN, A_MN, B_MN, KIND, TP>;
+  auto kern = cb2::gemm2sm_kernel<BN, A_MN, B_MN, KIND, TP, GLU>;
   static bool configured = false;
   if (!configured) {
     CB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, cb2::SMEM_TOTAL));
@@ -804,6 +850,42 @@ int cb_gemm2sm_bf16_ex(const void* A, const void* B, void* C, const void* bias, 
   if (bn == 256) return dispatch_layout<256>(a_mn, b_mn, ta, tb, tc, tw, g, pairs, s);
   if (bn == 224) return dispatch_layout<224>(a_mn, b_mn, ta, tb, tc, tw, g, pairs, s);
   return dispatch_layout<192>(a_mn, b_mn, ta, tb, tc, tw, g, pairs, s);
+}
+
+// Gate | up projection with the gated activation in the epilogue:
+//   GU[M, 2I] = A[M, K] W[2I, K]^T (+ bias[2I]),   ACT[M, I] = silu(GU[:, :I]) * GU[:, I:]
+// W holds the gate rows first, then the up rows (the fused weight as stored); both outputs are bf16.  A pair's
+// tile covers 256 rows and 128 activation columns: the leader loads the 128 gate rows of those columns, its peer the
+// 128 up rows, so every CTA finds gate and up of its 128 rows side by side in the accumulator.  I must be a
+// multiple of 128 (returns -5 otherwise; the caller then runs the projection and the activation separately).
+int cb_gemm2sm_bf16_glu(const void* A, const void* W, void* GU, void* ACT, const void* bias, int M, int I, int K,
+                        long long lda, long long ldw, long long ld_gu, long long ld_act, int* status, void* stream) {
+  if (M <= 0 || I <= 0 || K <= 0) return -1;
+  if (I % 128 != 0) return -5;
+  if (!cb_gemm2sm_supported(GU, ld_gu, 0) || !cb_gemm2sm_supported(ACT, ld_act, 0)) return -2;
+  CUtensorMap ta, tb, tc, tact;
+  int e = cbhost::make_tmap(&ta, A, K, M, lda, 64, cb2::BM);
+  if (e) return e;
+  e = cbhost::make_tmap(&tb, W, K, 2ull * I, ldw, 64, 128);
+  if (e) return e;
+  e = cbhost::make_tmap(&tc, GU, 2ull * I, M, ld_gu, 64, 32, 2);
+  if (e) return e;
+  e = cbhost::make_tmap(&tact, ACT, I, M, ld_act, 64, 32, 2);
+  if (e) return e;
+  cb2::Args g = {};
+  g.M = M; g.N = 2 * I; g.K = K;
+  g.glu_i = I;
+  g.num_m_pairs = (M + 2 * cb2::BM - 1) / (2 * cb2::BM);
+  g.num_n_tiles = I / 128;
+  g.num_tiles = g.num_m_pairs * g.num_n_tiles;
+  g.num_kb = (K + cb2::BK - 1) / cb2::BK;
+  g.num_kb1 = g.num_kb;
+  g.C = GU; g.ldc = ld_gu;
+  g.bias = static_cast<const cb::bf16*>(bias);
+  g.status = status;
+  int pairs = cbhost::num_sms() / 2;
+  if (pairs > g.num_tiles) pairs = g.num_tiles;
+  return launch2<256, 0, 0, 0, 0, 1>(ta, tb, tc, tact, g, pairs, static_cast<cudaStream_t>(stream));
 }
 
 // C[M,N] = A B^T + A2 B2^T (+bias) (+addend): the second product (inner dimension K2, small) is accumulated in the

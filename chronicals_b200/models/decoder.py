@@ -114,6 +114,11 @@ class FusedLinear(nn.Module):
             self.weight[sl[s]] -= self.lora_delta(s).to(self.weight.dtype)
         self.lora_merged = False
 
+    def is_plain(self) -> bool:
+        """No adapter branch and no FP8 path: the projection is one bf16 GEMM on ``weight``."""
+        return (not (self.has_lora and not self.lora_merged) and not getattr(self, "use_fp8_rowwise", False)
+                and not getattr(self, "use_mxfp8", False))
+
     def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
         if self.has_lora and not self.lora_merged:
             from ..lora.functional import fused_lora_forward
@@ -176,8 +181,12 @@ class MLP(nn.Module):
         self.gelu = cfg.hidden_act in ("gelu", "gelu_pytorch_tanh", "gelu_new")
 
     def forward(self, x, residual):
-        gu = self.gate_up_proj(x)
-        a = ops.geglu(gu) if self.gelu else ops.swiglu(gu)
+        fl = self.gate_up_proj
+        if not self.gelu and fl.is_plain():
+            a = ops.linear_swiglu(x, fl.weight, fl.bias)       # activation in the projection's epilogue
+        else:
+            gu = fl(x)
+            a = ops.geglu(gu) if self.gelu else ops.swiglu(gu)
         return self.down_proj(a, residual)
 
 

@@ -10,6 +10,7 @@ On a CUDA device the kernel library is mandatory; a missing library raises.
 from __future__ import annotations
 
 import math
+import os
 import weakref
 from typing import Optional, Tuple
 
@@ -26,6 +27,7 @@ __all__ = [
 
 # how often an op left the hand-written kernels for a library routine on a CUDA device (by reason)
 FALLBACKS: dict = {}
+_FUSED_GLU = os.environ.get("CHRONICALS_FUSED_GLU", "1") != "0"
 
 
 def _fast(*tensors: torch.Tensor) -> bool:
@@ -407,6 +409,71 @@ class _GLUFn(torch.autograd.Function):
                                      dgu.data_ptr() + 2 * I, M, I, I, I2, I2, int(ctx.gelu), _ext.stream_ptr())
         _ext.check(code, "glu_bwd")
         return dgu.view(ctx.shape), None
+
+
+class _LinearSwiGLUFn(torch.autograd.Function):
+    """``act = silu(x Wgᵀ + bg) * (x Wuᵀ + bu)`` for the fused gate | up weight ``w [2I, K]``.
+
+    Forward: one CTA-pair GEMM whose epilogue stores gate | up (kept for the backward pass) and the activation
+    (``cb_gemm2sm_bf16_glu``), so the ``[T, 2I]`` tensor is not read back by a separate activation kernel.
+    Backward: the stand-alone gated-activation backward on the stored gate | up, then the usual dgrad / wgrad.
+    The reference patches Liger's SwiGLU MLP in for the same purpose (chronicals/training/chronicals_trainer.py:704-816)."""
+
+    @staticmethod
+    def forward(ctx, x2, w, bias):
+        M, K = x2.shape
+        I = w.shape[0] // 2
+        gu = torch.empty(M, 2 * I, dtype=x2.dtype, device=x2.device)
+        act = torch.empty(M, I, dtype=x2.dtype, device=x2.device)
+        code = _ext.lib().cb_gemm2sm_bf16_glu(x2.data_ptr(), w.data_ptr(), gu.data_ptr(), act.data_ptr(), _ext.ptr(bias),
+                                              M, I, K, x2.stride(0), w.stride(0), gu.stride(0), act.stride(0),
+                                              _ext.status_buffer(x2.device).data_ptr(), _ext.stream_ptr())
+        if code > 0:
+            _ext.check(code, "gemm2sm_bf16_glu")
+        if code != 0:                                            # shape not covered: projection, then activation
+            gemm(x2, w, bias=bias, out=gu)
+            c2 = _ext.lib().cb_glu_fwd(gu.data_ptr(), gu.data_ptr() + 2 * I, act.data_ptr(), M, I, 2 * I, I, 0, _ext.stream_ptr())
+            _ext.check(c2, "glu_fwd")
+        ctx.save_for_backward(x2, w, gu)
+        ctx.has_bias = bias is not None
+        ctx.weight_ref = weakref.ref(w) if hasattr(w, "_cb_grad_out") else None
+        return act
+
+    @staticmethod
+    def backward(ctx, dact):
+        x2, w, gu = ctx.saved_tensors
+        M, I2 = gu.shape
+        I = I2 // 2
+        d2 = dact.reshape(M, I)
+        if not d2.is_contiguous():
+            d2 = d2.contiguous()
+        dgu = torch.empty_like(gu)
+        code = _ext.lib().cb_glu_bwd(d2.data_ptr(), gu.data_ptr(), gu.data_ptr() + 2 * I, dgu.data_ptr(),
+                                     dgu.data_ptr() + 2 * I, M, I, I, I2, I2, 0, _ext.stream_ptr())
+        _ext.check(code, "glu_bwd")
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dgu, w, b_mn=True)
+        if ctx.needs_input_grad[1]:
+            dw = wgrad(dgu, x2, out=grad_destination(ctx.weight_ref()) if ctx.weight_ref is not None else None)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = colsum(dgu)
+        return dx, dw, db
+
+
+def linear_swiglu(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``silu(gate) * up`` of the fused gate | up projection ``x @ w.T + bias`` (``w [2I, K]``, gate rows first),
+    with the activation computed in the projection's epilogue where the shape allows (``I % 128 == 0``).
+    ``CHRONICALS_FUSED_GLU=0`` in the environment keeps projection and activation apart."""
+    I = w.shape[0] // 2
+    if (_FUSED_GLU and _fast(x, w, bias) and I % 128 == 0 and x.shape[-1] % 8 == 0 and _ext.has_symbol("cb_gemm2sm_bf16_glu")
+            and w.stride(1) == 1):
+        x2 = x.reshape(-1, x.shape[-1])
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        a = _LinearSwiGLUFn.apply(x2, w, bias)
+        return a if x.dim() == 2 else a.view(*x.shape[:-1], I)
+    return swiglu(linear(x, w, bias))
 
 
 def swiglu(gate_up: torch.Tensor) -> torch.Tensor:

@@ -218,6 +218,37 @@ def test_linear_cross_entropy_full_vocabularies_against_fp32(V):
     _ext.check_status()
 
 
+@pytest.mark.parametrize("M,K,I,bias", [(300, 896, 4864, False), (513, 128, 256, True), (64, 64, 192, False)])
+def test_linear_swiglu_in_the_projection_epilogue(M, K, I, bias):
+    """silu(gate) * up written by the gate | up GEMM's epilogue: same values as the projection followed by the
+    stand-alone activation kernel (both round gate and up to bf16 first), same gradients; checked against fp32.
+    I = 192 is not a multiple of the 128-column tile and takes the two-kernel path."""
+    x = _rand(M, K).requires_grad_()
+    w = (_rand(2 * I, K, seed=1) * 0.05).requires_grad_()
+    b = (_rand(2 * I, seed=2) * 0.1).requires_grad_() if bias else None
+    act = ops.linear_swiglu(x, w, b)
+    g = _rand(M, I, seed=3)
+    act.backward(g)
+    x2, w2 = x.detach().clone().requires_grad_(), w.detach().clone().requires_grad_()
+    b2 = b.detach().clone().requires_grad_() if bias else None
+    two = ops.swiglu(ops.linear(x2, w2, b2))
+    two.backward(g)
+    assert torch.equal(act, two), f"fused and two-kernel activations differ by {(act.float() - two.float()).abs().max().item()}"
+    _close(x.grad, x2.grad, rtol=1e-2, atol=1e-3, what="linear_swiglu dx vs two-kernel path")
+    _close(w.grad, w2.grad, rtol=1e-2, atol=1e-3, what="linear_swiglu dw vs two-kernel path")
+    xr, wr = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    br = b.detach().float().requires_grad_() if bias else None
+    gu = torch.nn.functional.linear(xr, wr, br)
+    want = torch.nn.functional.silu(gu[:, :I]) * gu[:, I:]
+    want.backward(g.float())
+    _close(act, want, what="linear_swiglu fwd")
+    _close(x.grad, xr.grad, rtol=3e-2, atol=3e-2, what="linear_swiglu dx")
+    _close(w.grad, wr.grad, rtol=3e-2, atol=3e-2, what="linear_swiglu dw")
+    if bias:
+        _close(b.grad, br.grad, rtol=3e-2, atol=3e-2, what="linear_swiglu dbias")
+    _ext.check_status()
+
+
 def test_cross_entropy_logits_kernel():
     lg = _rand(200, 3000, dtype=torch.float32).requires_grad_()
     y = torch.randint(0, 3000, (200,), device=DEV)
