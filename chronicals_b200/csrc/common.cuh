@@ -337,6 +337,11 @@ __device__ __forceinline__ float ex2_fma(float x) {
   p = fmaf(p, f, 0.9999289512634277f);
   return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
 }
+__device__ __forceinline__ float tanh_approx(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

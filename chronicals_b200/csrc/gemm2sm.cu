@@ -537,7 +537,7 @@ gemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // Accumulator columns [0, BNH) are the gate, [BNH, BN) the up projection of activation columns
         // nt * BNH ...  Per 64 columns: gate -> C (kept as bf16 pairs), up -> C, silu(gate) * up -> the activation
         // tensor (map tmW), all three through the staging buffers and TMA stores.  The product uses the values as
-        // rounded to bf16 for C, so it equals the stand-alone kernel applied to the stored gate | up.
+        // rounded to bf16 for C, i.e. what the stand-alone kernel would read back.
 #pragma unroll 1
         for (int c0 = 0; c0 < BNH; c0 += 64) {
           const int acol = nt * BNH + c0;
@@ -563,8 +563,12 @@ gemm2sm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           for (int j = 0; j < 32; ++j) {
             const float2 gt = unpack_bf16x2(gp[j]);
             const float2 up = unpack_bf16x2(pack_bf16x2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1])));
-            r[2 * j] = __float_as_uint(gt.x * (1.f / (1.f + __expf(-gt.x))) * up.x);
-            r[2 * j + 1] = __float_as_uint(gt.y * (1.f / (1.f + __expf(-gt.y))) * up.y);
+            // silu(g) = g sigmoid(g) = h + h tanh(h) with h = g / 2: one special-function instruction and three
+            // FMA-pipe instructions per element (the epilogue warps run one per scheduler, so every dependent
+            // instruction costs its full latency; an exp2, a reciprocal and its refinement would not fit the tile time)
+            const float h0 = 0.5f * gt.x, h1 = 0.5f * gt.y;
+            r[2 * j] = __float_as_uint(fmaf(h0, tanh_approx(h0), h0) * up.x);
+            r[2 * j + 1] = __float_as_uint(fmaf(h1, tanh_approx(h1), h1) * up.y);
           }
           stage_bf16(r);
           flush(&tmW, acol, row0w, false, row0w < g.M);

@@ -219,13 +219,15 @@ def test_linear_cross_entropy_full_vocabularies_against_fp32(V):
 
 
 @pytest.mark.parametrize("M,K,I,bias", [(300, 896, 4864, False), (513, 128, 256, True), (64, 64, 192, False)])
-def test_linear_swiglu_in_the_projection_epilogue(M, K, I, bias):
-    """silu(gate) * up written by the gate | up GEMM's epilogue: same values as the projection followed by the
-    stand-alone activation kernel (both round gate and up to bf16 first), same gradients; checked against fp32.
+def test_linear_swiglu_in_the_projection_epilogue(M, K, I, bias, monkeypatch):
+    """silu(gate) * up written by the gate | up GEMM's epilogue: agrees with the projection followed by the
+    stand-alone activation kernel to bf16 rounding (both start from gate and up rounded to bf16; the epilogue
+    evaluates the sigmoid through tanh.approx), same gradients; checked against fp32.
     I = 192 is not a multiple of the 128-column tile and takes the two-kernel path."""
     x = _rand(M, K).requires_grad_()
     w = (_rand(2 * I, K, seed=1) * 0.05).requires_grad_()
     b = (_rand(2 * I, seed=2) * 0.1).requires_grad_() if bias else None
+    monkeypatch.setattr(ops, "_FUSED_GLU", "2")              # the fused kernel even where the environment turned it off
     act = ops.linear_swiglu(x, w, b)
     g = _rand(M, I, seed=3)
     act.backward(g)
@@ -233,7 +235,7 @@ def test_linear_swiglu_in_the_projection_epilogue(M, K, I, bias):
     b2 = b.detach().clone().requires_grad_() if bias else None
     two = ops.swiglu(ops.linear(x2, w2, b2))
     two.backward(g)
-    assert torch.equal(act, two), f"fused and two-kernel activations differ by {(act.float() - two.float()).abs().max().item()}"
+    _close(act, two, rtol=8e-3, atol=1e-3, what="linear_swiglu fused vs two-kernel activation", l2=4e-3)
     _close(x.grad, x2.grad, rtol=1e-2, atol=1e-3, what="linear_swiglu dx vs two-kernel path")
     _close(w.grad, w2.grad, rtol=1e-2, atol=1e-3, what="linear_swiglu dw vs two-kernel path")
     xr, wr = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
