@@ -174,6 +174,7 @@ def run_ours(args):
     import torch
     rank, local_rank, world = _dist_setup()
     from chronicals_b200 import ChronicalsConfig, ChronicalsTrainer, TrainingConfig, build_model
+    from chronicals_b200 import ops as _ops
     from chronicals_b200.ops import _ext
 
     dev = torch.device("cuda", local_rank)
@@ -264,7 +265,10 @@ def run_ours(args):
             "config": {"model": "Qwen2.5-0.5B architecture (24L, H896, 14q/2kv, d64, I4864, V151936, tied)",
                        "global_batch": MICRO_BATCH * world, "micro_batch_per_gpu": MICRO_BATCH, "seq_len": SEQ_LEN,
                        "parallelism": f"dp{world}", "optimizer": "AdamW (fp32 moments) + global-norm clip",
-                       "loss": "fused linear cross-entropy (no logits)", "cuda_graph": graph_used,
+                       "loss": ("fused linear cross-entropy (bf16 logits resident between forward and backward, "
+                                f"{MICRO_BATCH * SEQ_LEN * cfg.vocab_size * 2 / 2**30:.1f} GB)"
+                                if MICRO_BATCH * SEQ_LEN * cfg.vocab_size * 2 <= _ops.CCE_RESIDENT_BYTES
+                                else "fused linear cross-entropy (no logits)"), "cuda_graph": graph_used,
                        "comm": comm if world > 1 else "none",
                        "grad_reduce": ("per-bucket reduce-scatter from backward hooks on a side stream"
                                        if (world > 1 and comm == "fused" and not args.no_overlap) else

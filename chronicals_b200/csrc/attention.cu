@@ -69,7 +69,8 @@ __device__ unsigned long long cb_attn_phase[2][16];
 // the last wave consists of single-block tiles, whatever the mix of document lengths.  Every warp runs this by
 // itself with warp-wide votes (no shared memory, so it can precede the CTA's set-up); cost is one pass over the
 // document lengths per weight level.
-__device__ __forceinline__ bool locate_tile(const int* cu, int n_docs, int b, int& start, int& len, int& weight, int& nblk) {
+__device__ __forceinline__ bool locate_tile(const int* cu, int n_docs, int b, int& start, int& len, int& weight, int& nblk,
+                                            int* beyond = nullptr) {
   const int lane = threadIdx.x & 31;
   int maxnb = 0;
   for (int d = lane; d < n_docs; d += 32) maxnb = max(maxnb, (cu[d + 1] - cu[d] + 127) >> 7);
@@ -95,7 +96,22 @@ __device__ __forceinline__ bool locate_tile(const int* cu, int n_docs, int b, in
     }
     b -= tot;
   }
+  if (beyond != nullptr) *beyond = b;                  // index among the CTAs past the last tile
   return false;
+}
+
+// The grid holds at least ceil((T - cu[n_docs]) / 128) CTAs past the last tile (per head).  In the forward
+// kernels they write the zeros of the padding rows at or after cu[n_docs], 128 rows x D columns each, so the
+// caller need not clear the output first.
+template <int D>
+__device__ __forceinline__ void zero_padding_rows(const AttnArgs& a, int beyond, int h) {
+  const int valid = a.cu[a.n_docs];
+  const long long row0 = static_cast<long long>(valid) + static_cast<long long>(beyond) * 128;
+  constexpr int CH = D / 8;                            // 16-byte chunks per row of one head
+  for (int i = threadIdx.x; i < 128 * CH; i += blockDim.x) {
+    const long long t = row0 + i / CH;
+    if (t < a.T) reinterpret_cast<uint4*>(a.O + t * a.ldo + static_cast<long long>(h) * D)[i % CH] = make_uint4(0u, 0u, 0u, 0u);
+  }
 }
 
 // store 32 consecutive values of thread-row r as bf16 into a [128 x 128] operand image made of two
@@ -210,7 +226,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   constexpr uint32_t IDESC_PV = umma_idesc_bf16(128, D, 0, 1);
 
   int start, len, qb, nblk;
-  if (!locate_tile(a.cu, a.n_docs, blockIdx.y, start, len, qb, nblk)) return;
+  int beyond = 0;
+  if (!locate_tile(a.cu, a.n_docs, blockIdx.y, start, len, qb, nblk, &beyond)) {
+    zero_padding_rows<D>(a, beyond, blockIdx.x);
+    return;
+  }
   qb -= 1;                                             // weight = kv blocks up to the diagonal = qb + 1
   const int h = blockIdx.x;
   const int hkv = h / (a.hq / a.hk);
@@ -389,7 +409,11 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   constexpr uint32_t IDESC_PV = umma_idesc_bf16(128, D, 0, 1);
 
   int start, len, qb, nblk;
-  if (!locate_tile(a.cu, a.n_docs, blockIdx.y, start, len, qb, nblk)) return;
+  int beyond = 0;
+  if (!locate_tile(a.cu, a.n_docs, blockIdx.y, start, len, qb, nblk, &beyond)) {
+    zero_padding_rows<D>(a, beyond, blockIdx.x);
+    return;
+  }
   qb -= 1;                                             // weight = kv blocks up to the diagonal = qb + 1
   const int h = blockIdx.x;
   const int hkv = h / (a.hq / a.hk);
@@ -679,7 +703,11 @@ attn_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   constexpr uint32_t IDESC_PV = umma_idesc_bf16(128, D, 0, 1);
 
   int start, len, qb, nblk;
-  if (!locate_tile(a.cu, a.n_docs, blockIdx.y, start, len, qb, nblk)) return;
+  int beyond = 0;
+  if (!locate_tile(a.cu, a.n_docs, blockIdx.y, start, len, qb, nblk, &beyond)) {
+    zero_padding_rows<D>(a, beyond, blockIdx.x);
+    return;
+  }
   qb -= 1;
   const int h = blockIdx.x;
   const int hkv = h / (a.hq / a.hk);
@@ -1400,8 +1428,8 @@ int set_smem(K kern, int bytes) {
 extern "C" {
 
 // q [T, hq, D] (row pitch ldq elements), k / v [T, hk, D]; cu: int32 [n_docs + 1] on the device.
-// o [T, hq, D] with pitch ldo; lse [hq, T] fp32.  Rows at or beyond cu[n_docs] are left untouched
-// (the caller zero-fills o).  D is 64 or 128, hq a multiple of hk.
+// o [T, hq, D] with pitch ldo; lse [hq, T] fp32.  Rows of o at or beyond cu[n_docs] (padding) are written as
+// zeros by the kernel, their lse entries are left untouched.  D is 64 or 128, hq a multiple of hk.
 int cb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int* cu, int n_docs, int T,
                 int hq, int hk, int D, long long ldq, long long ldk, long long ldv, long long ldo, float scale,
                 int* status, void* stream) {

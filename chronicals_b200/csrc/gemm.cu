@@ -331,11 +331,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 const float sm = g.smoothing / static_cast<float>(g.V_total);
                 const float l2 = lse_r * 1.4426950408889634f;
                 const int rel = lab - col0;
+                // (softmax * coef - sm) * gs as  fma, ex2, fma  per element; the label's -(1 - smoothing) * gs is
+                // added afterwards by the few lanes whose label falls into these 32 columns (the epilogue warps
+                // run one per scheduler, so every instruction in this loop is paid at its full latency)
+                const float cg = coef * gs, smg = sm * gs;
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                  float p = exp2f(fmaf(v[j], 1.4426950408889634f, -l2)) * coef - sm;
-                  if (j == rel) p -= (1.f - g.smoothing);
-                  v[j] = p * gs;
+                for (int j = 0; j < 32; ++j) v[j] = fmaf(ex2_approx(fmaf(v[j], 1.4426950408889634f, -l2)), cg, -smg);
+                if (rel >= 0 && rel < 32) {
+                  const float hit = (1.f - g.smoothing) * gs;
+#pragma unroll
+                  for (int j = 0; j < 32; ++j)
+                    if (j == rel) v[j] -= hit;
                 }
               } else {
                 if (g.bias != nullptr) {
@@ -485,11 +491,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 const float sm = g.smoothing / static_cast<float>(g.V_total);
                 const float l2 = lse_r * 1.4426950408889634f;
                 const int rel = lab - col0;
+                // (softmax * coef - sm) * gs as  fma, ex2, fma  per element; the label's -(1 - smoothing) * gs is
+                // added afterwards by the few lanes whose label falls into these 32 columns (the epilogue warps
+                // run one per scheduler, so every instruction in this loop is paid at its full latency)
+                const float cg = coef * gs, smg = sm * gs;
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                  float p = exp2f(fmaf(v[j], 1.4426950408889634f, -l2)) * coef - sm;
-                  if (j == rel) p -= (1.f - g.smoothing);
-                  v[j] = p * gs;
+                for (int j = 0; j < 32; ++j) v[j] = fmaf(ex2_approx(fmaf(v[j], 1.4426950408889634f, -l2)), cg, -smg);
+                if (rel >= 0 && rel < 32) {
+                  const float hit = (1.f - g.smoothing) * gs;
+#pragma unroll
+                  for (int j = 0; j < 32; ++j)
+                    if (j == rel) v[j] -= hit;
                 }
               } else {
                 if (g.bias != nullptr) {

@@ -678,12 +678,84 @@ class _LinearCEFn(torch.autograd.Function):
         return dh, dw, None, None, None, None, None
 
 
+# The [tokens, vocab] logits are kept (bf16) between forward and backward when they are at most this many bytes:
+# on a 180 GB device a few GB cost nothing, and the backward pass then needs no second projection onto the
+# vocabulary (8192 tokens x 151,936 words: 2.5 GB kept, 2.2 TFLOP saved).  Larger products, or
+# CHRONICALS_CCE_RESIDENT_GB=0, take the path that never holds the logits.
+CCE_RESIDENT_BYTES = int(float(os.environ.get("CHRONICALS_CCE_RESIDENT_GB", "6")) * 2 ** 30)
+
+
+class _LinearCEResidentFn(torch.autograd.Function):
+    """Same loss and gradients as ``_LinearCEFn`` with the logits resident in device memory:
+
+    forward : logits = H Wᵀ (bf16, CTA-pair GEMM) -> one pass per row for log-sum-exp, target logit and loss;
+    backward: d(logits) written over the logits in one pass, then dH = G W and dW = Gᵀ H as two plain GEMMs over the
+              whole vocabulary.  The reference's cut cross-entropy (chronicals/kernels/cut_cross_entropy.py:252-424)
+    trades this memory for recomputation; ``_LinearCEFn`` is that form."""
+
+    @staticmethod
+    def forward(ctx, hidden, weight, labels, ignore_index, smoothing, z_weight, mean):
+        L = _ext.lib()
+        M, K = hidden.shape
+        V = weight.shape[0]
+        dev = hidden.device
+        logits = gemm(hidden, weight)
+        loss_rows = torch.empty(M, dtype=torch.float32, device=dev)
+        lse = torch.empty(M, dtype=torch.float32, device=dev)
+        code = L.cb_ce_logits(logits.data_ptr(), labels.data_ptr(), M, logits.stride(0), V, 1, ignore_index, smoothing,
+                              z_weight, loss_rows.data_ptr(), lse.data_ptr(), _ext.stream_ptr())
+        _ext.check(code, "ce_logits")
+        valid = (labels != ignore_index) & (labels >= 0) & (labels < V)
+        if mean:
+            n = valid.sum().clamp_min(1).float()
+            gscale = valid.float() / n
+            loss = loss_rows.sum() / n
+        else:
+            gscale = valid.float()
+            loss = loss_rows.sum()
+        ctx.save_for_backward(hidden, weight, labels, lse, gscale, logits)
+        ctx.cfg = (ignore_index, smoothing, z_weight)
+        ctx.weight_ref = weakref.ref(weight) if hasattr(weight, "_cb_grad_out") else None
+        ctx.set_materialize_grads(False)
+        return loss, loss_rows
+
+    @staticmethod
+    def backward(ctx, gout, grows):
+        hidden, weight, labels, lse, gscale, logits = ctx.saved_tensors
+        ignore_index, smoothing, z_weight = ctx.cfg
+        M, K = hidden.shape
+        V = weight.shape[0]
+        dev = hidden.device
+        if grows is None and gout is not None:
+            g1 = gout.float().reshape(1).contiguous()
+        else:
+            rows_scale = torch.zeros_like(gscale)
+            if gout is not None:
+                rows_scale = rows_scale + gscale * gout.float()
+            if grows is not None:
+                rows_scale = rows_scale + grows.float() * (labels != ignore_index)
+            gscale = rows_scale.contiguous()
+            g1 = torch.ones(1, dtype=torch.float32, device=dev)
+        # in place: the logits are not needed again (a second backward through this node is not supported)
+        code = _ext.lib().cb_ce_logits_grad(logits.data_ptr(), logits.data_ptr(), labels.data_ptr(), lse.data_ptr(),
+                                            gscale.data_ptr(), g1.data_ptr(), M, logits.stride(0), V, 1, ignore_index,
+                                            smoothing, z_weight, _ext.stream_ptr())
+        _ext.check(code, "ce_logits_grad")
+        dh = gemm(logits, weight, b_mn=True) if ctx.needs_input_grad[0] else None
+        dw = None
+        if ctx.needs_input_grad[1]:
+            dest = grad_destination(ctx.weight_ref()) if ctx.weight_ref is not None else None
+            dw = gemm(logits, hidden, a_mn=True, b_mn=True, out=dest)
+        return dh, dw, None, None, None, None, None
+
+
 def linear_cross_entropy(hidden: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor,
                          bias: Optional[torch.Tensor] = None, ignore_index: int = -100,
                          label_smoothing: float = 0.0, z_loss_weight: float = 0.0, reduction: str = "mean",
                          chunk_size: int = 8192) -> torch.Tensor:
-    """Cross-entropy of ``hidden @ weight.T`` against ``labels`` without ever
-    holding the ``[tokens, vocab]`` logits (labels must already be shifted)."""
+    """Cross-entropy of ``hidden @ weight.T`` against ``labels`` (already shifted).  Products of more than
+    ``CCE_RESIDENT_BYTES`` never hold the ``[tokens, vocab]`` logits (online log-sum-exp in the GEMM epilogue, d(logits)
+    recomputed in chunks); smaller ones keep them in bf16 between forward and backward, which is faster."""
     h = hidden.reshape(-1, hidden.shape[-1])
     y = labels.reshape(-1)
     if (_fast(h, weight) and bias is None and y.is_cuda and h.shape[1] % 8 == 0 and weight.stride(1) == 1
@@ -691,8 +763,12 @@ def linear_cross_entropy(hidden: torch.Tensor, weight: torch.Tensor, labels: tor
         if not h.is_contiguous():
             h = h.contiguous()
         y = y.long().contiguous()
-        loss, rows = _LinearCEFn.apply(h, weight, y, ignore_index, float(label_smoothing), float(z_loss_weight),
-                                       reduction == "mean")
+        fn = _LinearCEFn
+        if (h.shape[0] * weight.shape[0] * 2 <= CCE_RESIDENT_BYTES and weight.shape[0] % 8 == 0 and _gemm_ok(h)
+                and _gemm_ok(weight)):
+            fn = _LinearCEResidentFn
+        loss, rows = fn.apply(h, weight, y, ignore_index, float(label_smoothing), float(z_loss_weight),
+                              reduction == "mean")
         if reduction == "none":
             return rows
         if reduction == "sum":

@@ -24,7 +24,7 @@ class _AttnPackedFn(torch.autograd.Function):
     def forward(ctx, qkv, cu, hq, hk, d, scale):
         T, ld = qkv.shape[0], qkv.stride(0)
         nq, nk = hq * d, hk * d
-        o = torch.zeros(T, nq, dtype=qkv.dtype, device=qkv.device)
+        o = torch.empty(T, nq, dtype=qkv.dtype, device=qkv.device)     # the kernel writes the zeros of the padding rows
         lse = torch.empty(hq, T, dtype=torch.float32, device=qkv.device)
         esz = qkv.element_size()
         code = _ext.lib().cb_attn_fwd(qkv.data_ptr(), qkv.data_ptr() + nq * esz, qkv.data_ptr() + (nq + nk) * esz,

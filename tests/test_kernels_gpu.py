@@ -178,7 +178,11 @@ def test_embedding_fwd_bwd_deterministic():
 
 @pytest.mark.parametrize("T,H,V", [(256, 256, 4096), (300, 896, 5000), (128, 64, 520)])
 @pytest.mark.parametrize("smoothing,z", [(0.0, 0.0), (0.1, 1e-4)])
-def test_linear_cross_entropy_fwd_bwd(T, H, V, smoothing, z):
+@pytest.mark.parametrize("resident", [False, True])
+def test_linear_cross_entropy_fwd_bwd(T, H, V, smoothing, z, resident, monkeypatch):
+    """Both forms: logits never held (online log-sum-exp in the GEMM epilogue, chunked recomputation in the
+    backward pass) and logits resident in bf16 between forward and backward."""
+    monkeypatch.setattr(ops, "CCE_RESIDENT_BYTES", (1 << 40) if resident else 0)
     h = _rand(T, H).requires_grad_()
     w = _rand(V, H, scale=0.05, seed=1).requires_grad_()
     y = torch.randint(0, V, (T,), device=DEV)
@@ -195,9 +199,12 @@ def test_linear_cross_entropy_fwd_bwd(T, H, V, smoothing, z):
 
 
 @pytest.mark.parametrize("V", [32000, 151936])
-def test_linear_cross_entropy_full_vocabularies_against_fp32(V):
+@pytest.mark.parametrize("resident", [False, True])
+def test_linear_cross_entropy_full_vocabularies_against_fp32(V, resident, monkeypatch):
     """The vocabulary sizes of the benchmark configurations (4 and 38 splits of the forward, 4 and 19 chunks of the
-    backward), a token count that is not a multiple of the tile, labels in the first and last vocabulary rows."""
+    backward), a token count that is not a multiple of the tile, labels in the first and last vocabulary rows;
+    with and without resident logits."""
+    monkeypatch.setattr(ops, "CCE_RESIDENT_BYTES", (1 << 40) if resident else 0)
     T, H = 200, 256
     h = _rand(T, H).requires_grad_()
     w = _rand(V, H, scale=0.05, seed=1).requires_grad_()
