@@ -678,11 +678,14 @@ class _LinearCEFn(torch.autograd.Function):
         return dh, dw, None, None, None, None, None
 
 
-# The [tokens, vocab] logits are kept (bf16) between forward and backward when they are at most this many bytes:
-# on a 180 GB device a few GB cost nothing, and the backward pass then needs no second projection onto the
-# vocabulary (8192 tokens x 151,936 words: 2.5 GB kept, 2.2 TFLOP saved).  Larger products, or
-# CHRONICALS_CCE_RESIDENT_GB=0, take the path that never holds the logits.
-CCE_RESIDENT_BYTES = int(float(os.environ.get("CHRONICALS_CCE_RESIDENT_GB", "6")) * 2 ** 30)
+# Optional second form of the fused linear cross-entropy: with CHRONICALS_CCE_RESIDENT_GB=<n> (default 0: off) the
+# [tokens, vocab] logits are kept in bf16 between forward and backward when they take at most n GB, and the
+# backward pass needs no second projection onto the vocabulary (8192 tokens x 151,936 words: 2.5 GB kept,
+# 2.2 TFLOP saved).  Measured inside the CUDA-graph step of the 0.5B benchmark the two forms take the same time
+# (35.7 ms either way: the extra pass over 2.5 GB of logits and the long-K GEMMs cost what the recomputation did),
+# so the form that never holds the logits stays the default; with eager launches the resident form saves 55
+# launches per step.
+CCE_RESIDENT_BYTES = int(float(os.environ.get("CHRONICALS_CCE_RESIDENT_GB", "0")) * 2 ** 30)
 
 
 class _LinearCEResidentFn(torch.autograd.Function):
@@ -753,9 +756,9 @@ def linear_cross_entropy(hidden: torch.Tensor, weight: torch.Tensor, labels: tor
                          bias: Optional[torch.Tensor] = None, ignore_index: int = -100,
                          label_smoothing: float = 0.0, z_loss_weight: float = 0.0, reduction: str = "mean",
                          chunk_size: int = 8192) -> torch.Tensor:
-    """Cross-entropy of ``hidden @ weight.T`` against ``labels`` (already shifted).  Products of more than
-    ``CCE_RESIDENT_BYTES`` never hold the ``[tokens, vocab]`` logits (online log-sum-exp in the GEMM epilogue, d(logits)
-    recomputed in chunks); smaller ones keep them in bf16 between forward and backward, which is faster."""
+    """Cross-entropy of ``hidden @ weight.T`` against ``labels`` (already shifted) without ever holding the
+    ``[tokens, vocab]`` logits: online log-sum-exp in the GEMM epilogue, d(logits) recomputed in chunks.  Products of
+    at most ``CCE_RESIDENT_BYTES`` (0 unless ``CHRONICALS_CCE_RESIDENT_GB`` is set) keep bf16 logits instead."""
     h = hidden.reshape(-1, hidden.shape[-1])
     y = labels.reshape(-1)
     if (_fast(h, weight) and bias is None and y.is_cuda and h.shape[1] % 8 == 0 and weight.stride(1) == 1
