@@ -243,13 +243,21 @@ def run_ours(args):
 
     dp_profile = None
     graph_used = bool(trainer.use_cuda_graphs)            # as the timed steps ran
-    if args.dp_profile and hasattr(trainer.optimizer, "profile_report"):
+    if args.dp_profile:
         trainer.use_cuda_graphs = False                   # events cannot be read back from inside a replayed graph
-        trainer.optimizer.profile = True
+        sharded = hasattr(trainer.optimizer, "profile_report")
+        trainer.time_backward = True
+        if sharded:
+            trainer.optimizer.profile = True
         for i in range(3):
             trainer.training_step(dev_batches[i % len(dev_batches)])
-        dp_profile = trainer.optimizer.profile_report()
-        trainer.optimizer.profile = False
+        torch.cuda.synchronize()
+        dp_profile = trainer.optimizer.profile_report() if sharded else {}
+        e0, e1 = trainer._backward_events
+        dp_profile["backward_ms_eager"] = round(e0.elapsed_time(e1), 4)     # comparable between N = 1 and N > 1
+        trainer.time_backward = False
+        if sharded:
+            trainer.optimizer.profile = False
         _barrier_sync(world)
     tokens_per_step = MICRO_BATCH * SEQ_LEN * world
     value = tokens_per_step * args.steps / (ms / 1e3)

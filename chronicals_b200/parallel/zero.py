@@ -256,6 +256,9 @@ class ShardedFusedAdamW(torch.optim.Optimizer):
             b.pending = len(b.entries)
             b.ready = False
         self._n_ready = 0
+        if self.fused and self.profile and not torch.cuda.is_current_stream_capturing():
+            self._events["micro_start"] = torch.cuda.Event(enable_timing=True)
+            self._events["micro_start"].record(torch.cuda.current_stream(self.device))
 
     # ------------------------------------------------------------------------------------------ reduce-scatter
     def _reduce_bucket(self, b: _Bucket, overlapped: bool) -> None:
@@ -422,7 +425,10 @@ class ShardedFusedAdamW(torch.optim.Optimizer):
                          "overlapped": bool(overlapped), "rs_ms": round(a.elapsed_time(b), 4),
                          "ready_to_done_ms": round(e["ready"][i].elapsed_time(b), 4),
                          "done_before_bwd_end_ms": round(b.elapsed_time(e["bwd_end"]), 4)})
-        return {"buckets": rows, "exposed_wait_ms": round(e["bwd_end"].elapsed_time(e["joined"]), 4),
+        extra = {}
+        if "micro_start" in e:                       # backward pass of the last micro-step on the main stream
+            extra["bwd_ms"] = round(e["micro_start"].elapsed_time(e["bwd_end"]), 4)
+        return {**extra, "buckets": rows, "exposed_wait_ms": round(e["bwd_end"].elapsed_time(e["joined"]), 4),
                 "tail_ms": round(e["joined"].elapsed_time(e["step_end"]), 4),
                 "hidden_rs_ms": round(sum(r["rs_ms"] for r in rows if r["done_before_bwd_end_ms"] >= 0), 4)}
 

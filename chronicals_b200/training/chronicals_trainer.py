@@ -368,7 +368,15 @@ class ChronicalsTrainer:
         scaled = loss / a.gradient_accumulation_steps if a.gradient_accumulation_steps > 1 else loss
         if hasattr(self.optimizer, "begin_micro_step"):
             self.optimizer.begin_micro_step(last=do_step)     # bucket reduce-scatters start from the last backward only
+        timed = getattr(self, "time_backward", False) and self.device.type == "cuda" \
+            and not torch.cuda.is_current_stream_capturing()
+        if timed:                                             # eager profiling aid: device time of the backward pass
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
         scaled.backward()
+        if timed:
+            e1.record()
+            self._backward_events = (e0, e1)
         if not do_step:
             return
         if self.dp is not None:
