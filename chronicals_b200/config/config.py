@@ -262,12 +262,16 @@ class ParallelConfig:
     bucket_mb: float = 32.0
     comm_backend: str = "nccl"
     wait_budget_us: int = 2_000_000
-    # sharded optimizer (zero_stage 1, or the fused data-parallel path): gradient buckets of about this size are
-    # reduce-scattered from backward hooks on a side stream; ``overlap_grad_reduce=False`` reduces after the
-    # backward pass instead
+    # sharded optimizer (zero_stage 1, or the fused data-parallel path): the gradients live in buckets of about
+    # this size.  ``overlap_grad_reduce=True`` reduce-scatters each bucket from a backward hook on a side stream with
+    # ``reduce_grid`` blocks; the default reduces all buckets after the backward pass with the full grid behind one
+    # barrier.  Measured on 2 and 4 B200 (0.5B model): 37.1 / 37.9 ms per step after the pass, 38.0 / 38.4 ms
+    # overlapped with 148 blocks, 38.5 / 39.1 ms with 64 - the reduce kernels running beside the backward pass slow
+    # it by more than they hide (29.0 against 24.4 ms of backward pass on 2 GPUs), while all 26 buckets together
+    # take 1.7 ms when they have the GPU to themselves.
     shard_bucket_mb: float = 24.0
-    overlap_grad_reduce: bool = True
-    reduce_grid: int = 64
+    overlap_grad_reduce: bool = False
+    reduce_grid: int = 148
 
     @property
     def world_size(self) -> int:

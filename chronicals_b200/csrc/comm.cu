@@ -41,14 +41,12 @@ constexpr int PAYLOAD_FLOATS = 4;
 __global__ void symm_barrier_kernel(PeerTable pads, int my_rank, int W, unsigned long long* __restrict__ epoch_ctr,
                                     const float* __restrict__ payload_in, float* __restrict__ gathered_out,
                                     unsigned long long wait_limit_ns, int* status) {
-  __shared__ unsigned long long s_epoch;
-  if (threadIdx.x == 0) {
-    s_epoch = *epoch_ctr + 1;
-    *epoch_ctr = s_epoch;
-  }
+  // no shared memory in this kernel or in rs_bucket_kernel: they run beside persistent GEMM CTAs that leave an SM
+  // little more than the per-CTA reserve, and an SM that cannot take one of those CTAs delays the whole GEMM
+  const unsigned long long epoch = *epoch_ctr + 1;       // every thread reads the counter before thread 0 advances it
   __syncthreads();
+  if (threadIdx.x == 0) *epoch_ctr = epoch;
   if (status[0] != 0) return;
-  const unsigned long long epoch = s_epoch;
   const int r = threadIdx.x;
   if (r < W) {
     unsigned long long* peer_pad = static_cast<unsigned long long*>(pads.ptr[r]);
@@ -144,12 +142,12 @@ __global__ void sum_partials_kernel(const float* __restrict__ partials, int n, f
 // Per-bucket reduce-scatter that runs beside the backward pass on a second stream.  Same arithmetic as
 // rs_reduce_sqnorm_kernel, shaped to share SMs with the compute kernels: 128 threads per block and a
 // small grid (the host picks it), two 16-byte vectors per peer in flight per thread.  partials[block]
-// receives the block's sum of squares; the host sums all buckets' partials once after the last bucket.
+// receives each warp's sum of squares (RSB_THREADS / 32 slots per block); the host sums all buckets' partials once
+// after the last bucket.
 constexpr int RSB_THREADS = 128;
 __global__ void __launch_bounds__(RSB_THREADS)
 rs_bucket_kernel(PeerTable grads, int W, long long lo, long long hi, float* __restrict__ reduced,
                  float* __restrict__ partials, int* status) {
-  __shared__ float sred[RSB_THREADS / 32];
   float sq = 0.f;
   CB_DEBUG_CHECK_ST(status, ((lo | hi) & 7) == 0 && hi >= lo, CB_DBG_COMM_SLICE, lo);
   if (status[0] == 0) {
@@ -192,14 +190,7 @@ rs_bucket_kernel(PeerTable grads, int W, long long lo, long long hi, float* __re
     }
   }
   sq = warp_sum(sq);
-  if ((threadIdx.x & 31) == 0) sred[threadIdx.x >> 5] = sq;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    float t = 0.f;
-#pragma unroll
-    for (int i = 0; i < RSB_THREADS / 32; ++i) t += sred[i];
-    partials[blockIdx.x] = t;
-  }
+  if ((threadIdx.x & 31) == 0) partials[blockIdx.x * (RSB_THREADS / 32) + (threadIdx.x >> 5)] = sq;   // one slot per warp
 }
 
 // AdamW on the owned slice [lo, hi) and fused all-gather.  `gathered` holds every rank's payload

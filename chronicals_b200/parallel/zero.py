@@ -55,7 +55,7 @@ class _Bucket:
 class ShardedFusedAdamW(torch.optim.Optimizer):
     def __init__(self, params, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.01,
                  max_grad_norm: float = 1.0, group=None, master_weights: bool = False, wait_budget_us: int = 2_000_000,
-                 bucket_mb: float = 24.0, overlap: bool = True, rs_grid: int = 64):
+                 bucket_mb: float = 24.0, overlap: bool = False, rs_grid: int = 148):
         defaults = dict(lr=lr, betas=tuple(betas), eps=eps, weight_decay=weight_decay)
         super().__init__(params, defaults)
         if not (dist.is_available() and dist.is_initialized()):
@@ -164,12 +164,12 @@ class ShardedFusedAdamW(torch.optim.Optimizer):
         self.exp_avg_sq = torch.zeros(self.shard, dtype=torch.float32, device=dev)
         self.master = self._gather_local(self.param_flat).float() if master_weights else None
         if self.fused:
-            # sum-of-squares partials: one row of `full_grid` floats per bucket; a bucket reduced by the small
+            # sum-of-squares partials: one row of `4 * full_grid` floats (one per warp) per bucket; a bucket reduced by the small
             # co-resident grid fills only the head of its row, the rest stays zero (the buffer is cleared after
             # every step's sum)
             self.full_grid = 4 * torch.cuda.get_device_properties(dev).multi_processor_count
             self.rs_grid = max(1, min(self.rs_grid, self.full_grid))
-            self.partials = torch.zeros(len(self.buckets) * self.full_grid, dtype=torch.float32, device=dev)
+            self.partials = torch.zeros(len(self.buckets) * self.full_grid * 4, dtype=torch.float32, device=dev)   # 4 warps per block
             self.payload = torch.zeros(self.ctx.payload_floats, dtype=torch.float32, device=dev)
             self.hyper = torch.zeros(len(self.param_groups) * 8, dtype=torch.float32, device=dev)
             self.norm_out = torch.zeros(3, dtype=torch.float32, device=dev)
@@ -261,7 +261,7 @@ class ShardedFusedAdamW(torch.optim.Optimizer):
             self._events["micro_start"].record(torch.cuda.current_stream(self.device))
 
     # ------------------------------------------------------------------------------------------ reduce-scatter
-    def _reduce_bucket(self, b: _Bucket, overlapped: bool) -> None:
+    def _reduce_bucket(self, b: _Bucket, overlapped: bool, barrier: bool = True) -> None:
         lo, hi = self._slice(b)
         out = self.reduced[b.loc: b.loc + b.shard]
         for e in b.entries:
@@ -290,12 +290,13 @@ class ShardedFusedAdamW(torch.optim.Optimizer):
         with torch.cuda.stream(stream):
             if prof:
                 ev[0].record(stream)
-            self.ctx.barrier()                           # every rank holds this bucket's gradients
+            if barrier:
+                self.ctx.barrier()                       # every rank holds this bucket's gradients
             code = self.lib.cb_rs_bucket(self.grad_buf.ptrs, self.world, lo, hi, out.data_ptr(),
-                                         self.partials[b.index * self.full_grid:].data_ptr(), grid,
+                                         self.partials[b.index * self.full_grid * 4:].data_ptr(), grid,
                                          self.ctx.status.data_ptr(), stream.cuda_stream)
             _ext.check(code, "rs_bucket")
-            _ext.count_launch(2)
+            _ext.count_launch(2 if barrier else 1)
             if prof:
                 ev[1].record(stream)
 
@@ -328,9 +329,12 @@ class ShardedFusedAdamW(torch.optim.Optimizer):
                     e["p"].grad = None
                 elif g is None and not e.get("filled", False):
                     e["gview"].zero_()
+        first = True
         for b in self.buckets:
             if not (b.ready and self.overlap):
-                self._reduce_bucket(b, overlapped=False)
+                # after the backward pass one barrier covers every bucket that is still to be reduced
+                self._reduce_bucket(b, overlapped=False, barrier=first)
+                first = False
         if self.fused:
             main = torch.cuda.current_stream(self.device)
             prof = self.profile and not torch.cuda.is_current_stream_capturing()

@@ -70,7 +70,8 @@ def main():
     ref_q = [torch.nn.Parameter((torch.randn(*s2, device=dev) * 0.1).to(torch.bfloat16)) for s2 in dims]
     my_q = [torch.nn.Parameter(p.detach().clone()) for p in ref_q]
     o_ref2 = FusedAdamW(ref_q, lr=1e-2, betas=(0.9, 0.95), weight_decay=0.01, max_grad_norm=1.0)
-    o_my2 = ShardedFusedAdamW(my_q, lr=1e-2, betas=(0.9, 0.95), weight_decay=0.01, max_grad_norm=1.0, bucket_mb=0.1)
+    o_my2 = ShardedFusedAdamW(my_q, lr=1e-2, betas=(0.9, 0.95), weight_decay=0.01, max_grad_norm=1.0, bucket_mb=0.1,
+                              overlap=True, rs_grid=64)
     res["hook_buckets"] = len(o_my2.buckets)
 
     def loss_fn(ps, x):
