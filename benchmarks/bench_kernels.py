@@ -54,6 +54,32 @@ def timed(fn, iters=10, flush=True):
     return tot / iters
 
 
+def graph_timed(fn, iters=10):
+    """Mean device time of ``fn`` replayed from a CUDA graph (L2 flushed between replays)."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            fn()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, capture_error_mode="thread_local"):      # the autograd engine runs on its own thread
+        fn()
+    tot = 0.0
+    for _ in range(iters):
+        flush_l2()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        tot += a.elapsed_time(b)
+    del g
+    return tot / iters
+
+
 def bf(*shape, scale=1.0):
     return (torch.randn(*shape, device=DEV) * scale).to(torch.bfloat16)
 
@@ -171,10 +197,14 @@ def run_attn(results, peaks, iters, only=None):
             qkv.grad = None
         ms_fb = timed(fb, iters)
         ff, fbw = attention_flops(lens, hq, d), attention_flops(lens, hq, d, backward=True)
-        rf = {"kernel": "attn_fwd", "case": name, "ms": ms_f, "tflops": ff / ms_f / 1e9,
-              "frac_of_measured_bf16": ff / ms_f / 1e9 / peaks["bf16_tflops"]}
-        rb = {"kernel": "attn_fwd+bwd", "case": name, "ms": ms_fb, "tflops": fbw / ms_fb / 1e9,
-              "frac_of_measured_bf16": fbw / ms_fb / 1e9 / peaks["bf16_tflops"]}
+        # the same calls replayed from a CUDA graph, as they run inside the captured training step: eager launches
+        # of the short cases are bound by the host (allocation + four to six launches per call)
+        ms_f_graph = graph_timed(lambda: ops.attention_qkv_packed(qkv.detach(), cu, hq, hk, d), iters)
+        ms_fb_graph = graph_timed(fb, iters)
+        rf = {"kernel": "attn_fwd", "case": name, "ms": ms_f, "graph_ms": ms_f_graph, "tflops": ff / ms_f_graph / 1e9,
+              "frac_of_measured_bf16": ff / ms_f_graph / 1e9 / peaks["bf16_tflops"]}
+        rb = {"kernel": "attn_fwd+bwd", "case": name, "ms": ms_fb, "graph_ms": ms_fb_graph, "tflops": fbw / ms_fb_graph / 1e9,
+              "frac_of_measured_bf16": fbw / ms_fb_graph / 1e9 / peaks["bf16_tflops"]}
         if len(set(lens)) == 1:
             # torch's SDPA (its flash / cuDNN back end) on the same box, same run: forward, and forward + backward
             n, L = len(lens), lens[0]
@@ -189,9 +219,14 @@ def run_attn(results, peaks, iters, only=None):
                 with torch.no_grad():
                     torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
             rf["sdpa_fwd_ms"] = timed(lib_fwd, iters)
-            rf["sdpa_ms_over_ours"] = rf["sdpa_fwd_ms"] / ms_f
             rb["sdpa_fwd_bwd_ms"] = timed(lib, iters)
-            rb["sdpa_ms_over_ours"] = rb["sdpa_fwd_bwd_ms"] / ms_fb
+            try:
+                rf["sdpa_graph_ms"] = graph_timed(lib_fwd, iters)
+                rb["sdpa_graph_ms"] = graph_timed(lib, iters)
+                rf["sdpa_over_ours_graph"] = rf["sdpa_graph_ms"] / ms_f_graph
+                rb["sdpa_over_ours_graph"] = rb["sdpa_graph_ms"] / ms_fb_graph
+            except Exception as e:                           # a back end that cannot be captured
+                rf["sdpa_graph_ms"] = rb["sdpa_graph_ms"] = f"not captured: {type(e).__name__}"
         results.append(rf)
         results.append(rb)
         _ext.check_status()
