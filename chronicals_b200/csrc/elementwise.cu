@@ -7,6 +7,8 @@
 // triton_kernels.py:303-478 RMSNorm, :830-986 SwiGLU, :1296-1367 GeGLU,
 // :1448-1625 QK-RoPE, :127-210 cross-entropy) and the Liger kernels its trainer
 // patches in.
+#include <algorithm>
+#include <cstring>
 #include "common.cuh"
 
 // ---- optional index checks (compile with -DCHRONICALS_DEBUG_BOUNDS, e.g. CHRONICALS_DEBUG_BOUNDS=1 in the
@@ -627,6 +629,63 @@ ce_logits_grad_bf16v_kernel(const bf16* logits, bf16* dlogits, const long long* 
   }
 }
 
+// ------------------------------------------------------------------ LoRA on fused projections: pack / unpack
+// Up to four adapters (one per split of a fused projection) are multiplied as ONE pair of matrices:
+// A_cat [R, in] (the A matrices stacked) and the block-diagonal B_big [out, R] with adapter s's scaled B in rows
+// [row0_s, row0_s + nrows_s), columns [r0_s, r0_s + rank_s).  lora_pack_kernel builds both from the parameters in
+// one launch; lora_unpack_kernel turns the fp32 gradients of A_cat / B_big back into one bf16 gradient per
+// parameter (B's scaled like the forward), written into one flat buffer the caller slices.
+struct LoraPack {
+  const bf16* a[4];
+  const bf16* b[4];
+  int rank[4], r0[4], row0[4], nrows[4];
+  float scale[4];
+  long long ga_off[4], gb_off[4];      // unpack: element offsets of dA_s / dB_s in the flat gradient buffer
+  int n, in, out, R;
+};
+
+__global__ void lora_pack_kernel(const LoraPack p, bf16* __restrict__ a_cat, bf16* __restrict__ b_big) {
+  const long long na = static_cast<long long>(p.R) * p.in;
+  const long long nb = static_cast<long long>(p.out) * p.R;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < na + nb; i += stride) {
+    if (i < na) {
+      const int r = static_cast<int>(i / p.in), c = static_cast<int>(i - static_cast<long long>(r) * p.in);
+      bf16 v = __float2bfloat16(0.f);
+#pragma unroll
+      for (int s = 0; s < 4; ++s)
+        if (s < p.n && r >= p.r0[s] && r < p.r0[s] + p.rank[s]) v = p.a[s][static_cast<long long>(r - p.r0[s]) * p.in + c];
+      a_cat[i] = v;
+    } else {
+      const long long k = i - na;
+      const int o = static_cast<int>(k / p.R), j = static_cast<int>(k - static_cast<long long>(o) * p.R);
+      float v = 0.f;
+#pragma unroll
+      for (int s = 0; s < 4; ++s)
+        if (s < p.n && j >= p.r0[s] && j < p.r0[s] + p.rank[s] && o >= p.row0[s] && o < p.row0[s] + p.nrows[s])
+          v = __bfloat162float(p.b[s][static_cast<long long>(o - p.row0[s]) * p.rank[s] + (j - p.r0[s])]) * p.scale[s];
+      b_big[k] = __float2bfloat16(v);
+    }
+  }
+}
+
+__global__ void lora_unpack_kernel(const LoraPack p, const float* __restrict__ da_cat, const float* __restrict__ db_big,
+                                   bf16* __restrict__ flat) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  for (int s = 0; s < p.n; ++s) {
+    const long long na = static_cast<long long>(p.rank[s]) * p.in;
+    for (long long i = tid; i < na; i += stride)                         // dA_s: a row block of dA_cat
+      flat[p.ga_off[s] + i] = __float2bfloat16(da_cat[static_cast<long long>(p.r0[s]) * p.in + i]);
+    const long long nb = static_cast<long long>(p.nrows[s]) * p.rank[s];
+    for (long long i = tid; i < nb; i += stride) {                       // dB_s: a block of dB_big, scaled
+      const int o = static_cast<int>(i / p.rank[s]), j = static_cast<int>(i - static_cast<long long>(o) * p.rank[s]);
+      flat[p.gb_off[s] + i] =
+          __float2bfloat16(db_big[static_cast<long long>(p.row0[s] + o) * p.R + p.r0[s] + j] * p.scale[s]);
+    }
+  }
+}
+
 }  // namespace cb
 
 // =========================================================================================== host side
@@ -824,6 +883,51 @@ int cb_ce_logits_grad(const void* logits, void* dlogits, const long long* labels
   }
   if (is_bf16) cb::ce_logits_grad_kernel<cb::bf16><<<static_cast<unsigned>(rows), cb::EW_THREADS, 0, s>>>(static_cast<const cb::bf16*>(logits), static_cast<cb::bf16*>(dlogits), labels, lse, gscale, gout, ld, V, ignore_index, smoothing, z_weight);
   else cb::ce_logits_grad_kernel<float><<<static_cast<unsigned>(rows), cb::EW_THREADS, 0, s>>>(static_cast<const float*>(logits), static_cast<float*>(dlogits), labels, lse, gscale, gout, ld, V, ignore_index, smoothing, z_weight);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// desc: host array of 4 x {a_ptr, b_ptr} (u64), then int arrays rank[4], r0[4], row0[4], nrows[4], then float scale[4]
+// are passed separately to keep the ctypes side simple.
+static int fill_lora_pack(cb::LoraPack* p, const unsigned long long* a_ptrs, const unsigned long long* b_ptrs,
+                          const int* rank, const int* row0, const int* nrows, const float* scale, int n, int in, int out) {
+  if (n < 1 || n > 4 || in <= 0 || out <= 0) return -1;
+  memset(p, 0, sizeof(*p));
+  int r0 = 0;
+  long long off = 0;
+  for (int s = 0; s < n; ++s) {
+    p->a[s] = reinterpret_cast<const cb::bf16*>(a_ptrs[s]);
+    p->b[s] = reinterpret_cast<const cb::bf16*>(b_ptrs[s]);
+    p->rank[s] = rank[s]; p->r0[s] = r0; p->row0[s] = row0[s]; p->nrows[s] = nrows[s]; p->scale[s] = scale[s];
+    if (rank[s] <= 0 || row0[s] < 0 || nrows[s] <= 0 || row0[s] + nrows[s] > out) return -1;
+    p->ga_off[s] = off; off += static_cast<long long>(rank[s]) * in;
+    p->gb_off[s] = off; off += static_cast<long long>(nrows[s]) * rank[s];
+    r0 += rank[s];
+  }
+  p->n = n; p->in = in; p->out = out; p->R = r0;
+  return 0;
+}
+
+// a_cat [R, in] and b_big [out, R] (bf16, contiguous) from n adapters; R = sum of the ranks.
+int cb_lora_pack(const unsigned long long* a_ptrs, const unsigned long long* b_ptrs, const int* rank, const int* row0,
+                 const int* nrows, const float* scale, int n, int in, int out, void* a_cat, void* b_big, void* stream) {
+  cb::LoraPack p;
+  if (fill_lora_pack(&p, a_ptrs, b_ptrs, rank, row0, nrows, scale, n, in, out)) return -1;
+  const long long work = static_cast<long long>(p.R) * in + static_cast<long long>(out) * p.R;
+  cb::lora_pack_kernel<<<grid_for(work, cb::EW_THREADS, 4), cb::EW_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
+      p, static_cast<cb::bf16*>(a_cat), static_cast<cb::bf16*>(b_big));
+  return static_cast<int>(cudaGetLastError());
+}
+
+// flat (bf16) receives dA_0 | dB_0 | dA_1 | dB_1 | ... from the fp32 gradients of a_cat [R, in] and b_big [out, R].
+int cb_lora_unpack(const int* rank, const int* row0, const int* nrows, const float* scale, int n, int in, int out,
+                   const float* da_cat, const float* db_big, void* flat, void* stream) {
+  cb::LoraPack p;
+  unsigned long long dummy[4] = {0, 0, 0, 0};
+  if (fill_lora_pack(&p, dummy, dummy, rank, row0, nrows, scale, n, in, out)) return -1;
+  long long work = 0;
+  for (int s = 0; s < n; ++s) work = std::max(work, std::max(static_cast<long long>(rank[s]) * in, static_cast<long long>(nrows[s]) * rank[s]));
+  cb::lora_unpack_kernel<<<grid_for(work, cb::EW_THREADS, 4), cb::EW_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
+      p, da_cat, db_big, static_cast<cb::bf16*>(flat));
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -55,6 +55,8 @@ _PROTOTYPES = {
     "cb_gemm2sm_cost_milli": [I, I, I, I],
     "cb_gemm2sm_bf16_dual": [P, P, P, P, P, P, P, I, I, I, I, L, L, L, L, L, L, I, P, P],
     "cb_gemm2sm_bf16_glu": [P, P, P, P, P, I, I, I, L, L, L, L, P, P],
+    "cb_lora_pack": [P, P, P, P, P, P, I, I, I, P, P, P],
+    "cb_lora_unpack": [P, P, P, P, I, I, I, P, P, P, P],
     "cb_gemm2sm_fp8": [P, P, P, P, P, P, I, I, I, L, L, L, P, P],
     "cb_rowquant_e4m3": [P, P, P, L, I, L, L, P],
     "cb_gemm_bf16_splitk": [P, P, P, I, I, I, L, L, L, I, I, P, P],

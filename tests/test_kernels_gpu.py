@@ -551,6 +551,37 @@ def test_fused_lora_projection_with_dropout_stays_on_the_fused_path():
     _ext.check_status()
 
 
+def test_fused_lora_pack_and_unpack_kernels_match_the_operator_path(monkeypatch):
+    """A_cat / B_big built, and their gradients split per adapter, by the two small kernels give what the
+    PyTorch-operator assembly gives (same GEMMs in between): output and input gradient bit for bit, the adapter
+    gradients up to the summation order of the split-K GEMM."""
+    from collections import OrderedDict
+    from chronicals_b200.lora import functional as lf
+    from chronicals_b200.models.decoder import FusedLinear
+    out = {}
+    for use_pack in (True, False):
+        monkeypatch.setattr(lf, "_USE_PACK", use_pack)
+        torch.manual_seed(0)
+        fl = FusedLinear(256, OrderedDict(q=384, k=128, v=128), bias=True, dtype=torch.bfloat16, device=DEV)
+        with torch.no_grad():
+            fl.weight.normal_(0, 0.05)
+        fl.weight.requires_grad_(False)
+        for i, (name, r) in enumerate((("q", 16), ("k", 8), ("v", 16))):
+            fl.add_lora(name, rank=r, alpha=2.0 * r + i)
+            with torch.no_grad():
+                fl.lora_B[name].normal_(0, 0.05)
+        x = _rand(300, 256, seed=4).requires_grad_()
+        y = fl(x)
+        y.backward(_rand(300, 640, seed=5))
+        out[use_pack] = [y.detach(), x.grad] + [fl.lora_A[s].grad for s in ("q", "k", "v")] + [fl.lora_B[s].grad for s in ("q", "k", "v")]
+    for i, (a, b) in enumerate(zip(out[True], out[False])):
+        if i < 2:                                      # output and input gradient: same kernels on the same operands
+            assert torch.equal(a, b), (i, (a.float() - b.float()).abs().max().item())
+        else:                                          # adapter gradients pass a split-K sum whose order is not fixed
+            _close(a, b, rtol=1e-3, atol=1e-4, what=f"adapter gradient {i}", l2=1e-3)
+    _ext.check_status()
+
+
 def test_fused_lora_projection_matches_reference_formula():
     """Frozen fused QKV projection with rank-16 adapters on every split: forward, dX, dA, dB against the
     plain PEFT formula in fp32 (the base weight must receive no gradient)."""
