@@ -1370,12 +1370,13 @@ attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
 // dqkv[t] = bf16( dQ | sum over the query heads of a group of dK | same for dV ); one block per token,
 // four consecutive columns per thread (D is a multiple of 4, so a group never straddles heads)
-__global__ void attn_bwd_finalize_kernel(const float* __restrict__ dq_acc, const float* __restrict__ dk_part,
-                                         const float* __restrict__ dv_part, bf16* __restrict__ dqkv, long long ld,
+__global__ void attn_bwd_finalize_kernel(float* __restrict__ dq_acc, float* __restrict__ dk_part,
+                                         float* __restrict__ dv_part, bf16* __restrict__ dqkv, long long ld,
                                          int T, int hq, int hk, int D, const int* __restrict__ cu, int n_docs,
-                                         int part_heads) {
+                                         int part_heads, int clear) {
   // part_heads: heads per token in dk_part / dv_part — hq (one partial per query head, summed here) or hk
-  // (already accumulated per kv head by the kernel)
+  // (already accumulated per kv head by the kernel).  clear: write zeros back over every accumulator value read, so
+  // that a caller who keeps the scratch buffers between calls never has to clear them again.
   const long long t = blockIdx.x;
   const int nq = hq * D, nk = hk * D, g = part_heads / hk;
   bf16* out = dqkv + t * ld;
@@ -1385,13 +1386,15 @@ __global__ void attn_bwd_finalize_kernel(const float* __restrict__ dq_acc, const
     if (valid) {
       if (c < nq) {
         v = *reinterpret_cast<const float4*>(dq_acc + t * nq + c);
+        if (clear) *reinterpret_cast<float4*>(dq_acc + t * nq + c) = make_float4(0.f, 0.f, 0.f, 0.f);
       } else {
         const int cc = (c - nq) % nk, which = (c - nq) / nk;
         const int kvh = cc / D, d = cc % D;
-        const float* src = (which == 0 ? dk_part : dv_part) + (t * part_heads + static_cast<long long>(kvh) * g) * D + d;
+        float* src = (which == 0 ? dk_part : dv_part) + (t * part_heads + static_cast<long long>(kvh) * g) * D + d;
         for (int i = 0; i < g; ++i) {
           const float4 x = *reinterpret_cast<const float4*>(src + static_cast<long long>(i) * D);
           v.x += x.x; v.y += x.y; v.z += x.z; v.w += x.w;
+          if (clear) *reinterpret_cast<float4*>(src + static_cast<long long>(i) * D) = make_float4(0.f, 0.f, 0.f, 0.f);
         }
       }
     }
@@ -1496,7 +1499,7 @@ int cb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse
 int cb_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse,
                 const int* cu, int n_docs, int T, int hq, int hk, int D, long long ldq, long long ldk, long long ldv,
                 long long ldo, long long ld_do, float scale, float* delta, float* dq_acc, float* dk_part,
-                float* dv_part, void* dqkv, long long ld_dqkv, int* status, void* stream) {
+                float* dv_part, void* dqkv, long long ld_dqkv, int* status, void* stream, int scratch_is_zero) {
   if ((D != 64 && D != 128) || hq % hk != 0 || T <= 0 || n_docs <= 0) return -1;
   CUtensorMap mq, mk, mv, mdo;
   int e = attn_maps(&mq, &mk, &mv, q, k, v, T, hq, hk, D, ldq, ldk, ldv);
@@ -1521,7 +1524,9 @@ int cb_attn_bwd(const void* q, const void* k, const void* v, const void* o, cons
     cb::attn_delta_generic_kernel<<<static_cast<unsigned>((pairs * 32 + 255) / 256), 256, 0, s>>>(
         static_cast<const cb::bf16*>(d_o), static_cast<const cb::bf16*>(o), ld_do, ldo, T, hq, D, delta);
   }
-  CB_CHECK_CUDA(cudaMemsetAsync(dq_acc, 0, sizeof(float) * static_cast<size_t>(T) * hq * D, s));
+  // scratch_is_zero: the caller keeps dq_acc / dk_part / dv_part between calls; they arrive all zero and the finalize
+  // kernel leaves them all zero again, so the three clears are skipped
+  if (!scratch_is_zero) CB_CHECK_CUDA(cudaMemsetAsync(dq_acc, 0, sizeof(float) * static_cast<size_t>(T) * hq * D, s));
   cb::AttnArgs a = {};
   a.T = T; a.hq = hq; a.hk = hk; a.n_docs = n_docs; a.cu = cu; a.scale = scale;
   a.lse = const_cast<float*>(lse); a.delta = delta; a.dq_acc = dq_acc; a.dk_part = dk_part; a.dv_part = dv_part;
@@ -1530,8 +1535,10 @@ int cb_attn_bwd(const void* q, const void* k, const void* v, const void* o, cons
   // Two threads per score row, S / dP / dQ sharing TMEM columns, dK / dV accumulated per kv head with red.add
   // (so those buffers start from zero).  D = 64 additionally fits two CTAs per SM.
   const int part_heads = hk;
-  CB_CHECK_CUDA(cudaMemsetAsync(dk_part, 0, sizeof(float) * static_cast<size_t>(T) * hk * D, s));
-  CB_CHECK_CUDA(cudaMemsetAsync(dv_part, 0, sizeof(float) * static_cast<size_t>(T) * hk * D, s));
+  if (!scratch_is_zero) {
+    CB_CHECK_CUDA(cudaMemsetAsync(dk_part, 0, sizeof(float) * static_cast<size_t>(T) * hk * D, s));
+    CB_CHECK_CUDA(cudaMemsetAsync(dv_part, 0, sizeof(float) * static_cast<size_t>(T) * hk * D, s));
+  }
   if (D == 64) {
     static bool cfg = false;
     if (!cfg) { e = set_smem(cb::attn_bwd2_kernel<64>, cb::Bwd2Smem<64>::TOTAL); if (e) return e; cfg = true; }
@@ -1542,7 +1549,7 @@ int cb_attn_bwd(const void* q, const void* k, const void* v, const void* o, cons
     cb::attn_bwd2_kernel<128><<<grid, cb::BWD2_THREADS, cb::Bwd2Smem<128>::TOTAL, s>>>(mq, mk, mv, mdo, mdq, a);
   }
   cb::attn_bwd_finalize_kernel<<<T, 128, 0, s>>>(dq_acc, dk_part, dv_part, static_cast<cb::bf16*>(dqkv), ld_dqkv, T,
-                                                  hq, hk, D, cu, n_docs, part_heads);
+                                                  hq, hk, D, cu, n_docs, part_heads, scratch_is_zero ? 1 : 0);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -48,7 +48,7 @@ _PROTOTYPES = {
     "cb_ce_logits": [P, P, L, L, I, I, L, F, F, P, P, P],
     "cb_ce_logits_grad": [P, P, P, P, P, P, L, L, I, I, L, F, F, P],
     "cb_attn_fwd": [P, P, P, P, P, P, I, I, I, I, I, L, L, L, L, F, P, P],
-    "cb_attn_bwd": [P, P, P, P, P, P, P, I, I, I, I, I, L, L, L, L, L, F, P, P, P, P, P, L, P, P],
+    "cb_attn_bwd": [P, P, P, P, P, P, P, I, I, I, I, I, L, L, L, L, L, F, P, P, P, P, P, L, P, P, I],
     "cb_gemm2sm_bf16": [P, P, P, P, P, I, I, I, L, L, L, L, I, I, I, I, P, P],
     "cb_gemm2sm_supported": [P, L, I],
     "cb_gemm2sm_bf16_ex": [P, P, P, P, P, I, I, I, L, L, L, L, I, I, I, I, I, P, P],

@@ -279,6 +279,13 @@ class ShardedFusedAdamW(torch.optim.Optimizer):
             ev.record(main)
             self.side.wait_event(ev)                     # the bucket's gradients are complete on the main stream
             self._forked = True
+        elif getattr(self, "_forked", False) and barrier:
+            # Barriers share one epoch counter and one flag pad per rank, so two of them must never run at the same
+            # time: a barrier on the main stream waits for the side stream's reduce-scatters (and barriers) first.
+            # (Without this join the hook path timed out on 8 GPUs: "peer flag never arrived".)
+            ev = torch.cuda.Event()
+            ev.record(self.side)
+            main.wait_event(ev)
         grid = self.rs_grid if overlapped else self.full_grid
         prof = self.profile and not torch.cuda.is_current_stream_capturing()
         if prof:
