@@ -927,9 +927,10 @@ attn_fwd3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
         const float e0 = ex2_approx(fmaf(__uint_as_float(s0[2 * i]), sl2, -mb));
-        const float e1 = ex2_approx(fmaf(__uint_as_float(s0[2 * i + 1]), sl2, -mb));
+        // three exponentials in eight run on the FMA pipe: the exp2 unit is this loop's bound
+        const float x1 = fmaf(__uint_as_float(s0[2 * i + 1]), sl2, -mb);
+        const float e1 = (i & 1) ? ex2_fma(x1) : ex2_approx(x1);
         const float e2 = ex2_approx(fmaf(__uint_as_float(s1[2 * i]), sl2, -mb));
-        // one exponential in four runs on the FMA pipe: the exp2 unit is this loop's bound
         const float e3 = ex2_fma(fmaf(__uint_as_float(s1[2 * i + 1]), sl2, -mb));
         rs0 += e0 + e1;
         rs1 += e2 + e3;
@@ -1230,9 +1231,11 @@ attn_bwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
       } else {
 #pragma unroll
-        for (int k = 0; k < 16; ++k)
+        for (int k = 0; k < 16; ++k) {                  // one exponential in four on the FMA pipe (see ex2_fma)
+          const float x1 = fmaf(__uint_as_float(s[2 * k + 1]), sl2, -lse2);
           pk[cl][k] = pack_bf16x2(ex2_approx(fmaf(__uint_as_float(s[2 * k]), sl2, -lse2)),
-                                  ex2_approx(fmaf(__uint_as_float(s[2 * k + 1]), sl2, -lse2)));
+                                  (k & 1) ? ex2_fma(x1) : ex2_approx(x1));
+        }
       }
       store_row_chunk32_packed(sP, r, c, pk[cl]);
     }
