@@ -141,7 +141,7 @@ __global__ void sum_partials_kernel(const float* __restrict__ partials, int n, f
 
 // Per-bucket reduce-scatter that runs beside the backward pass on a second stream.  Same arithmetic as
 // rs_reduce_sqnorm_kernel, shaped to share SMs with the compute kernels: 128 threads per block and a
-// small grid (the host picks it), two 16-byte vectors per peer in flight per thread.  partials[block]
+// grid chosen by the host, one 16-byte vector per thread and pass with all ranks' loads in flight.  partials[block]
 // receives each warp's sum of squares (RSB_THREADS / 32 slots per block); the host sums all buckets' partials once
 // after the last bucket.
 constexpr int RSB_THREADS = 128;
@@ -154,39 +154,28 @@ rs_bucket_kernel(PeerTable grads, int W, long long lo, long long hi, float* __re
     const float inv = 1.f / static_cast<float>(W);
     const long long nvec = (hi - lo) >> 3;
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-    for (long long v = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; v < nvec; v += 2 * stride) {
-      const long long v2 = v + stride;
-      const bool two = v2 < nvec;
+    // One 16-byte vector per thread and pass, with the loads from up to eight ranks in flight at once (at eight
+    // ranks two loads per pass left the links at a third of their rate); the sum runs over the ranks in rank
+    // order, so every rank computes bit-identical values for its slice whatever the grid.
+    for (long long v = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; v < nvec; v += stride) {
       float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      float b[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      for (int r = 0; r < W; r += 2) {
-        const bf16* g0 = static_cast<const bf16*>(grads.ptr[r]) + lo;
-        const bool r1 = r + 1 < W;
-        const bf16* g1 = r1 ? static_cast<const bf16*>(grads.ptr[r + 1]) + lo : g0;
-        const uint4 z = make_uint4(0u, 0u, 0u, 0u);
-        const uint4 u00 = *reinterpret_cast<const uint4*>(g0 + (v << 3));
-        const uint4 u10 = r1 ? *reinterpret_cast<const uint4*>(g1 + (v << 3)) : z;
-        const uint4 u01 = two ? *reinterpret_cast<const uint4*>(g0 + (v2 << 3)) : z;
-        const uint4 u11 = (two && r1) ? *reinterpret_cast<const uint4*>(g1 + (v2 << 3)) : z;
-        acc_bf16x8(u00, a);
-        acc_bf16x8(u10, a);
-        acc_bf16x8(u01, b);
-        acc_bf16x8(u11, b);
+      for (int r0 = 0; r0 < W; r0 += 8) {
+        uint4 u[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          if (r0 + k < W) u[k] = *reinterpret_cast<const uint4*>(static_cast<const bf16*>(grads.ptr[r0 + k]) + lo + (v << 3));
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          if (r0 + k < W) acc_bf16x8(u[k], a);
       }
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         a[j] *= inv;
-        b[j] *= inv;
-        sq += a[j] * a[j] + b[j] * b[j];
+        sq += a[j] * a[j];
       }
       float4* o = reinterpret_cast<float4*>(reduced + (v << 3));
       o[0] = make_float4(a[0], a[1], a[2], a[3]);
       o[1] = make_float4(a[4], a[5], a[6], a[7]);
-      if (two) {
-        float4* o2 = reinterpret_cast<float4*>(reduced + (v2 << 3));
-        o2[0] = make_float4(b[0], b[1], b[2], b[3]);
-        o2[1] = make_float4(b[4], b[5], b[6], b[7]);
-      }
     }
   }
   sq = warp_sum(sq);
