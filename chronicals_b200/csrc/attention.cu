@@ -3,18 +3,26 @@
 //
 // Layout: q [T, hq, D], k/v [T, hk, D] packed tokens (any row pitch, so they may
 // be slices of one fused QKV buffer); documents are the intervals of
-// cu_seqlens.  One CTA owns one 128-row block of one document and one query
-// head.  Every thread owns one row of the 128 x 128 score tile: it reads its row
-// from TMEM with tcgen05.ld, so the online softmax needs no cross-thread
-// shuffles, and writes P (bf16) into shared memory in the 128-byte-swizzled
-// layout the next MMA consumes.
+// cu_seqlens.  A tile is one 128-row block of one document and one query head;
+// tiles are handed out by descending weight over all documents (locate_tile).
 //
 //   forward : S = Q K^T -> P = softmax -> O += P V        (2 MMAs per kv block)
 //   backward: S, dP = dO V^T -> P, dS -> dV += P^T dO, dK += dS^T Q, dQ = dS K
 //
-// The same swizzled image of a [128 x 64] bf16 tile serves as a K-major operand
-// (rows = M/N) and as an MN-major operand (rows = K), so P^T and dS^T need no
-// transposed copy.  All tensor maps cover this GPU's own memory only.
+// Forward kernels: attn_fwd3_kernel (default: 64-row kv blocks, double-buffered
+// S, O accumulated in TMEM, P consumed from TMEM, dedicated MMA and TMA warps, one
+// thread per score row, no CTA barrier in the loop); attn_fwd_kernel (first form:
+// 128-row kv blocks, O in registers) and attn_fwd2_kernel (two threads per row)
+// are kept for comparison (CB_ATTN_FWD=1 / 2).  Backward: attn_bwd2_kernel (one
+// CTA per kv block and head, two threads per score row, S / dP / dQ sharing TMEM
+// columns, dQ out by TMA reduce-add) with attn_delta_kernel before and
+// attn_bwd_finalize_kernel after it.
+//
+// Every thread that owns a score row reads it from TMEM with tcgen05.ld, so the
+// softmax needs no cross-thread shuffles.  The same swizzled image of a [128 x 64]
+// bf16 tile serves as a K-major operand (rows = M/N) and as an MN-major operand
+// (rows = K), so P^T and dS^T need no transposed copy.  All tensor maps cover this
+// GPU's own memory only.
 //
 // Replaces the reference's calls into flash-attn / SDPA (chronicals/kernels/
 // flash_attention_optimizer.py:845-994) and its forward-only Triton kernels
