@@ -326,16 +326,17 @@ __device__ __forceinline__ float ex2_approx(float x) {
 }
 // 2^x without the special-function unit, for x <= ~100: x = n + f with n = round(x), f in [-0.5, 0.5];
 // 2^f by a cubic (maximum relative error 7.7e-5, far inside bf16's 3.9e-3), 2^n by adding n to the exponent
-// field.  Inputs below -125 (masked scores arrive as -inf) give 2^-125 ~ 2e-38.  About ten FMA-pipe
+// field.  Inputs below -125 (masked scores arrive as -inf) give zero.  About ten FMA-pipe
 // instructions: used for a fraction of a softmax's exponentials where the 16-per-clock exp2 unit is the bound.
 __device__ __forceinline__ float ex2_fma(float x) {
-  x = fmaxf(x, -125.f);
-  const float t = x + 12582912.f;                      // 1.5 * 2^23: round(x) lands in the low mantissa bits
-  const float f = x - (t - 12582912.f);
+  const float xc = fmaxf(x, -125.f);
+  const float t = xc + 12582912.f;                     // 1.5 * 2^23: round(x) lands in the low mantissa bits
+  const float f = xc - (t - 12582912.f);
   float p = fmaf(0.05508868396282196f, f, 0.24260404706001282f);
   p = fmaf(p, f, 0.6932762265205383f);
   p = fmaf(p, f, 0.9999289512634277f);
-  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+  const float r = __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+  return x < -125.f ? 0.f : r;                         // masked scores (-inf) give an exact zero, like ex2.approx.ftz
 }
 __device__ __forceinline__ float tanh_approx(float x) {
   float y;
