@@ -188,3 +188,37 @@ def test_clip_coef():
     c = ref.clip_coef_from_sqnorm(torch.tensor(16.0), 1.0)
     assert abs(c.item() - 1.0 / (4.0 + 1e-6)) < 1e-6
     assert ref.clip_coef_from_sqnorm(torch.tensor(0.01), 1.0).item() == 1.0
+
+
+def test_fma_pipe_exp2_constants_and_bit_arithmetic():
+    """The softmax kernels compute part of their exponentials without the special-function unit (``ex2_fma`` in
+    ``csrc/common.cuh``): x = n + f, a cubic for 2^f, n added to the exponent field.  The same arithmetic in numpy
+    float32, with the constants read from the source, stays within 1e-4 of 2^x over the range the kernels use and
+    returns exact zeros for masked (-inf) inputs."""
+    import os
+    import re
+    import numpy as np
+    src = open(os.path.join(os.path.dirname(__file__), "..", "chronicals_b200", "csrc", "common.cuh")).read()
+    body = src[src.index("float ex2_fma(float x)"):]
+    body = body[:body.index("\n}\n")]
+    c3, c2 = [np.float32(v) for v in re.search(r"fmaf\(([0-9.]+)f, f, ([0-9.]+)f\)", body).groups()]
+    c1, c0 = [np.float32(v) for v in re.findall(r"fmaf\(p, f, ([0-9.]+)f\)", body)]
+    magic = np.float32(12582912.0)
+    assert "12582912.f" in body and "<< 23" in body
+
+    def ex2_fma(x):
+        x = x.astype(np.float32)
+        xc = np.maximum(x, np.float32(-125))
+        t = (xc + magic).astype(np.float32)
+        f = (xc - (t - magic).astype(np.float32)).astype(np.float32)
+        p = (c3 * f + c2).astype(np.float32)
+        p = (p * f + c1).astype(np.float32)
+        p = (p * f + c0).astype(np.float32)
+        bits = (p.view(np.int32).astype(np.int64) + ((t.view(np.int32).astype(np.int64) << 23) & 0xffffffff)) & 0xffffffff
+        r = bits.astype(np.uint32).view(np.float32)
+        return np.where(x < -125, np.float32(0), r)
+
+    xs = np.linspace(-124.9, 9.5, 100001).astype(np.float32)
+    err = np.abs(ex2_fma(xs) / np.exp2(xs.astype(np.float64)) - 1).max()
+    assert err < 1e-4, err
+    assert (ex2_fma(np.array([-np.inf, -300.0, -125.5], dtype=np.float32)) == 0).all()
