@@ -222,3 +222,45 @@ def test_fma_pipe_exp2_constants_and_bit_arithmetic():
     err = np.abs(ex2_fma(xs) / np.exp2(xs.astype(np.float64)) - 1).max()
     assert err < 1e-4, err
     assert (ex2_fma(np.array([-np.inf, -300.0, -125.5], dtype=np.float32)) == 0).all()
+
+
+def test_attention_tile_schedule_properties():
+    """The attention kernels hand out tiles (128-row blocks of documents) by descending weight over all documents
+    (``locate_tile`` in ``csrc/attention.cu``) and let the CTAs past the last tile zero the padding rows.  The same
+    enumeration restated in Python: every block of every document appears exactly once, weights never increase,
+    and the grid ``ceil(T / 128) + n_docs`` always leaves enough CTAs past the last tile to cover the padding."""
+    import random
+
+    def locate_tile(cu, b):
+        nb = [(cu[i + 1] - cu[i] + 127) >> 7 for i in range(len(cu) - 1)]
+        for level in range(max(nb, default=0), 0, -1):
+            docs = [d for d, n in enumerate(nb) if n >= level]          # document order
+            if b < len(docs):
+                return docs[b], level
+            b -= len(docs)
+        return None, b                                                  # index among the CTAs past the last tile
+
+    rng = random.Random(0)
+    for _ in range(200):
+        n_docs = rng.randint(1, 70)
+        lens = [rng.choice([0, 1, 63, 64, 65, 127, 128, 129, 300, 1024, 2500]) for _ in range(n_docs)]
+        cu = [0]
+        for length in lens:
+            cu.append(cu[-1] + length)
+        T = cu[-1] + rng.choice([0, 1, 127, 128, 500])
+        grid_y = (T + 127) // 128 + n_docs
+        seen, weights, beyond = set(), [], 0
+        for b in range(grid_y):
+            doc, w = locate_tile(cu, b)
+            if doc is None:
+                assert w == beyond                                        # consecutive indices past the last tile
+                beyond += 1
+                continue
+            assert beyond == 0, "tiles come first"
+            nblk = (lens[doc] + 127) >> 7
+            assert 1 <= w <= nblk
+            seen.add((doc, w))                                            # forward: q block w - 1; backward: kv block nblk - w
+            weights.append(w)
+        assert len(seen) == len(weights) == sum((length + 127) >> 7 for length in lens)
+        assert weights == sorted(weights, reverse=True)
+        assert beyond * 128 >= T - cu[-1], "CTAs past the last tile cover the padding rows"
